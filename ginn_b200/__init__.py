@@ -1,0 +1,12 @@
+"""ginn_b200: B200 (sm_100a) back end for ginn's Affine / Prod / BatchedProd / autobatch GEMMs.
+
+The product is the shared library ``libginn_b200.so`` (C ABI in ``include/ginn_b200.h``) and
+the header-only C++ layer in ``ginn_b200/include``.  This Python package is a thin ctypes
+binding used by the tests and the benchmark; it never computes anything itself and raises if
+the CUDA library is missing.
+"""
+from .binding import (  # noqa: F401
+    ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH, F16, F32, GinnB200Error, Group, Pair, PairGrad,
+    affine_backward, affine_forward, device_status, gemm, gemm_batched, grouped, launch_count,
+    lib, lib_path, set_option, version,
+)

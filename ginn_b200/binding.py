@@ -1,0 +1,258 @@
+"""ctypes binding of the C ABI declared in include/ginn_b200.h.
+
+Matrices are torch CUDA tensors viewed column-major, as ginn stores them: a (rows, cols)
+tensor with strides (1, ld).  ``colmajor`` / ``from_host`` build such tensors.  Batched operands
+are (rows, cols, batch) tensors with strides (1, ld, batch_stride).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+F32, F16 = 0, 1
+ACT_NONE, ACT_TANH, ACT_SIGMOID, ACT_RELU = 0, 1, 2, 3
+GROUPED_FORWARD, GROUPED_DX, GROUPED_DW = 0, 1, 2
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libginn_b200.so")
+_lib = None
+
+
+class GinnB200Error(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"ginn_b200 status {status}: {text}")
+        self.status = status
+
+
+class _Pair(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("lda", C.c_int64), ("b", C.c_void_p), ("ldb", C.c_int64),
+                ("k", C.c_int64)]
+
+
+class _PairGrad(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("lda", C.c_int64), ("b", C.c_void_p), ("ldb", C.c_int64),
+                ("k", C.c_int64), ("da", C.c_void_p), ("ldda", C.c_int64), ("db", C.c_void_p),
+                ("lddb", C.c_int64)]
+
+
+class _Group(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("ldw", C.c_int64), ("m", C.c_int64), ("k", C.c_int64),
+                ("bias", C.c_void_p), ("ncols", C.c_int64), ("x_cols", C.POINTER(C.c_void_p)),
+                ("y_cols", C.POINTER(C.c_void_p)), ("dx_cols", C.POINTER(C.c_void_p)),
+                ("dw", C.c_void_p), ("lddw", C.c_int64), ("dbias", C.c_void_p)]
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def lib():
+    """Loads libginn_b200.so; there is no fallback if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python -m ginn_b200.build` "
+            "(nvcc, sm_100a). ginn_b200 has no CPU or PyTorch fallback.")
+    L = C.CDLL(_LIB_PATH)
+    i64, vp, ci = C.c_int64, C.c_void_p, C.c_int
+    L.ginn_b200_gemm.argtypes = [ci, vp, ci, ci, ci, i64, i64, i64, vp, i64, vp, i64, vp, i64, ci]
+    L.ginn_b200_gemm_batched.argtypes = [ci, vp, ci, ci, ci, i64, i64, i64, vp, i64, i64, vp, i64,
+                                         i64, vp, i64, i64, i64, ci]
+    L.ginn_b200_affine_forward.argtypes = [ci, vp, ci, ci, C.POINTER(_Pair), i64, i64, vp, ci, vp,
+                                           i64]
+    L.ginn_b200_affine_backward.argtypes = [ci, vp, ci, ci, C.POINTER(_PairGrad), i64, i64, vp,
+                                            i64, vp, i64, ci, vp]
+    L.ginn_b200_grouped.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
+    L.ginn_b200_last_error.restype = C.c_char_p
+    L.ginn_b200_device_status.argtypes = [ci, ci]
+    L.ginn_b200_set_option.argtypes = [C.c_char_p, ci]
+    L.ginn_b200_launch_count.restype = i64
+    for name in ("ginn_b200_gemm", "ginn_b200_gemm_batched", "ginn_b200_affine_forward",
+                 "ginn_b200_affine_backward", "ginn_b200_grouped", "ginn_b200_device_status",
+                 "ginn_b200_version", "ginn_b200_set_option"):
+        getattr(L, name).restype = ci
+    _lib = L
+    return L
+
+
+def _check(status: int):
+    if status != 0:
+        raise GinnB200Error(status, lib().ginn_b200_last_error().decode())
+
+
+def _dtype_of(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.float16:
+        return F16
+    raise GinnB200Error(2, f"unsupported tensor dtype {t.dtype}")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dev(t: torch.Tensor) -> int:
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _ld(t: torch.Tensor) -> int:
+    assert t.dim() >= 2 and (t.shape[0] <= 1 or t.stride(0) == 1), "matrix must be column-major"
+    return max(int(t.stride(1)) if t.shape[1] > 1 else int(t.shape[0]), 1)
+
+
+def colmajor(rows: int, cols: int, dtype, device="cuda", ld: Optional[int] = None,
+             batches: Optional[int] = None, fill: Optional[float] = None) -> torch.Tensor:
+    """Uninitialised (or filled) column-major matrix, optionally padded (ld) or batched."""
+    ld = rows if ld is None else ld
+    n = ld * cols * (batches or 1)
+    buf = torch.empty(max(n, 1), dtype=dtype, device=device)
+    if fill is not None:
+        buf.fill_(fill)
+    if batches is None:
+        return torch.as_strided(buf, (rows, cols), (1, ld))
+    return torch.as_strided(buf, (rows, cols, batches), (1, ld, ld * cols))
+
+
+def from_host(a: np.ndarray, device="cuda", ld: Optional[int] = None) -> torch.Tensor:
+    """numpy (rows, cols[, batch]) array -> column-major torch tensor on the GPU."""
+    tdt = {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16}[a.dtype]
+    if a.ndim == 1:
+        return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    if a.ndim == 2:
+        out = colmajor(a.shape[0], a.shape[1], tdt, device, ld)
+    else:
+        out = colmajor(a.shape[0], a.shape[1], tdt, device, ld, a.shape[2])
+    out.copy_(torch.from_numpy(np.ascontiguousarray(a)))
+    return out
+
+
+def to_host(t: torch.Tensor) -> np.ndarray:
+    return t.detach().cpu().numpy()
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, trans_a=False, trans_b=False,
+         accumulate=False) -> torch.Tensor:
+    """c = op(a) @ op(b) (+ c).  Mirrors internal::gpu_prod (ginn/prod.h:211-253)."""
+    m, n = c.shape
+    k = a.shape[0] if trans_a else a.shape[1]
+    _check(lib().ginn_b200_gemm(_dev(c), _stream(c), _dtype_of(c), int(trans_a), int(trans_b), m,
+                                n, k, a.data_ptr(), _ld(a), b.data_ptr(), _ld(b), c.data_ptr(),
+                                _ld(c), int(accumulate)))
+    return c
+
+
+def gemm_batched(a, b, c, trans_a=False, trans_b=False, accumulate=False):
+    """c[:,:,i] = op(a[:,:,i]) @ op(b[:,:,i]) (+ c[:,:,i]); internal::gpu_batched_prod
+    (ginn/prod.h:255-310)."""
+    m, n, batches = c.shape
+    k = a.shape[0] if trans_a else a.shape[1]
+    sa = a.stride(2) if batches > 1 else a.shape[0] * a.shape[1]
+    sb = b.stride(2) if batches > 1 else b.shape[0] * b.shape[1]
+    sc = c.stride(2) if batches > 1 else c.shape[0] * c.shape[1]
+    _check(lib().ginn_b200_gemm_batched(
+        _dev(c), _stream(c), _dtype_of(c), int(trans_a), int(trans_b), m, n, k, a.data_ptr(),
+        _ld(a), sa, b.data_ptr(), _ld(b), sb, c.data_ptr(), _ld(c), sc, batches, int(accumulate)))
+    return c
+
+
+@dataclass
+class Pair:
+    a: torch.Tensor
+    b: torch.Tensor
+
+
+@dataclass
+class PairGrad:
+    a: torch.Tensor
+    b: torch.Tensor
+    da: Optional[torch.Tensor] = None
+    db: Optional[torch.Tensor] = None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def affine_forward(pairs: Sequence[Pair], bias: Optional[torch.Tensor], act: int,
+                   out: torch.Tensor) -> torch.Tensor:
+    """out = act(sum_i a_i @ b_i + bias); AffineNode::forward_ (ginn/node/affine.h:35-77)."""
+    arr = (_Pair * len(pairs))()
+    for i, p in enumerate(pairs):
+        arr[i] = _Pair(p.a.data_ptr(), _ld(p.a), p.b.data_ptr(), _ld(p.b), p.a.shape[1])
+    m, n = out.shape
+    _check(lib().ginn_b200_affine_forward(_dev(out), _stream(out), _dtype_of(out), len(pairs), arr,
+                                          m, n, _ptr(bias), act, out.data_ptr(), _ld(out)))
+    return out
+
+
+def affine_backward(pairs: Sequence[PairGrad], dout: torch.Tensor, out: Optional[torch.Tensor],
+                    act: int, dbias: Optional[torch.Tensor]) -> None:
+    """AffineNode::backward_ (ginn/node/affine.h:79-129): accumulates into da/db/dbias."""
+    arr = (_PairGrad * max(len(pairs), 1))()
+    for i, p in enumerate(pairs):
+        arr[i] = _PairGrad(p.a.data_ptr(), _ld(p.a), p.b.data_ptr(), _ld(p.b), p.a.shape[1],
+                           _ptr(p.da), _ld(p.da) if p.da is not None else 0, _ptr(p.db),
+                           _ld(p.db) if p.db is not None else 0)
+    m, n = dout.shape
+    _check(lib().ginn_b200_affine_backward(
+        _dev(dout), _stream(dout), _dtype_of(dout), len(pairs), arr, m, n, dout.data_ptr(),
+        _ld(dout), _ptr(out), _ld(out) if out is not None else 0, act, _ptr(dbias)))
+
+
+@dataclass
+class Group:
+    """One autobatch group: shared W (m x k) and per-node column vectors."""
+    w: torch.Tensor
+    x_cols: Sequence[torch.Tensor] = ()   # each (k,)
+    y_cols: Sequence[torch.Tensor] = ()   # each (m,): outputs (forward) or upstream grads
+    dx_cols: Sequence[torch.Tensor] = ()  # each (k,)
+    bias: Optional[torch.Tensor] = None
+    dw: Optional[torch.Tensor] = None
+    dbias: Optional[torch.Tensor] = None
+
+
+def grouped(mode: int, groups: Sequence[Group]) -> None:
+    """All groups of one autobatch level in one launch (ginn/autobatch.h:149-183)."""
+    if not groups:
+        return
+    arr = (_Group * len(groups))()
+    keep = []
+
+    def table(ts):
+        t = (C.c_void_p * max(len(ts), 1))(*[x.data_ptr() for x in ts])
+        keep.append(t)
+        return C.cast(t, C.POINTER(C.c_void_p))
+
+    for i, g in enumerate(groups):
+        m, k = g.w.shape
+        ncols = len(g.y_cols)
+        arr[i] = _Group(g.w.data_ptr(), _ld(g.w), m, k, _ptr(g.bias), ncols,
+                        table(g.x_cols) if len(g.x_cols) else None, table(g.y_cols),
+                        table(g.dx_cols) if len(g.dx_cols) else None, _ptr(g.dw),
+                        _ld(g.dw) if g.dw is not None else 0, _ptr(g.dbias))
+    w0 = groups[0].w
+    _check(lib().ginn_b200_grouped(_dev(w0), _stream(w0), _dtype_of(w0), mode, len(groups), arr))
+
+
+def device_status(device: int = 0, reset: bool = True) -> int:
+    return lib().ginn_b200_device_status(device, int(reset))
+
+
+def set_option(name: str, value: int) -> None:
+    _check(lib().ginn_b200_set_option(name.encode(), value))
+
+
+def launch_count() -> int:
+    return int(lib().ginn_b200_launch_count())
+
+
+def version() -> int:
+    return lib().ginn_b200_version()

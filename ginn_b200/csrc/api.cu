@@ -1,0 +1,468 @@
+// extern "C" layer: argument validation, path selection, per-device state.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/ginn_b200.h"
+#include "launch.h"
+
+namespace {
+
+using gb::Operand;
+using gb::Problem;
+
+thread_local std::string t_error;
+std::atomic<long long> g_launches{0};
+std::atomic<int> g_force_path{0};
+
+int fail(int status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_error = buf;
+  return status;
+}
+
+#define CU_TRY(expr)                                                                      \
+  do {                                                                                    \
+    cudaError_t e_ = (expr);                                                              \
+    if (e_ != cudaSuccess)                                                                \
+      return fail(GINN_B200_CUDA_ERROR, "%s failed: %s (%s:%d)", #expr,                   \
+                  cudaGetErrorString(e_), __FILE__, __LINE__);                            \
+  } while (0)
+
+constexpr int kMaxDevices = 64;
+constexpr size_t kStageBytes = 8u << 20;
+
+struct DevCtx {
+  std::mutex mu;
+  bool ready = false;
+  int num_sms = 0;
+  int* d_status = nullptr;
+  // staging ring for grouped launches (problem descriptors + pointer tables)
+  unsigned char* h_stage = nullptr;
+  unsigned char* d_stage = nullptr;
+  size_t stage_off = 0;
+};
+DevCtx g_ctx[kMaxDevices];
+
+int get_ctx(int device, DevCtx** out) {
+  if (device < 0 || device >= kMaxDevices)
+    return fail(GINN_B200_BAD_ARGUMENT, "device index %d out of range", device);
+  CU_TRY(cudaSetDevice(device));
+  DevCtx& c = g_ctx[device];
+  std::lock_guard<std::mutex> g(c.mu);
+  if (!c.ready) {
+    int major = 0;
+    CU_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10)
+      return fail(GINN_B200_UNSUPPORTED,
+                  "device %d has compute capability %d.x; this library is built for sm_100a only",
+                  device, major);
+    CU_TRY(cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, device));
+    CU_TRY(cudaMalloc(&c.d_status, sizeof(int)));
+    CU_TRY(cudaMemset(c.d_status, 0, sizeof(int)));
+    c.ready = true;
+  }
+  *out = &c;
+  return GINN_B200_OK;
+}
+
+int esize(int dtype) { return dtype == GINN_B200_F32 ? 4 : 2; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+Operand make_operand(int dtype, const void* base, long long ld, long long batch_stride,
+                     int batches, int k_contig, const void* ybase = nullptr,
+                     int dact = gb::ACT_NONE) {
+  Operand o;
+  std::memset(&o, 0, sizeof(o));
+  o.base = base;
+  o.ybase = dact != gb::ACT_NONE ? ybase : nullptr;
+  o.ld = ld;
+  o.batch_stride = batch_stride;
+  o.k_contig = k_contig;
+  o.dact = o.ybase ? dact : gb::ACT_NONE;
+  const long long es = esize(dtype);
+  bool v = k_contig && aligned16(base) && (ld * es) % 16 == 0;
+  if (batches > 1) v = v && (batch_stride * es) % 16 == 0;
+  if (o.ybase) v = v && aligned16(o.ybase);
+  o.vec = v ? 1 : 0;
+  return o;
+}
+
+enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3 };
+
+// Runs one Problem on the staged tcgen05 kernel or the CUDA-core kernel.
+int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0 || p.batches <= 0) return GINN_B200_OK;
+  long long ktot = 0;
+  for (int i = 0; i < p.npairs; ++i) ktot += p.k[i];
+  const int force = g_force_path.load();
+  bool small = (static_cast<long long>(p.M) * p.N <= 16) || ktot == 0;
+  if (force == PATH_SMALL) small = true;
+  if (force == PATH_STAGED && ktot > 0) small = false;
+  if (p.rowsum != nullptr && ktot > 0) small = false;
+  if (small) {
+    CU_TRY(gb::launch_small(dtype, p, stream));
+  } else {
+    const int bn = gb::staged_pick_bn(dtype, p.M, p.N, p.batches, ctx->num_sms);
+    CU_TRY(gb::launch_staged(dtype, p, bn, stream, ctx->d_status));
+  }
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+int check_common(int dtype, int64_t m, int64_t n, int64_t k) {
+  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
+    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
+  if (m < 0 || n < 0 || k < 0)
+    return fail(GINN_B200_BAD_ARGUMENT, "negative dimension m=%lld n=%lld k=%lld", (long long)m,
+                (long long)n, (long long)k);
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL)
+    return fail(GINN_B200_BAD_ARGUMENT, "dimension exceeds 2^31-1");
+  return GINN_B200_OK;
+}
+
+int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, int64_t m, int64_t n,
+              int64_t k, const void* a, int64_t lda, int64_t stride_a, const void* b, int64_t ldb,
+              int64_t stride_b, void* c, int64_t ldc, int64_t stride_c, int64_t batches,
+              int accumulate) {
+  if (int s = check_common(dtype, m, n, k)) return s;
+  if (batches < 0 || batches > 0x7fffffffLL)
+    return fail(GINN_B200_BAD_ARGUMENT, "bad batch count %lld", (long long)batches);
+  if (m == 0 || n == 0 || batches == 0) return GINN_B200_OK;
+  const int64_t a_rows = trans_a ? k : m, b_rows = trans_b ? n : k;
+  if (c == nullptr || (k > 0 && (a == nullptr || b == nullptr)))
+    return fail(GINN_B200_BAD_ARGUMENT, "null matrix pointer");
+  if (lda < (a_rows > 1 ? a_rows : 1) || ldb < (b_rows > 1 ? b_rows : 1) || ldc < m)
+    return fail(GINN_B200_BAD_ARGUMENT,
+                "leading dimension too small: lda=%lld (rows %lld) ldb=%lld (rows %lld) ldc=%lld "
+                "(rows %lld)",
+                (long long)lda, (long long)a_rows, (long long)ldb, (long long)b_rows,
+                (long long)ldc, (long long)m);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int force = g_force_path.load();
+
+  if (dtype == GINN_B200_F16 && k > 0 && (force == PATH_AUTO || force == PATH_TMA)) {
+    gb::HgemmArgs h;
+    h.A = a; h.B = b; h.C = c;
+    h.lda = lda; h.ldb = ldb; h.ldc = ldc;
+    h.strideA = stride_a; h.strideB = stride_b; h.strideC = stride_c;
+    h.transA = trans_a ? 1 : 0; h.transB = trans_b ? 1 : 0;
+    h.M = (int)m; h.N = (int)n; h.K = (int)k; h.batches = (int)batches;
+    h.accumulate = accumulate ? 1 : 0;
+    const bool big = m >= 128 && n >= 128 && k >= 128 &&
+                     ((m + 127) / 128) * ((n + 255) / 256) * batches >= ctx->num_sms / 2;
+    if ((big || force == PATH_TMA) && gb::hgemm_tma_supported(h)) {
+      CU_TRY(gb::launch_hgemm_tma(h, ctx->num_sms, stream, ctx->d_status));
+      g_launches.fetch_add(1);
+      return GINN_B200_OK;
+    }
+  }
+
+  Problem p;
+  std::memset(&p, 0, sizeof(p));
+  p.npairs = 1;
+  p.a[0] = make_operand(dtype, a, lda, stride_a, (int)batches, trans_a ? 1 : 0);
+  p.b[0] = make_operand(dtype, b, ldb, stride_b, (int)batches, trans_b ? 0 : 1);
+  p.k[0] = k;
+  p.M = (int)m; p.N = (int)n; p.batches = (int)batches;
+  p.c = c; p.ldc = ldc; p.c_batch_stride = stride_c;
+  p.act = gb::ACT_NONE;
+  p.accumulate = accumulate ? 1 : 0;
+  return run_problem(ctx, dtype, p, stream);
+}
+
+// Reserves `bytes` in the staging ring; returns host and device addresses of the slot.
+int stage_alloc(DevCtx* ctx, size_t bytes, unsigned char** h, unsigned char** d) {
+  bytes = (bytes + 255) & ~size_t(255);
+  if (bytes > kStageBytes)
+    return fail(GINN_B200_BAD_ARGUMENT, "grouped launch needs %zu staging bytes (limit %zu)",
+                bytes, kStageBytes);
+  std::lock_guard<std::mutex> g(ctx->mu);
+  if (!ctx->h_stage) {
+    CU_TRY(cudaMallocHost(&ctx->h_stage, kStageBytes));
+    CU_TRY(cudaMalloc(&ctx->d_stage, kStageBytes));
+  }
+  if (ctx->stage_off + bytes > kStageBytes) {
+    // Wrapping: earlier launches may still be reading their slots.
+    CU_TRY(cudaDeviceSynchronize());
+    ctx->stage_off = 0;
+  }
+  *h = ctx->h_stage + ctx->stage_off;
+  *d = ctx->d_stage + ctx->stage_off;
+  ctx->stage_off += bytes;
+  return GINN_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ginn_b200_gemm(int device, void* stream, int dtype, int trans_a, int trans_b, int64_t m,
+                   int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+                   void* c, int64_t ldc, int accumulate) {
+  return gemm_impl(device, stream, dtype, trans_a, trans_b, m, n, k, a, lda, 0, b, ldb, 0, c, ldc,
+                   0, 1, accumulate);
+}
+
+int ginn_b200_gemm_batched(int device, void* stream, int dtype, int trans_a, int trans_b,
+                           int64_t m, int64_t n, int64_t k, const void* a, int64_t lda,
+                           int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, void* c,
+                           int64_t ldc, int64_t stride_c, int64_t batches, int accumulate) {
+  return gemm_impl(device, stream, dtype, trans_a, trans_b, m, n, k, a, lda, stride_a, b, ldb,
+                   stride_b, c, ldc, stride_c, batches, accumulate);
+}
+
+int ginn_b200_affine_forward(int device, void* stream_, int dtype, int npairs,
+                             const ginn_b200_pair* pairs, int64_t m, int64_t n, const void* bias,
+                             int act, void* out, int64_t ldo) {
+  if (int s = check_common(dtype, m, n, 0)) return s;
+  if (npairs < 1 || npairs > gb::kMaxPairs || pairs == nullptr)
+    return fail(GINN_B200_BAD_ARGUMENT, "npairs=%d must be in 1..%d", npairs, gb::kMaxPairs);
+  if (act < GINN_B200_ACT_NONE || act > GINN_B200_ACT_RELU)
+    return fail(GINN_B200_UNSUPPORTED, "activation %d cannot be fused", act);
+  if (m == 0 || n == 0) return GINN_B200_OK;
+  if (out == nullptr || ldo < m) return fail(GINN_B200_BAD_ARGUMENT, "bad output (ldo=%lld)", (long long)ldo);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  Problem p;
+  std::memset(&p, 0, sizeof(p));
+  int np = 0;
+  for (int i = 0; i < npairs; ++i) {
+    const ginn_b200_pair& q = pairs[i];
+    if (q.k < 0 || q.k > 0x7fffffffLL) return fail(GINN_B200_BAD_ARGUMENT, "pair %d: bad k", i);
+    if (q.k == 0) continue;
+    if (!q.a || !q.b || q.lda < m || q.ldb < q.k)
+      return fail(GINN_B200_BAD_ARGUMENT, "pair %d: null pointer or leading dimension too small", i);
+    p.a[np] = make_operand(dtype, q.a, q.lda, 0, 1, 0);
+    p.b[np] = make_operand(dtype, q.b, q.ldb, 0, 1, 1);
+    p.k[np] = q.k;
+    ++np;
+  }
+  p.npairs = np;
+  p.M = (int)m; p.N = (int)n; p.batches = 1;
+  p.c = out; p.ldc = ldo;
+  p.bias = bias;
+  p.act = act;
+  p.accumulate = 0;
+  return run_problem(ctx, dtype, p, static_cast<cudaStream_t>(stream_));
+}
+
+int ginn_b200_affine_backward(int device, void* stream_, int dtype, int npairs,
+                              const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,
+                              const void* dout, int64_t lddout, const void* out, int64_t ldout,
+                              int act, void* dbias) {
+  if (int s = check_common(dtype, m, n, 0)) return s;
+  if (npairs < 0 || (npairs > 0 && pairs == nullptr))
+    return fail(GINN_B200_BAD_ARGUMENT, "bad pair list");
+  if (act < GINN_B200_ACT_NONE || act > GINN_B200_ACT_RELU)
+    return fail(GINN_B200_UNSUPPORTED, "activation %d cannot be fused", act);
+  if (m == 0 || n == 0) return GINN_B200_OK;
+  if (dout == nullptr || lddout < m) return fail(GINN_B200_BAD_ARGUMENT, "bad upstream gradient");
+  if (act != GINN_B200_ACT_NONE && (out == nullptr || ldout != lddout))
+    return fail(GINN_B200_BAD_ARGUMENT,
+                "the node value is required for the derivative and must share the gradient's "
+                "leading dimension (ldout=%lld, lddout=%lld)", (long long)ldout, (long long)lddout);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  bool dbias_done = dbias == nullptr;
+  for (int i = 0; i < npairs; ++i) {
+    const ginn_b200_pair_grad& q = pairs[i];
+    if (q.k < 0 || q.k > 0x7fffffffLL) return fail(GINN_B200_BAD_ARGUMENT, "pair %d: bad k", i);
+    if (q.k == 0) continue;
+    if (q.db) {  // db (k x n) += A^T (k x m) * dA (m x n)
+      if (!q.a || q.lda < m || q.lddb < q.k)
+        return fail(GINN_B200_BAD_ARGUMENT, "pair %d: bad A / db", i);
+      Problem p;
+      std::memset(&p, 0, sizeof(p));
+      p.npairs = 1;
+      p.a[0] = make_operand(dtype, q.a, q.lda, 0, 1, 1);
+      p.b[0] = make_operand(dtype, dout, lddout, 0, 1, 1, out, act);
+      p.k[0] = m;
+      p.M = (int)q.k; p.N = (int)n; p.batches = 1;
+      p.c = q.db; p.ldc = q.lddb;
+      p.accumulate = 1;
+      if (int s = run_problem(ctx, dtype, p, stream)) return s;
+    }
+    if (q.da) {  // da (m x k) += dA (m x n) * B^T (n x k)
+      if (!q.b || q.ldb < q.k || q.ldda < m)
+        return fail(GINN_B200_BAD_ARGUMENT, "pair %d: bad B / da", i);
+      Problem p;
+      std::memset(&p, 0, sizeof(p));
+      p.npairs = 1;
+      p.a[0] = make_operand(dtype, dout, lddout, 0, 1, 0, out, act);
+      p.b[0] = make_operand(dtype, q.b, q.ldb, 0, 1, 0);
+      p.k[0] = n;
+      p.M = (int)m; p.N = (int)q.k; p.batches = 1;
+      p.c = q.da; p.ldc = q.ldda;
+      p.accumulate = 1;
+      if (!dbias_done) {
+        p.rowsum = dbias;  // bias gradient rides on the loader of dA
+        dbias_done = true;
+      }
+      if (int s = run_problem(ctx, dtype, p, stream)) return s;
+    }
+  }
+  if (!dbias_done) {
+    CU_TRY(gb::launch_rowsum(dtype, dout, act != GINN_B200_ACT_NONE ? out : nullptr, act, lddout,
+                             (int)m, n, dbias, stream));
+    g_launches.fetch_add(1);
+  }
+  return GINN_B200_OK;
+}
+
+int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroups,
+                      const ginn_b200_group* groups) {
+  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
+    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
+  if (mode < GINN_B200_GROUPED_FORWARD || mode > GINN_B200_GROUPED_DW)
+    return fail(GINN_B200_BAD_ARGUMENT, "unknown grouped mode %d", mode);
+  if (ngroups < 0 || (ngroups > 0 && groups == nullptr))
+    return fail(GINN_B200_BAD_ARGUMENT, "bad group list");
+  if (ngroups == 0) return GINN_B200_OK;
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  // Size of the staging slot: descriptors first, then the pointer tables.
+  size_t table_bytes = 0;
+  long long max_n = 0, sum_tiles128 = 0;
+  for (int g = 0; g < ngroups; ++g) {
+    const ginn_b200_group& q = groups[g];
+    if (q.m < 0 || q.k < 0 || q.ncols < 0 || q.m > 0x7fffffffLL || q.k > 0x7fffffffLL ||
+        q.ncols > 0x7fffffffLL)
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dimensions", g);
+    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
+    if (!q.w || q.ldw < q.m || !q.y_cols)
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad W or column table", g);
+    if ((mode != GINN_B200_GROUPED_DX && !q.x_cols) || (mode == GINN_B200_GROUPED_DX && !q.dx_cols))
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: missing column table for mode %d", g, mode);
+    if (mode == GINN_B200_GROUPED_DW && (!q.dw || q.lddw < q.m))
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dW", g);
+    table_bytes += 2 * static_cast<size_t>(q.ncols) * sizeof(void*);
+    const long long N = mode == GINN_B200_GROUPED_DW ? q.k : q.ncols;
+    const long long M = mode == GINN_B200_GROUPED_DX ? q.k : q.m;
+    max_n = N > max_n ? N : max_n;
+    sum_tiles128 += ((M + 127) / 128) * ((N + 127) / 128);
+  }
+  if (max_n == 0) return GINN_B200_OK;
+  const size_t desc_bytes = (static_cast<size_t>(ngroups) * sizeof(Problem) + 15) & ~size_t(15);
+  unsigned char *h, *d;
+  if (int s = stage_alloc(ctx, desc_bytes + table_bytes, &h, &d)) return s;
+
+  int bn = 128;
+  if (max_n <= 32) bn = 32;
+  else if (max_n <= 64 || sum_tiles128 < ctx->num_sms) bn = 64;
+
+  Problem* hp = reinterpret_cast<Problem*>(h);
+  size_t off = desc_bytes;
+  int np = 0, tile = 0;
+  for (int g = 0; g < ngroups; ++g) {
+    const ginn_b200_group& q = groups[g];
+    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
+    const size_t tb = static_cast<size_t>(q.ncols) * sizeof(void*);
+    const void** h_t0 = reinterpret_cast<const void**>(h + off);
+    const void* const* d_t0 = reinterpret_cast<const void* const*>(d + off);
+    off += tb;
+    const void** h_t1 = reinterpret_cast<const void**>(h + off);
+    const void* const* d_t1 = reinterpret_cast<const void* const*>(d + off);
+    off += tb;
+    Problem& p = hp[np];
+    std::memset(&p, 0, sizeof(p));
+    p.npairs = 1;
+    p.batches = 1;
+    bool x_al = true, y_al = true;
+    if (mode == GINN_B200_GROUPED_FORWARD) {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        h_t0[j] = q.x_cols[j];
+        h_t1[j] = q.y_cols[j];
+        x_al = x_al && aligned16(q.x_cols[j]);
+      }
+      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 0);
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
+      p.b[0].cols = d_t0;
+      p.b[0].vec = x_al ? 1 : 0;
+      p.k[0] = q.k;
+      p.M = (int)q.m; p.N = (int)q.ncols;
+      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
+      p.bias = q.bias;
+      p.accumulate = 0;
+    } else if (mode == GINN_B200_GROUPED_DX) {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        h_t0[j] = q.y_cols[j];
+        h_t1[j] = q.dx_cols[j];
+        y_al = y_al && aligned16(q.y_cols[j]);
+      }
+      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 1);  // W^T: contraction over m
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
+      p.b[0].cols = d_t0;
+      p.b[0].vec = y_al ? 1 : 0;
+      p.k[0] = q.m;
+      p.M = (int)q.k; p.N = (int)q.ncols;
+      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
+      p.accumulate = 1;
+    } else {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        h_t0[j] = q.y_cols[j];
+        h_t1[j] = q.x_cols[j];
+      }
+      p.a[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // dy columns, contraction over j
+      p.a[0].cols = d_t0;
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // x columns
+      p.b[0].cols = d_t1;
+      p.k[0] = q.ncols;
+      p.M = (int)q.m; p.N = (int)q.k;
+      p.c = q.dw; p.ldc = q.lddw;
+      p.rowsum = q.dbias;
+      p.accumulate = 1;
+    }
+    p.tiles_m = (p.M + 127) / 128;
+    p.tiles_n = (p.N + bn - 1) / bn;
+    p.tile_start = tile;
+    tile += p.tiles_m * p.tiles_n;
+    ++np;
+  }
+  CU_TRY(cudaMemcpyAsync(d, h, off, cudaMemcpyHostToDevice, stream));
+  CU_TRY(gb::launch_staged_grouped(dtype, reinterpret_cast<const Problem*>(d), np, tile, bn, stream,
+                                   ctx->d_status));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+const char* ginn_b200_last_error(void) { return t_error.c_str(); }
+
+int ginn_b200_device_status(int device, int reset) {
+  DevCtx* ctx = nullptr;
+  if (get_ctx(device, &ctx) != GINN_B200_OK || ctx == nullptr) return -1;
+  int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpy(&v, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (reset && v != 0) cudaMemset(ctx->d_status, 0, sizeof(int));
+  return v;
+}
+
+int ginn_b200_version(void) { return 100; }
+
+int ginn_b200_set_option(const char* name, int value) {
+  if (name && std::strcmp(name, "force_path") == 0) {
+    if (value < 0 || value > 3) return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0..3");
+    g_force_path.store(value);
+    return GINN_B200_OK;
+  }
+  return fail(GINN_B200_UNSUPPORTED, "unknown option '%s'", name ? name : "(null)");
+}
+
+int64_t ginn_b200_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

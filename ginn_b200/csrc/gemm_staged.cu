@@ -1,0 +1,475 @@
+// General tcgen05 GEMM for ginn's column-major tensors ("staged" kernel).
+//
+// Producer warps read the operands with ordinary global loads, so any alignment, any
+// leading dimension, transposed operands, strided batches and gathered columns (pointer
+// tables) all go through one code path.  While a tile slice sits in registers the
+// producers
+//   * multiply by the derivative of the nonlinearity (dY (.) act'(Y)) when asked to,
+//   * accumulate the bias gradient (row sums of the A operand),
+//   * split fp32 values into two TF32 planes (hi = rna(x), lo = rna(x - hi)),
+// and then write K-major, 128-byte-swizzled tiles to shared memory.  One elected thread
+// issues tcgen05.mma (kind::tf32 three times per k-step for fp32: lo*hi + hi*lo + hi*hi;
+// kind::f16 once for fp16) into a TMEM accumulator; the epilogue reads TMEM with tcgen05.ld,
+// adds bias / previous C, applies the activation and stores coalesced along rows, which are
+// contiguous in column-major storage.
+//
+// Role layout of a CTA (160 threads): warps 0-3 produce, then run the epilogue (TMEM lane
+// quarter = warp index); warp 4 allocates TMEM and issues the MMAs.
+#include "ptx.cuh"
+#include "problem.h"
+#include "launch.h"
+
+namespace gb {
+
+template <typename T>
+struct TT;
+template <>
+struct TT<float> {
+  static constexpr int EPC = 4;     // elements per 16-byte chunk
+  static constexpr int PLANES = 2;  // hi and lo TF32 planes
+  static constexpr uint32_t FMT = 2;
+};
+template <>
+struct TT<__half> {
+  static constexpr int EPC = 8;
+  static constexpr int PLANES = 1;
+  static constexpr uint32_t FMT = 0;
+};
+
+constexpr int kBM = 128;           // rows of C per tile == TMEM lanes
+constexpr int kRowBytes = 128;     // bytes of K per tile row == swizzle span
+constexpr int kKSteps = 4;         // MMAs (per plane combination) per k-block: 32 bytes of K each
+constexpr int kProducerThreads = 128;
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+template <typename T>
+__device__ __forceinline__ T from_f(float x);
+template <>
+__device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+
+// Forward nonlinearities, following ginn/nonlin.h:93-95 (tanh), :116-118 (relu), :136-145 (sigmoid;
+// fp32 uses 0.5*tanh(0.5x)+0.5, Half the sign-split exponential form).
+template <typename T>
+__device__ __forceinline__ float act_forward(int act, float x) {
+  switch (act) {
+    case ACT_TANH: return tanhf(x);
+    case ACT_RELU: return fmaxf(x, 0.f);
+    case ACT_SIGMOID:
+      if (sizeof(T) == 2) {
+        if (x > 0.f) return 1.f / (1.f + expf(-x));
+        const float e = expf(x);
+        return e / (1.f + e);
+      }
+      return 0.5f * tanhf(0.5f * x) + 0.5f;
+    default: return x;
+  }
+}
+// Derivative times upstream gradient, expressed through the output y
+// (ginn/nonlin.h:96-106, :119-126, :146-152).
+template <typename T>
+__device__ __forceinline__ float act_backward(int act, float y, float dy) {
+  switch (act) {
+    case ACT_TANH: return sizeof(T) == 2 ? dy - y * y * dy : (1.f - y * y) * dy;
+    case ACT_RELU: return y > 0.f ? dy : 0.f;
+    case ACT_SIGMOID: return y * (1.f - y) * dy;
+    default: return dy;
+  }
+}
+
+__device__ __forceinline__ float tf32_rna(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+// 16 bytes of operand X(o, kk .. kk+EPC-1), zero outside the matrix, derivative applied.
+template <typename T>
+__device__ __forceinline__ uint4 fetch_chunk(const Operand& op, long long boff, int o, int O,
+                                             long long kk, long long K) {
+  constexpr int E = TT<T>::EPC;
+  uint4 du = make_uint4(0, 0, 0, 0), yu = make_uint4(0, 0, 0, 0);
+  if (o >= O || kk >= K) return du;
+  T* d = reinterpret_cast<T*>(&du);
+  T* y = reinterpret_cast<T*>(&yu);
+  const bool has_y = op.dact != ACT_NONE;
+  if (op.k_contig) {
+    const T* col = op.cols ? static_cast<const T*>(op.cols[o])
+                           : static_cast<const T*>(op.base) + boff + static_cast<long long>(o) * op.ld;
+    const T* ycol = nullptr;
+    if (has_y)
+      ycol = op.ycols ? static_cast<const T*>(op.ycols[o])
+                      : static_cast<const T*>(op.ybase) + boff + static_cast<long long>(o) * op.ld;
+    if (op.vec && kk + E <= K) {
+      du = __ldg(reinterpret_cast<const uint4*>(col + kk));
+      if (has_y) yu = __ldg(reinterpret_cast<const uint4*>(ycol + kk));
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        if (kk + e < K) {
+          d[e] = __ldg(col + kk + e);
+          if (has_y) y[e] = __ldg(ycol + kk + e);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      if (kk + e < K) {
+        const T* col = op.cols ? static_cast<const T*>(op.cols[kk + e])
+                               : static_cast<const T*>(op.base) + boff + (kk + e) * op.ld;
+        d[e] = __ldg(col + o);
+        if (has_y) {
+          const T* ycol = op.ycols ? static_cast<const T*>(op.ycols[kk + e])
+                                   : static_cast<const T*>(op.ybase) + boff + (kk + e) * op.ld;
+          y[e] = __ldg(ycol + o);
+        }
+      }
+    }
+  }
+  if (has_y) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) d[e] = from_f<T>(act_backward<T>(op.dact, to_f(y[e]), to_f(d[e])));
+  }
+  return du;
+}
+
+// Which (row, 16-byte chunk) of a ROWS x 128 B tile thread t handles in its i-th slot.
+//   k_contig: 8 consecutive threads read the 128 contiguous bytes of one row.
+//   else    : consecutive threads read consecutive rows (contiguous in memory) of one K column.
+template <int ROWS>
+__device__ __forceinline__ void slot_of(int k_contig, int i, int t, int& row, int& chunk) {
+  if (k_contig) {
+    row = i * 16 + (t >> 3);
+    chunk = t & 7;
+  } else {
+    const int L = i * kProducerThreads + t;
+    row = L % ROWS;
+    chunk = L / ROWS;
+  }
+}
+
+template <typename T, int ROWS>
+__device__ __forceinline__ void load_tile(const Operand& op, long long boff, int o0, int O,
+                                          long long k0, long long K, int t,
+                                          uint4 (&r)[ROWS / 16]) {
+#pragma unroll
+  for (int i = 0; i < ROWS / 16; ++i) {
+    int row, c;
+    slot_of<ROWS>(op.k_contig, i, t, row, c);
+    r[i] = fetch_chunk<T>(op, boff, o0 + row, O, k0 + c * TT<T>::EPC, K);
+  }
+}
+
+template <typename T, int ROWS>
+__device__ __forceinline__ void store_tile(int k_contig, int t, const uint4 (&r)[ROWS / 16],
+                                           uint8_t* plane0, uint8_t* plane1, float* rowsum) {
+#pragma unroll
+  for (int i = 0; i < ROWS / 16; ++i) {
+    int row, c;
+    slot_of<ROWS>(k_contig, i, t, row, c);
+    const uint32_t off = sw128_offset(row, c);
+    if (TT<T>::PLANES == 2) {
+      const float* x = reinterpret_cast<const float*>(&r[i]);
+      uint4 hu, lu;
+      float* h = reinterpret_cast<float*>(&hu);
+      float* l = reinterpret_cast<float*>(&lu);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float hi = tf32_rna(x[e]);
+        // inf/nan stay in the hi plane only: inf - inf would poison the lo plane.
+        const float lo = (fabsf(hi) <= 3.4028234e38f) ? tf32_rna(x[e] - hi) : 0.f;
+        h[e] = hi;
+        l[e] = lo;
+        if (rowsum) *rowsum += x[e];
+      }
+      *reinterpret_cast<uint4*>(plane0 + off) = hu;
+      *reinterpret_cast<uint4*>(plane1 + off) = lu;
+    } else {
+      if (rowsum) {
+        const __half* x = reinterpret_cast<const __half*>(&r[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) *rowsum += __half2float(x[e]);
+      }
+      *reinterpret_cast<uint4*>(plane0 + off) = r[i];
+    }
+  }
+}
+
+template <typename T, int BN>
+struct StageLayout {
+  static constexpr int A_PLANE = kBM * kRowBytes;
+  static constexpr int B_PLANE = BN * kRowBytes;
+  static constexpr int A_BYTES = A_PLANE * TT<T>::PLANES;
+  static constexpr int B_BYTES = B_PLANE * TT<T>::PLANES;
+  static constexpr int BYTES = A_BYTES + B_BYTES;
+};
+
+template <typename T, int BN, int STAGES, bool GROUPED>
+__global__ void __launch_bounds__(160, 1)
+gemm_staged_kernel(const __grid_constant__ Problem p0, const Problem* __restrict__ probs,
+                   int nprobs, int* __restrict__ status) {
+  using L = StageLayout<T, BN>;
+  constexpr int E = TT<T>::EPC;
+  constexpr int BK = 8 * E;  // elements of K per k-block
+  constexpr uint32_t NCOLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t IDESC = make_idesc(TT<T>::FMT, 0, 0, kBM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ Problem sprob;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- which problem / tile ----
+  int tile = blockIdx.x;
+  if (GROUPED) {
+    int g = 0;
+    for (int i = 0; i < nprobs; ++i)
+      if (tile >= probs[i].tile_start) g = i;
+    const int nwords = sizeof(Problem) / 4;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(probs + g);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(&sprob);
+    for (int i = tid; i < nwords; i += blockDim.x) dst[i] = src[i];
+    __syncthreads();
+  }
+  const Problem& P = GROUPED ? sprob : p0;
+  tile -= P.tile_start;
+  const int m_tile = tile % P.tiles_m;
+  const int rest = tile / P.tiles_m;
+  const int n_tile = rest % P.tiles_n;
+  const long long batch = rest / P.tiles_n;
+  const int m0 = m_tile * kBM;
+  const int n0 = n_tile * BN;
+
+  int nkb = 0;
+  for (int p = 0; p < P.npairs; ++p) nkb += static_cast<int>((P.k[p] + BK - 1) / BK);
+
+  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles_base - smem_u32(smem_raw));
+
+  // ---- setup ----
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(smem_u32(&full_bar[s]), kProducerThreads);
+        mbar_init(smem_u32(&empty_bar[s]), 1);
+      }
+      mbar_init(smem_u32(&accum_bar), 1);
+      fence_mbar_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), NCOLS);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp < 4) {
+    // ================= producers =================
+    bool ok = true;
+    float rs = 0.f;
+    const bool want_rowsum = P.rowsum != nullptr && n_tile == 0;
+    uint4 ra[kBM / 16];
+    uint4 rb[BN / 16];
+    int pair = 0;
+    long long k0 = 0;
+    if (nkb > 0) {
+      load_tile<T, kBM>(P.a[0], batch * P.a[0].batch_stride, m0, P.M, 0, P.k[0], tid, ra);
+      load_tile<T, BN>(P.b[0], batch * P.b[0].batch_stride, n0, P.N, 0, P.k[0], tid, rb);
+    }
+    int s = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < nkb; ++it) {
+      if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) {
+        ok = false;
+        break;
+      }
+      uint8_t* st = tiles_ptr + s * L::BYTES;
+      store_tile<T, kBM>(P.a[pair].k_contig, tid, ra, st, st + L::A_PLANE,
+                         (want_rowsum && pair == 0) ? &rs : nullptr);
+      store_tile<T, BN>(P.b[pair].k_contig, tid, rb, st + L::A_BYTES,
+                        st + L::A_BYTES + L::B_PLANE, nullptr);
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&full_bar[s]));
+      if (++s == STAGES) {
+        s = 0;
+        ph ^= 1u;
+      }
+      k0 += BK;
+      if (k0 >= P.k[pair]) {
+        ++pair;
+        k0 = 0;
+      }
+      if (it + 1 < nkb) {
+        load_tile<T, kBM>(P.a[pair], batch * P.a[pair].batch_stride, m0, P.M, k0, P.k[pair], tid,
+                          ra);
+        load_tile<T, BN>(P.b[pair], batch * P.b[pair].batch_stride, n0, P.N, k0, P.k[pair], tid,
+                         rb);
+      }
+    }
+    if (want_rowsum && ok) {
+      const int row = m0 + tid;
+      if (row < P.M) {
+        if (sizeof(T) == 4)
+          atomicAdd(static_cast<float*>(P.rowsum) + row, rs);
+        else
+          atomicAdd(static_cast<__half*>(P.rowsum) + row, __float2half_rn(rs));
+      }
+    }
+
+    // ================= epilogue =================
+    if (ok && mbar_wait(smem_u32(&accum_bar), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
+      tc_fence_after();
+      const int row = m0 + warp * 32 + lane;
+      const bool row_ok = row < P.M;
+      float bias = 0.f;
+      if (P.bias != nullptr && row_ok) bias = to_f(static_cast<const T*>(P.bias)[row]);
+      T* cbase = static_cast<T*>(P.c) + batch * P.c_batch_stride;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = n0 + c0 + j;
+          if (row_ok && col < P.N) {
+            T* cp = (P.ccols ? static_cast<T*>(P.ccols[col]) : cbase + static_cast<long long>(col) * P.ldc) + row;
+            float x = (nkb > 0 ? __uint_as_float(v[j]) : 0.f) + bias;
+            if (P.accumulate) x += to_f(*cp);
+            *cp = from_f<T>(act_forward<T>(P.act, x));
+          }
+        }
+      }
+    }
+  } else {
+    // ================= MMA issuer =================
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int it = 0; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&full_bar[s]), ph, status, DEV_TIMEOUT_FULL, it)) break;
+        tc_fence_after();
+        const uint32_t a0 = tiles_base + s * L::BYTES;
+        const uint32_t b0 = a0 + L::A_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+          const uint32_t first = (it > 0 || ks > 0) ? 1u : 0u;
+          if (TT<T>::PLANES == 2) {
+            const uint64_t a_hi = make_smem_desc(a0 + ks * 32, 16, 1024);
+            const uint64_t a_lo = make_smem_desc(a0 + L::A_PLANE + ks * 32, 16, 1024);
+            const uint64_t b_hi = make_smem_desc(b0 + ks * 32, 16, 1024);
+            const uint64_t b_lo = make_smem_desc(b0 + L::B_PLANE + ks * 32, 16, 1024);
+            mma_tf32(tmem, a_lo, b_hi, IDESC, first);
+            mma_tf32(tmem, a_hi, b_lo, IDESC, 1u);
+            mma_tf32(tmem, a_hi, b_hi, IDESC, 1u);
+          } else {
+            const uint64_t a = make_smem_desc(a0 + ks * 32, 16, 1024);
+            const uint64_t b = make_smem_desc(b0 + ks * 32, 16, 1024);
+            mma_f16(tmem, a, b, IDESC, first);
+          }
+        }
+        tc_commit(smem_u32(&empty_bar[s]));
+        if (++s == STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+      tc_commit(smem_u32(&accum_bar));
+    }
+    __syncwarp();
+  }
+
+  // ---- teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, NCOLS);
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// Host side
+// -------------------------------------------------------------------------------------------
+template <typename T, int BN>
+constexpr int stages_for() {
+  constexpr int per = StageLayout<T, BN>::BYTES;
+  constexpr int budget = 200 * 1024;
+  return (budget / per) > 6 ? 6 : (budget / per);
+}
+
+template <typename T, int BN, bool GROUPED>
+static cudaError_t launch_one(const Problem& p, const Problem* dprobs, int nprobs, int total_tiles,
+                              cudaStream_t stream, int* status) {
+  constexpr int STAGES = stages_for<T, BN>();
+  static_assert(STAGES >= 2, "need at least two stages");
+  auto kern = gemm_staged_kernel<T, BN, STAGES, GROUPED>;
+  const int smem = STAGES * StageLayout<T, BN>::BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  kern<<<total_tiles, 160, smem, stream>>>(p, dprobs, nprobs, status);
+  return cudaGetLastError();
+}
+
+int staged_pick_bn(int dtype, long long M, long long N, long long batches, int num_sms) {
+  (void)dtype;
+  if (N <= 32) return 32;
+  if (N <= 64) return 64;
+  // Prefer the widest tile that still gives every SM a CTA.
+  const long long tm = (M + kBM - 1) / kBM;
+  if (tm * ((N + 127) / 128) * batches >= num_sms) return 128;
+  if (tm * ((N + 63) / 64) * batches >= num_sms || N % 64 == 0) return 64;
+  return 128;
+}
+
+template <typename T>
+static cudaError_t launch_staged_t(Problem& p, int bn, cudaStream_t stream, int* status) {
+  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_n = (p.N + bn - 1) / bn;
+  p.tile_start = 0;
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
+  if (total <= 0) return cudaSuccess;
+  if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+  const int tt = static_cast<int>(total);
+  switch (bn) {
+    case 32: return launch_one<T, 32, false>(p, nullptr, 1, tt, stream, status);
+    case 64: return launch_one<T, 64, false>(p, nullptr, 1, tt, stream, status);
+    default: return launch_one<T, 128, false>(p, nullptr, 1, tt, stream, status);
+  }
+}
+
+cudaError_t launch_staged(int dtype, Problem& p, int bn, cudaStream_t stream, int* status) {
+  return dtype == 0 ? launch_staged_t<float>(p, bn, stream, status)
+                    : launch_staged_t<__half>(p, bn, stream, status);
+}
+
+template <typename T>
+static cudaError_t launch_grouped_t(const Problem* dprobs, int nprobs, int total_tiles, int bn,
+                                    cudaStream_t stream, int* status) {
+  Problem dummy{};
+  if (total_tiles <= 0) return cudaSuccess;
+  switch (bn) {
+    case 32: return launch_one<T, 32, true>(dummy, dprobs, nprobs, total_tiles, stream, status);
+    case 64: return launch_one<T, 64, true>(dummy, dprobs, nprobs, total_tiles, stream, status);
+    default: return launch_one<T, 128, true>(dummy, dprobs, nprobs, total_tiles, stream, status);
+  }
+}
+
+cudaError_t launch_staged_grouped(int dtype, const Problem* dprobs, int nprobs, int total_tiles,
+                                  int bn, cudaStream_t stream, int* status) {
+  return dtype == 0 ? launch_grouped_t<float>(dprobs, nprobs, total_tiles, bn, stream, status)
+                    : launch_grouped_t<__half>(dprobs, nprobs, total_tiles, bn, stream, status);
+}
+
+}  // namespace gb

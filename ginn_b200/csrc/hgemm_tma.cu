@@ -1,0 +1,368 @@
+// Persistent, warp-specialised fp16 GEMM (fp32 accumulation) for large, 16-byte-aligned
+// problems on column-major storage:  C = op(A) * op(B) [+ C], optionally strided-batched.
+//
+//   warp 0      : TMA producer.  One elected thread streams 128x64 A slices and 256x64 B slices
+//                 into a 4-stage ring of 128-byte-swizzled shared-memory tiles.
+//   warp 1      : allocates all 512 TMEM columns (two 128x256 fp32 accumulators) and issues
+//                 tcgen05.mma kind::f16; tcgen05.commit frees ring stages and publishes finished
+//                 accumulators.
+//   warps 2..5  : epilogue.  tcgen05.ld -> fp16 -> global, coalesced along rows; runs while the
+//                 MMA warp fills the other accumulator for the next tile.
+//
+// Column-major operands map onto the tensor core without any transposition copy:
+//   A not transposed (m x k, m contiguous)  -> MN-major operand, loaded as two 64(m) x 64(k) boxes
+//   A transposed     (k x m, k contiguous)  -> K-major operand, one 64(k) x 128(m) box
+//   B not transposed (k x n, k contiguous)  -> K-major operand, one 64(k) x 256(n) box
+//   B transposed     (n x k, n contiguous)  -> MN-major operand, four 64(n) x 64(k) boxes
+// Every CTA loads its own tiles; no cluster multicast is used anywhere.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+#include "ptx.cuh"
+#include "launch.h"
+
+namespace gb {
+
+namespace {
+
+constexpr int TBM = 128, TBN = 256, TBK = 64, TSTAGES = 4;
+constexpr int TA_BYTES = TBM * TBK * 2;  // 16 KiB
+constexpr int TB_BYTES = TBN * TBK * 2;  // 32 KiB
+constexpr int TSTAGE_BYTES = TA_BYTES + TB_BYTES;
+constexpr int TMN_ATOM_BYTES = 64 * TBK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
+constexpr int TGROUP_M = 16;                  // m-tiles per rasterisation group (L2 reuse)
+
+struct HParams {
+  __half* C;
+  long long ldc, strideC;
+  int M, N, K, batches;
+  int accumulate;
+  int tiles_m, tiles_n, total_tiles;
+};
+
+__device__ __forceinline__ void decode_tile(const HParams& p, int t, int& m_idx, int& n_idx,
+                                            int& batch) {
+  const int per_batch = p.tiles_m * p.tiles_n;
+  batch = t / per_batch;
+  const int r = t % per_batch;
+  const int group_span = TGROUP_M * p.tiles_n;
+  const int g = r / group_span;
+  const int first_m = g * TGROUP_M;
+  const int gm = min(TGROUP_M, p.tiles_m - first_m);
+  const int in_g = r % group_span;
+  m_idx = first_m + in_g % gm;
+  n_idx = in_g / gm;
+}
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(192, 1)
+hgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const HParams p, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[TSTAGES];
+  __shared__ __align__(8) uint64_t empty_bar[TSTAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int nkb = (p.K + TBK - 1) / TBK;
+  constexpr uint32_t IDESC = make_idesc(0, A_MN, B_MN, TBM, TBN);
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    if (lane == 0) {
+      for (int s = 0; s < TSTAGES; ++s) {
+        mbar_init(smem_u32(&full_bar[s]), 1);
+        mbar_init(smem_u32(&empty_bar[s]), 1);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(smem_u32(&acc_full[a]), 1);
+        mbar_init(smem_u32(&acc_empty[a]), 4);
+      }
+      fence_mbar_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        int m_idx, n_idx, batch;
+        decode_tile(p, t, m_idx, n_idx, batch);
+        const int m0 = m_idx * TBM, n0 = n_idx * TBN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, kb)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          const uint32_t a_s = tiles_base + s * TSTAGE_BYTES;
+          const uint32_t b_s = a_s + TA_BYTES;
+          const int k0 = kb * TBK;
+          mbar_arrive_expect_tx(bar, TSTAGE_BYTES);
+          if (A_MN) {
+            tma_load_3d(a_s, &tmA, bar, m0, k0, batch);
+            tma_load_3d(a_s + TMN_ATOM_BYTES, &tmA, bar, m0 + 64, k0, batch);
+          } else {
+            tma_load_3d(a_s, &tmA, bar, k0, m0, batch);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              tma_load_3d(b_s + j * TMN_ATOM_BYTES, &tmB, bar, n0 + 64 * j, k0, batch);
+          } else {
+            tma_load_3d(b_s, &tmB, bar, k0, n0, batch);
+          }
+          if (++s == TSTAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_ph ^ 1u, status, DEV_TIMEOUT_TMEM_FREE, it)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d = tmem + acc * TBN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, status, DEV_TIMEOUT_FULL, kb)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_s = tiles_base + s * TSTAGE_BYTES;
+          const uint32_t b_s = a_s + TA_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < TBK / 16; ++ks) {
+            // K-major: 16 elements of K = 32 bytes inside the 128-byte row.
+            // MN-major: 16 elements of K = two groups of eight 128-byte rows = 2048 bytes.
+            const uint64_t ad = A_MN ? make_smem_desc(a_s + ks * 2048, TMN_ATOM_BYTES, 1024)
+                                     : make_smem_desc(a_s + ks * 32, 16, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(b_s + ks * 2048, TMN_ATOM_BYTES, 1024)
+                                     : make_smem_desc(b_s + ks * 32, 16, 1024);
+            mma_f16(d, ad, bd, IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&empty_bar[s]));
+          if (++s == TSTAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        tc_commit(smem_u32(&acc_full[acc]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===================== epilogue =====================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+      int m_idx, n_idx, batch;
+      decode_tile(p, t, m_idx, n_idx, batch);
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1u;
+      if (!mbar_wait(smem_u32(&acc_full[acc]), acc_ph, status, DEV_TIMEOUT_ACCUM, it)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m_idx * TBM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int n0 = n_idx * TBN;
+      __half* cbase = p.C + static_cast<long long>(batch) * p.strideC + row;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + acc * TBN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TBN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c0, v);
+        tmem_ld_wait();
+        if (c0 + 32 == TBN) {
+          // Accumulator drained into registers: hand it back to the MMA warp.
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = n0 + c0 + j;
+            if (col < p.N) {
+              __half* cp = cbase + static_cast<long long>(col) * p.ldc;
+              float x = __uint_as_float(v[j]);
+              if (p.accumulate) x += __half2float(*cp);
+              *cp = __float2half_rn(x);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensor maps
+// ------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+  static EncodeFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) !=
+            cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeFn>(sym);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  unsigned long long d0, d1, d2, s1, s2;
+  unsigned b0, b1;
+  int dev;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    const unsigned long long* w = reinterpret_cast<const unsigned long long*>(&k);
+    size_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+    return h;
+  }
+};
+
+// fp16 3-D map: dim0 = contiguous extent, dim1 = number of stored columns, dim2 = batches.
+bool encode_map(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                unsigned long long d2, unsigned long long ld, unsigned long long batch_stride,
+                unsigned b0, unsigned b1) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.ptr = ptr;
+  key.d0 = d0; key.d1 = d1; key.d2 = d2;
+  key.s1 = ld * 2; key.s2 = batch_stride * 2;
+  key.b0 = b0; key.b1 = b1;
+  cudaGetDevice(&key.dev);
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {key.s1, key.s2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+template <int A_MN, int B_MN>
+cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const HParams& p, int grid,
+                           cudaStream_t stream, int* status) {
+  auto kern = hgemm_tma_kernel<A_MN, B_MN>;
+  const int smem = TSTAGES * TSTAGE_BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, 192, smem, stream>>>(ta, tb, p, status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool hgemm_tma_supported(const HgemmArgs& a) {
+  if (a.transA && a.transB) return false;
+  if (a.M < 1 || a.N < 1 || a.K < 1 || a.batches < 1) return false;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al16(a.A) || !al16(a.B)) return false;
+  if (a.lda % 8 || a.ldb % 8) return false;
+  if (a.batches > 1 && (a.strideA % 8 || a.strideB % 8)) return false;
+  return get_encode() != nullptr;
+}
+
+cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status) {
+  // Stored extents: A is (transA ? K x M : M x K), B is (transB ? N x K : K x N).
+  const unsigned long long a_rows = a.transA ? a.K : a.M, a_cols = a.transA ? a.M : a.K;
+  const unsigned long long b_rows = a.transB ? a.N : a.K, b_cols = a.transB ? a.K : a.N;
+  const unsigned long long sa = a.batches > 1 ? a.strideA : a.lda * a_cols;
+  const unsigned long long sb = a.batches > 1 ? a.strideB : a.ldb * b_cols;
+  CUtensorMap ta, tb;
+  // A: MN-major boxes are 64(m) x 64(k); K-major box is 64(k) x 128(m).
+  if (!encode_map(&ta, a.A, a_rows, a_cols, a.batches, a.lda, sa, 64, a.transA ? TBM : TBK))
+    return cudaErrorInvalidValue;
+  // B: K-major box is 64(k) x 256(n); MN-major boxes are 64(n) x 64(k).
+  if (!encode_map(&tb, a.B, b_rows, b_cols, a.batches, a.ldb, sb, 64, a.transB ? TBK : TBN))
+    return cudaErrorInvalidValue;
+  HParams p;
+  p.C = static_cast<__half*>(a.C);
+  p.ldc = a.ldc;
+  p.strideC = a.strideC;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batches = a.batches;
+  p.accumulate = a.accumulate;
+  p.tiles_m = (a.M + TBM - 1) / TBM;
+  p.tiles_n = (a.N + TBN - 1) / TBN;
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batches;
+  if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+  p.total_tiles = static_cast<int>(total);
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  if (!a.transA && !a.transB) return launch_variant<1, 0>(ta, tb, p, grid, stream, status);
+  if (a.transA && !a.transB) return launch_variant<0, 0>(ta, tb, p, grid, stream, status);
+  return launch_variant<1, 1>(ta, tb, p, grid, stream, status);
+}
+
+}  // namespace gb

@@ -1,0 +1,37 @@
+// Host-side launch entry points of the individual kernels (internal; the public surface is
+// the C ABI in include/ginn_b200.h).
+#pragma once
+#include <cuda_runtime.h>
+#include "problem.h"
+
+namespace gb {
+
+// --- staged tcgen05 kernel (gemm_staged.cu); dtype 0 = fp32 (3xTF32), 1 = fp16 ---
+int staged_pick_bn(int dtype, long long M, long long N, long long batches, int num_sms);
+cudaError_t launch_staged(int dtype, Problem& p, int bn, cudaStream_t stream, int* status);
+cudaError_t launch_staged_grouped(int dtype, const Problem* dprobs, int nprobs, int total_tiles,
+                                  int bn, cudaStream_t stream, int* status);
+
+// --- TMA-fed persistent fp16 kernel (hgemm_tma.cu) ---
+struct HgemmArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  long long lda, ldb, ldc;
+  long long strideA, strideB, strideC;  // elements
+  int transA, transB;
+  int M, N, K, batches;
+  int accumulate;
+};
+// Returns true when the TMA path can take the problem (alignment and size rules).
+bool hgemm_tma_supported(const HgemmArgs& a);
+cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
+
+// --- CUDA-core kernels for degenerate shapes and elementwise helpers (small.cu) ---
+// One warp per output element; used for tiny m*n (batched dot products) and k == 0.
+cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream);
+// rowsum[o] += sum_n dY[o, n] * act'(Y[o, n])   (bias gradient when no weight gradient is wanted)
+cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
+                          long long N, void* rowsum, cudaStream_t stream);
+
+}  // namespace gb

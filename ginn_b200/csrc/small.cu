@@ -1,0 +1,152 @@
+// CUDA-core kernels for the shapes the tensor-core tiles do not fit:
+//   * products with a tiny result (m*n of a few elements), e.g. the batched 1x1 dot products
+//     that SoftmaxOp::backward and LayerNormNode::backward send through gpu_batched_prod
+//     (ginn/nonlin.h:180-183, ginn/node/layernorm.h:61-64), and k == 0;
+//   * the bias gradient alone (row sums of dY (.) act'(Y)) when no weight gradient is wanted.
+// fp32 accumulation, one warp per output element, lanes strided along the contraction.
+#include <cuda_fp16.h>
+#include "launch.h"
+
+namespace gb {
+
+namespace {
+
+__device__ __forceinline__ float ld_f(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float ld_f(const __half* p) { return __half2float(__ldg(p)); }
+__device__ __forceinline__ void st_f(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_f(__half* p, float v) { *p = __float2half_rn(v); }
+
+template <typename T>
+__device__ __forceinline__ float act_forward(int act, float x) {
+  switch (act) {
+    case ACT_TANH: return tanhf(x);
+    case ACT_RELU: return fmaxf(x, 0.f);
+    case ACT_SIGMOID:
+      if (sizeof(T) == 2) {
+        if (x > 0.f) return 1.f / (1.f + expf(-x));
+        const float e = expf(x);
+        return e / (1.f + e);
+      }
+      return 0.5f * tanhf(0.5f * x) + 0.5f;
+    default: return x;
+  }
+}
+template <typename T>
+__device__ __forceinline__ float act_backward(int act, float y, float dy) {
+  switch (act) {
+    case ACT_TANH: return sizeof(T) == 2 ? dy - y * y * dy : (1.f - y * y) * dy;
+    case ACT_RELU: return y > 0.f ? dy : 0.f;
+    case ACT_SIGMOID: return y * (1.f - y) * dy;
+    default: return dy;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float fetch(const Operand& op, long long boff, long long o,
+                                       long long kk) {
+  const long long col = op.k_contig ? o : kk;
+  const long long row = op.k_contig ? kk : o;
+  const T* p = (op.cols ? static_cast<const T*>(op.cols[col])
+                        : static_cast<const T*>(op.base) + boff + col * op.ld) + row;
+  float v = ld_f(p);
+  if (op.dact != ACT_NONE) {
+    const T* py = (op.ycols ? static_cast<const T*>(op.ycols[col])
+                            : static_cast<const T*>(op.ybase) + boff + col * op.ld) + row;
+    // The staged kernel rounds dY (.) act'(Y) to T before the product; do the same here.
+    T r;
+    st_f(&r, act_backward<T>(op.dact, ld_f(py), v));
+    v = ld_f(&r);
+  }
+  return v;
+}
+
+template <typename T>
+__global__ void small_gemm_kernel(const __grid_constant__ Problem P) {
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long per_batch = static_cast<long long>(P.M) * P.N;
+  const long long total = per_batch * P.batches;
+  if (warp_global >= total) return;
+  const long long batch = warp_global / per_batch;
+  const long long rem = warp_global % per_batch;
+  const long long row = rem % P.M;
+  const long long col = rem / P.M;
+  float acc = 0.f;
+  for (int p = 0; p < P.npairs; ++p) {
+    const long long ab = batch * P.a[p].batch_stride, bb = batch * P.b[p].batch_stride;
+    for (long long kk = lane; kk < P.k[p]; kk += 32)
+      acc += fetch<T>(P.a[p], ab, row, kk) * fetch<T>(P.b[p], bb, col, kk);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    T* cp = (P.ccols ? static_cast<T*>(P.ccols[col])
+                     : static_cast<T*>(P.c) + batch * P.c_batch_stride + col * P.ldc) + row;
+    float x = acc;
+    if (P.bias) x += ld_f(static_cast<const T*>(P.bias) + row);
+    if (P.accumulate) x += ld_f(cp);
+    st_f(cp, act_forward<T>(P.act, x));
+  }
+}
+
+// One warp per row: rowsum[o] += sum_n dY[o,n] * act'(Y[o,n]).
+template <typename T>
+__global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y, int dact,
+                              long long ld, int M, long long N, T* __restrict__ rowsum) {
+  // Threads of a block cover 32 consecutive rows (coalesced along the column) and
+  // blockDim.y slices of the columns; partial sums meet in shared memory.
+  __shared__ float part[8][33];
+  const int row = blockIdx.x * 32 + threadIdx.x;
+  float acc = 0.f;
+  if (row < M) {
+    for (long long n = threadIdx.y; n < N; n += blockDim.y) {
+      float v = ld_f(dy + n * ld + row);
+      if (dact != ACT_NONE) {
+        T r;
+        st_f(&r, act_backward<T>(dact, ld_f(y + n * ld + row), v));
+        v = ld_f(&r);
+      }
+      acc += v;
+    }
+  }
+  part[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && row < M) {
+    float s = 0.f;
+    for (int j = 0; j < blockDim.y; ++j) s += part[j][threadIdx.x];
+    st_f(rowsum + row, ld_f(rowsum + row) + s);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream) {
+  const long long total = static_cast<long long>(p.M) * p.N * p.batches;
+  if (total <= 0) return cudaSuccess;
+  const int threads = 128;  // 4 warps = 4 outputs per block
+  const long long blocks = (total + 3) / 4;
+  if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+  if (dtype == 0)
+    small_gemm_kernel<float><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p);
+  else
+    small_gemm_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
+                          long long N, void* rowsum, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return cudaSuccess;
+  dim3 block(32, 8);
+  dim3 grid((M + 31) / 32);
+  if (dtype == 0)
+    rowsum_kernel<float><<<grid, block, 0, stream>>>(static_cast<const float*>(dy),
+                                                     static_cast<const float*>(y), dact, ld, M, N,
+                                                     static_cast<float*>(rowsum));
+  else
+    rowsum_kernel<__half><<<grid, block, 0, stream>>>(static_cast<const __half*>(dy),
+                                                      static_cast<const __half*>(y), dact, ld, M,
+                                                      N, static_cast<__half*>(rowsum));
+  return cudaGetLastError();
+}
+
+}  // namespace gb

@@ -1,0 +1,148 @@
+/* ginn_b200 -- C ABI of the B200 (sm_100a) back end for ginn's dense-contraction path.
+ *
+ * All matrices are column-major, as in ginn (ginn/tensor.h).  Pointers are device pointers on
+ * GPU `device`; `stream` is a cudaStream_t (NULL = legacy default stream).  Calls enqueue work
+ * and return; they never synchronise and never allocate from a ginn Device (the library keeps
+ * small internal buffers of its own).  Every function returns a ginn_b200_status; on a non-zero
+ * status ginn_b200_last_error() describes the failure for the calling thread.
+ *
+ * dtype: GINN_B200_F32 computes with three TF32 tensor-core products per term (fp32-level
+ * accuracy, fp32 accumulation); GINN_B200_F16 uses fp16 inputs/outputs with fp32 accumulation.
+ */
+#ifndef GINN_B200_H
+#define GINN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  GINN_B200_OK = 0,
+  GINN_B200_BAD_ARGUMENT = 1,  /* shape / pointer / leading-dimension check failed            */
+  GINN_B200_UNSUPPORTED = 2,   /* dtype or option not supported                               */
+  GINN_B200_CUDA_ERROR = 3,    /* a CUDA runtime call failed (text in ginn_b200_last_error)   */
+  GINN_B200_DEVICE_TIMEOUT = 4 /* a kernel gave up on a bounded wait (ginn_b200_device_status) */
+} ginn_b200_status;
+
+typedef enum { GINN_B200_F32 = 0, GINN_B200_F16 = 1 } ginn_b200_dtype;
+
+/* Nonlinearities that are fused into the kernels (ginn/nonlin.h:67-155). */
+typedef enum {
+  GINN_B200_ACT_NONE = 0,
+  GINN_B200_ACT_TANH = 1,
+  GINN_B200_ACT_SIGMOID = 2,
+  GINN_B200_ACT_RELU = 3
+} ginn_b200_act;
+
+/* C = op(A) * op(B) + (accumulate ? C : 0).   op(A) is m x k, op(B) is k x n.
+ * Replaces internal::gpu_gemm (ginn/prod.h:32-66) as called by internal::gpu_prod
+ * (ginn/prod.h:211-253): trans_a/trans_b are ProdTranspose First/Second, accumulate is
+ * ProdResult::Add, lda/ldb/ldc are the stored row counts. */
+int ginn_b200_gemm(int device, void* stream, int dtype, int trans_a, int trans_b, int64_t m,
+                   int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+                   void* c, int64_t ldc, int accumulate);
+
+/* Strided-batched form: matrix i of each operand starts stride_* elements after matrix i-1.
+ * Replaces internal::gpu_batched_gemm (ginn/prod.h:68-135) as called by
+ * internal::gpu_batched_prod (ginn/prod.h:255-310), including the m = n = 1 batched dot
+ * products of SoftmaxOp::backward (ginn/nonlin.h:180-183). */
+int ginn_b200_gemm_batched(int device, void* stream, int dtype, int trans_a, int trans_b,
+                           int64_t m, int64_t n, int64_t k, const void* a, int64_t lda,
+                           int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, void* c,
+                           int64_t ldc, int64_t stride_c, int64_t batches, int accumulate);
+
+/* One (A_i, B_i) term of an Affine node: A_i is m x k (leading dimension lda), B_i is k x n. */
+typedef struct {
+  const void* a;
+  int64_t lda;
+  const void* b;
+  int64_t ldb;
+  int64_t k;
+} ginn_b200_pair;
+
+/* out(m x n) = act( sum_i A_i * B_i + bias ), bias broadcast over columns; one kernel.
+ * Replaces the GPU branch of AffineNode::forward_ (ginn/node/affine.h:56-64,74-76): the bias
+ * broadcast kernel, the accumulating GEMMs and the separate nonlinearity kernel.
+ * npairs <= 4; bias may be NULL. */
+int ginn_b200_affine_forward(int device, void* stream, int dtype, int npairs,
+                             const ginn_b200_pair* pairs, int64_t m, int64_t n, const void* bias,
+                             int act, void* out, int64_t ldo);
+
+/* Gradient slots of one Affine term; NULL means "input has no gradient". */
+typedef struct {
+  const void* a; /* A_i value, m x k */
+  int64_t lda;
+  const void* b; /* B_i value, k x n */
+  int64_t ldb;
+  int64_t k;
+  void* da; /* += dA * B_i^T   (m x k, leading dimension ldda) */
+  int64_t ldda;
+  void* db; /* += A_i^T * dA   (k x n, leading dimension lddb) */
+  int64_t lddb;
+} ginn_b200_pair_grad;
+
+/* Backward of the Affine node, with dA = dout (.) act'(out) formed on the fly inside the
+ * operand loaders (no dpreactiv_ tensor is written):
+ *   dbias += rowsum(dA);   db_i += A_i^T * dA;   da_i += dA * B_i^T.
+ * Replaces the GPU branch of AffineNode::backward_ (ginn/node/affine.h:79-87,103-125).
+ * `out` is the node's value (needed for tanh/sigmoid/relu derivatives; may be NULL for
+ * ACT_NONE); dbias may be NULL. */
+int ginn_b200_affine_backward(int device, void* stream, int dtype, int npairs,
+                              const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,
+                              const void* dout, int64_t lddout, const void* out, int64_t ldout,
+                              int act, void* dbias);
+
+/* One group of an autobatch level: `ncols` products that share the left operand W (m x k).
+ * Column j of the right-hand side lives at x_cols[j] (k contiguous elements), column j of
+ * the result at y_cols[j] (m contiguous elements) -- the addresses of the individual nodes'
+ * tensors, so the concatenation copy of RowwiseCat and the bias broadcast of ColBroadcast
+ * (ginn/autobatch.h:80-113,149-183; ginn/node/layout.h:227-241,870-887) disappear.
+ * x_cols / y_cols are HOST arrays of DEVICE pointers; the library stages them. */
+typedef struct {
+  const void* w;
+  int64_t ldw;
+  int64_t m, k;
+  const void* bias; /* forward: added to every column (may be NULL); dW mode: unused */
+  int64_t ncols;
+  const void* const* x_cols; /* forward/dW: inputs x_j (k);  dX mode: unused              */
+  void* const* y_cols;       /* forward: outputs y_j (m);    dX/dW mode: upstream dy_j (m) */
+  void* const* dx_cols;      /* dX mode: dx_j (k), accumulated                              */
+  void* dw;                  /* dW mode: m x k, accumulated (leading dimension lddw)        */
+  int64_t lddw;
+  void* dbias;               /* dW mode: m, accumulated (may be NULL)                       */
+} ginn_b200_group;
+
+typedef enum {
+  GINN_B200_GROUPED_FORWARD = 0, /* y_j  = W * x_j + bias            */
+  GINN_B200_GROUPED_DX = 1,      /* dx_j += W^T * dy_j               */
+  GINN_B200_GROUPED_DW = 2       /* dW  += sum_j dy_j x_j^T, dbias += sum_j dy_j */
+} ginn_b200_grouped_mode;
+
+/* All groups of one autobatch level in ONE launch (device-side tile table lookup). */
+int ginn_b200_grouped(int device, void* stream, int dtype, int mode, int ngroups,
+                      const ginn_b200_group* groups);
+
+/* Text of the last failure on the calling thread ("" if none). */
+const char* ginn_b200_last_error(void);
+
+/* Reads (and, if reset != 0, clears) the device status word that kernels write when a bounded
+ * wait expires.  0 = healthy.  Synchronises the device. Returns -1 if the query itself fails. */
+int ginn_b200_device_status(int device, int reset);
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int ginn_b200_version(void);
+
+/* Test / benchmark knobs.  "force_path": 0 = automatic, 1 = staged tcgen05 kernel,
+ * 2 = TMA fp16 kernel (falls back to automatic when not applicable), 3 = CUDA-core kernel.
+ * Returns GINN_B200_UNSUPPORTED for unknown names. */
+int ginn_b200_set_option(const char* name, int value);
+
+/* Number of kernels this library has launched since load (all threads, all devices). */
+int64_t ginn_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GINN_B200_H */

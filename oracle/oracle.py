@@ -1,0 +1,186 @@
+"""TEST INFRASTRUCTURE -- not part of the product.  parity: pinned (see below).
+
+fp64 oracle for ginn's dense-contraction path, restated from the reference's CPU branches, and
+a ctypes wrapper of the C restatement in cpu_path.c (the reference's own fp32 arithmetic, also
+the timed CPU baseline).  Only tests/, bench.py's CPU legs and the smoke check may import this.
+
+Reference lines followed (paths inside the ginn source tree):
+  gemm / gemm_batched    ginn/node/prod.h:30-32,41-47,108-117,129-147; shapes and transposes as
+                         derived by internal::gpu_prod / gpu_batched_prod (ginn/prod.h:211-310)
+  rank folding           ginn/tensor.h:268-282 (trailing dims multiplied into the columns)
+  act_forward/backward   ginn/nonlin.h:67-155 (Identity, Tanh, Relu, Sigmoid)
+  affine_forward         ginn/node/affine.h:35-77
+  affine_backward        ginn/node/affine.h:79-129
+  autobatch semantics    ginn/autobatch.h:80-183: a merged product equals the per-node products
+
+Arithmetic: inputs exactly as handed to the GPU (fp32, or fp16-rounded), every product and sum
+in fp64, one rounding to the storage type where the reference materialises a tensor (node
+value, dpreactiv_, gradients).  The dense product itself lives in Eigen (libeigen/eigen pinned
+at 87300c93 by the reference's subprojects/eigen.wrap), which is not vendored with the reference;
+its published definition (C_ij = sum_p A_ip B_pj) is what is restated.  Pinning: the known-answer
+values of the reference's own tests (test/nodes.cu.cpp:1023-1200, ginn-py/test/test_nodes.py:
+804-936) are committed under tests/golden/ and checked by tests/test_oracle.py.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from typing import Optional, Sequence
+
+import numpy as np
+
+ACT_NONE, ACT_TANH, ACT_SIGMOID, ACT_RELU = 0, 1, 2, 3
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def f64(x) -> np.ndarray:
+    return np.asarray(x, dtype=np.float64)
+
+
+def fold2(shape: Sequence[int]) -> tuple:
+    """rows/cols of a ginn tensor: rank folded to 2 (ginn/tensor.h:268-282)."""
+    s = list(shape)
+    if len(s) == 0:
+        return (1, 1)
+    if len(s) == 1:
+        return (s[0], 1)
+    return (s[0], int(np.prod(s[1:])))
+
+
+def fold3(shape: Sequence[int]) -> tuple:
+    s = list(shape) + [1] * (3 - len(shape))
+    return (s[0], s[1], int(np.prod(s[2:])))
+
+
+def gemm(a, b, trans_a=False, trans_b=False, c=None, accumulate=False) -> np.ndarray:
+    """fp64 result of op(a) @ op(b) (+ c)."""
+    A = f64(a).T if trans_a else f64(a)
+    B = f64(b).T if trans_b else f64(b)
+    assert A.shape[1] == B.shape[0], "inner dimensions differ (GINN_ASSERT in gpu_prod)"
+    out = A @ B
+    if accumulate:
+        out = out + f64(c)
+    return out
+
+
+def gemm_batched(a, b, trans_a=False, trans_b=False, c=None, accumulate=False) -> np.ndarray:
+    """(rows, cols, batch) operands; serial loop over the batch like the reference."""
+    batches = a.shape[2]
+    outs = [gemm(a[:, :, i], b[:, :, i], trans_a, trans_b,
+                 None if c is None else c[:, :, i], accumulate) for i in range(batches)]
+    return np.stack(outs, axis=2)
+
+
+def act_forward(x, act: int, half: bool = False) -> np.ndarray:
+    x = f64(x)
+    if act == ACT_TANH:
+        return np.tanh(x)
+    if act == ACT_RELU:
+        return np.maximum(x, 0.0)
+    if act == ACT_SIGMOID:
+        # fp32: 0.5*tanh(0.5x)+0.5; Half: sign-split exponential.  Both equal the logistic function.
+        return 0.5 * np.tanh(0.5 * x) + 0.5
+    return x
+
+
+def act_backward(y, dy, act: int) -> np.ndarray:
+    y, dy = f64(y), f64(dy)
+    if act == ACT_TANH:
+        return (1.0 - y * y) * dy
+    if act == ACT_RELU:
+        return dy * (y > 0)
+    if act == ACT_SIGMOID:
+        return y * (1.0 - y) * dy
+    return dy
+
+
+def affine_forward(pairs, bias, act: int) -> np.ndarray:
+    """fp64 value of act(sum_i a_i @ b_i + bias[:, None])."""
+    acc = None
+    for a, b in pairs:
+        t = f64(a) @ f64(b)
+        acc = t if acc is None else acc + t
+    if bias is not None:
+        acc = acc + f64(bias).reshape(-1, 1)
+    return act_forward(acc, act)
+
+
+def affine_backward(pairs, dout, out, act: int, store_dtype) -> dict:
+    """Gradient contributions (fp64) of AffineNode::backward_.
+
+    `store_dtype` is the tensor scalar type: dA = dout (.) act'(out) is rounded to it once, as the
+    reference materialises it in dpreactiv_ before the products.
+    """
+    dA = act_backward(out, dout, act) if act != ACT_NONE else f64(dout)
+    dA = f64(dA.astype(store_dtype))
+    res = {"dbias": dA.sum(axis=1), "da": [], "db": []}
+    for a, b in pairs:
+        res["db"].append(f64(a).T @ dA)
+        res["da"].append(dA @ f64(b).T)
+    return res
+
+
+def rel_frobenius(x, ref) -> float:
+    x, ref = f64(x), f64(ref)
+    den = np.linalg.norm(ref.ravel())
+    num = np.linalg.norm((x - ref).ravel())
+    return float(num / den) if den > 0 else float(num)
+
+
+def elementwise_ok(x, ref, rel: float, atol: float = 1e-6) -> bool:
+    """The reference's own per-element rule (test/check_node.h:104-119): within `rel`
+    relatively, or both near zero."""
+    x, ref = f64(x), f64(ref)
+    return bool(np.all((np.abs(x - ref) <= rel * np.abs(ref)) | (np.abs(x - ref) <= atol)))
+
+
+# ----------------------------------------------------------------------------------------------
+# C restatement (cpu_path.c)
+# ----------------------------------------------------------------------------------------------
+_cpu = None
+
+
+def build_cpu_path(force: bool = False) -> str:
+    so = os.path.join(_HERE, "liboracle_cpu.so")
+    src = os.path.join(_HERE, "cpu_path.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+    return so
+
+
+def cpu_path():
+    global _cpu
+    if _cpu is None:
+        so = os.path.join(_HERE, "liboracle_cpu.so")
+        if not os.path.exists(so):
+            build_cpu_path()
+        L = C.CDLL(so)
+        vp, cl, ci = C.c_void_p, C.c_long, C.c_int
+        L.cpu_gemm.argtypes = [ci, ci, ci, cl, cl, cl, vp, cl, vp, cl, vp, cl, ci, ci]
+        L.cpu_gemm.restype = None
+        L.cpu_gemm_batched.argtypes = [ci, ci, ci, cl, cl, cl, vp, cl, cl, vp, cl, cl, vp, cl, cl,
+                                       cl, ci, ci]
+        L.cpu_gemm_batched.restype = None
+        L.cpu_max_threads.restype = ci
+        _cpu = L
+    return _cpu
+
+
+def _dt(a: np.ndarray) -> int:
+    return {np.dtype(np.float32): 0, np.dtype(np.float16): 1}[a.dtype]
+
+
+def cpu_gemm(a: np.ndarray, b: np.ndarray, trans_a=False, trans_b=False,
+             c: Optional[np.ndarray] = None, accumulate=False, threads: int = 1) -> np.ndarray:
+    """C restatement on F-ordered arrays; returns the result in the inputs' dtype."""
+    a = np.asfortranarray(a)
+    b = np.asfortranarray(b)
+    m = a.shape[1] if trans_a else a.shape[0]
+    k = a.shape[0] if trans_a else a.shape[1]
+    n = b.shape[0] if trans_b else b.shape[1]
+    out = np.zeros((m, n), dtype=a.dtype, order="F") if c is None else np.asfortranarray(c).copy(order="F")
+    cpu_path().cpu_gemm(_dt(a), int(trans_a), int(trans_b), m, n, k, a.ctypes.data,
+                        max(a.shape[0], 1), b.ctypes.data, max(b.shape[0], 1), out.ctypes.data,
+                        max(m, 1), int(accumulate), threads)
+    return out
