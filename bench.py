@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the Prod fwd+bwd hot path (large dense ProdNode, Half) on 1..N B200s.
+
+One step = what ProdNode does for one forward + backward pass (ginn/node/prod.h:28-66) with the
+gradients zeroed first, as Graph::reset_grad does (ginn/node.h:261-264):
+    dA = 0; dB = 0;  C = A*B;  dA += dC*B^T;  dB += A^T*dC
+A, B, dC are 8192 x 8192 fp16 (~N(0,1)), fp32 accumulation, column-major.
+
+Multi-GPU (weak scaling): every rank owns an 8192-column shard of B, C and dC and a replica of A
+(global B is 8192 x 8192*N).  Forward and dB need no exchange; dA is a sum over the sharded
+columns, so the dA contributions are all-reduced (NCCL) on a side stream while the dB product
+runs.
+
+Prints ONE JSON line (rank 0).  `--impl reference` instead times the CPU restatement of the
+reference's Eigen path (oracle/cpu_path.c) on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "prod_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+SIZE = 8192
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the restated reference path on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_fwd_bwd(size: int, threads: int, steps: int, warmup: int):
+    """Times `steps` fwd+bwd passes of the CPU port at size^3, fp16 storage.  Returns
+    (TFLOP/s, seconds per step)."""
+    from oracle import oracle as orc
+    rng = np.random.default_rng(20244)
+    a = np.asfortranarray(rng.standard_normal((size, size)).astype(np.float16))
+    b = np.asfortranarray(rng.standard_normal((size, size)).astype(np.float16))
+    dc = np.asfortranarray(rng.standard_normal((size, size)).astype(np.float16))
+    L = orc.cpu_path()
+    c = np.zeros((size, size), np.float16, order="F")
+    da = np.zeros((size, size), np.float16, order="F")
+    db = np.zeros((size, size), np.float16, order="F")
+
+    def step():
+        da.fill(0)
+        db.fill(0)
+        L.cpu_gemm(1, 0, 0, size, size, size, a.ctypes.data, size, b.ctypes.data, size,
+                   c.ctypes.data, size, 0, threads)
+        L.cpu_gemm(1, 0, 1, size, size, size, dc.ctypes.data, size, b.ctypes.data, size,
+                   da.ctypes.data, size, 1, threads)
+        L.cpu_gemm(1, 1, 0, size, size, size, a.ctypes.data, size, dc.ctypes.data, size,
+                   db.ctypes.data, size, 1, threads)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return 3 * 2 * size ** 3 / dt / 1e12, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    threads = orc.cpu_path().cpu_max_threads()
+    threads = max(threads, os.cpu_count() or 1)
+    size = args.cpu_size
+    val, dt = cpu_fwd_bwd(size, threads, max(args.steps, 1), min(args.warmup, 1))
+    sample = (f"{size}^3 fp16 fwd+bwd (3 GEMMs) per step instead of {SIZE}^3; same operation "
+              f"sequence, CPU port of the Eigen path (oracle/cpu_path.c), {threads} threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": "C4 large dense ProdNode Half fwd+bwd 8192^3 (bounded CPU sample)",
+                   "sample_size": size},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import ginn_b200 as gb
+    from ginn_b200 import binding as B
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n = args.size
+    g = torch.Generator(device=dev)
+    g.manual_seed(20244 + rank)
+    ga = torch.Generator(device=dev)
+    ga.manual_seed(20244)  # A is replicated: same seed on every rank
+
+    def randn_cm(gen):  # column-major n x n fp16
+        return torch.randn(n, n, device=dev, dtype=torch.float32, generator=gen).half().T
+
+    A, Bm, dC = randn_cm(ga), randn_cm(g), randn_cm(g)
+    Cm = torch.empty(n, n, device=dev, dtype=torch.float16).T
+    dA = torch.empty(n, n, device=dev, dtype=torch.float16).T
+    dB = torch.empty(n, n, device=dev, dtype=torch.float16).T
+    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    main = torch.cuda.current_stream(dev)
+    gemm_events = []
+
+    def step(record=False):
+        dA.zero_()
+        dB.zero_()
+        evs = []
+        if record:
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            evs[0].record()
+        gb.gemm(A, Bm, Cm)                                    # C  = A * B
+        if record:
+            evs[1].record(); evs[2].record()
+        gb.gemm(dC, Bm, dA, trans_b=True, accumulate=True)    # dA += dC * B^T
+        if record:
+            evs[3].record()
+        if world > 1:
+            ready = torch.cuda.Event()
+            ready.record(main)
+            comm_stream.wait_event(ready)
+            with torch.cuda.stream(comm_stream):
+                dist.all_reduce(dA.T)  # contiguous storage of the column-major matrix
+        if record:
+            evs[4].record()
+        gb.gemm(A, dC, dB, trans_a=True, accumulate=True)     # dB += A^T * dC
+        if record:
+            evs[5].record()
+            gemm_events.append(evs)
+        if world > 1:
+            main.wait_stream(comm_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    status = gb.device_status(local, True)
+    if status != 0:
+        raise RuntimeError(f"device status {status:#x} after warm-up")
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = gb.launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(record=True)
+    e1.record()
+    barrier()
+    launches = gb.launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    kern_ms = []
+    for evs in gemm_events:
+        kern_ms += [evs[0].elapsed_time(evs[1]), evs[2].elapsed_time(evs[3]),
+                    evs[4].elapsed_time(evs[5])]
+    status = gb.device_status(local, True)
+    if status != 0:
+        raise RuntimeError(f"device status {status:#x} after the timed region")
+
+    flops_step = 3 * 2 * n ** 3
+    value = world * flops_step / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        hA, hB, hdC = (torch.empty(n * n, dtype=torch.float16).pin_memory() for _ in range(3))
+        hC, hdA, hdB = (torch.empty(n * n, dtype=torch.float16).pin_memory() for _ in range(3))
+        hA.copy_(A.T.reshape(-1).cpu()); hB.copy_(Bm.T.reshape(-1).cpu()); hdC.copy_(dC.T.reshape(-1).cpu())
+
+        def e2e_step():
+            A.T.reshape(-1).copy_(hA, non_blocking=True)
+            Bm.T.reshape(-1).copy_(hB, non_blocking=True)
+            dC.T.reshape(-1).copy_(hdC, non_blocking=True)
+            step()
+            hC.copy_(Cm.T.reshape(-1), non_blocking=True)
+            hdA.copy_(dA.T.reshape(-1), non_blocking=True)
+            hdB.copy_(dB.T.reshape(-1), non_blocking=True)
+
+        e2e_step()
+        barrier()
+        k = max(1, min(args.steps, 5))
+        e0.record()
+        for _ in range(k):
+            e2e_step()
+        e1.record()
+        barrier()
+        ms_e = e0.elapsed_time(e1) / k
+        if world > 1:
+            t = torch.tensor([ms_e], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e = t.item()
+        nbytes = 3 * n * n * 2
+        e2e = {"value": world * flops_step / (ms_e * 1e-3) / 1e12, "unit": UNIT,
+               "ms_per_step": ms_e, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_src = measured_peaks()
+    timed_s = ms * args.steps * 1e-3
+    sustained = timed_s >= 1.0
+    peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+    avg_kernel_ms = sum(kern_ms) / len(kern_ms)
+    achieved = 2 * n ** 3 / (avg_kernel_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "kernel": "hgemm_tma_kernel (three transpose variants, one launch each per step)",
+                "avg_launch_ms": avg_kernel_ms,
+                "peak_kind": f"{'sustained' if sustained else 'burst'} cuBLAS bf16, of {peak_src}"}
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu:
+        from oracle import oracle as orc
+        threads = max(orc.cpu_path().cpu_max_threads(), os.cpu_count() or 1)
+        v, dt = cpu_fwd_bwd(args.cpu_size, threads, 1, 1)
+        cpu_baseline = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": f"one fwd+bwd pass at {args.cpu_size}^3 fp16 ({dt:.2f} s), "
+                                  f"CPU port of the Eigen path (oracle/cpu_path.c)"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"C4 large dense ProdNode Half fwd+bwd {n}^3 per GPU "
+                               "(C=A*B, dA+=dC*B^T, dB+=A^T*dC, grads zeroed each step)",
+                   "size": n, "l2": "inputs and outputs (768 MiB) exceed the 126 MB L2",
+                   "sharding": "columns of B/C/dC per rank; dA all-reduced over NCCL" if world > 1
+                   else "single GPU"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": roofline, "cpu_baseline": cpu_baseline,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_affine(args):
+    """Secondary workload (profiling aid): one fp32 AffineNode fwd+bwd, tanh, through the fused
+    entry points.  Shapes default to config 5's hidden layer (1024 x 1024, batch 4096)."""
+    import torch
+    import ginn_b200 as gb
+    from ginn_b200 import binding as B
+    torch.cuda.set_device(0)
+    m, n, k = args.m, args.n, args.k
+    g = torch.Generator(device="cuda").manual_seed(20241)
+    a = (6 / (0.5 * (m + k))) ** 0.5
+    W = ((torch.rand(k, m, device="cuda", generator=g) * 2 - 1) * a).T
+    X = torch.randn(n, k, device="cuda", generator=g).T
+    b = (torch.rand(m, device="cuda", generator=g) * 2 - 1) * a
+    dY = torch.randn(n, m, device="cuda", generator=g).T
+    Y = B.colmajor(m, n, torch.float32, fill=0.0)
+    dW, dX = B.colmajor(m, k, torch.float32, fill=0.0), B.colmajor(k, n, torch.float32, fill=0.0)
+    db = torch.zeros(m, device="cuda")
+
+    def step():
+        dW.zero_(); dX.zero_(); db.zero_()
+        gb.affine_forward([gb.Pair(W, X)], b, gb.ACT_TANH, Y)
+        gb.affine_backward([gb.PairGrad(W, X, dW, dX)], dY, Y, gb.ACT_TANH, db)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    assert gb.device_status(0, True) == 0
+    print(json.dumps({"metric": "affine_fwd_bwd_tflops", "value": 3 * 2 * m * n * k / ms / 1e9,
+                      "unit": UNIT, "n_gpus": 1, "steps": args.steps, "ms_per_step": ms,
+                      "dtype": "f32 (3xTF32)", "data": "synthetic",
+                      "config": {"workload": f"Affine tanh fwd+bwd W {m}x{k}, X {k}x{n}"}}),
+          flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=SIZE, help="matrix extent (default: the C4 config)")
+    ap.add_argument("--cpu-size", type=int, default=3072, help="extent of the bounded CPU sample")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32"])
+    ap.add_argument("--m", type=int, default=1024)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=1024)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.workload == "affine_f32":
+        run_affine(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

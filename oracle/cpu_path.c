@@ -28,10 +28,10 @@
 #endif
 
 #define MR 16
-#define NR 6
+#define NR 8
 #define KC 256
 #define MC 256 /* multiple of MR */
-#define NC 3072 /* multiple of NR */
+#define NC 1024 /* multiple of NR */
 
 typedef _Float16 half_t;
 
@@ -53,22 +53,21 @@ static inline float b_at(int dtype, const void* B, long ldb, int tb, long p, lon
   return tb ? ld_elem(dtype, B, j + p * ldb) : ld_elem(dtype, B, p + j * ldb);
 }
 
-/* acc(MR x NR) += Apanel(MR x kc, p-major) * Bpanel(kc x NR, p-major) */
-__attribute__((target_clones("arch=skylake-avx512", "arch=haswell", "default"))) static void micro_kernel(
-    long kc, const float* restrict ap, const float* restrict bp, float* restrict acc) {
-  float c[NR][MR];
-  for (int j = 0; j < NR; ++j)
-    for (int i = 0; i < MR; ++i) c[j][i] = 0.f;
+/* acc(MR x NR) += Apanel(MR x kc, p-major) * Bpanel(kc x NR, p-major).
+ * One MR-wide vector per column of the register tile; the compiler lowers it to the widest
+ * SIMD of each clone (one zmm, two ymm, four xmm). */
+typedef float vmr_t __attribute__((vector_size(MR * 4), aligned(4)));
+__attribute__((target_clones("avx512f", "avx2", "default"))) static void
+micro_kernel(long kc, const float* restrict ap, const float* restrict bp, float* restrict acc) {
+  vmr_t c[NR];
+  for (int j = 0; j < NR; ++j) c[j] = (vmr_t){0};
   for (long p = 0; p < kc; ++p) {
-    const float* a = ap + p * MR;
+    const vmr_t a = *(const vmr_t*)(ap + p * MR);
     const float* b = bp + p * NR;
-    for (int j = 0; j < NR; ++j) {
-      const float bj = b[j];
-      for (int i = 0; i < MR; ++i) c[j][i] += a[i] * bj;
-    }
+#pragma GCC unroll 8
+    for (int j = 0; j < NR; ++j) c[j] += a * b[j];
   }
-  for (int j = 0; j < NR; ++j)
-    for (int i = 0; i < MR; ++i) acc[j * MR + i] = c[j][i];
+  for (int j = 0; j < NR; ++j) *(vmr_t*)(acc + j * MR) = c[j];
 }
 
 /* C(m x n) = op(A) * op(B) + (accumulate ? C : 0), fp32 accumulation, threads over column blocks. */
@@ -86,7 +85,7 @@ void cpu_gemm(int dtype, int ta, int tb, long m, long n, long k, const void* A, 
     float* apack = (float*)aligned_alloc(64, sizeof(float) * MC * KC);
     float* bpack = (float*)aligned_alloc(64, sizeof(float) * KC * NC);
     float* ctile = (float*)aligned_alloc(64, sizeof(float) * MC * NC);
-    float acc[MR * NR];
+    float acc[MR * NR] __attribute__((aligned(64)));
 #ifdef _OPENMP
 #pragma omp for schedule(dynamic)
 #endif
@@ -100,17 +99,39 @@ void cpu_gemm(int dtype, int ta, int tb, long m, long n, long k, const void* A, 
       for (long pc = 0; pc < k; pc += KC) {
         const long kb = k - pc < KC ? k - pc : KC;
         /* pack B block: panels of NR columns, p-major, zero padded */
-        for (long jr = 0; jr < nb; jr += NR)
-          for (long p = 0; p < kb; ++p)
-            for (int jj = 0; jj < NR; ++jj)
-              bpack[jr * KC + p * NR + jj] =
-                  (jr + jj < nb) ? b_at(dtype, B, ldb, tb, pc + p, jc + jr + jj) : 0.f;
+        for (long jr = 0; jr < nb; jr += NR) {
+          float* dst = bpack + jr * KC;
+          for (int jj = 0; jj < NR; ++jj) {
+            if (jr + jj >= nb) {
+              for (long p = 0; p < kb; ++p) dst[p * NR + jj] = 0.f;
+            } else if (dtype == 0) {
+              const float* src = (const float*)B + (tb ? (jc + jr + jj) + pc * ldb : pc + (jc + jr + jj) * ldb);
+              const long st = tb ? ldb : 1;
+              for (long p = 0; p < kb; ++p) dst[p * NR + jj] = src[p * st];
+            } else {
+              const half_t* src = (const half_t*)B + (tb ? (jc + jr + jj) + pc * ldb : pc + (jc + jr + jj) * ldb);
+              const long st = tb ? ldb : 1;
+              for (long p = 0; p < kb; ++p) dst[p * NR + jj] = (float)src[p * st];
+            }
+          }
+        }
         /* pack A block: panels of MR rows, p-major, zero padded */
-        for (long ir = 0; ir < mb; ir += MR)
-          for (long p = 0; p < kb; ++p)
-            for (int ii = 0; ii < MR; ++ii)
-              apack[ir * KC + p * MR + ii] =
-                  (ir + ii < mb) ? a_at(dtype, A, lda, ta, ic + ir + ii, pc + p) : 0.f;
+        for (long ir = 0; ir < mb; ir += MR) {
+          float* dst = apack + ir * KC;
+          const int rows = mb - ir < MR ? (int)(mb - ir) : MR;
+          for (long p = 0; p < kb; ++p) {
+            if (dtype == 0) {
+              const float* src = (const float*)A + (ta ? (pc + p) + (ic + ir) * lda : (ic + ir) + (pc + p) * lda);
+              const long st = ta ? lda : 1;
+              for (int ii = 0; ii < rows; ++ii) dst[p * MR + ii] = src[ii * st];
+            } else {
+              const half_t* src = (const half_t*)A + (ta ? (pc + p) + (ic + ir) * lda : (ic + ir) + (pc + p) * lda);
+              const long st = ta ? lda : 1;
+              for (int ii = 0; ii < rows; ++ii) dst[p * MR + ii] = (float)src[ii * st];
+            }
+            for (int ii = rows; ii < MR; ++ii) dst[p * MR + ii] = 0.f;
+          }
+        }
         for (long jr = 0; jr < nb; jr += NR)
           for (long ir = 0; ir < mb; ir += MR) {
             micro_kernel(kb, apack + ir * KC, bpack + jr * KC, acc);

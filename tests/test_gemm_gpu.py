@@ -1,0 +1,206 @@
+"""GPU parity of ginn_b200_gemm / ginn_b200_gemm_batched (through the C ABI) against the oracle.
+
+Mirrors the reference's CPU-vs-GPU protocol (test/check_node.h:27-121): identical inputs, every
+output within tolerance, accumulation (`+=`) checked by running a product twice into one buffer.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from ginn_b200 import binding as B
+from helpers import check, check_elementwise, randn
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 1, 1), (2, 2, 3), (5, 7, 9), (16, 16, 16), (17, 33, 65), (31, 63, 127),
+          (64, 64, 64), (65, 129, 33), (128, 128, 32), (128, 32, 128), (130, 70, 300),
+          (129, 257, 100), (512, 128, 784)]
+TRANS = [(False, False), (True, False), (False, True), (True, True)]
+
+
+def run_gemm(gb, rng, dt, m, n, k, ta, tb, acc, ld_pad=0, offset=0):
+    a = randn(rng, (k, m) if ta else (m, k), dt)
+    b = randn(rng, (n, k) if tb else (k, n), dt)
+    c0 = randn(rng, (m, n), dt)
+    if ld_pad or offset:
+        def place(x):
+            t = B.colmajor(x.shape[0], x.shape[1] + 1, torch.from_numpy(x[:1, :1]).dtype,
+                           ld=x.shape[0] + ld_pad)
+            v = torch.as_strided(t, x.shape, (1, x.shape[0] + ld_pad), storage_offset=offset)
+            v.copy_(torch.from_numpy(x))
+            return v
+        A, Bm, C = place(a), place(b), place(c0)
+    else:
+        A, Bm, C = B.from_host(a), B.from_host(b), B.from_host(c0)
+    gb.gemm(A, Bm, C, ta, tb, acc)
+    torch.cuda.synchronize()
+    ref = orc.gemm(a, b, ta, tb, c0, acc)
+    got = B.to_host(C)
+    check(got, ref, dt, f"m{m} n{n} k{k} ta{ta} tb{tb} acc{acc}")
+    return got, ref
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+@pytest.mark.parametrize("path", [1, 0])
+def test_shape_sweep_all_transposes(gpu, dt, path):
+    gpu.set_option("force_path", path)
+    rng = np.random.default_rng(11)
+    for (m, n, k) in SHAPES:
+        for ta, tb in TRANS:
+            run_gemm(gpu, rng, dt, m, n, k, ta, tb, False)
+    for ta, tb in TRANS:
+        run_gemm(gpu, rng, dt, 130, 70, 300, ta, tb, True)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_padded_leading_dimension_and_unaligned_base(gpu, dt):
+    """ginn's PreallocGpu hands out unaligned bump pointers (ginn/dev.h:237-245) and
+    RowwiseUncat views start at arbitrary column offsets (ginn/node/layout.h:283-289)."""
+    gpu.set_option("force_path", 1)
+    rng = np.random.default_rng(12)
+    for (m, n, k) in [(37, 41, 53), (128, 64, 96), (200, 100, 260)]:
+        for ta, tb in TRANS[:3]:
+            for pad, off in [(3, 0), (0, 1), (5, 3)]:
+                run_gemm(gpu, rng, dt, m, n, k, ta, tb, True, pad, off)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_reference_elementwise_rule(gpu, dt):
+    """WithinRel(cpu, eps2) per element, as check_expr does, on a well-scaled product."""
+    rng = np.random.default_rng(13)
+    a = np.abs(randn(rng, (96, 200), dt)) + 0.5
+    b = np.abs(randn(rng, (200, 80), dt)) + 0.5
+    C = B.colmajor(96, 80, B.from_host(a).dtype, fill=0.0)
+    gpu.gemm(B.from_host(a), B.from_host(b), C)
+    torch.cuda.synchronize()
+    check_elementwise(B.to_host(C), orc.gemm(a, b), dt)
+
+
+def test_prod_known_answer(gpu, kat):
+    """test/nodes.cu.cpp:1023-1041 through every path that accepts the shape."""
+    p = kat["prod"]
+    for dt, eps in [(np.float32, kat["eps"]["f32"]), (np.float16, kat["eps"]["f16_prod"])]:
+        for path in (0, 1, 3):
+            gpu.set_option("force_path", path)
+            W, V = np.asarray(p["W"], dt), np.asarray(p["V"], dt)
+            C = B.colmajor(2, 2, B.from_host(W).dtype, fill=0.0)
+            gpu.gemm(B.from_host(W), B.from_host(V), C)
+            torch.cuda.synchronize()
+            np.testing.assert_allclose(B.to_host(C), np.asarray(p["WV"]), rtol=max(eps, 2e-6), atol=1e-6)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_batched_against_per_slice_products(gpu, dt):
+    """test/nodes.cu.cpp:1043-1115, plus the attention shapes of min-GPT scaled down."""
+    rng = np.random.default_rng(14)
+    cases = [((2, 3, 4), (3, 5, 4), False, False), ((64, 16, 6), (16, 64, 6), False, False),
+             ((64, 16, 6), (64, 48, 6), True, False), ((64, 16, 5), (48, 16, 5), False, True),
+             ((256, 64, 8), (64, 256, 8), False, False), ((64, 256, 8), (256, 256, 8), False, False)]
+    for sa, sb, ta, tb in cases:
+        a, b = randn(rng, sa, dt) + 1, randn(rng, sb, dt) - 1
+        m = sa[1] if ta else sa[0]
+        n = sb[0] if tb else sb[1]
+        c0 = randn(rng, (m, n, sa[2]), dt)
+        for acc in (False, True):
+            C = B.from_host(c0)
+            gpu.gemm_batched(B.from_host(a), B.from_host(b), C, ta, tb, acc)
+            torch.cuda.synchronize()
+            check(B.to_host(C), orc.gemm_batched(a, b, ta, tb, c0, acc), dt, f"{sa}x{sb}")
+
+
+def test_batched_high_rank_folds_to_three(gpu):
+    rng = np.random.default_rng(15)
+    a, b = randn(rng, (2, 3, 2, 2), np.float32), randn(rng, (3, 5, 2, 2), np.float32)
+    a3 = a.reshape(orc.fold3(a.shape), order="F")
+    b3 = b.reshape(orc.fold3(b.shape), order="F")
+    C = B.colmajor(2, 5, torch.float32, batches=4, fill=0.0)
+    gpu.gemm_batched(B.from_host(a3), B.from_host(b3), C)
+    torch.cuda.synchronize()
+    got = B.to_host(C).reshape((2, 5, 2, 2), order="F")
+    for i in range(2):
+        for j in range(2):
+            np.testing.assert_allclose(got[:, :, i, j], a[:, :, i, j] @ b[:, :, i, j], rtol=1e-5, atol=1e-6)
+
+
+def test_batched_dot_products_of_softmax_backward(gpu):
+    """m = n = 1 batched products (ginn/nonlin.h:180-183, ginn/node/layernorm.h:61-64)."""
+    rng = np.random.default_rng(16)
+    rows, cols = 50, 3000
+    y, dy = randn(rng, (rows, cols), np.float32), randn(rng, (rows, cols), np.float32)
+    out = B.colmajor(1, 1, torch.float32, batches=cols, fill=0.0)
+    gpu.gemm_batched(B.from_host(y.reshape(1, rows, cols)), B.from_host(dy.reshape(rows, 1, cols)), out)
+    torch.cuda.synchronize()
+    check(B.to_host(out).ravel(), (y.astype(np.float64) * dy).sum(0), np.float32)
+
+
+@pytest.mark.parametrize("trans", TRANS[:3])
+def test_tma_path_half(gpu, trans):
+    gpu.set_option("force_path", 2)
+    rng = np.random.default_rng(17)
+    ta, tb = trans
+    for (m, n, k) in [(128, 256, 64), (136, 264, 72), (256, 512, 512), (384, 256, 1000)]:
+        for acc in (False, True):
+            run_gemm(gpu, rng, np.float16, m, n, k, ta, tb, acc)
+    a, b = randn(rng, (256, 128, 5), np.float16), randn(rng, (128, 256, 5), np.float16)
+    C = B.colmajor(256, 256, torch.float16, batches=5, fill=0.0)
+    gpu.gemm_batched(B.from_host(a), B.from_host(b), C)
+    torch.cuda.synchronize()
+    check(B.to_host(C), orc.gemm_batched(a, b), np.float16)
+
+
+def test_large_half_product_by_linearity(gpu):
+    """C4 size (8192^3): (A*B)*v must equal A*(B*v).  Both sides are formed from fp16-rounded
+    data with fp32 matrix-vector products, so the check is independent of any other GEMM."""
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A = torch.randn(n, n, device="cuda", generator=g).half().T
+    Bm = torch.randn(n, n, device="cuda", generator=g).half().T
+    dC = torch.randn(n, n, device="cuda", generator=g).half().T
+    v = torch.randn(n, 1, device="cuda", generator=g, dtype=torch.float64)
+    C = torch.empty(n, n, device="cuda", dtype=torch.float16).T
+    gpu.gemm(A, Bm, C)
+    lhs, rhs = C.double() @ v, A.double() @ (Bm.double() @ v)
+    assert ((lhs - rhs).norm() / rhs.norm()).item() < 5e-3
+    dA = torch.zeros(n, n, device="cuda", dtype=torch.float16).T
+    gpu.gemm(dC, Bm, dA, trans_b=True, accumulate=True)
+    lhs, rhs = dA.double() @ v, dC.double() @ (Bm.double().T @ v)
+    assert ((lhs - rhs).norm() / rhs.norm()).item() < 5e-3
+    dB = torch.zeros(n, n, device="cuda", dtype=torch.float16).T
+    gpu.gemm(A, dC, dB, trans_a=True, accumulate=True)
+    lhs, rhs = dB.double() @ v, A.double().T @ (dC.double() @ v)
+    assert ((lhs - rhs).norm() / rhs.norm()).item() < 5e-3
+
+
+def test_fp32_accuracy_holds_at_large_k(gpu):
+    """dW of the MLP config contracts over the 4096-column batch."""
+    rng = np.random.default_rng(18)
+    for (m, n, k, ta, tb) in [(128, 96, 4096, False, True), (256, 128, 8192, False, False)]:
+        run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, True)
+
+
+def test_empty_and_degenerate_shapes(gpu):
+    rng = np.random.default_rng(19)
+    c0 = randn(rng, (4, 5), np.float32)
+    C = B.from_host(c0)
+    a, b = B.colmajor(4, 0, torch.float32), B.colmajor(0, 5, torch.float32)
+    gpu.gemm(a, b, C, accumulate=True)       # k == 0, Add: C unchanged
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(B.to_host(C), c0)
+    gpu.gemm(a, b, C, accumulate=False)      # k == 0, Assign: C = 0
+    torch.cuda.synchronize()
+    assert not B.to_host(C).any()
+    lib = gpu.lib()
+    assert lib.ginn_b200_gemm(0, None, 0, 0, 0, 0, 5, 3, None, 1, None, 3, None, 1, 0) == 0  # m == 0
+
+
+def test_argument_errors_are_reported(gpu):
+    lib = gpu.lib()
+    x = torch.zeros(16, device="cuda")
+    p = x.data_ptr()
+    assert lib.ginn_b200_gemm(0, None, 7, 0, 0, 2, 2, 2, p, 2, p, 2, p, 2, 0) == 2      # dtype
+    assert lib.ginn_b200_gemm(0, None, 0, 0, 0, 4, 2, 2, p, 2, p, 2, p, 4, 0) == 1      # lda < m
+    assert lib.ginn_b200_gemm(0, None, 0, 0, 0, -1, 2, 2, p, 2, p, 2, p, 2, 0) == 1     # negative
+    assert lib.ginn_b200_gemm(0, None, 0, 0, 0, 2, 2, 2, None, 2, p, 2, p, 2, 0) == 1   # null
+    assert b"null" in lib.ginn_b200_last_error()
+    assert lib.ginn_b200_gemm(999, None, 0, 0, 0, 2, 2, 2, p, 2, p, 2, p, 2, 0) == 1    # device

@@ -1,0 +1,83 @@
+"""GPU parity of the grouped (autobatch level) entry point: one launch for all groups of a
+level must equal the per-node products the un-batched graph computes (the before/after
+protocol of test/autobatch.cpp:37-70)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from ginn_b200 import binding as B
+from ginn_b200.binding import GROUPED_DW, GROUPED_DX, GROUPED_FORWARD
+from helpers import check, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def make_level(rng, specs):
+    """specs: list of (m, k, ncols).  Returns binding groups and host copies."""
+    groups, host = [], []
+    for m, k, nc in specs:
+        W, bias = randn(rng, (m, k), np.float32, 0.1), randn(rng, m, np.float32)
+        xs = [randn(rng, k, np.float32) for _ in range(nc)]
+        dys = [randn(rng, m, np.float32) for _ in range(nc)]
+        host.append((W, bias, xs, dys))
+        groups.append(dict(w=B.from_host(W), bias=B.from_host(bias),
+                           x=[B.from_host(x) for x in xs], dy=[B.from_host(d) for d in dys]))
+    return groups, host
+
+
+@pytest.mark.parametrize("specs", [
+    [(8, 5, 1)], [(1024, 384, 7)], [(1024, 384, 256)], [(96, 40, 100), (200, 64, 3), (33, 17, 45)],
+    [(1024, 384, 150), (256, 256, 31)],
+])
+def test_level_equals_per_node_products(gpu, specs):
+    rng = np.random.default_rng(41)
+    groups, host = make_level(rng, specs)
+    ys = [[torch.zeros(g["w"].shape[0], device="cuda") for _ in g["x"]] for g in groups]
+    gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=y, bias=g["bias"])
+                                  for g, y in zip(groups, ys)])
+    dxs = [[torch.ones(g["w"].shape[1], device="cuda") for _ in g["x"]] for g in groups]
+    dws = [B.colmajor(*g["w"].shape, torch.float32, fill=1.0) for g in groups]
+    dbs = [torch.ones(g["w"].shape[0], device="cuda") for g in groups]
+    gpu.grouped(GROUPED_DX, [gpu.Group(w=g["w"], y_cols=g["dy"], dx_cols=dx)
+                             for g, dx in zip(groups, dxs)])
+    gpu.grouped(GROUPED_DW, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=g["dy"], dw=dw, dbias=db)
+                             for g, dw, db in zip(groups, dws, dbs)])
+    torch.cuda.synchronize()
+    for (W, bias, xs, dys), y, dx, dw, db in zip(host, ys, dxs, dws, dbs):
+        X, DY = np.stack(xs, 1), np.stack(dys, 1)
+        check(np.stack([B.to_host(t) for t in y], 1), orc.affine_forward([(W, X)], bias, 0), np.float32, "fwd")
+        check(np.stack([B.to_host(t) for t in dx], 1), 1 + orc.gemm(W, DY, trans_a=True), np.float32, "dX")
+        check(B.to_host(dw), 1 + orc.gemm(DY, X, trans_b=True), np.float32, "dW")
+        check(B.to_host(db), 1 + DY.astype(np.float64).sum(1), np.float32, "dbias")
+
+
+def test_unaligned_column_vectors(gpu):
+    """Columns that are views at odd offsets (what RowwiseUncat produces) take the scalar path."""
+    rng = np.random.default_rng(42)
+    m, k, nc = 64, 30, 9
+    W = randn(rng, (m, k), np.float32)
+    pool = torch.zeros(nc * (k + 1) + 1, device="cuda")
+    xs_h = [randn(rng, k, np.float32) for _ in range(nc)]
+    xs = []
+    for j, x in enumerate(xs_h):
+        v = pool[1 + j * (k + 1): 1 + j * (k + 1) + k]
+        v.copy_(torch.from_numpy(x))
+        xs.append(v)
+    ys = [torch.zeros(m, device="cuda") for _ in range(nc)]
+    gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=B.from_host(W), x_cols=xs, y_cols=ys)])
+    torch.cuda.synchronize()
+    check(np.stack([B.to_host(t) for t in ys], 1), orc.gemm(W, np.stack(xs_h, 1)), np.float32)
+
+
+def test_many_levels_reuse_the_staging_ring(gpu):
+    rng = np.random.default_rng(43)
+    groups, host = make_level(rng, [(128, 64, 20)])
+    g = groups[0]
+    W, bias, xs, _ = host[0]
+    ref = orc.affine_forward([(W, np.stack(xs, 1))], bias, 0)
+    for _ in range(300):
+        ys = [torch.zeros(128, device="cuda") for _ in xs]
+        gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=ys, bias=g["bias"])])
+    torch.cuda.synchronize()
+    check(np.stack([B.to_host(t) for t in ys], 1), ref, np.float32)
