@@ -13,8 +13,16 @@ namespace {
 
 __device__ __forceinline__ float ld_f(const float* p) { return __ldg(p); }
 __device__ __forceinline__ float ld_f(const __half* p) { return __half2float(__ldg(p)); }
+// Plain (coherent) loads for locations this kernel also writes.
+__device__ __forceinline__ float ld_rw(const float* p) { return *p; }
+__device__ __forceinline__ float ld_rw(const __half* p) { return __half2float(*p); }
 __device__ __forceinline__ void st_f(float* p, float v) { *p = v; }
 __device__ __forceinline__ void st_f(__half* p, float v) { *p = __float2half_rn(v); }
+// Value of v after one rounding to the storage type T (in registers; no memory access).
+template <typename T>
+__device__ __forceinline__ float round_to(float v) {
+  return sizeof(T) == 2 ? __half2float(__float2half_rn(v)) : v;
+}
 
 template <typename T>
 __device__ __forceinline__ float act_forward(int act, float x) {
@@ -53,9 +61,7 @@ __device__ __forceinline__ float fetch(const Operand& op, long long boff, long l
     const T* py = (op.ycols ? static_cast<const T*>(op.ycols[col])
                             : static_cast<const T*>(op.ybase) + boff + col * op.ld) + row;
     // The staged kernel rounds dY (.) act'(Y) to T before the product; do the same here.
-    T r;
-    st_f(&r, act_backward<T>(op.dact, ld_f(py), v));
-    v = ld_f(&r);
+    v = round_to<T>(act_backward<T>(op.dact, ld_f(py), v));
   }
   return v;
 }
@@ -84,7 +90,7 @@ __global__ void small_gemm_kernel(const __grid_constant__ Problem P) {
                      : static_cast<T*>(P.c) + batch * P.c_batch_stride + col * P.ldc) + row;
     float x = acc;
     if (P.bias) x += ld_f(static_cast<const T*>(P.bias) + row);
-    if (P.accumulate) x += ld_f(cp);
+    if (P.accumulate) x += ld_rw(cp);
     st_f(cp, act_forward<T>(P.act, x));
   }
 }
@@ -101,11 +107,7 @@ __global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y,
   if (row < M) {
     for (long long n = threadIdx.y; n < N; n += blockDim.y) {
       float v = ld_f(dy + n * ld + row);
-      if (dact != ACT_NONE) {
-        T r;
-        st_f(&r, act_backward<T>(dact, ld_f(y + n * ld + row), v));
-        v = ld_f(&r);
-      }
+      if (dact != ACT_NONE) v = round_to<T>(act_backward<T>(dact, ld_f(y + n * ld + row), v));
       acc += v;
     }
   }
@@ -114,7 +116,7 @@ __global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y,
   if (threadIdx.y == 0 && row < M) {
     float s = 0.f;
     for (int j = 0; j < blockDim.y; ++j) s += part[j][threadIdx.x];
-    st_f(rowsum + row, ld_f(rowsum + row) + s);
+    st_f(rowsum + row, ld_rw(rowsum + row) + s);
   }
 }
 
