@@ -111,6 +111,8 @@ int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
   if (p.rowsum != nullptr && ktot > 0) small = false;
   if (small) {
     CU_TRY(gb::launch_small(dtype, p, stream));
+  } else if (dtype == GINN_B200_F32 && force != PATH_STAGED && gb::sgemm3x_supported(p)) {
+    CU_TRY(gb::launch_sgemm3x(p, stream, ctx->d_status));
   } else {
     const int bn = gb::staged_pick_bn(dtype, p.M, p.N, p.batches, ctx->num_sms);
     CU_TRY(gb::launch_staged(dtype, p, bn, stream, ctx->d_status));

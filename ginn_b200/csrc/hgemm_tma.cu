@@ -33,12 +33,18 @@ constexpr int TB_BYTES = TBN * TBK * 2;  // 32 KiB
 constexpr int TSTAGE_BYTES = TA_BYTES + TB_BYTES;
 constexpr int TMN_ATOM_BYTES = 64 * TBK * 2;  // one 64(mn) x 64(k) box of an MN-major operand
 constexpr int TGROUP_M = 16;                  // m-tiles per rasterisation group (L2 reuse)
+// Epilogue staging: per epilogue warp a 32(col) x 32(row) fp32 tile, column pitch 36 floats so
+// that both the row-per-lane writes and the 8-rows-per-lane reads are bank-conflict free.
+constexpr int TEPI_PITCH = 36;
+constexpr int TEPI_WARP_BYTES = 32 * TEPI_PITCH * 4;
+constexpr int TEPI_BYTES = 4 * TEPI_WARP_BYTES;
 
 struct HParams {
   __half* C;
   long long ldc, strideC;
   int M, N, K, batches;
   int accumulate;
+  int vec_c;  // 1: C allows 16-byte accesses (base, ldc and batch stride multiples of 8 halves)
   int tiles_m, tiles_n, total_tiles;
 };
 
@@ -198,13 +204,26 @@ hgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         break;
       }
       tc_fence_after();
-      const int row = m_idx * TBM + q * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int row0 = m_idx * TBM + q * 32;  // first row of this warp's TMEM lane quarter
       const int n0 = n_idx * TBN;
-      __half* cbase = p.C + static_cast<long long>(batch) * p.strideC + row;
+      __half* cbase = p.C + static_cast<long long>(batch) * p.strideC;
       const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + acc * TBN;
+      float* stage = reinterpret_cast<float*>(smem_raw + (tiles_base - smem_u32(smem_raw)) +
+                                              TSTAGES * TSTAGE_BYTES + q * TEPI_WARP_BYTES);
 #pragma unroll 1
       for (int c0 = 0; c0 < TBN; c0 += 32) {
+        // Each lane owns 4 pieces of the 32x32 chunk: 8 consecutive rows of one column (16 B of C).
+        uint4 cold[4];
+        if (p.accumulate && p.vec_c) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int piece = lane + 32 * i;
+            const int col = n0 + c0 + (piece >> 2), row = row0 + (piece & 3) * 8;
+            cold[i] = make_uint4(0, 0, 0, 0);
+            if (col < p.N && row + 8 <= p.M)
+              cold[i] = *reinterpret_cast<const uint4*>(cbase + static_cast<long long>(col) * p.ldc + row);
+          }
+        }
         uint32_t v[32];
         tmem_ld32(taddr + c0, v);
         tmem_ld_wait();
@@ -214,18 +233,39 @@ hgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
         }
-        if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = n0 + c0 + j;
-            if (col < p.N) {
-              __half* cp = cbase + static_cast<long long>(col) * p.ldc;
-              float x = __uint_as_float(v[j]);
-              if (p.accumulate) x += __half2float(*cp);
-              *cp = __float2half_rn(x);
+        for (int j = 0; j < 32; ++j) stage[j * TEPI_PITCH + lane] = __uint_as_float(v[j]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int piece = lane + 32 * i;
+          const int cl = piece >> 2, rg = piece & 3;
+          const int col = n0 + c0 + cl, row = row0 + rg * 8;
+          if (col >= p.N || row >= p.M) continue;
+          const float4 x0 = *reinterpret_cast<const float4*>(stage + cl * TEPI_PITCH + rg * 8);
+          const float4 x1 = *reinterpret_cast<const float4*>(stage + cl * TEPI_PITCH + rg * 8 + 4);
+          float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+          __half* cp = cbase + static_cast<long long>(col) * p.ldc + row;
+          if (p.vec_c && row + 8 <= p.M) {
+            if (p.accumulate) {
+              const __half* o = reinterpret_cast<const __half*>(&cold[i]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) x[e] += __half2float(o[e]);
+            }
+            uint4 out;
+            __half2* oh = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
+            *reinterpret_cast<uint4*>(cp) = out;
+          } else {
+            for (int e = 0; e < 8 && row + e < p.M; ++e) {
+              float y = x[e];
+              if (p.accumulate) y += __half2float(cp[e]);
+              cp[e] = __float2half_rn(y);
             }
           }
         }
+        __syncwarp();
       }
     }
   }
@@ -275,18 +315,22 @@ struct MapKeyHash {
   }
 };
 
-// fp16 3-D map: dim0 = contiguous extent, dim1 = number of stored columns, dim2 = batches.
-bool encode_map(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
-                unsigned long long d2, unsigned long long ld, unsigned long long batch_stride,
-                unsigned b0, unsigned b1) {
+}  // namespace
+
+// 3-D tiled map: dim0 = contiguous extent, dim1 = number of stored columns, dim2 = batches.
+// esize 2 = fp16, 4 = fp32.  Boxes are b0 x b1 x 1; swizzle128 selects the 128-byte swizzle
+// (otherwise none).  Maps are cached per (device, pointer, geometry).
+bool encode_tmap(CUtensorMap* out, int esize, const void* ptr, unsigned long long d0,
+                 unsigned long long d1, unsigned long long d2, unsigned long long ld,
+                 unsigned long long batch_stride, unsigned b0, unsigned b1, bool swizzle128) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   MapKey key;
   std::memset(&key, 0, sizeof(key));
   key.ptr = ptr;
   key.d0 = d0; key.d1 = d1; key.d2 = d2;
-  key.s1 = ld * 2; key.s2 = batch_stride * 2;
-  key.b0 = b0; key.b1 = b1;
+  key.s1 = ld * esize; key.s2 = batch_stride * esize;
+  key.b0 = b0; key.b1 = b1 | (swizzle128 ? 0x10000u : 0u) | (static_cast<unsigned>(esize) << 20);
   cudaGetDevice(&key.dev);
   {
     std::lock_guard<std::mutex> g(mu);
@@ -302,8 +346,10 @@ bool encode_map(CUtensorMap* out, const void* ptr, unsigned long long d0, unsign
   cuuint64_t strides[2] = {key.s1, key.s2};
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(ptr), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  CUresult r = enc(out, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                   3, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   std::lock_guard<std::mutex> g(mu);
@@ -312,11 +358,21 @@ bool encode_map(CUtensorMap* out, const void* ptr, unsigned long long d0, unsign
   return true;
 }
 
+bool tmap_encoder_available() { return get_encode() != nullptr; }
+
+namespace {
+
+bool encode_map(CUtensorMap* out, const void* ptr, unsigned long long d0, unsigned long long d1,
+                unsigned long long d2, unsigned long long ld, unsigned long long batch_stride,
+                unsigned b0, unsigned b1) {
+  return encode_tmap(out, 2, ptr, d0, d1, d2, ld, batch_stride, b0, b1, true);
+}
+
 template <int A_MN, int B_MN>
 cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const HParams& p, int grid,
                            cudaStream_t stream, int* status) {
   auto kern = hgemm_tma_kernel<A_MN, B_MN>;
-  const int smem = TSTAGES * TSTAGE_BYTES + 1024;
+  const int smem = TSTAGES * TSTAGE_BYTES + TEPI_BYTES + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   kern<<<grid, 192, smem, stream>>>(ta, tb, p, status);
@@ -354,6 +410,8 @@ cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t strea
   p.strideC = a.strideC;
   p.M = a.M; p.N = a.N; p.K = a.K; p.batches = a.batches;
   p.accumulate = a.accumulate;
+  p.vec_c = ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0 && a.ldc % 8 == 0 &&
+             (a.batches == 1 || a.strideC % 8 == 0)) ? 1 : 0;
   p.tiles_m = (a.M + TBM - 1) / TBM;
   p.tiles_n = (a.N + TBN - 1) / TBN;
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batches;

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include "problem.h"
 
+struct CUtensorMap_st;  // CUDA driver tensor-map descriptor (cuda.h)
+
 namespace gb {
 
 // --- staged tcgen05 kernel (gemm_staged.cu); dtype 0 = fp32 (3xTF32), 1 = fp16 ---
@@ -26,6 +28,18 @@ struct HgemmArgs {
 // Returns true when the TMA path can take the problem (alignment and size rules).
 bool hgemm_tma_supported(const HgemmArgs& a);
 cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
+
+// --- tensor maps (defined in hgemm_tma.cu) ---
+bool encode_tmap(::CUtensorMap_st* out, int esize, const void* ptr, unsigned long long d0,
+                 unsigned long long d1, unsigned long long d2, unsigned long long ld,
+                 unsigned long long batch_stride, unsigned b0, unsigned b1, bool swizzle128);
+bool tmap_encoder_available();
+
+// --- TMA-fed fp32 (3xTF32) kernel (sgemm3x_tma.cu) ---
+// True when every operand of the problem can be described by a tensor map (16-byte aligned
+// bases, leading dimensions and batch strides; no column tables) and the problem has k > 0.
+bool sgemm3x_supported(const Problem& p);
+cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status);
 
 // --- CUDA-core kernels for degenerate shapes and elementwise helpers (small.cu) ---
 // One warp per output element; used for tiny m*n (batched dot products) and k == 0.

@@ -1,0 +1,444 @@
+// TMA-fed fp32 GEMM with three TF32 tensor-core products per term ("3xTF32") for ginn's
+// column-major tensors:  C = act( sum_p A_p * B_p + bias [+ C] ), optionally strided-batched,
+// optionally with one operand formed on the fly as dY (.) act'(Y) and with the bias gradient
+// (row sums of the A operand) accumulated on the side.
+//
+// Pipeline inside a CTA (one 128 x 128 tile of C):
+//   warp 0     TMA producer: raw fp32 slices (128 rows x 32 k) of A, B (and Y) into a ring.
+//   warps 2-5  transform A, warps 6-9 transform B: raw slice -> registers -> (derivative) ->
+//              hi = rna_tf32(x), lo = x - hi -> two K-major, 128-byte-swizzled planes.  Operands
+//              whose outer index is contiguous in memory are transposed here, for free.
+//   warp 1     MMA issuer: per 8-wide k-step  cross += lo*hi, cross += hi*lo, main[j] += hi*hi.
+//   warps 2-9  epilogue: sum the accumulators, bias / previous C / activation, store.
+//
+// Accuracy: the tensor core truncates when it adds into its fp32 accumulator, which biases a
+// long accumulation chain (measured: relative error grows linearly with K, about 7e-9 per unit
+// of K with one accumulator).  The chain is therefore cut: the large hi*hi terms rotate over
+// three accumulators (k-block j goes to accumulator j mod 3), the small cross terms use a
+// fourth, and the epilogue adds the four in fp32 with round-to-nearest.
+#include <cuda.h>
+#include <cstring>
+#include "ptx.cuh"
+#include "launch.h"
+
+namespace gb {
+
+namespace {
+
+constexpr int SBM = 128, SBN = 128, SBK = 32;
+constexpr int RAW_TILE = SBM * SBK * 4;   // 16 KiB: one raw operand slice
+constexpr int PLANE = 16384;              // one 128-row K-major plane
+constexpr int PLANE_STAGE = 4 * PLANE;    // A hi, A lo, B hi, B lo
+constexpr int PLANE_STAGES = 2;
+constexpr int RAW_BYTES_TOTAL = 96 * 1024;  // 3 stages of (A,B) or 2 stages of (A,B,Y)
+constexpr int XFORM_THREADS = 256;
+constexpr int NTHREADS = 64 + XFORM_THREADS;
+constexpr uint32_t CROSS_COL = 384;
+
+struct SParams {
+  CUtensorMap tmA[kMaxPairs];
+  CUtensorMap tmB[kMaxPairs];
+  CUtensorMap tmY;
+  int k[kMaxPairs];
+  int a_kc[kMaxPairs];
+  int b_kc[kMaxPairs];
+  int npairs;
+  int dop;   // 0: none, 1: A operand carries the derivative, 2: B operand
+  int dact;
+  int M, N;
+  int tiles_m, tiles_n;
+  float* C;
+  long long ldc, strideC;
+  const float* bias;
+  float* rowsum;
+  int act;
+  int accumulate;
+};
+
+__device__ __forceinline__ float act_forward(int act, float x) {
+  switch (act) {
+    case ACT_TANH: return tanhf(x);
+    case ACT_RELU: return fmaxf(x, 0.f);
+    case ACT_SIGMOID: return 0.5f * tanhf(0.5f * x) + 0.5f;
+    default: return x;
+  }
+}
+__device__ __forceinline__ float act_backward(int act, float y, float dy) {
+  switch (act) {
+    case ACT_TANH: return (1.f - y * y) * dy;
+    case ACT_RELU: return y > 0.f ? dy : 0.f;
+    case ACT_SIGMOID: return y * (1.f - y) * dy;
+    default: return dy;
+  }
+}
+
+// hi = round-to-nearest TF32 of x; lo = x - hi (exact in fp32; the tensor core keeps its top
+// 11 significant bits).  Non-finite values stay in the hi plane only.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  hi = __uint_as_float(u);
+  lo = ((u & 0x7f800000u) == 0x7f800000u) ? 0.f : x - hi;
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t raw_full[3];
+  __shared__ __align__(8) uint64_t raw_empty[3];
+  __shared__ __align__(8) uint64_t plane_full[PLANE_STAGES];
+  __shared__ __align__(8) uint64_t plane_empty[PLANE_STAGES];
+  __shared__ __align__(8) uint64_t acc_full;
+  __shared__ uint32_t tmem_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t planes_base = base;                               // PLANE_STAGES * 64 KiB
+  const uint32_t raws_base = base + PLANE_STAGES * PLANE_STAGE;    // 96 KiB
+  const int raw_stages = p.dop ? 2 : 3;
+  const int raw_stage_bytes = p.dop ? 3 * RAW_TILE : 2 * RAW_TILE;
+
+  int tile = blockIdx.x;
+  const int m_tile = tile % p.tiles_m;
+  tile /= p.tiles_m;
+  const int n_tile = tile % p.tiles_n;
+  const int batch = tile / p.tiles_n;
+  const int m0 = m_tile * SBM, n0 = n_tile * SBN;
+
+  int nkb = 0;
+  for (int i = 0; i < p.npairs; ++i) nkb += (p.k[i] + SBK - 1) / SBK;
+
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < p.npairs; ++i) {
+      prefetch_tmap(&p.tmA[i]);
+      prefetch_tmap(&p.tmB[i]);
+    }
+    if (p.dop) prefetch_tmap(&p.tmY);
+  }
+  if (warp == 1) {
+    if (lane == 0) {
+      for (int s = 0; s < 3; ++s) {
+        mbar_init(smem_u32(&raw_full[s]), 1);
+        mbar_init(smem_u32(&raw_empty[s]), XFORM_THREADS);
+      }
+      for (int s = 0; s < PLANE_STAGES; ++s) {
+        mbar_init(smem_u32(&plane_full[s]), XFORM_THREADS);
+        mbar_init(smem_u32(&plane_empty[s]), 1);
+      }
+      mbar_init(smem_u32(&acc_full), 1);
+      fence_mbar_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      int pair = 0, k0 = 0;
+      for (int it = 0; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&raw_empty[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) break;
+        const uint32_t bar = smem_u32(&raw_full[s]);
+        const uint32_t dst = raws_base + s * raw_stage_bytes;
+        mbar_arrive_expect_tx(bar, raw_stage_bytes);
+        // k-contiguous operand: one 32(k) x 128(outer) box, 128-byte swizzle.
+        // outer-contiguous operand: four 32(outer) x 32(k) boxes, unswizzled.
+        if (p.a_kc[pair]) {
+          tma_load_3d(dst, &p.tmA[pair], bar, k0, m0, batch);
+        } else {
+#pragma unroll
+          for (int a = 0; a < 4; ++a)
+            tma_load_3d(dst + a * 4096, &p.tmA[pair], bar, m0 + 32 * a, k0, batch);
+        }
+        if (p.b_kc[pair]) {
+          tma_load_3d(dst + RAW_TILE, &p.tmB[pair], bar, k0, n0, batch);
+        } else {
+#pragma unroll
+          for (int a = 0; a < 4; ++a)
+            tma_load_3d(dst + RAW_TILE + a * 4096, &p.tmB[pair], bar, n0 + 32 * a, k0, batch);
+        }
+        if (p.dop) {
+          const int kc = p.dop == 1 ? p.a_kc[0] : p.b_kc[0];
+          const int o0 = p.dop == 1 ? m0 : n0;
+          if (kc) {
+            tma_load_3d(dst + 2 * RAW_TILE, &p.tmY, bar, k0, o0, batch);
+          } else {
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+              tma_load_3d(dst + 2 * RAW_TILE + a * 4096, &p.tmY, bar, o0 + 32 * a, k0, batch);
+          }
+        }
+        if (++s == raw_stages) {
+          s = 0;
+          ph ^= 1u;
+        }
+        k0 += SBK;
+        if (k0 >= p.k[pair]) {
+          ++pair;
+          k0 = 0;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (elect_one()) {
+      constexpr uint32_t IDESC = make_idesc(2, 0, 0, SBM, SBN);
+      int s = 0;
+      uint32_t ph = 0;
+      for (int it = 0; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&plane_full[s]), ph, status, DEV_TIMEOUT_FULL, it)) break;
+        tc_fence_after();
+        const uint32_t a_hi = planes_base + s * PLANE_STAGE;
+        const uint32_t a_lo = a_hi + PLANE;
+        const uint32_t b_hi = a_hi + 2 * PLANE;
+        const uint32_t b_lo = a_hi + 3 * PLANE;
+        const uint32_t d_main = tmem + (it % 3) * SBN;
+        const uint32_t d_cross = tmem + CROSS_COL;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t dah = make_smem_desc(a_hi + ks * 32, 16, 1024);
+          const uint64_t dal = make_smem_desc(a_lo + ks * 32, 16, 1024);
+          const uint64_t dbh = make_smem_desc(b_hi + ks * 32, 16, 1024);
+          const uint64_t dbl = make_smem_desc(b_lo + ks * 32, 16, 1024);
+          mma_tf32(d_cross, dal, dbh, IDESC, (it > 0 || ks > 0) ? 1u : 0u);
+          mma_tf32(d_cross, dah, dbl, IDESC, 1u);
+          mma_tf32(d_main, dah, dbh, IDESC, (it >= 3 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&plane_empty[s]));
+        if (++s == PLANE_STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+      tc_commit(smem_u32(&acc_full));
+    }
+    __syncwarp();
+  } else {
+    // ===================== transform (warps 2-5: A, warps 6-9: B) =====================
+    const int xt = threadIdx.x - 64;
+    const int grp = xt >> 7;  // 0 = A operand, 1 = B operand
+    const int t = xt & 127;
+    const bool want_rowsum = grp == 0 && p.rowsum != nullptr && n_tile == 0;
+    float rs = 0.f;
+    bool ok = true;
+    int rs_i = 0, ps_i = 0;
+    uint32_t rph = 0, pph = 0;
+    int pair = 0, k0 = 0;
+    for (int it = 0; it < nkb; ++it) {
+      if (!mbar_wait(smem_u32(&raw_full[rs_i]), rph, status, DEV_TIMEOUT_FULL, 0x100 + it) ||
+          !mbar_wait(smem_u32(&plane_empty[ps_i]), pph ^ 1u, status, DEV_TIMEOUT_EMPTY,
+                     0x100 + it)) {
+        ok = false;
+        break;
+      }
+      const uint8_t* raw_stage = base_ptr + PLANE_STAGES * PLANE_STAGE + rs_i * raw_stage_bytes;
+      const uint8_t* src = raw_stage + grp * RAW_TILE;
+      const uint8_t* ysrc = raw_stage + 2 * RAW_TILE;
+      uint8_t* dst_hi = base_ptr + ps_i * PLANE_STAGE + grp * 2 * PLANE;
+      uint8_t* dst_lo = dst_hi + PLANE;
+      const int kc = grp ? p.b_kc[pair] : p.a_kc[pair];
+      const bool has_y = p.dop == grp + 1;
+      if (kc) {
+        // Raw slice already is K-major and swizzled: transform in place, piece by piece.
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int off = (t + 128 * i) * 16;
+          float4 x = *reinterpret_cast<const float4*>(src + off);
+          if (has_y) {
+            const float4 y = *reinterpret_cast<const float4*>(ysrc + off);
+            x.x = act_backward(p.dact, y.x, x.x);
+            x.y = act_backward(p.dact, y.y, x.y);
+            x.z = act_backward(p.dact, y.z, x.z);
+            x.w = act_backward(p.dact, y.w, x.w);
+          }
+          float4 h, l;
+          split_tf32(x.x, h.x, l.x);
+          split_tf32(x.y, h.y, l.y);
+          split_tf32(x.z, h.z, l.z);
+          split_tf32(x.w, h.w, l.w);
+          *reinterpret_cast<float4*>(dst_hi + off) = h;
+          *reinterpret_cast<float4*>(dst_lo + off) = l;
+        }
+      } else {
+        // Raw slice is [atom][k][32 outer]: thread t owns outer index t and transposes its row.
+        const float* col = reinterpret_cast<const float*>(src + (t >> 5) * 4096) + (t & 31);
+        const float* ycol = reinterpret_cast<const float*>(ysrc + (t >> 5) * 4096) + (t & 31);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float x[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            x[e] = col[(4 * c + e) * 32];
+            if (has_y) x[e] = act_backward(p.dact, ycol[(4 * c + e) * 32], x[e]);
+            if (want_rowsum && pair == 0) rs += x[e];
+          }
+          float4 h, l;
+          split_tf32(x[0], h.x, l.x);
+          split_tf32(x[1], h.y, l.y);
+          split_tf32(x[2], h.z, l.z);
+          split_tf32(x[3], h.w, l.w);
+          const uint32_t off = sw128_offset(t, c);
+          *reinterpret_cast<float4*>(dst_hi + off) = h;
+          *reinterpret_cast<float4*>(dst_lo + off) = l;
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&plane_full[ps_i]));
+      mbar_arrive(smem_u32(&raw_empty[rs_i]));
+      if (++rs_i == raw_stages) {
+        rs_i = 0;
+        rph ^= 1u;
+      }
+      if (++ps_i == PLANE_STAGES) {
+        ps_i = 0;
+        pph ^= 1u;
+      }
+      k0 += SBK;
+      if (k0 >= p.k[pair]) {
+        ++pair;
+        k0 = 0;
+      }
+    }
+    if (want_rowsum && ok && m0 + t < p.M) atomicAdd(p.rowsum + m0 + t, rs);
+
+    // ===================== epilogue (all eight warps; 64 columns each) =====================
+    if (ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int half = (warp - 2) >> 2;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float bias = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
+      float* crow = p.C + static_cast<long long>(batch) * p.strideC + row;
+      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+        float acc[32];
+        const bool load_c = p.accumulate && row_ok;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = n0 + c0 + j;
+          acc[j] = (load_c && col < p.N) ? crow[static_cast<long long>(col) * p.ldc] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] += bias;
+        uint32_t v[32];
+        tmem_ld32(tbase + CROSS_COL + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+#pragma unroll 1
+        for (int a = 0; a < 3 && a < nkb; ++a) {
+          tmem_ld32(tbase + a * SBN + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = n0 + c0 + j;
+            if (col < p.N) crow[static_cast<long long>(col) * p.ldc] = act_forward(p.act, acc[j]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+bool operand_tma_ok(const Operand& o, int batches) {
+  if (o.cols != nullptr || o.ycols != nullptr) return false;
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  if (!al(o.base) || (o.ybase && !al(o.ybase))) return false;
+  if (o.ld % 4 != 0) return false;
+  if (batches > 1 && o.batch_stride % 4 != 0) return false;
+  return true;
+}
+
+// Stored extents of operand X(outer O, inner K): k-contiguous -> K rows x O columns.
+bool encode_operand(CUtensorMap* out, const void* ptr, const Operand& o, long long O, long long K,
+                    int batches) {
+  const unsigned long long rows = o.k_contig ? K : O, cols = o.k_contig ? O : K;
+  const unsigned long long bs = batches > 1 ? o.batch_stride : o.ld * cols;
+  return encode_tmap(out, 4, ptr, rows, cols, batches, o.ld, bs ? bs : 4, 32,
+                     o.k_contig ? SBM : SBK, o.k_contig != 0);
+}
+
+}  // namespace
+
+bool sgemm3x_supported(const Problem& p) {
+  if (p.npairs < 1 || p.ccols != nullptr || !tmap_encoder_available()) return false;
+  int nderiv = 0;
+  for (int i = 0; i < p.npairs; ++i) {
+    if (p.k[i] <= 0 || p.k[i] > 0x7fffffffLL) return false;
+    if (!operand_tma_ok(p.a[i], p.batches) || !operand_tma_ok(p.b[i], p.batches)) return false;
+    nderiv += (p.a[i].dact != ACT_NONE) + (p.b[i].dact != ACT_NONE);
+  }
+  if (nderiv > 1 || (nderiv == 1 && p.npairs != 1)) return false;
+  if (p.rowsum != nullptr && p.a[0].k_contig) return false;
+  return true;
+}
+
+cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
+  SParams sp;
+  std::memset(&sp, 0, sizeof(sp));
+  sp.npairs = p.npairs;
+  for (int i = 0; i < p.npairs; ++i) {
+    sp.k[i] = static_cast<int>(p.k[i]);
+    sp.a_kc[i] = p.a[i].k_contig;
+    sp.b_kc[i] = p.b[i].k_contig;
+    if (!encode_operand(&sp.tmA[i], p.a[i].base, p.a[i], p.M, p.k[i], p.batches) ||
+        !encode_operand(&sp.tmB[i], p.b[i].base, p.b[i], p.N, p.k[i], p.batches))
+      return cudaErrorInvalidValue;
+  }
+  if (p.a[0].dact != ACT_NONE) {
+    sp.dop = 1;
+    sp.dact = p.a[0].dact;
+    if (!encode_operand(&sp.tmY, p.a[0].ybase, p.a[0], p.M, p.k[0], p.batches))
+      return cudaErrorInvalidValue;
+  } else if (p.b[0].dact != ACT_NONE) {
+    sp.dop = 2;
+    sp.dact = p.b[0].dact;
+    if (!encode_operand(&sp.tmY, p.b[0].ybase, p.b[0], p.N, p.k[0], p.batches))
+      return cudaErrorInvalidValue;
+  }
+  sp.M = p.M;
+  sp.N = p.N;
+  sp.tiles_m = (p.M + SBM - 1) / SBM;
+  sp.tiles_n = (p.N + SBN - 1) / SBN;
+  sp.C = static_cast<float*>(p.c);
+  sp.ldc = p.ldc;
+  sp.strideC = p.c_batch_stride;
+  sp.bias = static_cast<const float*>(p.bias);
+  sp.rowsum = static_cast<float*>(p.rowsum);
+  sp.act = p.act;
+  sp.accumulate = p.accumulate;
+  const long long total = static_cast<long long>(sp.tiles_m) * sp.tiles_n * p.batches;
+  if (total <= 0) return cudaSuccess;
+  if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+  const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
+  cudaError_t e = cudaFuncSetAttribute(sgemm3x_tma_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  sgemm3x_tma_kernel<<<static_cast<unsigned>(total), NTHREADS, smem, stream>>>(sp, status);
+  return cudaGetLastError();
+}
+
+}  // namespace gb
