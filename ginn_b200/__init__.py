@@ -7,6 +7,6 @@ the CUDA library is missing.
 """
 from .binding import (  # noqa: F401
     ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH, F16, F32, GinnB200Error, Group, Pair, PairGrad,
-    affine_backward, affine_forward, device_status, gemm, gemm_batched, grouped, launch_count,
+    affine_backward, affine_forward, device_status, gemm, gemm_batched, grouped, grouped_static, launch_count,
     lib, lib_path, set_option, version,
 )

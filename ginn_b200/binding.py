@@ -70,6 +70,8 @@ def lib():
     L.ginn_b200_affine_backward.argtypes = [ci, vp, ci, ci, C.POINTER(_PairGrad), i64, i64, vp,
                                             i64, vp, i64, ci, vp]
     L.ginn_b200_grouped.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
+    L.ginn_b200_grouped_static.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
+    L.ginn_b200_grouped_static.restype = ci
     L.ginn_b200_last_error.restype = C.c_char_p
     L.ginn_b200_device_status.argtypes = [ci, ci]
     L.ginn_b200_set_option.argtypes = [C.c_char_p, ci]
@@ -219,8 +221,18 @@ class Group:
     dbias: Optional[torch.Tensor] = None
 
 
+def grouped_static(mode: int, groups: Sequence[Group]) -> None:
+    """`grouped` through the entry point that allocates nothing (fixed 256 KiB descriptor array
+    inside the library); for hosts that may not call the CUDA allocator."""
+    _grouped_call(lib().ginn_b200_grouped_static, mode, groups)
+
+
 def grouped(mode: int, groups: Sequence[Group]) -> None:
     """All groups of one autobatch level in one launch (ginn/autobatch.h:149-183)."""
+    _grouped_call(lib().ginn_b200_grouped, mode, groups)
+
+
+def _grouped_call(fn, mode: int, groups: Sequence[Group]) -> None:
     if not groups:
         return
     arr = (_Group * len(groups))()
@@ -239,7 +251,7 @@ def grouped(mode: int, groups: Sequence[Group]) -> None:
                         table(g.dx_cols) if len(g.dx_cols) else None, _ptr(g.dw),
                         _ld(g.dw) if g.dw is not None else 0, _ptr(g.dbias))
     w0 = groups[0].w
-    _check(lib().ginn_b200_grouped(_dev(w0), _stream(w0), _dtype_of(w0), mode, len(groups), arr))
+    _check(fn(_dev(w0), _stream(w0), _dtype_of(w0), mode, len(groups), arr))
 
 
 def device_status(device: int = 0, reset: bool = True) -> int:

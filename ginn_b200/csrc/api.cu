@@ -442,6 +442,143 @@ int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroup
   return GINN_B200_OK;
 }
 
+// Same work as ginn_b200_grouped, for callers that may not allocate (see include/ginn_b200.h).
+// Nothing here calls cudaMalloc, cudaMallocHost, cudaFree or any allocating library routine:
+// the device-side descriptors go into a fixed array inside the library image
+// (gemm_staged.cu), the host-side image is assembled in a fixed buffer below.
+int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int ngroups,
+                             const ginn_b200_group* groups) {
+  static std::mutex image_mu;
+  alignas(16) static unsigned char image[gb::kGroupedStaticBytes];
+  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
+    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
+  if (mode < GINN_B200_GROUPED_FORWARD || mode > GINN_B200_GROUPED_DW)
+    return fail(GINN_B200_BAD_ARGUMENT, "unknown grouped mode %d", mode);
+  if (ngroups < 0 || (ngroups > 0 && groups == nullptr))
+    return fail(GINN_B200_BAD_ARGUMENT, "bad group list");
+  if (ngroups == 0) return GINN_B200_OK;
+  if (device < 0 || device >= kMaxDevices)
+    return fail(GINN_B200_BAD_ARGUMENT, "device index %d out of range", device);
+  CU_TRY(cudaSetDevice(device));
+  int major = 0, num_sms = 0;
+  CU_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  if (major != 10)
+    return fail(GINN_B200_UNSUPPORTED, "device %d is not an sm_100 GPU", device);
+  CU_TRY(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  size_t table_bytes = 0;
+  long long max_n = 0, sum_tiles128 = 0;
+  int live = 0;
+  for (int g = 0; g < ngroups; ++g) {
+    const ginn_b200_group& q = groups[g];
+    if (q.m < 0 || q.k < 0 || q.ncols < 0 || q.m > 0x7fffffffLL || q.k > 0x7fffffffLL ||
+        q.ncols > 0x7fffffffLL)
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dimensions", g);
+    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
+    if (!q.w || q.ldw < q.m || !q.y_cols)
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad W or column table", g);
+    if ((mode != GINN_B200_GROUPED_DX && !q.x_cols) || (mode == GINN_B200_GROUPED_DX && !q.dx_cols))
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: missing column table for mode %d", g, mode);
+    if (mode == GINN_B200_GROUPED_DW && (!q.dw || q.lddw < q.m))
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dW", g);
+    table_bytes += 2 * static_cast<size_t>(q.ncols) * sizeof(void*);
+    const long long N = mode == GINN_B200_GROUPED_DW ? q.k : q.ncols;
+    const long long M = mode == GINN_B200_GROUPED_DX ? q.k : q.m;
+    max_n = N > max_n ? N : max_n;
+    sum_tiles128 += ((M + 127) / 128) * ((N + 127) / 128);
+    ++live;
+  }
+  if (live == 0) return GINN_B200_OK;
+  const size_t desc_bytes = (static_cast<size_t>(live) * sizeof(Problem) + 15) & ~size_t(15);
+  const size_t need = desc_bytes + table_bytes;
+  if (need > gb::kGroupedStaticBytes)
+    return fail(GINN_B200_BAD_ARGUMENT,
+                "level too large for the allocation-free entry point: %zu bytes of descriptors "
+                "and column tables, limit %zu (%d groups, 16 bytes per column); split the level "
+                "or use ginn_b200_grouped",
+                need, gb::kGroupedStaticBytes, live);
+  void* scratch = nullptr;
+  CU_TRY(gb::grouped_static_scratch(device, &scratch));
+  unsigned char* d = static_cast<unsigned char*>(scratch);
+
+  int bn = 128;
+  if (max_n <= 32) bn = 32;
+  else if (max_n <= 64 || sum_tiles128 < num_sms) bn = 64;
+
+  std::lock_guard<std::mutex> lock(image_mu);
+  Problem* hp = reinterpret_cast<Problem*>(image);
+  size_t off = desc_bytes;
+  int np = 0, tile = 0;
+  for (int g = 0; g < ngroups; ++g) {
+    const ginn_b200_group& q = groups[g];
+    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
+    const size_t tb = static_cast<size_t>(q.ncols) * sizeof(void*);
+    const void** t0 = reinterpret_cast<const void**>(image + off);
+    const void* const* d_t0 = reinterpret_cast<const void* const*>(d + off);
+    off += tb;
+    const void** t1 = reinterpret_cast<const void**>(image + off);
+    const void* const* d_t1 = reinterpret_cast<const void* const*>(d + off);
+    off += tb;
+    Problem& p = hp[np];
+    std::memset(&p, 0, sizeof(p));
+    p.npairs = 1;
+    p.batches = 1;
+    bool al = true;
+    if (mode == GINN_B200_GROUPED_FORWARD) {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        t0[j] = q.x_cols[j];
+        t1[j] = q.y_cols[j];
+        al = al && aligned16(q.x_cols[j]);
+      }
+      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 0);
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
+      p.b[0].cols = d_t0;
+      p.b[0].vec = al ? 1 : 0;
+      p.k[0] = q.k;
+      p.M = (int)q.m; p.N = (int)q.ncols;
+      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
+      p.bias = q.bias;
+    } else if (mode == GINN_B200_GROUPED_DX) {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        t0[j] = q.y_cols[j];
+        t1[j] = q.dx_cols[j];
+        al = al && aligned16(q.y_cols[j]);
+      }
+      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 1);
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
+      p.b[0].cols = d_t0;
+      p.b[0].vec = al ? 1 : 0;
+      p.k[0] = q.m;
+      p.M = (int)q.k; p.N = (int)q.ncols;
+      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
+      p.accumulate = 1;
+    } else {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        t0[j] = q.y_cols[j];
+        t1[j] = q.x_cols[j];
+      }
+      p.a[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);
+      p.a[0].cols = d_t0;
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);
+      p.b[0].cols = d_t1;
+      p.k[0] = q.ncols;
+      p.M = (int)q.m; p.N = (int)q.k;
+      p.c = q.dw; p.ldc = q.lddw;
+      p.rowsum = q.dbias;
+      p.accumulate = 1;
+    }
+    p.tiles_m = (p.M + 127) / 128;
+    p.tiles_n = (p.N + bn - 1) / bn;
+    p.tile_start = tile;
+    tile += p.tiles_m * p.tiles_n;
+    ++np;
+  }
+  CU_TRY(gb::launch_staged_grouped_static(dtype, image, off, scratch, np, tile, bn, stream));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
 const char* ginn_b200_last_error(void) { return t_error.c_str(); }
 
 int ginn_b200_device_status(int device, int reset) {

@@ -15,6 +15,7 @@
 //
 // Role layout of a CTA (160 threads): warps 0-3 produce, then run the epilogue (TMEM lane
 // quarter = warp index); warp 4 allocates TMEM and issues the MMAs.
+#include <mutex>
 #include "ptx.cuh"
 #include "problem.h"
 #include "launch.h"
@@ -470,6 +471,63 @@ cudaError_t launch_staged_grouped(int dtype, const Problem* dprobs, int nprobs, 
                                   int bn, cudaStream_t stream, int* status) {
   return dtype == 0 ? launch_grouped_t<float>(dprobs, nprobs, total_tiles, bn, stream, status)
                     : launch_grouped_t<__half>(dprobs, nprobs, total_tiles, bn, stream, status);
+}
+
+// -------------------------------------------------------------------------------------------
+// Grouped launch that allocates nothing.
+//
+// The ordinary grouped launch keeps its problem descriptors and column-pointer tables in a
+// cudaMalloc'ed ring.  Some hosts cannot allocate at the point where they call: a caller that
+// runs inside a memory pool it must not disturb, or one that has pledged a fixed footprint
+// (ginn's PreallocGpuDevice style of accounting, where every byte taken from the GPU is counted).
+// For them the same kernel reads its descriptors from a fixed array that is part of the
+// library image, so nothing is requested from the CUDA allocator at call time.
+//
+// The array exists once per GPU that loads the library and stays until the process exits.
+// All calls on a GPU share it, and it always holds whatever the last call put there; the part a
+// call uses is completely rewritten by that call, so nothing in it needs clearing.  Two calls
+// whose GPU work overlaps (different streams) would overwrite each other's descriptors: keep
+// calls of this variant on one stream, or order them with events.
+// -------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_grouped_static_scratch[kGroupedStaticBytes];
+
+namespace {
+struct StaticScratchSlot {
+  void* ptr = nullptr;
+  bool ready = false;
+};
+StaticScratchSlot g_static_slots[64];
+std::mutex g_static_mu;
+}  // namespace
+
+// `device` must be current.  In host code the array's name is only a handle, not a device
+// address, so the address is looked up once per device and cached.
+cudaError_t grouped_static_scratch(int device, void** ptr) {
+  if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> g(g_static_mu);
+  StaticScratchSlot& slot = g_static_slots[device];
+  if (!slot.ready) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_grouped_static_scratch);
+    if (e != cudaSuccess) return e;
+    slot.ptr = p;
+    slot.ready = true;
+  }
+  *ptr = slot.ptr;
+  return cudaSuccess;
+}
+
+// Copies the host image (descriptors followed by pointer tables, already holding device
+// addresses inside the static array) and launches the grouped kernel on it.
+cudaError_t launch_staged_grouped_static(int dtype, const void* host_image, size_t bytes,
+                                         void* scratch, int nprobs, int total_tiles, int bn,
+                                         cudaStream_t stream) {
+  if (bytes > kGroupedStaticBytes) return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemcpyAsync(scratch, host_image, bytes, cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return e;
+  // No status word: a wait that runs out still ends the kernel, it is just not recorded.
+  return launch_staged_grouped(dtype, static_cast<const Problem*>(scratch), nprobs, total_tiles,
+                               bn, stream, nullptr);
 }
 
 }  // namespace gb

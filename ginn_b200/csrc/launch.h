@@ -2,6 +2,7 @@
 // the C ABI in include/ginn_b200.h).
 #pragma once
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include "problem.h"
 
 struct CUtensorMap_st;  // CUDA driver tensor-map descriptor (cuda.h)
@@ -13,6 +14,13 @@ int staged_pick_bn(int dtype, long long M, long long N, long long batches, int n
 cudaError_t launch_staged(int dtype, Problem& p, int bn, cudaStream_t stream, int* status);
 cudaError_t launch_staged_grouped(int dtype, const Problem* dprobs, int nprobs, int total_tiles,
                                   int bn, cudaStream_t stream, int* status);
+
+// Allocation-free grouped launch: descriptors live in a fixed array inside the library image.
+constexpr size_t kGroupedStaticBytes = 256 * 1024;
+cudaError_t grouped_static_scratch(int device, void** ptr);
+cudaError_t launch_staged_grouped_static(int dtype, const void* host_image, size_t bytes,
+                                         void* scratch, int nprobs, int total_tiles, int bn,
+                                         cudaStream_t stream);
 
 // --- TMA-fed persistent fp16 kernel (hgemm_tma.cu) ---
 struct HgemmArgs {

@@ -124,6 +124,31 @@ typedef enum {
 int ginn_b200_grouped(int device, void* stream, int dtype, int mode, int ngroups,
                       const ginn_b200_group* groups);
 
+/* ginn_b200_grouped for callers that must not allocate.  No counterpart in the reference.
+ *
+ * ginn_b200_grouped keeps the per-level problem descriptors and column-pointer tables in
+ * buffers it obtains from cudaMalloc / cudaMallocHost on first use.  A host that runs with a
+ * fixed GPU-memory budget -- for example a ginn program built around PreallocGpuDevice, whose
+ * tests account for every byte taken from the device (ginn/dev.h:214-261, test/dev.cu.cpp) --
+ * or one that calls from a place where the CUDA allocator must not be entered, can use this
+ * entry point instead.  It computes exactly the same thing with the same kernel, but the
+ * descriptors live in a fixed 256 KiB array that is part of the library itself (each GPU that
+ * loads the library carries it until the process ends), and the call makes no cudaMalloc,
+ * cudaFree or other allocating call.
+ *
+ * Limit: descriptors plus tables of one call must fit in 256 KiB -- about 640 bytes per group
+ * and 16 bytes per column, e.g. 32 groups with 15000 columns in total.  Larger levels are
+ * refused with GINN_B200_BAD_ARGUMENT; split them or use ginn_b200_grouped.
+ * The first call on each device looks up the array's device address; make that first call
+ * outside any stream capture.  Because the descriptors are copied from ordinary host memory,
+ * the call may wait for work already queued on `stream`.  All calls on a GPU share the one
+ * array, and it keeps what the last call wrote; the part a call uses is rewritten in full, so
+ * nothing has to be cleared, but two calls whose GPU work overlaps (different streams without
+ * an event between them) would corrupt each other -- keep these calls on one stream.  A kernel
+ * that gives up on a bounded wait is not recorded in the device status word by this variant. */
+int ginn_b200_grouped_static(int device, void* stream, int dtype, int mode, int ngroups,
+                             const ginn_b200_group* groups);
+
 /* Text of the last failure on the calling thread ("" if none). */
 const char* ginn_b200_last_error(void);
 
