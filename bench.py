@@ -30,6 +30,10 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one hgemm_tma_kernel launch at 8192^3, from the
+# ncu capture summarised in profiles/hgemm_tma_prod8192.md (mean of the captured launches).
+NCU_TRAFFIC_BYTES = {8192: 1.245e9}
+
 METRIC = "prod_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 SIZE = 8192
@@ -59,7 +63,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu)],
+                 "-lms", "20", "-i", str(self.gpu)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -166,6 +170,7 @@ def run_gpu(args):
     import torch.distributed as dist
     import ginn_b200 as gb
     from ginn_b200 import binding as B
+    from ginn_b200.parallel import ShardedProd
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -191,33 +196,36 @@ def run_gpu(args):
     main = torch.cuda.current_stream(dev)
     gemm_events = []
 
+    def allreduce_async(t):
+        if world == 1:
+            return lambda: None
+        ready = torch.cuda.Event()
+        ready.record(main)
+        comm_stream.wait_event(ready)
+        with torch.cuda.stream(comm_stream):
+            dist.all_reduce(t.T)  # contiguous storage of the column-major matrix
+        return lambda: main.wait_stream(comm_stream)
+
+    prod = ShardedProd(lambda a, b, c, ta, tb, acc: gb.gemm(a, b, c, ta, tb, acc),
+                       lambda t: t.zero_(), allreduce_async)
+
     def step(record=False):
-        dA.zero_()
-        dB.zero_()
-        evs = []
-        if record:
-            evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
-            evs[0].record()
-        gb.gemm(A, Bm, Cm)                                    # C  = A * B
-        if record:
-            evs[1].record(); evs[2].record()
-        gb.gemm(dC, Bm, dA, trans_b=True, accumulate=True)    # dA += dC * B^T
-        if record:
-            evs[3].record()
-        if world > 1:
-            ready = torch.cuda.Event()
-            ready.record(main)
-            comm_stream.wait_event(ready)
-            with torch.cuda.stream(comm_stream):
-                dist.all_reduce(dA.T)  # contiguous storage of the column-major matrix
-        if record:
-            evs[4].record()
-        gb.gemm(A, dC, dB, trans_a=True, accumulate=True)     # dB += A^T * dC
-        if record:
-            evs[5].record()
-            gemm_events.append(evs)
-        if world > 1:
-            main.wait_stream(comm_stream)
+        if not record:
+            prod.step(A, Bm, dC, Cm, dA, dB)
+            return
+        # CUDA events around each of the three products, on the stream they are launched on
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        state = {"first": True}
+
+        def gemm_timed(a, b, c, ta, tb, acc):
+            if state["first"]:
+                evs[0].record()
+                state["first"] = False
+            gb.gemm(a, b, c, ta, tb, acc)
+
+        timed = ShardedProd(gemm_timed, lambda t: t.zero_(), allreduce_async)
+        timed.step(A, Bm, dC, Cm, dA, dB, between=lambda i: evs[i + 1].record())
+        gemm_events.append(evs)
 
     def barrier():
         if world > 1:
@@ -251,8 +259,7 @@ def run_gpu(args):
         ms = t.item()
     kern_ms = []
     for evs in gemm_events:
-        kern_ms += [evs[0].elapsed_time(evs[1]), evs[2].elapsed_time(evs[3]),
-                    evs[4].elapsed_time(evs[5])]
+        kern_ms += [evs[i].elapsed_time(evs[i + 1]) for i in range(3)]
     status = gb.device_status(local, True)
     if status != 0:
         raise RuntimeError(f"device status {status:#x} after the timed region")
@@ -305,7 +312,7 @@ def run_gpu(args):
     avg_kernel_ms = sum(kern_ms) / len(kern_ms)
     achieved = 2 * n ** 3 / (avg_kernel_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(n),
                 "kernel": "hgemm_tma_kernel (three transpose variants, one launch each per step)",
                 "avg_launch_ms": avg_kernel_ms,
                 "peak_kind": f"{'sustained' if sustained else 'burst'} cuBLAS bf16, of {peak_src}"}
@@ -380,7 +387,7 @@ def run_affine(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=SIZE, help="matrix extent (default: the C4 config)")

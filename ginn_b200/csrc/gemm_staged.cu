@@ -6,15 +6,21 @@
 // producers
 //   * multiply by the derivative of the nonlinearity (dY (.) act'(Y)) when asked to,
 //   * accumulate the bias gradient (row sums of the A operand),
-//   * split fp32 values into two TF32 planes (hi = rna(x), lo = rna(x - hi)),
+//   * split fp32 values into two TF32 planes (hi = rna(x), lo = x - hi),
 // and then write K-major, 128-byte-swizzled tiles to shared memory.  One elected thread
-// issues tcgen05.mma (kind::tf32 three times per k-step for fp32: lo*hi + hi*lo + hi*hi;
-// kind::f16 once for fp16) into a TMEM accumulator; the epilogue reads TMEM with tcgen05.ld,
-// adds bias / previous C, applies the activation and stores coalesced along rows, which are
-// contiguous in column-major storage.
+// issues tcgen05.mma into TMEM; the epilogue reads TMEM with tcgen05.ld, adds bias / previous
+// C, applies the activation and stores coalesced along rows, which are contiguous in
+// column-major storage.
 //
-// Role layout of a CTA (160 threads): warps 0-3 produce, then run the epilogue (TMEM lane
-// quarter = warp index); warp 4 allocates TMEM and issues the MMAs.
+// fp32 uses kind::tf32 three times per k-step.  The tensor core truncates when it adds into
+// its fp32 accumulator, which biases long accumulation chains, so the chain is cut: the small
+// cross terms lo*hi + hi*lo go to one accumulator, the hi*hi terms rotate over three more
+// (k-block j -> accumulator j mod 3) and the epilogue adds the four with round-to-nearest.
+// fp16 uses kind::f16 once per k-step and a single accumulator.
+//
+// Role layout of a CTA (288 threads): warps 0-3 produce the A slice, warps 4-7 the B slice,
+// then all eight run the epilogue (TMEM lane quarter = warp index mod 4, half of the columns
+// each); warp 8 allocates TMEM and issues the MMAs.
 #include <mutex>
 #include "ptx.cuh"
 #include "problem.h"
@@ -28,19 +34,22 @@ template <>
 struct TT<float> {
   static constexpr int EPC = 4;     // elements per 16-byte chunk
   static constexpr int PLANES = 2;  // hi and lo TF32 planes
+  static constexpr int ACCS = 4;    // cross + three rotating main accumulators
   static constexpr uint32_t FMT = 2;
 };
 template <>
 struct TT<__half> {
   static constexpr int EPC = 8;
   static constexpr int PLANES = 1;
+  static constexpr int ACCS = 1;
   static constexpr uint32_t FMT = 0;
 };
 
 constexpr int kBM = 128;           // rows of C per tile == TMEM lanes
 constexpr int kRowBytes = 128;     // bytes of K per tile row == swizzle span
 constexpr int kKSteps = 4;         // MMAs (per plane combination) per k-block: 32 bytes of K each
-constexpr int kProducerThreads = 128;
+constexpr int kGroupThreads = 128; // producer threads per operand
+constexpr int kStagedThreads = 2 * kGroupThreads + 32;
 
 __device__ __forceinline__ float to_f(float x) { return x; }
 __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
@@ -80,124 +89,154 @@ __device__ __forceinline__ float act_backward(int act, float y, float dy) {
   }
 }
 
-__device__ __forceinline__ float tf32_rna(float x) {
+// hi = round-to-nearest TF32 of x; lo = x - hi (exact in fp32).  Non-finite values stay in the
+// hi plane only: inf - inf would poison the lo plane.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   uint32_t u;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
+  hi = __uint_as_float(u);
+  lo = ((u & 0x7f800000u) == 0x7f800000u) ? 0.f : x - hi;
 }
 
-// 16 bytes of operand X(o, kk .. kk+EPC-1), zero outside the matrix, derivative applied.
-template <typename T>
-__device__ __forceinline__ uint4 fetch_chunk(const Operand& op, long long boff, int o, int O,
-                                             long long kk, long long K) {
-  constexpr int E = TT<T>::EPC;
-  uint4 du = make_uint4(0, 0, 0, 0), yu = make_uint4(0, 0, 0, 0);
-  if (o >= O || kk >= K) return du;
-  T* d = reinterpret_cast<T*>(&du);
-  T* y = reinterpret_cast<T*>(&yu);
-  const bool has_y = op.dact != ACT_NONE;
-  if (op.k_contig) {
-    const T* col = op.cols ? static_cast<const T*>(op.cols[o])
-                           : static_cast<const T*>(op.base) + boff + static_cast<long long>(o) * op.ld;
-    const T* ycol = nullptr;
-    if (has_y)
-      ycol = op.ycols ? static_cast<const T*>(op.ycols[o])
-                      : static_cast<const T*>(op.ybase) + boff + static_cast<long long>(o) * op.ld;
-    if (op.vec && kk + E <= K) {
-      du = __ldg(reinterpret_cast<const uint4*>(col + kk));
-      if (has_y) yu = __ldg(reinterpret_cast<const uint4*>(ycol + kk));
-    } else {
+// Per-thread view of one operand for one tile.  Everything that does not change along K is
+// worked out once in init(); load() then only adds the k offset.
+//   k_contig : slot i covers row i*16 + t/8, 16-byte chunk t%8 (8 threads read one 128-byte row)
+//   else     : the thread owns one row (t % ROWS) and slot i covers chunk (i*128 + t) / ROWS;
+//              consecutive threads read consecutive rows, which are contiguous in memory.
+template <typename T, int ROWS>
+struct TileLoader {
+  static constexpr int NS = ROWS / 16;
+  static constexpr int E = TT<T>::EPC;
+  const Operand* op;
+  const T* ptr[NS];   // k_contig: column base of each slot's row (nullptr = outside the matrix)
+  const T* yptr[NS];
+  const T* rowp;      // outer-contiguous: base + row (nullptr = outside)
+  const T* yrowp;
+  int t;
+  int row;            // outer-contiguous: row inside the tile
+  int o;              // outer-contiguous: global outer index
+  bool has_y;
+
+  __device__ __forceinline__ void init(const Operand& op_, long long boff, int o0, int O, int t_) {
+    op = &op_;
+    t = t_;
+    has_y = op_.dact != ACT_NONE;
+    rowp = yrowp = nullptr;
+    row = t_ % ROWS;
+    o = o0 + row;
+    if (op_.k_contig) {
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        if (kk + e < K) {
-          d[e] = __ldg(col + kk + e);
-          if (has_y) y[e] = __ldg(ycol + kk + e);
+      for (int i = 0; i < NS; ++i) {
+        const int oi = o0 + i * 16 + (t_ >> 3);
+        ptr[i] = yptr[i] = nullptr;
+        if (oi < O) {
+          ptr[i] = op_.cols ? static_cast<const T*>(op_.cols[oi])
+                            : static_cast<const T*>(op_.base) + boff + static_cast<long long>(oi) * op_.ld;
+          if (has_y)
+            yptr[i] = op_.ycols ? static_cast<const T*>(op_.ycols[oi])
+                                : static_cast<const T*>(op_.ybase) + boff + static_cast<long long>(oi) * op_.ld;
         }
       }
+    } else if (o < O && op_.cols == nullptr) {
+      rowp = static_cast<const T*>(op_.base) + boff + o;
+      if (has_y) yrowp = static_cast<const T*>(op_.ybase) + boff + o;
     }
-  } else {
+    if (!op_.k_contig) {
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      if (kk + e < K) {
-        const T* col = op.cols ? static_cast<const T*>(op.cols[kk + e])
-                               : static_cast<const T*>(op.base) + boff + (kk + e) * op.ld;
-        d[e] = __ldg(col + o);
-        if (has_y) {
-          const T* ycol = op.ycols ? static_cast<const T*>(op.ycols[kk + e])
-                                   : static_cast<const T*>(op.ybase) + boff + (kk + e) * op.ld;
-          y[e] = __ldg(ycol + o);
+      for (int i = 0; i < NS; ++i) ptr[i] = yptr[i] = nullptr;
+    }
+  }
+
+  __device__ __forceinline__ void load(long long k0, long long K, int O, uint4 (&r)[NS]) const {
+    const Operand& P = *op;
+    if (P.k_contig) {
+      const long long kk = k0 + (t & 7) * E;
+#pragma unroll
+      for (int i = 0; i < NS; ++i) {
+        uint4 du = make_uint4(0, 0, 0, 0), yu = make_uint4(0, 0, 0, 0);
+        if (ptr[i] != nullptr && kk < K) {
+          T* d = reinterpret_cast<T*>(&du);
+          T* y = reinterpret_cast<T*>(&yu);
+          if (P.vec && kk + E <= K) {
+            du = __ldg(reinterpret_cast<const uint4*>(ptr[i] + kk));
+            if (has_y) yu = __ldg(reinterpret_cast<const uint4*>(yptr[i] + kk));
+          } else {
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              if (kk + e < K) {
+                d[e] = __ldg(ptr[i] + kk + e);
+                if (has_y) y[e] = __ldg(yptr[i] + kk + e);
+              }
+            }
+          }
+          if (has_y) {
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+              d[e] = from_f<T>(act_backward<T>(P.dact, to_f(y[e]), to_f(d[e])));
+          }
         }
+        r[i] = du;
       }
-    }
-  }
-  if (has_y) {
-#pragma unroll
-    for (int e = 0; e < E; ++e) d[e] = from_f<T>(act_backward<T>(op.dact, to_f(y[e]), to_f(d[e])));
-  }
-  return du;
-}
-
-// Which (row, 16-byte chunk) of a ROWS x 128 B tile thread t handles in its i-th slot.
-//   k_contig: 8 consecutive threads read the 128 contiguous bytes of one row.
-//   else    : consecutive threads read consecutive rows (contiguous in memory) of one K column.
-template <int ROWS>
-__device__ __forceinline__ void slot_of(int k_contig, int i, int t, int& row, int& chunk) {
-  if (k_contig) {
-    row = i * 16 + (t >> 3);
-    chunk = t & 7;
-  } else {
-    const int L = i * kProducerThreads + t;
-    row = L % ROWS;
-    chunk = L / ROWS;
-  }
-}
-
-template <typename T, int ROWS>
-__device__ __forceinline__ void load_tile(const Operand& op, long long boff, int o0, int O,
-                                          long long k0, long long K, int t,
-                                          uint4 (&r)[ROWS / 16]) {
-#pragma unroll
-  for (int i = 0; i < ROWS / 16; ++i) {
-    int row, c;
-    slot_of<ROWS>(op.k_contig, i, t, row, c);
-    r[i] = fetch_chunk<T>(op, boff, o0 + row, O, k0 + c * TT<T>::EPC, K);
-  }
-}
-
-template <typename T, int ROWS>
-__device__ __forceinline__ void store_tile(int k_contig, int t, const uint4 (&r)[ROWS / 16],
-                                           uint8_t* plane0, uint8_t* plane1, float* rowsum) {
-#pragma unroll
-  for (int i = 0; i < ROWS / 16; ++i) {
-    int row, c;
-    slot_of<ROWS>(k_contig, i, t, row, c);
-    const uint32_t off = sw128_offset(row, c);
-    if (TT<T>::PLANES == 2) {
-      const float* x = reinterpret_cast<const float*>(&r[i]);
-      uint4 hu, lu;
-      float* h = reinterpret_cast<float*>(&hu);
-      float* l = reinterpret_cast<float*>(&lu);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float hi = tf32_rna(x[e]);
-        // inf/nan stay in the hi plane only: inf - inf would poison the lo plane.
-        const float lo = (fabsf(hi) <= 3.4028234e38f) ? tf32_rna(x[e] - hi) : 0.f;
-        h[e] = hi;
-        l[e] = lo;
-        if (rowsum) *rowsum += x[e];
-      }
-      *reinterpret_cast<uint4*>(plane0 + off) = hu;
-      *reinterpret_cast<uint4*>(plane1 + off) = lu;
     } else {
-      if (rowsum) {
-        const __half* x = reinterpret_cast<const __half*>(&r[i]);
+      const bool row_ok = o < O;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) *rowsum += __half2float(x[e]);
+      for (int i = 0; i < NS; ++i) {
+        const int chunk = (i * kGroupThreads + t) / ROWS;
+        const long long kk = k0 + chunk * E;
+        uint4 du = make_uint4(0, 0, 0, 0);
+        T* d = reinterpret_cast<T*>(&du);
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            if (kk + e < K) {
+              float yv = 0.f;
+              if (P.cols != nullptr) {
+                d[e] = __ldg(static_cast<const T*>(P.cols[kk + e]) + o);
+                if (has_y) yv = to_f(__ldg(static_cast<const T*>(P.ycols[kk + e]) + o));
+              } else {
+                d[e] = __ldg(rowp + (kk + e) * P.ld);
+                if (has_y) yv = to_f(__ldg(yrowp + (kk + e) * P.ld));
+              }
+              if (has_y) d[e] = from_f<T>(act_backward<T>(P.dact, yv, to_f(d[e])));
+            }
+          }
+        }
+        r[i] = du;
       }
-      *reinterpret_cast<uint4*>(plane0 + off) = r[i];
     }
   }
-}
+
+  // Writes the slots into the swizzled K-major plane(s); optionally adds the values to *rowsum
+  // (meaningful for outer-contiguous operands, where the thread owns one row).
+  __device__ __forceinline__ void store(const uint4 (&r)[NS], uint8_t* plane0, uint8_t* plane1,
+                                        float* rowsum) const {
+    const int kc = op->k_contig;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+      const int srow = kc ? i * 16 + (t >> 3) : row;
+      const int chunk = kc ? (t & 7) : (i * kGroupThreads + t) / ROWS;
+      const uint32_t off = sw128_offset(srow, chunk);
+      if (TT<T>::PLANES == 2) {
+        const float* x = reinterpret_cast<const float*>(&r[i]);
+        float4 h, l;
+        split_tf32(x[0], h.x, l.x);
+        split_tf32(x[1], h.y, l.y);
+        split_tf32(x[2], h.z, l.z);
+        split_tf32(x[3], h.w, l.w);
+        if (rowsum) *rowsum += (x[0] + x[1]) + (x[2] + x[3]);
+        *reinterpret_cast<float4*>(plane0 + off) = h;
+        *reinterpret_cast<float4*>(plane1 + off) = l;
+      } else {
+        if (rowsum) {
+          const __half* x = reinterpret_cast<const __half*>(&r[i]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) *rowsum += __half2float(x[e]);
+        }
+        *reinterpret_cast<uint4*>(plane0 + off) = r[i];
+      }
+    }
+  }
+};
 
 template <typename T, int BN>
 struct StageLayout {
@@ -208,15 +247,58 @@ struct StageLayout {
   static constexpr int BYTES = A_BYTES + B_BYTES;
 };
 
+template <typename T, int ROWS>
+__device__ __forceinline__ bool produce(const Problem& P, bool is_a, int o0, int O, long long batch,
+                                        int tg, int nkb, int stages, int stage_bytes,
+                                        uint8_t* tiles_ptr, int plane_off, int plane_bytes,
+                                        uint64_t* full_bar, uint64_t* empty_bar, float* rowsum,
+                                        int* status) {
+  constexpr int E = TT<T>::EPC;
+  constexpr int BK = 8 * E;
+  TileLoader<T, ROWS> ld;
+  uint4 r[ROWS / 16];
+  int pair = 0;
+  long long k0 = 0;
+  const Operand* op = is_a ? &P.a[0] : &P.b[0];
+  ld.init(*op, batch * op->batch_stride, o0, O, tg);
+  if (nkb > 0) ld.load(0, P.k[0], O, r);
+  int s = 0;
+  uint32_t ph = 0;
+  for (int it = 0; it < nkb; ++it) {
+    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) return false;
+    uint8_t* st = tiles_ptr + s * stage_bytes + plane_off;
+    ld.store(r, st, st + plane_bytes, (rowsum != nullptr && pair == 0) ? rowsum : nullptr);
+    fence_proxy_async_smem();
+    mbar_arrive(smem_u32(&full_bar[s]));
+    if (++s == stages) {
+      s = 0;
+      ph ^= 1u;
+    }
+    k0 += BK;
+    if (k0 >= P.k[pair]) {
+      ++pair;
+      k0 = 0;
+      if (it + 1 < nkb) {
+        op = is_a ? &P.a[pair] : &P.b[pair];
+        ld.init(*op, batch * op->batch_stride, o0, O, tg);
+      }
+    }
+    if (it + 1 < nkb) ld.load(k0, P.k[pair], O, r);
+  }
+  return true;
+}
+
 template <typename T, int BN, int STAGES, bool GROUPED>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(kStagedThreads, 1)
 gemm_staged_kernel(const __grid_constant__ Problem p0, const Problem* __restrict__ probs,
                    int nprobs, int* __restrict__ status) {
   using L = StageLayout<T, BN>;
   constexpr int E = TT<T>::EPC;
   constexpr int BK = 8 * E;  // elements of K per k-block
-  constexpr uint32_t NCOLS = BN < 32 ? 32 : BN;
+  constexpr int ACCS = TT<T>::ACCS;
+  constexpr uint32_t NCOLS = (ACCS * BN) < 32 ? 32 : (ACCS * BN);
   constexpr uint32_t IDESC = make_idesc(TT<T>::FMT, 0, 0, kBM, BN);
+  constexpr uint32_t CROSS_COL = 3 * BN;  // fp32 only: accumulator of the lo*hi + hi*lo terms
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -257,10 +339,10 @@ gemm_staged_kernel(const __grid_constant__ Problem p0, const Problem* __restrict
   uint8_t* tiles_ptr = smem_raw + (tiles_base - smem_u32(smem_raw));
 
   // ---- setup ----
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       for (int s = 0; s < STAGES; ++s) {
-        mbar_init(smem_u32(&full_bar[s]), kProducerThreads);
+        mbar_init(smem_u32(&full_bar[s]), 2 * kGroupThreads);
         mbar_init(smem_u32(&empty_bar[s]), 1);
       }
       mbar_init(smem_u32(&accum_bar), 1);
@@ -275,51 +357,21 @@ gemm_staged_kernel(const __grid_constant__ Problem p0, const Problem* __restrict
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  if (warp < 4) {
+  if (warp < 8) {
     // ================= producers =================
-    bool ok = true;
+    const bool is_a = warp < 4;
+    const int tg = tid & (kGroupThreads - 1);
     float rs = 0.f;
-    const bool want_rowsum = P.rowsum != nullptr && n_tile == 0;
-    uint4 ra[kBM / 16];
-    uint4 rb[BN / 16];
-    int pair = 0;
-    long long k0 = 0;
-    if (nkb > 0) {
-      load_tile<T, kBM>(P.a[0], batch * P.a[0].batch_stride, m0, P.M, 0, P.k[0], tid, ra);
-      load_tile<T, BN>(P.b[0], batch * P.b[0].batch_stride, n0, P.N, 0, P.k[0], tid, rb);
-    }
-    int s = 0;
-    uint32_t ph = 0;
-    for (int it = 0; it < nkb; ++it) {
-      if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) {
-        ok = false;
-        break;
-      }
-      uint8_t* st = tiles_ptr + s * L::BYTES;
-      store_tile<T, kBM>(P.a[pair].k_contig, tid, ra, st, st + L::A_PLANE,
-                         (want_rowsum && pair == 0) ? &rs : nullptr);
-      store_tile<T, BN>(P.b[pair].k_contig, tid, rb, st + L::A_BYTES,
-                        st + L::A_BYTES + L::B_PLANE, nullptr);
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&full_bar[s]));
-      if (++s == STAGES) {
-        s = 0;
-        ph ^= 1u;
-      }
-      k0 += BK;
-      if (k0 >= P.k[pair]) {
-        ++pair;
-        k0 = 0;
-      }
-      if (it + 1 < nkb) {
-        load_tile<T, kBM>(P.a[pair], batch * P.a[pair].batch_stride, m0, P.M, k0, P.k[pair], tid,
-                          ra);
-        load_tile<T, BN>(P.b[pair], batch * P.b[pair].batch_stride, n0, P.N, k0, P.k[pair], tid,
-                         rb);
-      }
-    }
+    const bool want_rowsum = is_a && P.rowsum != nullptr && n_tile == 0;
+    bool ok;
+    if (is_a)
+      ok = produce<T, kBM>(P, true, m0, P.M, batch, tg, nkb, STAGES, L::BYTES, tiles_ptr, 0,
+                           L::A_PLANE, full_bar, empty_bar, want_rowsum ? &rs : nullptr, status);
+    else
+      ok = produce<T, BN>(P, false, n0, P.N, batch, tg, nkb, STAGES, L::BYTES, tiles_ptr,
+                          L::A_BYTES, L::B_PLANE, full_bar, empty_bar, nullptr, status);
     if (want_rowsum && ok) {
-      const int row = m0 + tid;
+      const int row = m0 + tg;
       if (row < P.M) {
         if (sizeof(T) == 4)
           atomicAdd(static_cast<float*>(P.rowsum) + row, rs);
@@ -329,26 +381,64 @@ gemm_staged_kernel(const __grid_constant__ Problem p0, const Problem* __restrict
     }
 
     // ================= epilogue =================
-    if (ok && mbar_wait(smem_u32(&accum_bar), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
+    constexpr int COLS_PER_HALF = BN >= 64 ? BN / 2 : BN;
+    const int half = warp >> 2;
+    const bool has_cols = BN >= 64 || half == 0;
+    if (ok && has_cols && mbar_wait(smem_u32(&accum_bar), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
       tc_fence_after();
-      const int row = m0 + warp * 32 + lane;
+      const int q = warp & 3;
+      const int row = m0 + q * 32 + lane;
       const bool row_ok = row < P.M;
       float bias = 0.f;
       if (P.bias != nullptr && row_ok) bias = to_f(static_cast<const T*>(P.bias)[row]);
       T* cbase = static_cast<T*>(P.c) + batch * P.c_batch_stride;
+      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
+      const int cbeg = BN >= 64 ? half * COLS_PER_HALF : 0;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
-        tmem_ld_wait();
+      for (int c0 = cbeg; c0 < cbeg + COLS_PER_HALF; c0 += 32) {
+        float acc[32];
+        // previous C first, so the loads are in flight while TMEM is read
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int col = n0 + c0 + j;
-          if (row_ok && col < P.N) {
-            T* cp = (P.ccols ? static_cast<T*>(P.ccols[col]) : cbase + static_cast<long long>(col) * P.ldc) + row;
-            float x = (nkb > 0 ? __uint_as_float(v[j]) : 0.f) + bias;
-            if (P.accumulate) x += to_f(*cp);
-            *cp = from_f<T>(act_forward<T>(P.act, x));
+          float v = bias;
+          if (P.accumulate && row_ok && col < P.N) {
+            const T* src = (P.ccols ? static_cast<const T*>(P.ccols[col])
+                                    : cbase + static_cast<long long>(col) * P.ldc) + row;
+            v += to_f(*src);
+          }
+          acc[j] = v;
+        }
+        uint32_t v[32];
+        if (nkb > 0) {
+          if (ACCS == 4) {
+            tmem_ld32(tbase + CROSS_COL + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+#pragma unroll 1
+            for (int a = 0; a < 3 && a < nkb; ++a) {
+              tmem_ld32(tbase + a * BN + c0, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+            }
+          } else {
+            tmem_ld32(tbase + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+          }
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = n0 + c0 + j;
+            if (col < P.N) {
+              T* dst = (P.ccols ? static_cast<T*>(P.ccols[col])
+                                : cbase + static_cast<long long>(col) * P.ldc) + row;
+              *dst = from_f<T>(act_forward<T>(P.act, acc[j]));
+            }
           }
         }
       }
@@ -365,19 +455,18 @@ gemm_staged_kernel(const __grid_constant__ Problem p0, const Problem* __restrict
         const uint32_t b0 = a0 + L::A_BYTES;
 #pragma unroll
         for (int ks = 0; ks < kKSteps; ++ks) {
-          const uint32_t first = (it > 0 || ks > 0) ? 1u : 0u;
           if (TT<T>::PLANES == 2) {
             const uint64_t a_hi = make_smem_desc(a0 + ks * 32, 16, 1024);
             const uint64_t a_lo = make_smem_desc(a0 + L::A_PLANE + ks * 32, 16, 1024);
             const uint64_t b_hi = make_smem_desc(b0 + ks * 32, 16, 1024);
             const uint64_t b_lo = make_smem_desc(b0 + L::B_PLANE + ks * 32, 16, 1024);
-            mma_tf32(tmem, a_lo, b_hi, IDESC, first);
-            mma_tf32(tmem, a_hi, b_lo, IDESC, 1u);
-            mma_tf32(tmem, a_hi, b_hi, IDESC, 1u);
+            mma_tf32(tmem + CROSS_COL, a_lo, b_hi, IDESC, (it > 0 || ks > 0) ? 1u : 0u);
+            mma_tf32(tmem + CROSS_COL, a_hi, b_lo, IDESC, 1u);
+            mma_tf32(tmem + (it % 3) * BN, a_hi, b_hi, IDESC, (it >= 3 || ks > 0) ? 1u : 0u);
           } else {
             const uint64_t a = make_smem_desc(a0 + ks * 32, 16, 1024);
             const uint64_t b = make_smem_desc(b0 + ks * 32, 16, 1024);
-            mma_f16(tmem, a, b, IDESC, first);
+            mma_f16(tmem, a, b, IDESC, (it > 0 || ks > 0) ? 1u : 0u);
           }
         }
         tc_commit(smem_u32(&empty_bar[s]));
@@ -394,7 +483,7 @@ gemm_staged_kernel(const __grid_constant__ Problem p0, const Problem* __restrict
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, NCOLS);
   }
@@ -419,7 +508,7 @@ static cudaError_t launch_one(const Problem& p, const Problem* dprobs, int nprob
   const int smem = STAGES * StageLayout<T, BN>::BYTES + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  kern<<<total_tiles, 160, smem, stream>>>(p, dprobs, nprobs, status);
+  kern<<<total_tiles, kStagedThreads, smem, stream>>>(p, dprobs, nprobs, status);
   return cudaGetLastError();
 }
 
