@@ -44,7 +44,8 @@ class _Group(C.Structure):
     _fields_ = [("w", C.c_void_p), ("ldw", C.c_int64), ("m", C.c_int64), ("k", C.c_int64),
                 ("bias", C.c_void_p), ("ncols", C.c_int64), ("x_cols", C.POINTER(C.c_void_p)),
                 ("y_cols", C.POINTER(C.c_void_p)), ("dx_cols", C.POINTER(C.c_void_p)),
-                ("dw", C.c_void_p), ("lddw", C.c_int64), ("dbias", C.c_void_p)]
+                ("dw", C.c_void_p), ("lddw", C.c_int64), ("dbias", C.c_void_p),
+                ("accumulate", C.c_int)]
 
 
 def lib_path() -> str:
@@ -219,6 +220,7 @@ class Group:
     bias: Optional[torch.Tensor] = None
     dw: Optional[torch.Tensor] = None
     dbias: Optional[torch.Tensor] = None
+    accumulate: bool = False              # forward: y += W x (+ bias)
 
 
 def grouped_static(mode: int, groups: Sequence[Group]) -> None:
@@ -249,7 +251,8 @@ def _grouped_call(fn, mode: int, groups: Sequence[Group]) -> None:
         arr[i] = _Group(g.w.data_ptr(), _ld(g.w), m, k, _ptr(g.bias), ncols,
                         table(g.x_cols) if len(g.x_cols) else None, table(g.y_cols),
                         table(g.dx_cols) if len(g.dx_cols) else None, _ptr(g.dw),
-                        _ld(g.dw) if g.dw is not None else 0, _ptr(g.dbias))
+                        _ld(g.dw) if g.dw is not None else 0, _ptr(g.dbias),
+                        int(g.accumulate))
     w0 = groups[0].w
     _check(fn(_dev(w0), _stream(w0), _dtype_of(w0), mode, len(groups), arr))
 

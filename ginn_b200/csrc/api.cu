@@ -399,7 +399,7 @@ int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroup
       p.M = (int)q.m; p.N = (int)q.ncols;
       p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
       p.bias = q.bias;
-      p.accumulate = 0;
+      p.accumulate = q.accumulate ? 1 : 0;
     } else if (mode == GINN_B200_GROUPED_DX) {
       for (int64_t j = 0; j < q.ncols; ++j) {
         h_t0[j] = q.y_cols[j];
@@ -539,6 +539,7 @@ int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int
       p.M = (int)q.m; p.N = (int)q.ncols;
       p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
       p.bias = q.bias;
+      p.accumulate = q.accumulate ? 1 : 0;
     } else if (mode == GINN_B200_GROUPED_DX) {
       for (int64_t j = 0; j < q.ncols; ++j) {
         t0[j] = q.y_cols[j];

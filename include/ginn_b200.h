@@ -112,10 +112,11 @@ typedef struct {
   void* dw;                  /* dW mode: m x k, accumulated (leading dimension lddw)        */
   int64_t lddw;
   void* dbias;               /* dW mode: m, accumulated (may be NULL)                       */
+  int accumulate;            /* forward: y_j += W * x_j (+ bias) instead of y_j = ...       */
 } ginn_b200_group;
 
 typedef enum {
-  GINN_B200_GROUPED_FORWARD = 0, /* y_j  = W * x_j + bias            */
+  GINN_B200_GROUPED_FORWARD = 0, /* y_j  = W * x_j + bias  (+= when the group says accumulate) */
   GINN_B200_GROUPED_DX = 1,      /* dx_j += W^T * dy_j               */
   GINN_B200_GROUPED_DW = 2       /* dW  += sum_j dy_j x_j^T, dbias += sum_j dy_j */
 } ginn_b200_grouped_mode;
