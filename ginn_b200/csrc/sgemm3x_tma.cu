@@ -5,11 +5,11 @@
 //
 // Pipeline inside a CTA (one 128 x 128 tile of C):
 //   warp 0     TMA producer: raw fp32 slices (128 rows x 32 k) of A, B (and Y) into a ring.
-//   warps 2-5  transform A, warps 6-9 transform B: raw slice -> registers -> (derivative) ->
+//   warps 2-9  transform A, warps 10-17 transform B: raw slice -> registers -> (derivative) ->
 //              hi = rna_tf32(x), lo = x - hi -> two K-major, 128-byte-swizzled planes.  Operands
 //              whose outer index is contiguous in memory are transposed here, for free.
 //   warp 1     MMA issuer: per 8-wide k-step  cross += lo*hi, cross += hi*lo, main[j] += hi*hi.
-//   warps 2-9  epilogue: sum the accumulators, bias / previous C / activation, store.
+//   warps 2-17 epilogue: sum the accumulators, bias / previous C / activation, store.
 //
 // Accuracy: the tensor core truncates when it adds into its fp32 accumulator, which biases a
 // long accumulation chain (measured: relative error grows linearly with K, about 7e-9 per unit
@@ -31,7 +31,7 @@ constexpr int PLANE = 16384;              // one 128-row K-major plane
 constexpr int PLANE_STAGE = 4 * PLANE;    // A hi, A lo, B hi, B lo
 constexpr int PLANE_STAGES = 2;
 constexpr int RAW_BYTES_TOTAL = 96 * 1024;  // 3 stages of (A,B) or 2 stages of (A,B,Y)
-constexpr int XFORM_THREADS = 256;
+constexpr int XFORM_THREADS = 512;   // 8 warps per operand
 constexpr int NTHREADS = 64 + XFORM_THREADS;
 constexpr uint32_t CROSS_COL = 384;
 
@@ -79,6 +79,66 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
   hi = __uint_as_float(u);
   lo = ((u & 0x7f800000u) == 0x7f800000u) ? 0.f : x - hi;
+}
+
+// Transform of a k-contiguous raw slice: it already is K-major and swizzled (TMA box 32 k x 128
+// outer with the 128-byte swizzle), so hi and lo go to the same offsets of their planes.
+// 256 threads, 4 pieces of 16 bytes each.
+template <bool HAS_Y>
+__device__ __forceinline__ void transform_kc(const uint8_t* src, const uint8_t* ysrc,
+                                             uint8_t* dst_hi, uint8_t* dst_lo, int t, int dact) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int off = (t + 256 * i) * 16;
+    float4 x = *reinterpret_cast<const float4*>(src + off);
+    if (HAS_Y) {
+      const float4 y = *reinterpret_cast<const float4*>(ysrc + off);
+      x.x = act_backward(dact, y.x, x.x);
+      x.y = act_backward(dact, y.y, x.y);
+      x.z = act_backward(dact, y.z, x.z);
+      x.w = act_backward(dact, y.w, x.w);
+    }
+    float4 h, l;
+    split_tf32(x.x, h.x, l.x);
+    split_tf32(x.y, h.y, l.y);
+    split_tf32(x.z, h.z, l.z);
+    split_tf32(x.w, h.w, l.w);
+    *reinterpret_cast<float4*>(dst_hi + off) = h;
+    *reinterpret_cast<float4*>(dst_lo + off) = l;
+  }
+}
+
+// Transform of an outer-contiguous raw slice [atom][k][32 outer] (four unswizzled TMA boxes):
+// thread t owns outer index t % 128 and half of the 32 k values, reads them with
+// conflict-free scalar loads (lanes = consecutive outer indices) and writes the transposed,
+// swizzled K-major chunks.  Returns the sum of the values it handled (bias gradient).
+template <bool HAS_Y>
+__device__ __forceinline__ float transform_oc(const uint8_t* src, const uint8_t* ysrc,
+                                              uint8_t* dst_hi, uint8_t* dst_lo, int t, int dact) {
+  const int o = t & 127;
+  const int kbase = (t >> 7) * 16;
+  const float* col = reinterpret_cast<const float*>(src + (o >> 5) * 4096) + (o & 31);
+  const float* ycol = reinterpret_cast<const float*>(ysrc + (o >> 5) * 4096) + (o & 31);
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      x[e] = col[(kbase + 4 * c + e) * 32];
+      if (HAS_Y) x[e] = act_backward(dact, ycol[(kbase + 4 * c + e) * 32], x[e]);
+    }
+    sum += (x[0] + x[1]) + (x[2] + x[3]);
+    float4 h, l;
+    split_tf32(x[0], h.x, l.x);
+    split_tf32(x[1], h.y, l.y);
+    split_tf32(x[2], h.z, l.z);
+    split_tf32(x[3], h.w, l.w);
+    const uint32_t off = sw128_offset(o, (kbase >> 2) + c);
+    *reinterpret_cast<float4*>(dst_hi + off) = h;
+    *reinterpret_cast<float4*>(dst_lo + off) = l;
+  }
+  return sum;
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -224,10 +284,10 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     }
     __syncwarp();
   } else {
-    // ===================== transform (warps 2-5: A, warps 6-9: B) =====================
+    // ===================== transform (warps 2-9: A, warps 10-17: B) =====================
     const int xt = threadIdx.x - 64;
-    const int grp = xt >> 7;  // 0 = A operand, 1 = B operand
-    const int t = xt & 127;
+    const int grp = xt >> 8;  // 0 = A operand, 1 = B operand
+    const int t = xt & 255;
     const bool want_rowsum = grp == 0 && p.rowsum != nullptr && n_tile == 0;
     float rs = 0.f;
     bool ok = true;
@@ -249,48 +309,14 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       const int kc = grp ? p.b_kc[pair] : p.a_kc[pair];
       const bool has_y = p.dop == grp + 1;
       if (kc) {
-        // Raw slice already is K-major and swizzled: transform in place, piece by piece.
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int off = (t + 128 * i) * 16;
-          float4 x = *reinterpret_cast<const float4*>(src + off);
-          if (has_y) {
-            const float4 y = *reinterpret_cast<const float4*>(ysrc + off);
-            x.x = act_backward(p.dact, y.x, x.x);
-            x.y = act_backward(p.dact, y.y, x.y);
-            x.z = act_backward(p.dact, y.z, x.z);
-            x.w = act_backward(p.dact, y.w, x.w);
-          }
-          float4 h, l;
-          split_tf32(x.x, h.x, l.x);
-          split_tf32(x.y, h.y, l.y);
-          split_tf32(x.z, h.z, l.z);
-          split_tf32(x.w, h.w, l.w);
-          *reinterpret_cast<float4*>(dst_hi + off) = h;
-          *reinterpret_cast<float4*>(dst_lo + off) = l;
-        }
+        if (has_y)
+          transform_kc<true>(src, ysrc, dst_hi, dst_lo, t, p.dact);
+        else
+          transform_kc<false>(src, ysrc, dst_hi, dst_lo, t, p.dact);
       } else {
-        // Raw slice is [atom][k][32 outer]: thread t owns outer index t and transposes its row.
-        const float* col = reinterpret_cast<const float*>(src + (t >> 5) * 4096) + (t & 31);
-        const float* ycol = reinterpret_cast<const float*>(ysrc + (t >> 5) * 4096) + (t & 31);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float x[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            x[e] = col[(4 * c + e) * 32];
-            if (has_y) x[e] = act_backward(p.dact, ycol[(4 * c + e) * 32], x[e]);
-            if (want_rowsum && pair == 0) rs += x[e];
-          }
-          float4 h, l;
-          split_tf32(x[0], h.x, l.x);
-          split_tf32(x[1], h.y, l.y);
-          split_tf32(x[2], h.z, l.z);
-          split_tf32(x[3], h.w, l.w);
-          const uint32_t off = sw128_offset(t, c);
-          *reinterpret_cast<float4*>(dst_hi + off) = h;
-          *reinterpret_cast<float4*>(dst_lo + off) = l;
-        }
+        const float part = has_y ? transform_oc<true>(src, ysrc, dst_hi, dst_lo, t, p.dact)
+                                 : transform_oc<false>(src, ysrc, dst_hi, dst_lo, t, p.dact);
+        if (want_rowsum && pair == 0) rs += part;
       }
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&plane_full[ps_i]));
@@ -309,20 +335,21 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
         k0 = 0;
       }
     }
-    if (want_rowsum && ok && m0 + t < p.M) atomicAdd(p.rowsum + m0 + t, rs);
+    // two threads share a row (one per k half): both add their part
+    if (want_rowsum && ok && m0 + (t & 127) < p.M) atomicAdd(p.rowsum + m0 + (t & 127), rs);
 
-    // ===================== epilogue (all eight warps; 64 columns each) =====================
+    // ===================== epilogue (all sixteen warps; 32 columns each) =====================
     if (ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
       tc_fence_after();
       const int q = warp & 3;
-      const int half = (warp - 2) >> 2;
+      const int cgrp = (warp - 2) >> 2;  // 0..3
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const float bias = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
       float* crow = p.C + static_cast<long long>(batch) * p.strideC + row;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+      {
+        const int c0 = cgrp * 32;
         float acc[32];
         const bool load_c = p.accumulate && row_ok;
 #pragma unroll
