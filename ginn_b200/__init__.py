@@ -6,7 +6,8 @@ binding used by the tests and the benchmark; it never computes anything itself a
 the CUDA library is missing.
 """
 from .binding import (  # noqa: F401
-    ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH, F16, F32, GinnB200Error, Group, Pair, PairGrad,
+    ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH, F16, F32, GinnB200Error, Group, GroupedCall, Pair,
+    PairGrad,
     affine_backward, affine_forward, device_status, gemm, gemm_batched, grouped, grouped_static, launch_count,
     lib, lib_path, set_option, version,
 )

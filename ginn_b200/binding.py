@@ -234,9 +234,8 @@ def grouped(mode: int, groups: Sequence[Group]) -> None:
     _grouped_call(lib().ginn_b200_grouped, mode, groups)
 
 
-def _grouped_call(fn, mode: int, groups: Sequence[Group]) -> None:
-    if not groups:
-        return
+def _build_groups(groups: Sequence[Group]):
+    """ctypes image of a level: the group array plus the pointer tables it refers to."""
     arr = (_Group * len(groups))()
     keep = []
 
@@ -253,8 +252,31 @@ def _grouped_call(fn, mode: int, groups: Sequence[Group]) -> None:
                         table(g.dx_cols) if len(g.dx_cols) else None, _ptr(g.dw),
                         _ld(g.dw) if g.dw is not None else 0, _ptr(g.dbias),
                         int(g.accumulate))
+    return arr, keep
+
+
+def _grouped_call(fn, mode: int, groups: Sequence[Group]) -> None:
+    if not groups:
+        return
+    arr, _keep = _build_groups(groups)
     w0 = groups[0].w
     _check(fn(_dev(w0), _stream(w0), _dtype_of(w0), mode, len(groups), arr))
+
+
+class GroupedCall:
+    """A level whose tables are built once and launched many times (the tensors must stay
+    alive and in place, as the nodes of a re-evaluated ginn graph do)."""
+
+    def __init__(self, mode: int, groups: Sequence[Group], static: bool = False):
+        self.mode, self.n = mode, len(groups)
+        self.groups = list(groups)
+        self.arr, self._keep = _build_groups(groups)
+        self.fn = lib().ginn_b200_grouped_static if static else lib().ginn_b200_grouped
+        w0 = groups[0].w
+        self.dev, self.dtype, self.w0 = _dev(w0), _dtype_of(w0), w0
+
+    def __call__(self):
+        _check(self.fn(self.dev, _stream(self.w0), self.dtype, self.mode, self.n, self.arr))
 
 
 def device_status(device: int = 0, reset: bool = True) -> int:

@@ -113,6 +113,8 @@ int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
     CU_TRY(gb::launch_small(dtype, p, stream));
   } else if (dtype == GINN_B200_F32 && force != PATH_STAGED && gb::sgemm3x_supported(p)) {
     CU_TRY(gb::launch_sgemm3x(p, stream, ctx->d_status));
+  } else if (dtype == GINN_B200_F32 && force != PATH_STAGED && gb::sgemm3x_gather_supported(p)) {
+    CU_TRY(gb::launch_sgemm3x_gather(p, stream, ctx->d_status));
   } else {
     const int bn = gb::staged_pick_bn(dtype, p.M, p.N, p.batches, ctx->num_sms);
     CU_TRY(gb::launch_staged(dtype, p, bn, stream, ctx->d_status));
@@ -363,9 +365,14 @@ int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroup
   unsigned char *h, *d;
   if (int s = stage_alloc(ctx, desc_bytes + table_bytes, &h, &d)) return s;
 
+  // fp32 levels run on the gather front end of the 3xTF32 kernel (128 x 128 tiles); fp16 levels
+  // on the staged kernel.
+  const bool use_gather = dtype == GINN_B200_F32 && g_force_path.load() != PATH_STAGED;
   int bn = 128;
-  if (max_n <= 32) bn = 32;
-  else if (max_n <= 64 || sum_tiles128 < ctx->num_sms) bn = 64;
+  if (!use_gather) {
+    if (max_n <= 32) bn = 32;
+    else if (max_n <= 64 || sum_tiles128 < ctx->num_sms) bn = 64;
+  }
 
   Problem* hp = reinterpret_cast<Problem*>(h);
   size_t off = desc_bytes;
@@ -436,8 +443,12 @@ int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroup
     ++np;
   }
   CU_TRY(cudaMemcpyAsync(d, h, off, cudaMemcpyHostToDevice, stream));
-  CU_TRY(gb::launch_staged_grouped(dtype, reinterpret_cast<const Problem*>(d), np, tile, bn, stream,
-                                   ctx->d_status));
+  if (use_gather)
+    CU_TRY(gb::launch_sgemm3x_gather_grouped(reinterpret_cast<const Problem*>(d), np, tile, stream,
+                                             ctx->d_status));
+  else
+    CU_TRY(gb::launch_staged_grouped(dtype, reinterpret_cast<const Problem*>(d), np, tile, bn,
+                                     stream, ctx->d_status));
   g_launches.fetch_add(1);
   return GINN_B200_OK;
 }

@@ -49,6 +49,12 @@ bool tmap_encoder_available();
 bool sgemm3x_supported(const Problem& p);
 cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status);
 
+// Same pipeline with a cp.async gather front end: any alignment, column tables, grouped launches.
+bool sgemm3x_gather_supported(const Problem& p);
+cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status);
+cudaError_t launch_sgemm3x_gather_grouped(const Problem* dprobs, int nprobs, int total_tiles,
+                                          cudaStream_t stream, int* status);
+
 // --- CUDA-core kernels for degenerate shapes and elementwise helpers (small.cu) ---
 // One warp per output element; used for tiny m*n (batched dot products) and k == 0.
 cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream);

@@ -390,6 +390,341 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   }
 }
 
+
+// ===========================================================================================
+// Gather front end: the same transform / MMA / epilogue pipeline, but the raw slices are
+// brought in by the transform threads themselves with cp.async (4- or 16-byte pieces, zero
+// filled outside the matrix) instead of TMA.  It takes what a tensor map cannot describe:
+// unaligned bases and leading dimensions, and operands whose columns live at unrelated
+// addresses (the per-node tensors of an autobatch level), and it reads its problem either from
+// the kernel parameters or, for a grouped launch, from a device array of descriptors.
+// ===========================================================================================
+constexpr int GNTHREADS = 32 + XFORM_THREADS;  // warp 0: MMA issuer; warps 1-8: A; warps 9-16: B
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+// Arrive on `bar` once all cp.async issued so far by this thread have landed (the barrier's
+// expected count already includes this arrival).
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 bytes (4 floats) from src to dst, of which `valid` (0..4) elements exist; the rest is zero.
+__device__ __forceinline__ void fill_piece(uint32_t dst, const float* src, int valid,
+                                           const void* safe) {
+  if (valid <= 0) {
+    cp_async16(dst, safe, 0);
+  } else if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+    cp_async16(dst, src, valid * 4);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      cp_async4(dst + 4 * e, e < valid ? static_cast<const void*>(src + e) : safe, e < valid ? 4 : 0);
+  }
+}
+
+// Fills one raw slice (128 outer x 32 k) of operand `op` for k-block starting at k0, in the same
+// two layouts the TMA front end produces.  `y` selects the Y matrix of a derivative operand.
+__device__ __forceinline__ void fill_raw(const Operand& op, bool y, long long boff, int o0, int O,
+                                         long long k0, long long K, uint32_t dst_tile, int t) {
+  const float* base = static_cast<const float*>(y ? op.ybase : op.base);
+  const void* const* cols = y ? op.ycols : op.cols;
+  const void* safe = cols ? static_cast<const void*>(cols) : static_cast<const void*>(base);
+  if (op.k_contig) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int id = t + 256 * i;
+      const int row = id >> 3, c = id & 7;
+      const int o = o0 + row;
+      const long long kk = k0 + 4 * c;
+      int valid = 0;
+      const float* src = nullptr;
+      if (o < O && kk < K) {
+        const float* col = cols ? static_cast<const float*>(cols[o]) : base + boff + static_cast<long long>(o) * op.ld;
+        src = col + kk;
+        valid = K - kk >= 4 ? 4 : static_cast<int>(K - kk);
+      }
+      fill_piece(dst_tile + sw128_offset(row, c), src, valid, safe);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int id = t + 256 * i;
+      const int kk = id >> 5, oc = id & 31;
+      const int o = o0 + 4 * oc;
+      int valid = 0;
+      const float* src = nullptr;
+      if (k0 + kk < K && o < O) {
+        const float* col = cols ? static_cast<const float*>(cols[k0 + kk]) : base + boff + (k0 + kk) * op.ld;
+        src = col + o;
+        valid = O - o >= 4 ? 4 : O - o;
+      }
+      fill_piece(dst_tile + (oc >> 3) * 4096 + kk * 128 + (oc & 7) * 16, src, valid, safe);
+    }
+  }
+}
+
+template <bool GROUPED>
+__global__ void __launch_bounds__(GNTHREADS, 1)
+sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restrict__ probs,
+                      int nprobs, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t raw_full[2][3];   // [operand group][stage]: slice landed
+  __shared__ __align__(8) uint64_t raw_empty[2][3];  // [operand group][stage]: slice consumed
+  __shared__ __align__(8) uint64_t plane_full[PLANE_STAGES];
+  __shared__ __align__(8) uint64_t plane_empty[PLANE_STAGES];
+  __shared__ __align__(8) uint64_t acc_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ Problem sprob;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t planes_base = base;
+  const uint32_t raws_base = base + PLANE_STAGES * PLANE_STAGE;
+
+  int tile = blockIdx.x;
+  if (GROUPED) {
+    int g = 0;
+    for (int i = 0; i < nprobs; ++i)
+      if (tile >= probs[i].tile_start) g = i;
+    const int nwords = sizeof(Problem) / 4;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(probs + g);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(&sprob);
+    for (int i = threadIdx.x; i < nwords; i += blockDim.x) dst[i] = src[i];
+    __syncthreads();
+  }
+  const Problem& P = GROUPED ? sprob : p0;
+  tile -= P.tile_start;
+  const int m_tile = tile % P.tiles_m;
+  const int rest = tile / P.tiles_m;
+  const int n_tile = rest % P.tiles_n;
+  const long long batch = rest / P.tiles_n;
+  const int m0 = m_tile * SBM, n0 = n_tile * SBN;
+
+  int nkb = 0;
+  for (int i = 0; i < P.npairs; ++i) nkb += static_cast<int>((P.k[i] + SBK - 1) / SBK);
+  const int dop = P.a[0].dact != ACT_NONE ? 1 : (P.b[0].dact != ACT_NONE ? 2 : 0);
+  const int dact = dop == 1 ? P.a[0].dact : (dop == 2 ? P.b[0].dact : ACT_NONE);
+  const int raw_stages = dop ? 2 : 3;
+  const int raw_stage_bytes = dop ? 3 * RAW_TILE : 2 * RAW_TILE;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int g = 0; g < 2; ++g)
+        for (int s = 0; s < 3; ++s) {
+          mbar_init(smem_u32(&raw_full[g][s]), 256);
+          mbar_init(smem_u32(&raw_empty[g][s]), 256);
+        }
+      for (int s = 0; s < PLANE_STAGES; ++s) {
+        mbar_init(smem_u32(&plane_full[s]), XFORM_THREADS);
+        mbar_init(smem_u32(&plane_empty[s]), 1);
+      }
+      mbar_init(smem_u32(&acc_full), 1);
+      fence_mbar_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 0) {
+    // ===================== MMA issuer =====================
+    if (elect_one()) {
+      constexpr uint32_t IDESC = make_idesc(2, 0, 0, SBM, SBN);
+      int s = 0;
+      uint32_t ph = 0;
+      for (int it = 0; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&plane_full[s]), ph, status, DEV_TIMEOUT_FULL, it)) break;
+        tc_fence_after();
+        const uint32_t a_hi = planes_base + s * PLANE_STAGE;
+        const uint32_t a_lo = a_hi + PLANE;
+        const uint32_t b_hi = a_hi + 2 * PLANE;
+        const uint32_t b_lo = a_hi + 3 * PLANE;
+        const uint32_t d_main = tmem + (it % 3) * SBN;
+        const uint32_t d_cross = tmem + CROSS_COL;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t dah = make_smem_desc(a_hi + ks * 32, 16, 1024);
+          const uint64_t dal = make_smem_desc(a_lo + ks * 32, 16, 1024);
+          const uint64_t dbh = make_smem_desc(b_hi + ks * 32, 16, 1024);
+          const uint64_t dbl = make_smem_desc(b_lo + ks * 32, 16, 1024);
+          mma_tf32(d_cross, dal, dbh, IDESC, (it > 0 || ks > 0) ? 1u : 0u);
+          mma_tf32(d_cross, dah, dbl, IDESC, 1u);
+          mma_tf32(d_main, dah, dbh, IDESC, (it >= 3 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&plane_empty[s]));
+        if (++s == PLANE_STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+      tc_commit(smem_u32(&acc_full));
+    }
+    __syncwarp();
+  } else {
+    // ============ fill + transform (warps 1-8: A operand, warps 9-16: B operand) ============
+    const int xt = threadIdx.x - 32;
+    const int grp = xt >> 8;
+    const int t = xt & 255;
+    const int o0 = grp ? n0 : m0;
+    const int O = grp ? P.N : P.M;
+    const bool has_y = dop == grp + 1;
+    const bool want_rowsum = grp == 0 && P.rowsum != nullptr && n_tile == 0;
+    float rs = 0.f;
+    bool ok = true;
+
+    // k-block `j` of the whole contraction -> (pair, k0)
+    auto fill = [&](int j, int stage) -> bool {
+      // the (j / raw_stages)-th use of this stage: wait until its previous slice was consumed
+      const uint32_t use = static_cast<uint32_t>(j / raw_stages);
+      if (!mbar_wait(smem_u32(&raw_empty[grp][stage]), (use & 1u) ^ 1u, status, DEV_TIMEOUT_EMPTY,
+                     0x300 + j))
+        return false;
+      int pair = 0;
+      long long k0 = static_cast<long long>(j) * SBK;
+      while (pair + 1 < P.npairs && k0 >= ((P.k[pair] + SBK - 1) / SBK) * SBK) {
+        k0 -= ((P.k[pair] + SBK - 1) / SBK) * SBK;
+        ++pair;
+      }
+      const Operand& op = grp ? P.b[pair] : P.a[pair];
+      const uint32_t dst = raws_base + stage * raw_stage_bytes;
+      fill_raw(op, false, batch * op.batch_stride, o0, O, k0, P.k[pair], dst + grp * RAW_TILE, t);
+      if (has_y)
+        fill_raw(op, true, batch * op.batch_stride, o0, O, k0, P.k[pair], dst + 2 * RAW_TILE, t);
+      cp_async_arrive(smem_u32(&raw_full[grp][stage]));
+      return true;
+    };
+
+    for (int j = 0; j < raw_stages - 1 && j < nkb; ++j) ok = ok && fill(j, j);
+    int rs_i = 0, ps_i = 0;
+    uint32_t rph = 0, pph = 0;
+    int pair = 0;
+    long long k0 = 0;
+    for (int it = 0; it < nkb; ++it) {
+      const int ahead = it + raw_stages - 1;
+      if (ok && ahead < nkb) ok = fill(ahead, ahead % raw_stages);
+      if (!ok ||
+          !mbar_wait(smem_u32(&raw_full[grp][rs_i]), rph, status, DEV_TIMEOUT_FULL, 0x200 + it) ||
+          !mbar_wait(smem_u32(&plane_empty[ps_i]), pph ^ 1u, status, DEV_TIMEOUT_EMPTY,
+                     0x200 + it)) {
+        ok = false;
+        break;
+      }
+      const uint8_t* raw_stage = base_ptr + PLANE_STAGES * PLANE_STAGE + rs_i * raw_stage_bytes;
+      const uint8_t* src = raw_stage + grp * RAW_TILE;
+      const uint8_t* ysrc = raw_stage + 2 * RAW_TILE;
+      uint8_t* dst_hi = base_ptr + ps_i * PLANE_STAGE + grp * 2 * PLANE;
+      uint8_t* dst_lo = dst_hi + PLANE;
+      const int kc = grp ? P.b[pair].k_contig : P.a[pair].k_contig;
+      if (kc) {
+        if (has_y)
+          transform_kc<true>(src, ysrc, dst_hi, dst_lo, t, dact);
+        else
+          transform_kc<false>(src, ysrc, dst_hi, dst_lo, t, dact);
+      } else {
+        const float part = has_y ? transform_oc<true>(src, ysrc, dst_hi, dst_lo, t, dact)
+                                 : transform_oc<false>(src, ysrc, dst_hi, dst_lo, t, dact);
+        if (want_rowsum && pair == 0) rs += part;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&plane_full[ps_i]));
+      mbar_arrive(smem_u32(&raw_empty[grp][rs_i]));  // this thread is done reading the raw stage
+      if (++rs_i == raw_stages) {
+        rs_i = 0;
+        rph ^= 1u;
+      }
+      if (++ps_i == PLANE_STAGES) {
+        ps_i = 0;
+        pph ^= 1u;
+      }
+      k0 += SBK;
+      if (k0 >= P.k[pair]) {
+        ++pair;
+        k0 = 0;
+      }
+    }
+    if (want_rowsum && ok && m0 + (t & 127) < P.M)
+      atomicAdd(static_cast<float*>(P.rowsum) + m0 + (t & 127), rs);
+
+    // ===================== epilogue (sixteen warps; 32 columns each) =====================
+    if (ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int c0 = ((warp - 1) >> 2) * 32;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < P.M;
+      const float bias = (P.bias != nullptr && row_ok) ? static_cast<const float*>(P.bias)[row] : 0.f;
+      float* cbase = static_cast<float*>(P.c) + batch * P.c_batch_stride;
+      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = n0 + c0 + j;
+        float v = bias;
+        if (P.accumulate && row_ok && col < P.N) {
+          const float* src = (P.ccols ? static_cast<const float*>(P.ccols[col])
+                                      : cbase + static_cast<long long>(col) * P.ldc) + row;
+          v += *src;
+        }
+        acc[j] = v;
+      }
+      uint32_t v[32];
+      tmem_ld32(tbase + CROSS_COL + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+#pragma unroll 1
+      for (int a = 0; a < 3 && a < nkb; ++a) {
+        tmem_ld32(tbase + a * SBN + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = n0 + c0 + j;
+          if (col < P.N) {
+            float* dst = (P.ccols ? static_cast<float*>(P.ccols[col])
+                                  : cbase + static_cast<long long>(col) * P.ldc) + row;
+            *dst = act_forward(P.act, acc[j]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <bool GROUPED>
+cudaError_t launch_gather(const Problem& p, const Problem* dprobs, int nprobs, int total_tiles,
+                          cudaStream_t stream, int* status) {
+  auto kern = sgemm3x_gather_kernel<GROUPED>;
+  const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  kern<<<total_tiles, GNTHREADS, smem, stream>>>(p, dprobs, nprobs, status);
+  return cudaGetLastError();
+}
+
 bool operand_tma_ok(const Operand& o, int batches) {
   if (o.cols != nullptr || o.ycols != nullptr) return false;
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
@@ -466,6 +801,38 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   if (e != cudaSuccess) return e;
   sgemm3x_tma_kernel<<<static_cast<unsigned>(total), NTHREADS, smem, stream>>>(sp, status);
   return cudaGetLastError();
+}
+
+// fp32 problems a tensor map cannot describe (any alignment, column tables); k > 0, at most one
+// derivative operand and then a single pair; the bias gradient needs an outer-contiguous A.
+bool sgemm3x_gather_supported(const Problem& p) {
+  if (p.npairs < 1) return false;
+  int nderiv = 0;
+  for (int i = 0; i < p.npairs; ++i) {
+    if (p.k[i] <= 0 || p.k[i] > 0x7fffffffLL) return false;
+    nderiv += (p.a[i].dact != ACT_NONE) + (p.b[i].dact != ACT_NONE);
+  }
+  if (nderiv > 1 || (nderiv == 1 && p.npairs != 1)) return false;
+  if (p.rowsum != nullptr && p.a[0].k_contig) return false;
+  return true;
+}
+
+cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status) {
+  p.tiles_m = (p.M + SBM - 1) / SBM;
+  p.tiles_n = (p.N + SBN - 1) / SBN;
+  p.tile_start = 0;
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
+  if (total <= 0) return cudaSuccess;
+  if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+  return launch_gather<false>(p, nullptr, 1, static_cast<int>(total), stream, status);
+}
+
+// Descriptors in device memory, tiles_m / tiles_n / tile_start filled for 128 x 128 tiles.
+cudaError_t launch_sgemm3x_gather_grouped(const Problem* dprobs, int nprobs, int total_tiles,
+                                          cudaStream_t stream, int* status) {
+  if (total_tiles <= 0) return cudaSuccess;
+  Problem dummy{};
+  return launch_gather<true>(dummy, dprobs, nprobs, total_tiles, stream, status);
 }
 
 }  // namespace gb

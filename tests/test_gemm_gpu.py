@@ -54,10 +54,11 @@ def test_shape_sweep_all_transposes(gpu, dt, path):
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float16])
-def test_padded_leading_dimension_and_unaligned_base(gpu, dt):
+@pytest.mark.parametrize("path", [1, 0])
+def test_padded_leading_dimension_and_unaligned_base(gpu, dt, path):
     """ginn's PreallocGpu hands out unaligned bump pointers (ginn/dev.h:237-245) and
     RowwiseUncat views start at arbitrary column offsets (ginn/node/layout.h:283-289)."""
-    gpu.set_option("force_path", 1)
+    gpu.set_option("force_path", path)
     rng = np.random.default_rng(12)
     for (m, n, k) in [(37, 41, 53), (128, 64, 96), (200, 100, 260)]:
         for ta, tb in TRANS[:3]:
