@@ -111,10 +111,14 @@ int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
   if (p.rowsum != nullptr && ktot > 0) small = false;
   if (small) {
     CU_TRY(gb::launch_small(dtype, p, stream));
-  } else if (dtype == GINN_B200_F32 && force != PATH_STAGED && gb::sgemm3x_supported(p)) {
-    CU_TRY(gb::launch_sgemm3x(p, stream, ctx->d_status));
-  } else if (dtype == GINN_B200_F32 && force != PATH_STAGED && gb::sgemm3x_gather_supported(p)) {
-    CU_TRY(gb::launch_sgemm3x_gather(p, stream, ctx->d_status));
+  } else if (dtype == GINN_B200_F32 && force != PATH_STAGED &&
+             (gb::sgemm3x_supported(p) || gb::sgemm3x_gather_supported(p))) {
+    const long long tiles = static_cast<long long>((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batches;
+    p.split_k = gb::sgemm3x_pick_split(p, tiles, ctx->num_sms);
+    if (gb::sgemm3x_supported(p))
+      CU_TRY(gb::launch_sgemm3x(p, stream, ctx->d_status));
+    else
+      CU_TRY(gb::launch_sgemm3x_gather(p, stream, ctx->d_status));
   } else {
     const int bn = gb::staged_pick_bn(dtype, p.M, p.N, p.batches, ctx->num_sms);
     CU_TRY(gb::launch_staged(dtype, p, bn, stream, ctx->d_status));
@@ -439,7 +443,9 @@ int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroup
     p.tiles_m = (p.M + 127) / 128;
     p.tiles_n = (p.N + bn - 1) / bn;
     p.tile_start = tile;
-    tile += p.tiles_m * p.tiles_n;
+    if (use_gather)
+      p.split_k = gb::sgemm3x_pick_split(p, sum_tiles128, ctx->num_sms);
+    tile += p.tiles_m * p.tiles_n * (p.split_k > 1 ? p.split_k : 1);
     ++np;
   }
   CU_TRY(cudaMemcpyAsync(d, h, off, cudaMemcpyHostToDevice, stream));
@@ -513,9 +519,12 @@ int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int
   CU_TRY(gb::grouped_static_scratch(device, &scratch));
   unsigned char* d = static_cast<unsigned char*>(scratch);
 
+  const bool use_gather = dtype == GINN_B200_F32 && g_force_path.load() != PATH_STAGED;
   int bn = 128;
-  if (max_n <= 32) bn = 32;
-  else if (max_n <= 64 || sum_tiles128 < num_sms) bn = 64;
+  if (!use_gather) {
+    if (max_n <= 32) bn = 32;
+    else if (max_n <= 64 || sum_tiles128 < num_sms) bn = 64;
+  }
 
   std::lock_guard<std::mutex> lock(image_mu);
   Problem* hp = reinterpret_cast<Problem*>(image);
@@ -583,10 +592,12 @@ int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int
     p.tiles_m = (p.M + 127) / 128;
     p.tiles_n = (p.N + bn - 1) / bn;
     p.tile_start = tile;
-    tile += p.tiles_m * p.tiles_n;
+    if (use_gather) p.split_k = gb::sgemm3x_pick_split(p, sum_tiles128, num_sms);
+    tile += p.tiles_m * p.tiles_n * (p.split_k > 1 ? p.split_k : 1);
     ++np;
   }
-  CU_TRY(gb::launch_staged_grouped_static(dtype, image, off, scratch, np, tile, bn, stream));
+  CU_TRY(gb::launch_staged_grouped_static(dtype, image, off, scratch, np, tile, bn, use_gather,
+                                          stream));
   g_launches.fetch_add(1);
   return GINN_B200_OK;
 }

@@ -610,11 +610,15 @@ cudaError_t grouped_static_scratch(int device, void** ptr) {
 // addresses inside the static array) and launches the grouped kernel on it.
 cudaError_t launch_staged_grouped_static(int dtype, const void* host_image, size_t bytes,
                                          void* scratch, int nprobs, int total_tiles, int bn,
-                                         cudaStream_t stream) {
+                                         bool fp32_gather, cudaStream_t stream) {
   if (bytes > kGroupedStaticBytes) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemcpyAsync(scratch, host_image, bytes, cudaMemcpyHostToDevice, stream);
   if (e != cudaSuccess) return e;
   // No status word: a wait that runs out still ends the kernel, it is just not recorded.
+  // fp32 levels use the same kernel as the allocating entry point (3xTF32 gather front end).
+  if (fp32_gather)
+    return launch_sgemm3x_gather_grouped(static_cast<const Problem*>(scratch), nprobs,
+                                         total_tiles, stream, nullptr);
   return launch_staged_grouped(dtype, static_cast<const Problem*>(scratch), nprobs, total_tiles,
                                bn, stream, nullptr);
 }

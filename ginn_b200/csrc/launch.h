@@ -20,7 +20,7 @@ constexpr size_t kGroupedStaticBytes = 256 * 1024;
 cudaError_t grouped_static_scratch(int device, void** ptr);
 cudaError_t launch_staged_grouped_static(int dtype, const void* host_image, size_t bytes,
                                          void* scratch, int nprobs, int total_tiles, int bn,
-                                         cudaStream_t stream);
+                                         bool fp32_gather, cudaStream_t stream);
 
 // --- TMA-fed persistent fp16 kernel (hgemm_tma.cu) ---
 struct HgemmArgs {
@@ -49,6 +49,7 @@ bool tmap_encoder_available();
 bool sgemm3x_supported(const Problem& p);
 cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status);
 
+int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms);
 // Same pipeline with a cp.async gather front end: any alignment, column tables, grouped launches.
 bool sgemm3x_gather_supported(const Problem& p);
 cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status);

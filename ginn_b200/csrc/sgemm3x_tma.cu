@@ -53,6 +53,8 @@ struct SParams {
   float* rowsum;
   int act;
   int accumulate;
+  int split_k;  // CTAs per output tile along K (1 = none); > 1 only with accumulate, no bias/act
+  int batches;
 };
 
 __device__ __forceinline__ float act_forward(int act, float x) {
@@ -164,11 +166,17 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   const int m_tile = tile % p.tiles_m;
   tile /= p.tiles_m;
   const int n_tile = tile % p.tiles_n;
-  const int batch = tile / p.tiles_n;
+  tile /= p.tiles_n;
+  const int batch = tile % p.batches;
+  const int split = tile / p.batches;
   const int m0 = m_tile * SBM, n0 = n_tile * SBN;
 
-  int nkb = 0;
-  for (int i = 0; i < p.npairs; ++i) nkb += (p.k[i] + SBK - 1) / SBK;
+  int nkb_total = 0;
+  for (int i = 0; i < p.npairs; ++i) nkb_total += (p.k[i] + SBK - 1) / SBK;
+  // k-blocks [kb_begin, kb_begin + nkb) belong to this CTA (single pair when split)
+  const int kb_begin = static_cast<int>(static_cast<long long>(nkb_total) * split / p.split_k);
+  const int nkb =
+      static_cast<int>(static_cast<long long>(nkb_total) * (split + 1) / p.split_k) - kb_begin;
 
   if (warp == 0 && lane == 0) {
     for (int i = 0; i < p.npairs; ++i) {
@@ -204,7 +212,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     if (elect_one()) {
       int s = 0;
       uint32_t ph = 0;
-      int pair = 0, k0 = 0;
+      int pair = 0, k0 = kb_begin * SBK;
       for (int it = 0; it < nkb; ++it) {
         if (!mbar_wait(smem_u32(&raw_empty[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) break;
         const uint32_t bar = smem_u32(&raw_full[s]);
@@ -293,7 +301,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     bool ok = true;
     int rs_i = 0, ps_i = 0;
     uint32_t rph = 0, pph = 0;
-    int pair = 0, k0 = 0;
+    int pair = 0, k0 = kb_begin * SBK;
     for (int it = 0; it < nkb; ++it) {
       if (!mbar_wait(smem_u32(&raw_full[rs_i]), rph, status, DEV_TIMEOUT_FULL, 0x100 + it) ||
           !mbar_wait(smem_u32(&plane_empty[ps_i]), pph ^ 1u, status, DEV_TIMEOUT_EMPTY,
@@ -351,7 +359,8 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       {
         const int c0 = cgrp * 32;
         float acc[32];
-        const bool load_c = p.accumulate && row_ok;
+        const bool split_k = p.split_k > 1;
+        const bool load_c = p.accumulate && row_ok && !split_k;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int col = n0 + c0 + j;
@@ -375,7 +384,13 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int col = n0 + c0 + j;
-            if (col < p.N) crow[static_cast<long long>(col) * p.ldc] = act_forward(p.act, acc[j]);
+            if (col < p.N) {
+              float* dst = crow + static_cast<long long>(col) * p.ldc;
+              if (split_k)
+                atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
+              else
+                *dst = act_forward(p.act, acc[j]);
+            }
           }
         }
       }
@@ -504,13 +519,19 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
   const Problem& P = GROUPED ? sprob : p0;
   tile -= P.tile_start;
   const int m_tile = tile % P.tiles_m;
-  const int rest = tile / P.tiles_m;
+  int rest = tile / P.tiles_m;
   const int n_tile = rest % P.tiles_n;
-  const long long batch = rest / P.tiles_n;
+  rest /= P.tiles_n;
+  const long long batch = rest % P.batches;
+  const int split = rest / P.batches;
+  const int nsplit = P.split_k > 1 ? P.split_k : 1;
   const int m0 = m_tile * SBM, n0 = n_tile * SBN;
 
-  int nkb = 0;
-  for (int i = 0; i < P.npairs; ++i) nkb += static_cast<int>((P.k[i] + SBK - 1) / SBK);
+  int nkb_total = 0;
+  for (int i = 0; i < P.npairs; ++i) nkb_total += static_cast<int>((P.k[i] + SBK - 1) / SBK);
+  const int kb_begin = static_cast<int>(static_cast<long long>(nkb_total) * split / nsplit);
+  const int nkb =
+      static_cast<int>(static_cast<long long>(nkb_total) * (split + 1) / nsplit) - kb_begin;
   const int dop = P.a[0].dact != ACT_NONE ? 1 : (P.b[0].dact != ACT_NONE ? 2 : 0);
   const int dact = dop == 1 ? P.a[0].dact : (dop == 2 ? P.b[0].dact : ACT_NONE);
   const int raw_stages = dop ? 2 : 3;
@@ -593,7 +614,7 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
                      0x300 + j))
         return false;
       int pair = 0;
-      long long k0 = static_cast<long long>(j) * SBK;
+      long long k0 = static_cast<long long>(kb_begin + j) * SBK;
       while (pair + 1 < P.npairs && k0 >= ((P.k[pair] + SBK - 1) / SBK) * SBK) {
         k0 -= ((P.k[pair] + SBK - 1) / SBK) * SBK;
         ++pair;
@@ -611,7 +632,7 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
     int rs_i = 0, ps_i = 0;
     uint32_t rph = 0, pph = 0;
     int pair = 0;
-    long long k0 = 0;
+    long long k0 = static_cast<long long>(kb_begin) * SBK;  // kb_begin > 0 only with one pair
     for (int it = 0; it < nkb; ++it) {
       const int ahead = it + raw_stages - 1;
       if (ok && ahead < nkb) ok = fill(ahead, ahead % raw_stages);
@@ -669,11 +690,12 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
       float* cbase = static_cast<float*>(P.c) + batch * P.c_batch_stride;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
       float acc[32];
+      const bool split_k = nsplit > 1;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const int col = n0 + c0 + j;
         float v = bias;
-        if (P.accumulate && row_ok && col < P.N) {
+        if (P.accumulate && !split_k && row_ok && col < P.N) {
           const float* src = (P.ccols ? static_cast<const float*>(P.ccols[col])
                                       : cbase + static_cast<long long>(col) * P.ldc) + row;
           v += *src;
@@ -699,7 +721,10 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
           if (col < P.N) {
             float* dst = (P.ccols ? static_cast<float*>(P.ccols[col])
                                   : cbase + static_cast<long long>(col) * P.ldc) + row;
-            *dst = act_forward(P.act, acc[j]);
+            if (split_k)
+              atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
+            else
+              *dst = act_forward(P.act, acc[j]);
           }
         }
       }
@@ -792,7 +817,9 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   sp.rowsum = static_cast<float*>(p.rowsum);
   sp.act = p.act;
   sp.accumulate = p.accumulate;
-  const long long total = static_cast<long long>(sp.tiles_m) * sp.tiles_n * p.batches;
+  sp.split_k = p.split_k > 1 ? p.split_k : 1;
+  sp.batches = p.batches;
+  const long long total = static_cast<long long>(sp.tiles_m) * sp.tiles_n * p.batches * sp.split_k;
   if (total <= 0) return cudaSuccess;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
@@ -801,6 +828,19 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   if (e != cudaSuccess) return e;
   sgemm3x_tma_kernel<<<static_cast<unsigned>(total), NTHREADS, smem, stream>>>(sp, status);
   return cudaGetLastError();
+}
+
+// Number of K splits for a problem of `tiles` output tiles: only where partial sums can simply be
+// added to C (accumulate, no bias, no activation, one pair), when the tiles alone leave most SMs
+// idle, and never below four k-blocks per CTA.
+int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms) {
+  if (!p.accumulate || p.act != ACT_NONE || p.bias != nullptr || p.npairs != 1) return 1;
+  const long long nkb = (p.k[0] + SBK - 1) / SBK;
+  if (tiles <= 0 || tiles * 2 > num_sms || nkb < 8) return 1;
+  long long s = num_sms / tiles;
+  if (s > nkb / 4) s = nkb / 4;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : static_cast<int>(s);
 }
 
 // fp32 problems a tensor map cannot describe (any alignment, column tables); k > 0, at most one
@@ -821,7 +861,8 @@ cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status) 
   p.tiles_m = (p.M + SBM - 1) / SBM;
   p.tiles_n = (p.N + SBN - 1) / SBN;
   p.tile_start = 0;
-  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches *
+                          (p.split_k > 1 ? p.split_k : 1);
   if (total <= 0) return cudaSuccess;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   return launch_gather<false>(p, nullptr, 1, static_cast<int>(total), stream, status);
