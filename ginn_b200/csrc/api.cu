@@ -97,7 +97,7 @@ Operand make_operand(int dtype, const void* base, long long ld, long long batch_
   return o;
 }
 
-enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3 };
+enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3, PATH_PAIR = 4 };
 
 // Runs one Problem on the staged tcgen05 kernel or the CUDA-core kernel.
 int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
@@ -160,7 +160,8 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int force = g_force_path.load();
 
-  if (dtype == GINN_B200_F16 && k > 0 && (force == PATH_AUTO || force == PATH_TMA)) {
+  if (dtype == GINN_B200_F16 && k > 0 &&
+      (force == PATH_AUTO || force == PATH_TMA || force == PATH_PAIR)) {
     gb::HgemmArgs h;
     h.A = a; h.B = b; h.C = c;
     h.lda = lda; h.ldb = ldb; h.ldc = ldc;
@@ -170,6 +171,13 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
     h.accumulate = accumulate ? 1 : 0;
     const bool big = m >= 128 && n >= 128 && k >= 128 &&
                      ((m + 127) / 128) * ((n + 255) / 256) * batches >= ctx->num_sms / 2;
+    const bool big_pair = big && m >= 256 && n >= 256 &&
+                          ((m + 255) / 256) * ((n + 255) / 256) * batches >= ctx->num_sms / 4;
+    if ((force == PATH_PAIR || (force == PATH_AUTO && big_pair)) && gb::hgemm_pair_supported(h)) {
+      CU_TRY(gb::launch_hgemm_pair(h, ctx->num_sms, stream, ctx->d_status));
+      g_launches.fetch_add(1);
+      return GINN_B200_OK;
+    }
     if ((big || force == PATH_TMA) && gb::hgemm_tma_supported(h)) {
       CU_TRY(gb::launch_hgemm_tma(h, ctx->num_sms, stream, ctx->d_status));
       g_launches.fetch_add(1);
@@ -618,7 +626,7 @@ int ginn_b200_version(void) { return 100; }
 
 int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "force_path") == 0) {
-    if (value < 0 || value > 3) return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0..3");
+    if (value < 0 || value > 4) return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0..4");
     g_force_path.store(value);
     return GINN_B200_OK;
   }

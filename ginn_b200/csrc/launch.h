@@ -37,6 +37,10 @@ struct HgemmArgs {
 bool hgemm_tma_supported(const HgemmArgs& a);
 cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
 
+// --- fp16 kernel on CTA pairs, 256 x 256 tiles (hgemm_pair.cu) ---
+bool hgemm_pair_supported(const HgemmArgs& a);
+cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
+
 // --- tensor maps (defined in hgemm_tma.cu) ---
 bool encode_tmap(::CUtensorMap_st* out, int esize, const void* ptr, unsigned long long d0,
                  unsigned long long d1, unsigned long long d2, unsigned long long ld,

@@ -161,7 +161,8 @@ int ginn_b200_device_status(int device, int reset);
 int ginn_b200_version(void);
 
 /* Test / benchmark knobs.  "force_path": 0 = automatic, 1 = staged tcgen05 kernel,
- * 2 = TMA fp16 kernel (falls back to automatic when not applicable), 3 = CUDA-core kernel.
+ * 2 = one-CTA TMA fp16 kernel, 4 = CTA-pair fp16 kernel (both fall back to automatic when not
+ * applicable), 3 = CUDA-core kernel.
  * Returns GINN_B200_UNSUPPORTED for unknown names. */
 int ginn_b200_set_option(const char* name, int value);
 

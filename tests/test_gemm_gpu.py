@@ -136,8 +136,10 @@ def test_batched_dot_products_of_softmax_backward(gpu):
 
 
 @pytest.mark.parametrize("trans", TRANS[:3])
-def test_tma_path_half(gpu, trans):
-    gpu.set_option("force_path", 2)
+@pytest.mark.parametrize("path", [2, 4])
+def test_tma_path_half(gpu, trans, path):
+    """Path 2: one CTA per 128 x 256 tile; path 4: CTA pairs (cta_group::2) on 256 x 256 tiles."""
+    gpu.set_option("force_path", path)
     rng = np.random.default_rng(17)
     ta, tb = trans
     for (m, n, k) in [(128, 256, 64), (136, 264, 72), (256, 512, 512), (384, 256, 1000)]:
