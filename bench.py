@@ -206,6 +206,8 @@ def run_gpu(args):
             dist.all_reduce(t.T)  # contiguous storage of the column-major matrix
         return lambda: main.wait_stream(comm_stream)
 
+    margin = args.sm_margin if args.sm_margin >= 0 else (24 if world > 1 else 0)
+    gb.set_option("sm_margin", margin)
     prod = ShardedProd(lambda a, b, c, ta, tb, acc: gb.gemm(a, b, c, ta, tb, acc),
                        lambda t: t.zero_(), allreduce_async)
 
@@ -394,6 +396,88 @@ def run_affine(args):
           flush=True)
 
 
+def run_config_workload(args):
+    """Secondary workloads: the other benchmark configurations (fp32), harnessed in
+    ginn_b200/workloads.py.  Same timing rules as the main arm; one JSON line from rank 0."""
+    import torch
+    import torch.distributed as dist
+    import ginn_b200 as gb
+    from ginn_b200 import workloads as wl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    extra = {}
+    if args.workload == "attention_f32":
+        w = wl.Attention(dev)
+        metric, name = "attention_fwd_bwd_tflops", "C3 min-GPT attention via BatchedProd, fp32, 256 x (256x64x256)"
+    elif args.workload == "lstm_autobatch":
+        w = wl.LstmAutobatch(dev)
+        t0 = time.perf_counter()
+        w.rewrite()
+        extra["rewrite_ms"] = (time.perf_counter() - t0) * 1e3
+        extra["levels"], extra["nodes"] = w.T, w.nodes
+        if args.cuda_graph:
+            w.capture()
+        extra["cuda_graph"] = bool(args.cuda_graph)
+        metric, name = "autobatch_nodes_per_s", "C2 autobatched LSTM gates, fp32, 256 seqs len 5..40, W 1024x384"
+    else:
+        comm = torch.cuda.Stream(device=dev) if world > 1 else None
+
+        def allreduce(t):
+            dist.all_reduce(t)
+        w = wl.MlpDataParallel(dev, rank, world, allreduce=allreduce if world > 1 else None)
+        metric, name = "mlp_dp_tflops", "C5 data-parallel MLP 784-1024-1024-10, fp32, batch 4096 per GPU, Adam"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        w.step()
+    barrier()
+    assert gb.device_status(local, True) == 0
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = gb.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        w.step()
+    e1.record()
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    clocks = sampler.stop() if sampler else None
+    assert gb.device_status(local, True) == 0
+    if rank == 0:
+        tflops = world * w.flops / (ms * 1e-3) / 1e12
+        value = world * w.units / (ms * 1e-3) if args.workload == "lstm_autobatch" else tflops
+        line = {"metric": metric, "value": value,
+                "unit": "nodes/s" if args.workload == "lstm_autobatch" else UNIT,
+                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": ms, "wall_ms_per_step": wall_ms, "tflops": tflops,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32 (3xTF32)", "data": "synthetic", "config": {"workload": name},
+                "clocks": clocks, "gpu_launches": int(gb.launch_count() - launches0)}
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,7 +488,12 @@ def main():
     ap.add_argument("--cpu-size", type=int, default=3072, help="extent of the bounded CPU sample")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32"])
+    ap.add_argument("--sm-margin", type=int, default=-1,
+                    help="SMs left free for NCCL while the dB product overlaps the all-reduce "
+                         "(default: 0 on one GPU, 24 otherwise)")
+    ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32", "attention_f32", "lstm_autobatch", "mlp_dp"])
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="lstm_autobatch: replay the level sequence from a CUDA graph")
     ap.add_argument("--m", type=int, default=1024)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -413,6 +502,8 @@ def main():
         run_reference(args)
     elif args.workload == "affine_f32":
         run_affine(args)
+    elif args.workload in ("attention_f32", "lstm_autobatch", "mlp_dp"):
+        run_config_workload(args)
     else:
         run_gpu(args)
 

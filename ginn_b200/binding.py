@@ -73,6 +73,11 @@ def lib():
     L.ginn_b200_grouped.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
     L.ginn_b200_grouped_static.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
     L.ginn_b200_grouped_static.restype = ci
+    L.ginn_b200_level_create.argtypes = [ci, ci, ci, ci, C.POINTER(_Group), C.POINTER(vp)]
+    L.ginn_b200_level_run.argtypes = [vp, vp]
+    L.ginn_b200_level_destroy.argtypes = [vp]
+    for name in ("ginn_b200_level_create", "ginn_b200_level_run", "ginn_b200_level_destroy"):
+        getattr(L, name).restype = ci
     L.ginn_b200_last_error.restype = C.c_char_p
     L.ginn_b200_device_status.argtypes = [ci, ci]
     L.ginn_b200_set_option.argtypes = [C.c_char_p, ci]
@@ -264,19 +269,36 @@ def _grouped_call(fn, mode: int, groups: Sequence[Group]) -> None:
 
 
 class GroupedCall:
-    """A level whose tables are built once and launched many times (the tensors must stay
-    alive and in place, as the nodes of a re-evaluated ginn graph do)."""
+    """A level prepared once and launched many times (ginn_b200_level_*): descriptors and column
+    tables stay resident on the device, a call is one kernel launch.  The tensors must stay
+    alive and in place, as the nodes of a re-evaluated ginn graph do.  With static=True the
+    allocation-free entry point is used instead (tables rebuilt from the kept host arrays)."""
 
     def __init__(self, mode: int, groups: Sequence[Group], static: bool = False):
         self.mode, self.n = mode, len(groups)
         self.groups = list(groups)
         self.arr, self._keep = _build_groups(groups)
-        self.fn = lib().ginn_b200_grouped_static if static else lib().ginn_b200_grouped
         w0 = groups[0].w
         self.dev, self.dtype, self.w0 = _dev(w0), _dtype_of(w0), w0
+        self.static = static
+        self.handle = None
+        if not static:
+            h = C.c_void_p()
+            _check(lib().ginn_b200_level_create(self.dev, self.dtype, mode, self.n, self.arr,
+                                                C.byref(h)))
+            self.handle = h
 
     def __call__(self):
-        _check(self.fn(self.dev, _stream(self.w0), self.dtype, self.mode, self.n, self.arr))
+        if self.static:
+            _check(lib().ginn_b200_grouped_static(self.dev, _stream(self.w0), self.dtype,
+                                                  self.mode, self.n, self.arr))
+        else:
+            _check(lib().ginn_b200_level_run(self.handle, _stream(self.w0)))
+
+    def __del__(self):
+        if getattr(self, "handle", None) is not None and _lib is not None:
+            _lib.ginn_b200_level_destroy(self.handle)
+            self.handle = None
 
 
 def device_status(device: int = 0, reset: bool = True) -> int:

@@ -18,6 +18,7 @@ using gb::Problem;
 thread_local std::string t_error;
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_force_path{0};
+std::atomic<int> g_sm_margin{0};  // SMs the persistent kernels leave free (e.g. for NCCL)
 
 int fail(int status, const char* fmt, ...) {
   char buf[512];
@@ -97,6 +98,12 @@ Operand make_operand(int dtype, const void* base, long long ld, long long batch_
   return o;
 }
 
+// SMs a persistent kernel may occupy: all of them minus the margin the host asked to keep free.
+int persistent_sms(const DevCtx* ctx) {
+  const int n = ctx->num_sms - g_sm_margin.load();
+  return n < 2 ? 2 : n;
+}
+
 enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3, PATH_PAIR = 4 };
 
 // Runs one Problem on the staged tcgen05 kernel or the CUDA-core kernel.
@@ -174,12 +181,12 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
     const bool big_pair = big && m >= 256 && n >= 256 &&
                           ((m + 255) / 256) * ((n + 255) / 256) * batches >= ctx->num_sms / 4;
     if ((force == PATH_PAIR || (force == PATH_AUTO && big_pair)) && gb::hgemm_pair_supported(h)) {
-      CU_TRY(gb::launch_hgemm_pair(h, ctx->num_sms, stream, ctx->d_status));
+      CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), stream, ctx->d_status));
       g_launches.fetch_add(1);
       return GINN_B200_OK;
     }
     if ((big || force == PATH_TMA) && gb::hgemm_tma_supported(h)) {
-      CU_TRY(gb::launch_hgemm_tma(h, ctx->num_sms, stream, ctx->d_status));
+      CU_TRY(gb::launch_hgemm_tma(h, persistent_sms(ctx), stream, ctx->d_status));
       g_launches.fetch_add(1);
       return GINN_B200_OK;
     }
@@ -218,6 +225,142 @@ int stage_alloc(DevCtx* ctx, size_t bytes, unsigned char** h, unsigned char** d)
   *d = ctx->d_stage + ctx->stage_off;
   ctx->stage_off += bytes;
   return GINN_B200_OK;
+}
+
+
+// ---- grouped levels: validation, image layout, launch (shared by the three entry points) ----
+struct LevelPlan {
+  size_t desc_bytes = 0;  // descriptors, padded to 16 bytes
+  size_t bytes = 0;       // descriptors + both pointer tables of every live group
+  int live = 0;           // groups with m, k, ncols > 0
+  long long max_n = 0, sum_tiles128 = 0;
+};
+struct LevelLaunch {
+  int nprobs = 0, tiles = 0, bn = 128;
+  bool use_gather = false;
+};
+
+int plan_level(int dtype, int mode, int ngroups, const ginn_b200_group* groups, LevelPlan* plan) {
+  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
+    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
+  if (mode < GINN_B200_GROUPED_FORWARD || mode > GINN_B200_GROUPED_DW)
+    return fail(GINN_B200_BAD_ARGUMENT, "unknown grouped mode %d", mode);
+  if (ngroups < 0 || (ngroups > 0 && groups == nullptr))
+    return fail(GINN_B200_BAD_ARGUMENT, "bad group list");
+  size_t table_bytes = 0;
+  for (int g = 0; g < ngroups; ++g) {
+    const ginn_b200_group& q = groups[g];
+    if (q.m < 0 || q.k < 0 || q.ncols < 0 || q.m > 0x7fffffffLL || q.k > 0x7fffffffLL ||
+        q.ncols > 0x7fffffffLL)
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dimensions", g);
+    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
+    if (!q.w || q.ldw < q.m || !q.y_cols)
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad W or column table", g);
+    if ((mode != GINN_B200_GROUPED_DX && !q.x_cols) || (mode == GINN_B200_GROUPED_DX && !q.dx_cols))
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: missing column table for mode %d", g, mode);
+    if (mode == GINN_B200_GROUPED_DW && (!q.dw || q.lddw < q.m))
+      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dW", g);
+    table_bytes += 2 * static_cast<size_t>(q.ncols) * sizeof(void*);
+    const long long N = mode == GINN_B200_GROUPED_DW ? q.k : q.ncols;
+    const long long M = mode == GINN_B200_GROUPED_DX ? q.k : q.m;
+    plan->max_n = N > plan->max_n ? N : plan->max_n;
+    plan->sum_tiles128 += ((M + 127) / 128) * ((N + 127) / 128);
+    ++plan->live;
+  }
+  plan->desc_bytes = (static_cast<size_t>(plan->live) * sizeof(Problem) + 15) & ~size_t(15);
+  plan->bytes = plan->desc_bytes + table_bytes;
+  return GINN_B200_OK;
+}
+
+// Writes descriptors and pointer tables into the host image `h`; `d` is the device address the
+// image will have, so that the descriptors can point at their tables.
+LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_group* groups,
+                             const LevelPlan& plan, int num_sms, unsigned char* h,
+                             unsigned char* d) {
+  LevelLaunch ll;
+  // fp32 levels run on the gather front end of the 3xTF32 kernel (128 x 128 tiles); fp16 levels
+  // on the staged kernel.
+  ll.use_gather = dtype == GINN_B200_F32 && g_force_path.load() != PATH_STAGED;
+  if (!ll.use_gather) {
+    if (plan.max_n <= 32) ll.bn = 32;
+    else if (plan.max_n <= 64 || plan.sum_tiles128 < num_sms) ll.bn = 64;
+  }
+  Problem* hp = reinterpret_cast<Problem*>(h);
+  size_t off = plan.desc_bytes;
+  for (int g = 0; g < ngroups; ++g) {
+    const ginn_b200_group& q = groups[g];
+    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
+    const size_t tb = static_cast<size_t>(q.ncols) * sizeof(void*);
+    const void** t0 = reinterpret_cast<const void**>(h + off);
+    const void* const* d_t0 = reinterpret_cast<const void* const*>(d + off);
+    off += tb;
+    const void** t1 = reinterpret_cast<const void**>(h + off);
+    void* const* d_t1 = reinterpret_cast<void* const*>(d + off);
+    off += tb;
+    Problem& p = hp[ll.nprobs];
+    std::memset(&p, 0, sizeof(p));
+    p.npairs = 1;
+    p.batches = 1;
+    bool al = true;
+    if (mode == GINN_B200_GROUPED_FORWARD) {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        t0[j] = q.x_cols[j];
+        t1[j] = q.y_cols[j];
+        al = al && aligned16(q.x_cols[j]);
+      }
+      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 0);
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
+      p.b[0].cols = d_t0;
+      p.b[0].vec = al ? 1 : 0;
+      p.k[0] = q.k;
+      p.M = (int)q.m; p.N = (int)q.ncols;
+      p.ccols = d_t1;
+      p.bias = q.bias;
+      p.accumulate = q.accumulate ? 1 : 0;
+    } else if (mode == GINN_B200_GROUPED_DX) {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        t0[j] = q.y_cols[j];
+        t1[j] = q.dx_cols[j];
+        al = al && aligned16(q.y_cols[j]);
+      }
+      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 1);  // W^T: contraction over m
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
+      p.b[0].cols = d_t0;
+      p.b[0].vec = al ? 1 : 0;
+      p.k[0] = q.m;
+      p.M = (int)q.k; p.N = (int)q.ncols;
+      p.ccols = d_t1;
+      p.accumulate = 1;
+    } else {
+      for (int64_t j = 0; j < q.ncols; ++j) {
+        t0[j] = q.y_cols[j];
+        t1[j] = q.x_cols[j];
+      }
+      p.a[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // dy columns, contraction over j
+      p.a[0].cols = d_t0;
+      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // x columns
+      p.b[0].cols = reinterpret_cast<const void* const*>(d_t1);
+      p.k[0] = q.ncols;
+      p.M = (int)q.m; p.N = (int)q.k;
+      p.c = q.dw; p.ldc = q.lddw;
+      p.rowsum = q.dbias;
+      p.accumulate = 1;
+    }
+    p.tiles_m = (p.M + 127) / 128;
+    p.tiles_n = (p.N + ll.bn - 1) / ll.bn;
+    p.tile_start = ll.tiles;
+    if (ll.use_gather) p.split_k = gb::sgemm3x_pick_split(p, plan.sum_tiles128, num_sms);
+    ll.tiles += p.tiles_m * p.tiles_n * (p.split_k > 1 ? p.split_k : 1);
+    ++ll.nprobs;
+  }
+  return ll;
+}
+
+cudaError_t launch_level(int dtype, const LevelLaunch& ll, const Problem* dprobs,
+                         cudaStream_t stream, int* status) {
+  if (ll.use_gather)
+    return gb::launch_sgemm3x_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
+  return gb::launch_staged_grouped(dtype, dprobs, ll.nprobs, ll.tiles, ll.bn, stream, status);
 }
 
 }  // namespace
@@ -340,129 +483,17 @@ int ginn_b200_affine_backward(int device, void* stream_, int dtype, int npairs,
 
 int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroups,
                       const ginn_b200_group* groups) {
-  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
-    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
-  if (mode < GINN_B200_GROUPED_FORWARD || mode > GINN_B200_GROUPED_DW)
-    return fail(GINN_B200_BAD_ARGUMENT, "unknown grouped mode %d", mode);
-  if (ngroups < 0 || (ngroups > 0 && groups == nullptr))
-    return fail(GINN_B200_BAD_ARGUMENT, "bad group list");
-  if (ngroups == 0) return GINN_B200_OK;
+  LevelPlan plan;
+  if (int s = plan_level(dtype, mode, ngroups, groups, &plan)) return s;
+  if (plan.live == 0) return GINN_B200_OK;
   DevCtx* ctx;
   if (int s = get_ctx(device, &ctx)) return s;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-
-  // Size of the staging slot: descriptors first, then the pointer tables.
-  size_t table_bytes = 0;
-  long long max_n = 0, sum_tiles128 = 0;
-  for (int g = 0; g < ngroups; ++g) {
-    const ginn_b200_group& q = groups[g];
-    if (q.m < 0 || q.k < 0 || q.ncols < 0 || q.m > 0x7fffffffLL || q.k > 0x7fffffffLL ||
-        q.ncols > 0x7fffffffLL)
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dimensions", g);
-    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
-    if (!q.w || q.ldw < q.m || !q.y_cols)
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad W or column table", g);
-    if ((mode != GINN_B200_GROUPED_DX && !q.x_cols) || (mode == GINN_B200_GROUPED_DX && !q.dx_cols))
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: missing column table for mode %d", g, mode);
-    if (mode == GINN_B200_GROUPED_DW && (!q.dw || q.lddw < q.m))
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dW", g);
-    table_bytes += 2 * static_cast<size_t>(q.ncols) * sizeof(void*);
-    const long long N = mode == GINN_B200_GROUPED_DW ? q.k : q.ncols;
-    const long long M = mode == GINN_B200_GROUPED_DX ? q.k : q.m;
-    max_n = N > max_n ? N : max_n;
-    sum_tiles128 += ((M + 127) / 128) * ((N + 127) / 128);
-  }
-  if (max_n == 0) return GINN_B200_OK;
-  const size_t desc_bytes = (static_cast<size_t>(ngroups) * sizeof(Problem) + 15) & ~size_t(15);
   unsigned char *h, *d;
-  if (int s = stage_alloc(ctx, desc_bytes + table_bytes, &h, &d)) return s;
-
-  // fp32 levels run on the gather front end of the 3xTF32 kernel (128 x 128 tiles); fp16 levels
-  // on the staged kernel.
-  const bool use_gather = dtype == GINN_B200_F32 && g_force_path.load() != PATH_STAGED;
-  int bn = 128;
-  if (!use_gather) {
-    if (max_n <= 32) bn = 32;
-    else if (max_n <= 64 || sum_tiles128 < ctx->num_sms) bn = 64;
-  }
-
-  Problem* hp = reinterpret_cast<Problem*>(h);
-  size_t off = desc_bytes;
-  int np = 0, tile = 0;
-  for (int g = 0; g < ngroups; ++g) {
-    const ginn_b200_group& q = groups[g];
-    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
-    const size_t tb = static_cast<size_t>(q.ncols) * sizeof(void*);
-    const void** h_t0 = reinterpret_cast<const void**>(h + off);
-    const void* const* d_t0 = reinterpret_cast<const void* const*>(d + off);
-    off += tb;
-    const void** h_t1 = reinterpret_cast<const void**>(h + off);
-    const void* const* d_t1 = reinterpret_cast<const void* const*>(d + off);
-    off += tb;
-    Problem& p = hp[np];
-    std::memset(&p, 0, sizeof(p));
-    p.npairs = 1;
-    p.batches = 1;
-    bool x_al = true, y_al = true;
-    if (mode == GINN_B200_GROUPED_FORWARD) {
-      for (int64_t j = 0; j < q.ncols; ++j) {
-        h_t0[j] = q.x_cols[j];
-        h_t1[j] = q.y_cols[j];
-        x_al = x_al && aligned16(q.x_cols[j]);
-      }
-      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 0);
-      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
-      p.b[0].cols = d_t0;
-      p.b[0].vec = x_al ? 1 : 0;
-      p.k[0] = q.k;
-      p.M = (int)q.m; p.N = (int)q.ncols;
-      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
-      p.bias = q.bias;
-      p.accumulate = q.accumulate ? 1 : 0;
-    } else if (mode == GINN_B200_GROUPED_DX) {
-      for (int64_t j = 0; j < q.ncols; ++j) {
-        h_t0[j] = q.y_cols[j];
-        h_t1[j] = q.dx_cols[j];
-        y_al = y_al && aligned16(q.y_cols[j]);
-      }
-      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 1);  // W^T: contraction over m
-      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
-      p.b[0].cols = d_t0;
-      p.b[0].vec = y_al ? 1 : 0;
-      p.k[0] = q.m;
-      p.M = (int)q.k; p.N = (int)q.ncols;
-      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
-      p.accumulate = 1;
-    } else {
-      for (int64_t j = 0; j < q.ncols; ++j) {
-        h_t0[j] = q.y_cols[j];
-        h_t1[j] = q.x_cols[j];
-      }
-      p.a[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // dy columns, contraction over j
-      p.a[0].cols = d_t0;
-      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // x columns
-      p.b[0].cols = d_t1;
-      p.k[0] = q.ncols;
-      p.M = (int)q.m; p.N = (int)q.k;
-      p.c = q.dw; p.ldc = q.lddw;
-      p.rowsum = q.dbias;
-      p.accumulate = 1;
-    }
-    p.tiles_m = (p.M + 127) / 128;
-    p.tiles_n = (p.N + bn - 1) / bn;
-    p.tile_start = tile;
-    if (use_gather)
-      p.split_k = gb::sgemm3x_pick_split(p, sum_tiles128, ctx->num_sms);
-    tile += p.tiles_m * p.tiles_n * (p.split_k > 1 ? p.split_k : 1);
-    ++np;
-  }
-  CU_TRY(cudaMemcpyAsync(d, h, off, cudaMemcpyHostToDevice, stream));
-  if (use_gather)
-    CU_TRY(gb::launch_sgemm3x_gather_grouped(reinterpret_cast<const Problem*>(d), np, tile, stream,
-                                             ctx->d_status));
-  else
-    CU_TRY(gb::launch_staged_grouped(dtype, reinterpret_cast<const Problem*>(d), np, tile, bn,
-                                     stream, ctx->d_status));
+  if (int s = stage_alloc(ctx, plan.bytes, &h, &d)) return s;
+  LevelLaunch ll = fill_level_image(dtype, mode, ngroups, groups, plan, ctx->num_sms, h, d);
+  CU_TRY(cudaMemcpyAsync(d, h, plan.bytes, cudaMemcpyHostToDevice, stream));
+  CU_TRY(launch_level(dtype, ll, reinterpret_cast<const Problem*>(d), stream, ctx->d_status));
   g_launches.fetch_add(1);
   return GINN_B200_OK;
 }
@@ -475,13 +506,9 @@ int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int
                              const ginn_b200_group* groups) {
   static std::mutex image_mu;
   alignas(16) static unsigned char image[gb::kGroupedStaticBytes];
-  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
-    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
-  if (mode < GINN_B200_GROUPED_FORWARD || mode > GINN_B200_GROUPED_DW)
-    return fail(GINN_B200_BAD_ARGUMENT, "unknown grouped mode %d", mode);
-  if (ngroups < 0 || (ngroups > 0 && groups == nullptr))
-    return fail(GINN_B200_BAD_ARGUMENT, "bad group list");
-  if (ngroups == 0) return GINN_B200_OK;
+  LevelPlan plan;
+  if (int s = plan_level(dtype, mode, ngroups, groups, &plan)) return s;
+  if (plan.live == 0) return GINN_B200_OK;
   if (device < 0 || device >= kMaxDevices)
     return fail(GINN_B200_BAD_ARGUMENT, "device index %d out of range", device);
   CU_TRY(cudaSetDevice(device));
@@ -490,123 +517,76 @@ int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int
   if (major != 10)
     return fail(GINN_B200_UNSUPPORTED, "device %d is not an sm_100 GPU", device);
   CU_TRY(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device));
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-
-  size_t table_bytes = 0;
-  long long max_n = 0, sum_tiles128 = 0;
-  int live = 0;
-  for (int g = 0; g < ngroups; ++g) {
-    const ginn_b200_group& q = groups[g];
-    if (q.m < 0 || q.k < 0 || q.ncols < 0 || q.m > 0x7fffffffLL || q.k > 0x7fffffffLL ||
-        q.ncols > 0x7fffffffLL)
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dimensions", g);
-    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
-    if (!q.w || q.ldw < q.m || !q.y_cols)
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad W or column table", g);
-    if ((mode != GINN_B200_GROUPED_DX && !q.x_cols) || (mode == GINN_B200_GROUPED_DX && !q.dx_cols))
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: missing column table for mode %d", g, mode);
-    if (mode == GINN_B200_GROUPED_DW && (!q.dw || q.lddw < q.m))
-      return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dW", g);
-    table_bytes += 2 * static_cast<size_t>(q.ncols) * sizeof(void*);
-    const long long N = mode == GINN_B200_GROUPED_DW ? q.k : q.ncols;
-    const long long M = mode == GINN_B200_GROUPED_DX ? q.k : q.m;
-    max_n = N > max_n ? N : max_n;
-    sum_tiles128 += ((M + 127) / 128) * ((N + 127) / 128);
-    ++live;
-  }
-  if (live == 0) return GINN_B200_OK;
-  const size_t desc_bytes = (static_cast<size_t>(live) * sizeof(Problem) + 15) & ~size_t(15);
-  const size_t need = desc_bytes + table_bytes;
-  if (need > gb::kGroupedStaticBytes)
+  if (plan.bytes > gb::kGroupedStaticBytes)
     return fail(GINN_B200_BAD_ARGUMENT,
                 "level too large for the allocation-free entry point: %zu bytes of descriptors "
                 "and column tables, limit %zu (%d groups, 16 bytes per column); split the level "
                 "or use ginn_b200_grouped",
-                need, gb::kGroupedStaticBytes, live);
+                plan.bytes, gb::kGroupedStaticBytes, plan.live);
   void* scratch = nullptr;
   CU_TRY(gb::grouped_static_scratch(device, &scratch));
-  unsigned char* d = static_cast<unsigned char*>(scratch);
-
-  const bool use_gather = dtype == GINN_B200_F32 && g_force_path.load() != PATH_STAGED;
-  int bn = 128;
-  if (!use_gather) {
-    if (max_n <= 32) bn = 32;
-    else if (max_n <= 64 || sum_tiles128 < num_sms) bn = 64;
-  }
-
   std::lock_guard<std::mutex> lock(image_mu);
-  Problem* hp = reinterpret_cast<Problem*>(image);
-  size_t off = desc_bytes;
-  int np = 0, tile = 0;
-  for (int g = 0; g < ngroups; ++g) {
-    const ginn_b200_group& q = groups[g];
-    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
-    const size_t tb = static_cast<size_t>(q.ncols) * sizeof(void*);
-    const void** t0 = reinterpret_cast<const void**>(image + off);
-    const void* const* d_t0 = reinterpret_cast<const void* const*>(d + off);
-    off += tb;
-    const void** t1 = reinterpret_cast<const void**>(image + off);
-    const void* const* d_t1 = reinterpret_cast<const void* const*>(d + off);
-    off += tb;
-    Problem& p = hp[np];
-    std::memset(&p, 0, sizeof(p));
-    p.npairs = 1;
-    p.batches = 1;
-    bool al = true;
-    if (mode == GINN_B200_GROUPED_FORWARD) {
-      for (int64_t j = 0; j < q.ncols; ++j) {
-        t0[j] = q.x_cols[j];
-        t1[j] = q.y_cols[j];
-        al = al && aligned16(q.x_cols[j]);
-      }
-      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 0);
-      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
-      p.b[0].cols = d_t0;
-      p.b[0].vec = al ? 1 : 0;
-      p.k[0] = q.k;
-      p.M = (int)q.m; p.N = (int)q.ncols;
-      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
-      p.bias = q.bias;
-      p.accumulate = q.accumulate ? 1 : 0;
-    } else if (mode == GINN_B200_GROUPED_DX) {
-      for (int64_t j = 0; j < q.ncols; ++j) {
-        t0[j] = q.y_cols[j];
-        t1[j] = q.dx_cols[j];
-        al = al && aligned16(q.y_cols[j]);
-      }
-      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 1);
-      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
-      p.b[0].cols = d_t0;
-      p.b[0].vec = al ? 1 : 0;
-      p.k[0] = q.m;
-      p.M = (int)q.k; p.N = (int)q.ncols;
-      p.ccols = reinterpret_cast<void* const*>(const_cast<void**>(reinterpret_cast<const void* const*>(d_t1)));
-      p.accumulate = 1;
-    } else {
-      for (int64_t j = 0; j < q.ncols; ++j) {
-        t0[j] = q.y_cols[j];
-        t1[j] = q.x_cols[j];
-      }
-      p.a[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);
-      p.a[0].cols = d_t0;
-      p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);
-      p.b[0].cols = d_t1;
-      p.k[0] = q.ncols;
-      p.M = (int)q.m; p.N = (int)q.k;
-      p.c = q.dw; p.ldc = q.lddw;
-      p.rowsum = q.dbias;
-      p.accumulate = 1;
-    }
-    p.tiles_m = (p.M + 127) / 128;
-    p.tiles_n = (p.N + bn - 1) / bn;
-    p.tile_start = tile;
-    if (use_gather) p.split_k = gb::sgemm3x_pick_split(p, sum_tiles128, num_sms);
-    tile += p.tiles_m * p.tiles_n * (p.split_k > 1 ? p.split_k : 1);
-    ++np;
-  }
-  CU_TRY(gb::launch_staged_grouped_static(dtype, image, off, scratch, np, tile, bn, use_gather,
-                                          stream));
+  LevelLaunch ll = fill_level_image(dtype, mode, ngroups, groups, plan, num_sms, image,
+                                    static_cast<unsigned char*>(scratch));
+  CU_TRY(gb::launch_staged_grouped_static(dtype, image, plan.bytes, scratch, ll.nprobs, ll.tiles,
+                                          ll.bn, ll.use_gather, static_cast<cudaStream_t>(stream_)));
   g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+// A level whose descriptors stay resident on the device: built once, launched many times.
+struct ginn_b200_level {
+  int device;
+  int dtype;
+  LevelLaunch ll;
+  unsigned char* d_image;
+};
+
+int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
+                           const ginn_b200_group* groups, ginn_b200_level** out) {
+  if (out == nullptr) return fail(GINN_B200_BAD_ARGUMENT, "null output handle");
+  *out = nullptr;
+  LevelPlan plan;
+  if (int s = plan_level(dtype, mode, ngroups, groups, &plan)) return s;
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  ginn_b200_level* lv = new ginn_b200_level{device, dtype, LevelLaunch{}, nullptr};
+  if (plan.live > 0) {
+    std::vector<unsigned char> h(plan.bytes);
+    cudaError_t e = cudaMalloc(&lv->d_image, plan.bytes);
+    if (e == cudaSuccess) {
+      lv->ll = fill_level_image(dtype, mode, ngroups, groups, plan, ctx->num_sms, h.data(),
+                                lv->d_image);
+      e = cudaMemcpy(lv->d_image, h.data(), plan.bytes, cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+      cudaFree(lv->d_image);
+      delete lv;
+      return fail(GINN_B200_CUDA_ERROR, "preparing a level failed: %s", cudaGetErrorString(e));
+    }
+  }
+  *out = lv;
+  return GINN_B200_OK;
+}
+
+int ginn_b200_level_run(ginn_b200_level* level, void* stream) {
+  if (level == nullptr) return fail(GINN_B200_BAD_ARGUMENT, "null level");
+  if (level->d_image == nullptr) return GINN_B200_OK;
+  DevCtx* ctx;
+  if (int s = get_ctx(level->device, &ctx)) return s;
+  CU_TRY(launch_level(level->dtype, level->ll, reinterpret_cast<const Problem*>(level->d_image),
+                      static_cast<cudaStream_t>(stream), ctx->d_status));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+int ginn_b200_level_destroy(ginn_b200_level* level) {
+  if (level == nullptr) return GINN_B200_OK;
+  if (level->d_image) {
+    cudaSetDevice(level->device);
+    cudaFree(level->d_image);
+  }
+  delete level;
   return GINN_B200_OK;
 }
 
@@ -628,6 +608,11 @@ int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "force_path") == 0) {
     if (value < 0 || value > 4) return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0..4");
     g_force_path.store(value);
+    return GINN_B200_OK;
+  }
+  if (name && std::strcmp(name, "sm_margin") == 0) {
+    if (value < 0 || value > 128) return fail(GINN_B200_BAD_ARGUMENT, "sm_margin must be 0..128");
+    g_sm_margin.store(value);
     return GINN_B200_OK;
   }
   return fail(GINN_B200_UNSUPPORTED, "unknown option '%s'", name ? name : "(null)");

@@ -1,0 +1,250 @@
+"""Harnesses for the benchmark configurations other than the large Half product.
+
+Each harness builds seeded synthetic inputs of its configuration's shapes, drives the products
+through the C ABI (ginn_b200.binding) and keeps everything that is not a matrix product --
+softmax, LSTM cell arithmetic, cross-entropy, Adam -- as plain torch elementwise "glue", which is
+excluded from the flop counts.  bench.py selects them with --workload.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import binding as B
+from .binding import GROUPED_DW, GROUPED_DX, GROUPED_FORWARD
+
+
+def _xavier(rows, cols, gen, device):
+    """ginn's Xavier: U(-a, a), a = sqrt(6 / (0.5 (rows + cols)))  (ginn/init/init.h:45-51)."""
+    a = math.sqrt(6.0 / (0.5 * (rows + cols)))
+    buf = (torch.rand(cols, rows, device=device, generator=gen) * 2 - 1) * a
+    return buf.T  # column-major rows x cols
+
+
+class Attention:
+    """Config 3: min-GPT attention through BatchedProd (examples/min-gpt.cu.cpp:108-157):
+    S = K' * Q, column softmax, O = V * P, and the four backward products; 256 (batch, head)
+    pairs, T = 256, head size 64, fp32."""
+
+    def __init__(self, device, T=256, hs=64, nb=256, seed=20243):
+        g = torch.Generator(device=device).manual_seed(seed)
+        sd = math.sqrt(1 / 8)
+
+        def cm(r, c, scale=1.0):
+            t = B.colmajor(r, c, torch.float32, device, batches=nb)
+            t.copy_(torch.randn(r, c, nb, device=device, generator=g) * scale)
+            return t
+
+        self.k, self.q, self.v = cm(T, hs, sd), cm(hs, T, sd), cm(hs, T, sd)
+        self.dO = cm(hs, T)
+        z = lambda r, c: B.colmajor(r, c, torch.float32, device, batches=nb, fill=0.0)
+        self.S, self.P, self.dP, self.dS = z(T, T), z(T, T), z(T, T), z(T, T)
+        self.O, self.dV, self.dQ, self.dK = z(hs, T), z(hs, T), z(hs, T), z(T, hs)
+        self.flops = 6 * nb * 2 * T * hs * T
+        self.units = nb
+
+    def step(self):
+        gb = B
+        for t in (self.dV, self.dQ, self.dK, self.dP):
+            t.zero_()
+        gb.gemm_batched(self.k, self.q, self.S)
+        self.P.copy_(torch.softmax(self.S, dim=0))
+        gb.gemm_batched(self.v, self.P, self.O)
+        gb.gemm_batched(self.dO, self.P, self.dV, trans_b=True, accumulate=True)
+        gb.gemm_batched(self.v, self.dO, self.dP, trans_a=True, accumulate=True)
+        self.dS.copy_(self.P * (self.dP - (self.P * self.dP).sum(dim=0, keepdim=True)))
+        gb.gemm_batched(self.dS, self.q, self.dK, trans_b=True, accumulate=True)
+        gb.gemm_batched(self.k, self.dS, self.dQ, trans_a=True, accumulate=True)
+
+
+class LstmAutobatch:
+    """Config 2 (recurrent variant): `nseq` sequences of length U{5..40}; per sequence and step
+    gates = Affine(W, [x_t; h_{t-1}], b) with one shared W (4H x (E+H)) -- the graph ginn's
+    Autobatch turns into one merged product per step.  Step t of every live sequence is one
+    grouped launch (forward, dX, dW); every column is addressed through the pointer tables, as the
+    nodes' own tensors would be.  Loss = sum of the final hidden states."""
+
+    def __init__(self, device, nseq=256, H=256, E=128, seed=20242, static=False):
+        g = torch.Generator(device=device).manual_seed(seed)
+        cpu_g = torch.Generator().manual_seed(seed)
+        lens = torch.randint(5, 41, (nseq,), generator=cpu_g).sort(descending=True).values
+        self.lens, self.H, self.E, self.nseq = lens, H, E, nseq
+        self.T = int(lens.max())
+        self.n = [int((lens > t).sum()) for t in range(self.T)]  # live sequences = a prefix
+        self.nodes = int(lens.sum())
+        self.W = _xavier(4 * H, E + H, g, device)
+        self.b = _xavier(4 * H, 1, g, device).reshape(-1).contiguous()
+        self.dW = B.colmajor(4 * H, E + H, torch.float32, device, fill=0.0)
+        self.db = torch.zeros(4 * H, device=device)
+        cm = lambda r, c: B.colmajor(r, c, torch.float32, device, fill=0.0)
+        self.XH = [cm(E + H, n) for n in self.n]
+        self.dXH = [cm(E + H, n) for n in self.n]
+        self.G = [cm(4 * H, n) for n in self.n]
+        self.dG = [cm(4 * H, n) for n in self.n]
+        self.c = [cm(H, n) for n in self.n]
+        self.h = [cm(H, n) for n in self.n]
+        for t in range(self.T):
+            self.XH[t][:E].copy_(torch.randn(E, self.n[t], device=device, generator=g))
+        self.XH[0][E:].copy_(torch.randn(H, self.n[0], device=device, generator=g))
+        self.flops = 3 * 2 * 4 * H * (E + H) * self.nodes
+        self.units = self.nodes
+        self.static = static
+        self.fwd = self.dx = self.dw = None
+        self.graph = None
+
+    def rewrite(self):
+        """The host-side part of autobatching: one prepared grouped call per level and pass."""
+        cols = lambda m: [m[:, j] for j in range(m.shape[1])]
+        mk = lambda mode, grp: B.GroupedCall(mode, [grp], static=self.static)
+        self.fwd, self.dx, self.dw = [], [], []
+        for t in range(self.T):
+            x, y, dy, dx = cols(self.XH[t]), cols(self.G[t]), cols(self.dG[t]), cols(self.dXH[t])
+            self.fwd.append(mk(GROUPED_FORWARD, B.Group(w=self.W, x_cols=x, y_cols=y, bias=self.b)))
+            self.dx.append(mk(GROUPED_DX, B.Group(w=self.W, y_cols=dy, dx_cols=dx)))
+            self.dw.append(mk(GROUPED_DW, B.Group(w=self.W, x_cols=x, y_cols=dy, dw=self.dW,
+                                                  dbias=self.db)))
+
+    def forward(self):
+        H, E = self.H, self.E
+        self.gates = []
+        for t in range(self.T):
+            self.fwd[t]()
+            G, n = self.G[t], self.n[t]
+            i, f, gg, o = (torch.sigmoid(G[:H]), torch.sigmoid(G[H:2 * H]), torch.tanh(G[2 * H:3 * H]),
+                           torch.sigmoid(G[3 * H:]))
+            c_prev = self.c[t - 1][:, :n] if t > 0 else torch.zeros_like(self.c[t])
+            self.c[t].copy_(f * c_prev + i * gg)
+            tc = torch.tanh(self.c[t])
+            self.h[t].copy_(o * tc)
+            self.gates.append((i, f, gg, o, tc, c_prev))
+            if t + 1 < self.T:
+                self.XH[t + 1][E:].copy_(self.h[t][:, :self.n[t + 1]])
+
+    def reset_grad(self):
+        self.dW.zero_()
+        self.db.zero_()
+        for d in self.dXH:
+            d.zero_()
+
+    def backward(self):
+        H, E = self.H, self.E
+        dh_next = dc_next = None  # gradients flowing from step t+1 (a prefix of the columns)
+        for t in reversed(range(self.T)):
+            n = self.n[t]
+            i, f, gg, o, tc, c_prev = self.gates[t]
+            dh = torch.zeros(H, n, device=self.W.device)
+            dc = torch.zeros(H, n, device=self.W.device)
+            if dh_next is not None:
+                dh[:, :dh_next.shape[1]] += dh_next
+                dc[:, :dc_next.shape[1]] += dc_next
+            ends = self.n[t + 1] if t + 1 < self.T else 0
+            dh[:, ends:] += 1.0                      # sequences that end here feed the loss
+            dc = dc + dh * o * (1 - tc * tc)
+            dG = self.dG[t]
+            dG[:H].copy_(dc * gg * i * (1 - i))
+            dG[H:2 * H].copy_(dc * c_prev * f * (1 - f))
+            dG[2 * H:3 * H].copy_(dc * i * (1 - gg * gg))
+            dG[3 * H:].copy_(dh * tc * o * (1 - o))
+            self.dx[t]()
+            self.dw[t]()
+            dh_next, dc_next = self.dXH[t][E:], dc * f
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+            return
+        self.forward()
+        self.reset_grad()
+        self.backward()
+
+    def capture(self):
+        """Records one forward + reset_grad + backward pass (prepared levels and glue) into a CUDA
+        graph; later steps replay it.  The prepared levels make no host-to-device copies, so
+        the capture holds only kernel launches."""
+        self.graph = None
+        side = torch.cuda.Stream(device=self.W.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step()  # warm up allocator and library state outside the capture
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward()
+            self.reset_grad()
+            self.backward()
+        self.graph = g
+
+
+class MlpDataParallel:
+    """Config 5: Affine+ReLU 784 -> 1024 -> 1024 -> 10, softmax cross-entropy summed over the
+    batch, Adam (lr 1e-3, per-element clip 5, eps 1e-8, betas 0.9/0.999: ginn/update/update.h:
+    92-133), 4096 columns per rank (the examples/mnist-dp.cu pattern, one process per GPU).
+    All gradients live in one flat buffer that is all-reduced once per step; every rank then
+    applies the same Adam update, so the replicas stay identical."""
+
+    DIMS = (784, 1024, 1024, 10)
+
+    def __init__(self, device, rank=0, world=1, batch=4096, allreduce=None):
+        gw = torch.Generator(device=device).manual_seed(123457)          # same weights everywhere
+        gd = torch.Generator(device=device).manual_seed(123457 + 1 + rank)  # own data per rank
+        d = self.DIMS
+        sizes = [d[i + 1] * d[i] for i in range(3)] + [d[i + 1] for i in range(3)]
+        total = sum(sizes)
+        self.params = torch.empty(total, device=device)
+        self.grads = torch.zeros(total, device=device)
+        self.m = torch.zeros(total, device=device)
+        self.v = torch.zeros(total, device=device)
+        views, gviews, off = [], [], 0
+        for n in sizes:
+            views.append(self.params[off:off + n])
+            gviews.append(self.grads[off:off + n])
+            off += n
+        cmv = lambda flat, r, c: torch.as_strided(flat, (r, c), (1, r))
+        self.W = [cmv(views[i], d[i + 1], d[i]) for i in range(3)]
+        self.dW = [cmv(gviews[i], d[i + 1], d[i]) for i in range(3)]
+        self.b, self.db = views[3:], gviews[3:]
+        for i in range(3):
+            self.W[i].copy_(_xavier(d[i + 1], d[i], gw, device))
+            self.b[i].copy_(_xavier(d[i + 1], 1, gw, device).reshape(-1))
+        self.x = B.colmajor(d[0], batch, torch.float32, device)
+        self.x.copy_(torch.rand(d[0], batch, device=device, generator=gd))
+        self.labels = torch.randint(0, 10, (batch,), device=device, generator=gd)
+        self.h = [self.x] + [B.colmajor(d[i + 1], batch, torch.float32, device, fill=0.0) for i in range(3)]
+        self.dh = [None] + [B.colmajor(d[i + 1], batch, torch.float32, device, fill=0.0) for i in range(3)]
+        self.acts = (B.ACT_RELU, B.ACT_RELU, B.ACT_NONE)
+        self.allreduce, self.world, self.batch, self.t = allreduce, world, batch, 0
+        self.loss = torch.zeros((), device=device)
+        fwd = sum(2 * d[i + 1] * d[i] * batch for i in range(3))
+        self.flops = 2 * fwd + sum(2 * d[i + 1] * d[i] * batch for i in (1, 2))  # fwd + dW + dX(2,3)
+        self.units = batch
+
+    def step(self):
+        gb = B
+        self.grads.zero_()
+        for i in (1, 2):
+            self.dh[i].zero_()
+        for i in range(3):
+            gb.affine_forward([gb.Pair(self.W[i], self.h[i])], self.b[i], self.acts[i], self.h[i + 1])
+        logits = self.h[3]
+        logp = torch.log_softmax(logits, dim=0)
+        cols = torch.arange(self.batch, device=logits.device)
+        self.loss = -logp[self.labels, cols].sum()
+        dlog = torch.exp(logp)
+        dlog[self.labels, cols] -= 1.0
+        self.dh[3].copy_(dlog)
+        for i in (2, 1, 0):
+            gb.affine_backward([gb.PairGrad(self.W[i], self.h[i], self.dW[i],
+                                            self.dh[i] if i > 0 else None)],
+                               self.dh[i + 1], self.h[i + 1], self.acts[i], self.db[i])
+        if self.allreduce is not None and self.world > 1:
+            self.allreduce(self.grads)
+        # Adam on the flat buffers (glue)
+        self.t += 1
+        g = self.grads.clamp_(-5.0, 5.0)
+        self.m.mul_(0.9).add_(g, alpha=0.1)
+        self.v.mul_(0.999).addcmul_(g, g, value=0.001)
+        mhat = self.m / (1 - 0.9 ** self.t)
+        vhat = self.v / (1 - 0.999 ** self.t)
+        self.params.addcdiv_(mhat, vhat.sqrt_().add_(1e-8), value=-1e-3)

@@ -150,6 +150,20 @@ int ginn_b200_grouped(int device, void* stream, int dtype, int mode, int ngroups
 int ginn_b200_grouped_static(int device, void* stream, int dtype, int mode, int ngroups,
                              const ginn_b200_group* groups);
 
+/* A level prepared once and launched many times -- the schedule cache ginn's Autobatch lacks: the
+ * reference rebuilds RowwiseCat / Prod / RowwiseUncat nodes and re-copies every column on each
+ * evaluation (ginn/autobatch.h:149-183, ginn/node/layout.h:227-241).  ginn_b200_level_create
+ * validates the groups and keeps descriptors and column tables resident in device memory;
+ * ginn_b200_level_run is then a single kernel launch with no host-to-device copy, so it can
+ * also be captured in a CUDA graph.  The tensors named by the groups must stay where they are
+ * while the level is in use (the nodes of a re-evaluated ginn graph do).  Create and destroy
+ * synchronise with the device; run does not. */
+typedef struct ginn_b200_level ginn_b200_level;
+int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
+                           const ginn_b200_group* groups, ginn_b200_level** out);
+int ginn_b200_level_run(ginn_b200_level* level, void* stream);
+int ginn_b200_level_destroy(ginn_b200_level* level);
+
 /* Text of the last failure on the calling thread ("" if none). */
 const char* ginn_b200_last_error(void);
 
@@ -163,6 +177,8 @@ int ginn_b200_version(void);
 /* Test / benchmark knobs.  "force_path": 0 = automatic, 1 = staged tcgen05 kernel,
  * 2 = one-CTA TMA fp16 kernel, 4 = CTA-pair fp16 kernel (both fall back to automatic when not
  * applicable), 3 = CUDA-core kernel.
+ * "sm_margin": number of SMs the persistent fp16 kernels leave unoccupied (default 0), so that a
+ * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles.
  * Returns GINN_B200_UNSUPPORTED for unknown names. */
 int ginn_b200_set_option(const char* name, int value);
 

@@ -81,3 +81,32 @@ def test_many_levels_reuse_the_staging_ring(gpu):
         gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=ys, bias=g["bias"])])
     torch.cuda.synchronize()
     check(np.stack([B.to_host(t) for t in ys], 1), ref, np.float32)
+
+
+def test_prepared_level_equals_one_shot_call_and_survives_reuse(gpu):
+    """ginn_b200_level_create / run: same result as ginn_b200_grouped, launch after launch."""
+    rng = np.random.default_rng(44)
+    groups, host = make_level(rng, [(1024, 384, 33), (96, 40, 7)])
+    ys = [[torch.zeros(g["w"].shape[0], device="cuda") for _ in g["x"]] for g in groups]
+    level = gpu.GroupedCall(GROUPED_FORWARD, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=y, bias=g["bias"])
+                                              for g, y in zip(groups, ys)])
+    for rep in range(3):
+        for y in ys:
+            for t in y:
+                t.fill_(float("nan"))
+        level()
+        torch.cuda.synchronize()
+        for (W, bias, xs, _), y in zip(host, ys):
+            check(np.stack([B.to_host(t) for t in y], 1),
+                  orc.affine_forward([(W, np.stack(xs, 1))], bias, 0), np.float32, f"rep {rep}")
+    dws = [B.colmajor(*g["w"].shape, torch.float32, fill=0.0) for g in groups]
+    dbs = [torch.zeros(g["w"].shape[0], device="cuda") for g in groups]
+    dw_level = gpu.GroupedCall(GROUPED_DW, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=g["dy"], dw=dw, dbias=db)
+                                            for g, dw, db in zip(groups, dws, dbs)])
+    dw_level()
+    dw_level()      # gradients accumulate across launches
+    torch.cuda.synchronize()
+    for (W, bias, xs, dys), dw, db in zip(host, dws, dbs):
+        X, DY = np.stack(xs, 1), np.stack(dys, 1)
+        check(B.to_host(dw), 2 * orc.gemm(DY, X, trans_b=True), np.float32, "dW")
+        check(B.to_host(db), 2 * DY.astype(np.float64).sum(1), np.float32, "dbias")
