@@ -30,9 +30,9 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one hgemm_tma_kernel launch at 8192^3, from the
-# ncu capture summarised in profiles/hgemm_tma_prod8192.md (mean of the captured launches).
-NCU_TRAFFIC_BYTES = {8192: 1.245e9}
+# dram__bytes_read.sum + dram__bytes_write.sum of one hgemm_pair_kernel launch at 8192^3, from the
+# ncu capture summarised in profiles/hgemm_pair_prod8192.md (mean of the three captured launches).
+NCU_TRAFFIC_BYTES = {8192: 1.551e9}
 
 METRIC = "prod_fwd_bwd_tflops"
 UNIT = "TFLOP/s"

@@ -610,6 +610,11 @@ int ginn_b200_set_option(const char* name, int value) {
     g_force_path.store(value);
     return GINN_B200_OK;
   }
+  if (name && std::strcmp(name, "pair_group_m") == 0) {
+    if (value < 0 || value > 1024) return fail(GINN_B200_BAD_ARGUMENT, "pair_group_m must be 0..1024");
+    gb::g_pair_group_m = value;
+    return GINN_B200_OK;
+  }
   if (name && std::strcmp(name, "sm_margin") == 0) {
     if (value < 0 || value > 128) return fail(GINN_B200_BAD_ARGUMENT, "sm_margin must be 0..128");
     g_sm_margin.store(value);

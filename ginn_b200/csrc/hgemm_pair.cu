@@ -29,7 +29,6 @@ constexpr int PA_BYTES = 128 * PBK * 2;          // 16 KiB: this CTA's A rows
 constexpr int PB_BYTES = 128 * PBK * 2;          // 16 KiB: this CTA's half of B
 constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
 constexpr int PATOM_BYTES = 64 * PBK * 2;        // one 64 x 64 box of an MN-major operand
-constexpr int PGROUP_M = 8;                      // m-tiles per rasterisation group
 constexpr int PEPI_PITCH = 36;
 constexpr int PEPI_WARP_BYTES = 32 * PEPI_PITCH * 4;
 constexpr int PEPI_BYTES = 4 * PEPI_WARP_BYTES;
@@ -41,6 +40,7 @@ struct PParams {
   int accumulate;
   int vec_c;
   int tiles_m, tiles_n, total_tiles;
+  int group_m;  // m-tiles per rasterisation group (L2 reuse of the A rows across waves)
 };
 
 __device__ __forceinline__ void pair_decode_tile(const PParams& p, int t, int& m_idx, int& n_idx,
@@ -48,10 +48,10 @@ __device__ __forceinline__ void pair_decode_tile(const PParams& p, int t, int& m
   const int per_batch = p.tiles_m * p.tiles_n;
   batch = t / per_batch;
   const int r = t % per_batch;
-  const int group_span = PGROUP_M * p.tiles_n;
+  const int group_span = p.group_m * p.tiles_n;
   const int g = r / group_span;
-  const int first_m = g * PGROUP_M;
-  const int gm = min(PGROUP_M, p.tiles_m - first_m);
+  const int first_m = g * p.group_m;
+  const int gm = min(p.group_m, p.tiles_m - first_m);
   const int in_g = r % group_span;
   m_idx = first_m + in_g % gm;
   n_idx = in_g / gm;
@@ -314,6 +314,8 @@ cudaError_t launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, co
 
 }  // namespace
 
+int g_pair_group_m = 0;  // tuning knob (0 = default)
+
 bool hgemm_pair_supported(const HgemmArgs& a) {
   if (!hgemm_tma_supported(a)) return false;
   // 16-byte accesses to C keep the two epilogues cheap; fall back to the one-CTA kernel otherwise.
@@ -344,6 +346,7 @@ cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, cudaStream_t stre
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batches;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   p.total_tiles = static_cast<int>(total);
+  p.group_m = g_pair_group_m > 0 ? g_pair_group_m : 8;
   if (!a.transA && !a.transB) return launch_pair_variant<1, 0>(ta, tb, p, num_sms, stream, status);
   if (a.transA && !a.transB) return launch_pair_variant<0, 0>(ta, tb, p, num_sms, stream, status);
   return launch_pair_variant<1, 1>(ta, tb, p, num_sms, stream, status);

@@ -38,6 +38,7 @@ bool hgemm_tma_supported(const HgemmArgs& a);
 cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
 
 // --- fp16 kernel on CTA pairs, 256 x 256 tiles (hgemm_pair.cu) ---
+extern int g_pair_group_m;
 bool hgemm_pair_supported(const HgemmArgs& a);
 cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
 
