@@ -276,21 +276,54 @@ def run_gpu(args):
         hC, hdA, hdB = (torch.empty(n * n, dtype=torch.float16).pin_memory() for _ in range(3))
         hA.copy_(A.T.reshape(-1).cpu()); hB.copy_(Bm.T.reshape(-1).cpu()); hdC.copy_(dC.T.reshape(-1).cpu())
 
+        # Copies run on their own streams so that they overlap the products inside a step:
+        # dC arrives while C = A*B runs, C leaves while the two backward products run.
+        h2d, d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
         def e2e_step():
-            A.T.reshape(-1).copy_(hA, non_blocking=True)
-            Bm.T.reshape(-1).copy_(hB, non_blocking=True)
-            dC.T.reshape(-1).copy_(hdC, non_blocking=True)
-            step()
-            hC.copy_(Cm.T.reshape(-1), non_blocking=True)
-            hdA.copy_(dA.T.reshape(-1), non_blocking=True)
-            hdB.copy_(dB.T.reshape(-1), non_blocking=True)
+            start = torch.cuda.Event()
+            start.record(main)                      # previous step's products and copies are queued
+            h2d.wait_event(start)
+            d2h_prev = torch.cuda.Event()
+            d2h_prev.record(d2h)
+            main.wait_event(d2h_prev)               # results of the previous step have left
+            ev_ab, ev_dc, ev_c = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+            with torch.cuda.stream(h2d):
+                A.T.reshape(-1).copy_(hA, non_blocking=True)
+                Bm.T.reshape(-1).copy_(hB, non_blocking=True)
+                ev_ab.record(h2d)
+                dC.T.reshape(-1).copy_(hdC, non_blocking=True)
+                ev_dc.record(h2d)
+            main.wait_event(ev_ab)
+
+            def after(i):
+                if i == 0:
+                    ev_c.record(main)
+                    main.wait_event(ev_dc)
+                    d2h.wait_event(ev_c)
+                    with torch.cuda.stream(d2h):
+                        hC.copy_(Cm.T.reshape(-1), non_blocking=True)
+
+            prod.step(A, Bm, dC, Cm, dA, dB, between=after)
+            done = torch.cuda.Event()
+            done.record(main)
+            d2h.wait_event(done)
+            with torch.cuda.stream(d2h):
+                hdA.copy_(dA.T.reshape(-1), non_blocking=True)
+                hdB.copy_(dB.T.reshape(-1), non_blocking=True)
+
+        def e2e_finish():
+            main.wait_stream(d2h)
+            main.wait_stream(h2d)
 
         e2e_step()
+        e2e_finish()
         barrier()
         k = max(1, min(args.steps, 5))
         e0.record()
         for _ in range(k):
             e2e_step()
+        e2e_finish()
         e1.record()
         barrier()
         ms_e = e0.elapsed_time(e1) / k

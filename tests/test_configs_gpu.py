@@ -144,3 +144,31 @@ def test_config2_lstm_gate_levels(gpu):
             db_ref += DG.sum(1)
     check(B.to_host(dW), dW_ref, np.float32, "dW over levels")
     check(B.to_host(db), db_ref, np.float32, "db over levels")
+
+
+def test_lstm_harness_matches_autograd(gpu):
+    """The benchmark's autobatched LSTM harness (grouped launches + elementwise glue) against
+    torch autograd in fp64 on the same small problem: dW and db of the shared gate weights."""
+    from ginn_b200.workloads import LstmAutobatch
+    w = LstmAutobatch(torch.device("cuda", 0), nseq=9, H=32, E=16, seed=3)
+    w.rewrite()
+    w.step()
+    torch.cuda.synchronize()
+    H, E = w.H, w.E
+    W = w.W.double().clone().requires_grad_(True)
+    b = w.b.double().clone().requires_grad_(True)
+    h = w.XH[0][E:].double()
+    c = torch.zeros(H, w.n[0], dtype=torch.float64, device="cuda")
+    loss = 0.0
+    for t in range(w.T):
+        n = w.n[t]
+        xh = torch.cat([w.XH[t][:E].double(), h[:, :n]], 0)
+        G = W @ xh + b[:, None]
+        i, f, g, o = torch.sigmoid(G[:H]), torch.sigmoid(G[H:2 * H]), torch.tanh(G[2 * H:3 * H]), torch.sigmoid(G[3 * H:])
+        c = f * c[:, :n] + i * g
+        h = o * torch.tanh(c)
+        ends = w.n[t + 1] if t + 1 < w.T else 0
+        loss = loss + h[:, ends:].sum()
+    loss.backward()
+    check(B.to_host(w.dW), W.grad.cpu().numpy(), np.float32, "dW")
+    check(B.to_host(w.db), b.grad.cpu().numpy(), np.float32, "db")
