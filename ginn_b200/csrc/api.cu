@@ -40,12 +40,15 @@ int fail(int status, const char* fmt, ...) {
 
 constexpr int kMaxDevices = 64;
 constexpr size_t kStageBytes = 8u << 20;
+constexpr unsigned kCounters = 64;  // launches in flight at once that need their own counter
 
 struct DevCtx {
   std::mutex mu;
   bool ready = false;
   int num_sms = 0;
   int* d_status = nullptr;
+  int* d_counters = nullptr;     // tile-queue counters of the persistent fp16 kernel, round robin
+  unsigned next_counter = 0;
   // staging ring for grouped launches (problem descriptors + pointer tables)
   unsigned char* h_stage = nullptr;
   unsigned char* d_stage = nullptr;
@@ -69,6 +72,8 @@ int get_ctx(int device, DevCtx** out) {
     CU_TRY(cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, device));
     CU_TRY(cudaMalloc(&c.d_status, sizeof(int)));
     CU_TRY(cudaMemset(c.d_status, 0, sizeof(int)));
+    CU_TRY(cudaMalloc(&c.d_counters, kCounters * sizeof(int)));
+    CU_TRY(cudaMemset(c.d_counters, 0, kCounters * sizeof(int)));
     c.ready = true;
   }
   *out = &c;
@@ -107,7 +112,7 @@ int persistent_sms(const DevCtx* ctx) {
 enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3, PATH_PAIR = 4 };
 
 // Runs one Problem on the staged tcgen05 kernel or the CUDA-core kernel.
-int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
+int run_problem_once(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0 || p.batches <= 0) return GINN_B200_OK;
   long long ktot = 0;
   for (int i = 0; i < p.npairs; ++i) ktot += p.k[i];
@@ -131,6 +136,64 @@ int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
     CU_TRY(gb::launch_staged(dtype, p, bn, stream, ctx->d_status));
   }
   g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+// Operand restricted to contraction indices [k0, ...): only for operands without column tables.
+Operand shift_k(const Operand& o, int dtype, long long k0) {
+  Operand r = o;
+  const long long step = (o.k_contig ? 1 : o.ld) * k0 * esize(dtype);
+  r.base = static_cast<const char*>(o.base) + step;
+  if (o.ybase) r.ybase = static_cast<const char*>(o.ybase) + step;
+  if (r.vec && !aligned16(r.base)) r.vec = 0;
+  return r;
+}
+
+// fp32 accuracy guard.  The 3xTF32 kernels keep the 1e-5 bound for contractions of up to
+// kMaxChainK per launch (their accumulation chain is cut four ways, but the tensor core still
+// truncates on every add).  Longer contractions are issued as several launches that accumulate
+// into C, so each partial result is rounded to nearest in memory; bias goes with the first
+// launch, the activation with the last.
+constexpr long long kMaxChainK = 8192;
+
+int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
+  bool chain = dtype == GINN_B200_F32 && g_force_path.load() != PATH_SMALL;
+  long long kmax = 0, ktot = 0;
+  for (int i = 0; i < p.npairs; ++i) {
+    kmax = p.k[i] > kmax ? p.k[i] : kmax;
+    ktot += p.k[i];
+    if (p.a[i].cols || p.b[i].cols) chain = false;
+  }
+  if (!chain || ktot <= kMaxChainK) return run_problem_once(ctx, dtype, p, stream);
+  struct Piece { int pair; long long k0, k; };
+  std::vector<Piece> pieces;
+  for (int i = 0; i < p.npairs; ++i)
+    for (long long k0 = 0; k0 < p.k[i]; k0 += kMaxChainK)
+      pieces.push_back({i, k0, p.k[i] - k0 < kMaxChainK ? p.k[i] - k0 : kMaxChainK});
+  size_t at = 0;
+  bool first = true;
+  while (at < pieces.size()) {
+    Problem q = p;
+    q.npairs = 0;
+    long long ksum = 0;
+    while (at < pieces.size() && q.npairs < gb::kMaxPairs && ksum + pieces[at].k <= kMaxChainK &&
+           !(pieces[at].pair == 0 && q.npairs > 0)) {  // pair 0 leads a launch: it carries rowsum
+      const Piece& pc = pieces[at];
+      q.a[q.npairs] = shift_k(p.a[pc.pair], dtype, pc.k0);
+      q.b[q.npairs] = shift_k(p.b[pc.pair], dtype, pc.k0);
+      q.k[q.npairs] = pc.k;
+      ksum += pc.k;
+      ++q.npairs;
+      ++at;
+    }
+    const bool last = at == pieces.size();
+    q.rowsum = (pieces[at - q.npairs].pair == 0) ? p.rowsum : nullptr;
+    q.bias = first ? p.bias : nullptr;
+    q.accumulate = first ? p.accumulate : 1;
+    q.act = last ? p.act : gb::ACT_NONE;
+    if (int s = run_problem_once(ctx, dtype, q, stream)) return s;
+    first = false;
+  }
   return GINN_B200_OK;
 }
 
@@ -181,7 +244,12 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
     const bool big_pair = big && m >= 256 && n >= 256 &&
                           ((m + 255) / 256) * ((n + 255) / 256) * batches >= ctx->num_sms / 4;
     if ((force == PATH_PAIR || (force == PATH_AUTO && big_pair)) && gb::hgemm_pair_supported(h)) {
-      CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), stream, ctx->d_status));
+      int* counter;
+      {
+        std::lock_guard<std::mutex> g(ctx->mu);
+        counter = ctx->d_counters + (ctx->next_counter++ % kCounters);
+      }
+      CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), counter, stream, ctx->d_status));
       g_launches.fetch_add(1);
       return GINN_B200_OK;
     }

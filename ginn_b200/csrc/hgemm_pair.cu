@@ -32,6 +32,11 @@ constexpr int PATOM_BYTES = 64 * PBK * 2;        // one 64 x 64 box of an MN-maj
 constexpr int PEPI_PITCH = 36;
 constexpr int PEPI_WARP_BYTES = 32 * PEPI_PITCH * 4;
 constexpr int PEPI_BYTES = 4 * PEPI_WARP_BYTES;
+// Ring through which the even CTA's producer announces tile numbers to every other role of the
+// pair.  Depth: the producer is never more than three tiles ahead of the slowest reader (the
+// six-stage ring holds less than one tile, the MMA warp runs at most two accumulators ahead
+// of the epilogues), so eight slots cannot be overrun.
+constexpr int PSCHED = 8;
 
 struct PParams {
   __half* C;
@@ -41,6 +46,11 @@ struct PParams {
   int vec_c;
   int tiles_m, tiles_n, total_tiles;
   int group_m;  // m-tiles per rasterisation group (L2 reuse of the A rows across waves)
+  // Work queue: tiles [0, #pairs) are taken statically, every further tile is claimed with an
+  // atomic add on *counter (zeroed before the launch).  A pair that starts late -- because
+  // another kernel, e.g. an NCCL collective, holds its SMs for a while -- then simply finds
+  // fewer tiles left instead of delaying the end of the launch.
+  int* counter;
 };
 
 __device__ __forceinline__ void pair_decode_tile(const PParams& p, int t, int& m_idx, int& n_idx,
@@ -66,6 +76,8 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __shared__ __align__(8) uint64_t empty_bar[PSTAGES];  // one per CTA
   __shared__ __align__(8) uint64_t acc_full[2];         // one per CTA
   __shared__ __align__(8) uint64_t acc_empty[2];        // used in the even CTA (8 arrivals)
+  __shared__ __align__(8) uint64_t sched_full[PSCHED];  // one per CTA: tile number announced
+  __shared__ int tile_ring[PSCHED];
   __shared__ uint32_t tmem_slot;
 
   const int warp = threadIdx.x >> 5;
@@ -91,6 +103,7 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         mbar_init(smem_u32(&acc_full[a]), 1);
         mbar_init(smem_u32(&acc_empty[a]), 8);
       }
+      for (int i = 0; i < PSCHED; ++i) mbar_init(smem_u32(&sched_full[i]), 1);
       fence_mbar_init();
     }
     __syncwarp();
@@ -103,13 +116,36 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
+  // Tile number of this pair's i-th tile, as announced by the even CTA's producer (-1 = none).
+  auto announced_tile = [&](int i) -> int {
+    const int slot = i % PSCHED;
+    if (!mbar_wait_cluster(smem_u32(&sched_full[slot]), (i / PSCHED) & 1u, status,
+                           DEV_TIMEOUT_FULL, 0x400 + (i & 0xff)))
+      return -1;
+    return *reinterpret_cast<volatile int*>(&tile_ring[slot]);
+  };
+  // Even CTA's producer: claim the i-th tile and announce it to both CTAs.
+  auto claim_tile = [&](int i) -> int {
+    int t = cluster_id;
+    if (i > 0) t = nclusters + atomicAdd(p.counter, 1);
+    if (t >= p.total_tiles) t = -1;
+    const int slot = i % PSCHED;
+    *reinterpret_cast<volatile int*>(&tile_ring[slot]) = t;
+    st_shared_remote(mapa_shared(smem_u32(&tile_ring[slot]), 1), static_cast<uint32_t>(t));
+    mbar_arrive(smem_u32(&sched_full[slot]));
+    mbar_arrive_remote(mapa_shared(smem_u32(&sched_full[slot]), 1));
+    return t;
+  };
+
   if (warp == 0) {
     // ===================== TMA producer (both CTAs) =====================
     if (elect_one()) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = cluster_id; t < p.total_tiles && ok; t += nclusters) {
+      for (int i = 0; ok; ++i) {
+        const int t = rank == 0 ? claim_tile(i) : announced_tile(i);
+        if (t < 0) break;
         int m_idx, n_idx, batch;
         pair_decode_tile(p, t, m_idx, n_idx, batch);
         const int m0 = m_idx * PBM + static_cast<int>(rank) * 128;
@@ -152,7 +188,8 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      for (int t = cluster_id; t < p.total_tiles && ok; t += nclusters, ++it) {
+      for (; ok; ++it) {
+        if (announced_tile(it) < 0) break;
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1u;
         if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_ph ^ 1u, status, DEV_TIMEOUT_TMEM_FREE, it)) {
@@ -196,7 +233,9 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
-    for (int t = cluster_id; t < p.total_tiles && ok; t += nclusters, ++it) {
+    for (; ok; ++it) {
+      const int t = announced_tile(it);
+      if (t < 0) break;
       int m_idx, n_idx, batch;
       pair_decode_tile(p, t, m_idx, n_idx, batch);
       const int acc = it & 1;
@@ -323,7 +362,8 @@ bool hgemm_pair_supported(const HgemmArgs& a) {
          (a.batches == 1 || a.strideC % 8 == 0);
 }
 
-cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status) {
+cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int* counter, cudaStream_t stream,
+                              int* status) {
   const unsigned long long a_rows = a.transA ? a.K : a.M, a_cols = a.transA ? a.M : a.K;
   const unsigned long long b_rows = a.transB ? a.N : a.K, b_cols = a.transB ? a.K : a.N;
   const unsigned long long sa = a.batches > 1 ? a.strideA : a.lda * a_cols;
@@ -347,6 +387,9 @@ cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, cudaStream_t stre
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   p.total_tiles = static_cast<int>(total);
   p.group_m = g_pair_group_m > 0 ? g_pair_group_m : 8;
+  p.counter = counter;
+  cudaError_t ce = cudaMemsetAsync(counter, 0, sizeof(int), stream);
+  if (ce != cudaSuccess) return ce;
   if (!a.transA && !a.transB) return launch_pair_variant<1, 0>(ta, tb, p, num_sms, stream, status);
   if (a.transA && !a.transB) return launch_pair_variant<0, 0>(ta, tb, p, num_sms, stream, status);
   return launch_pair_variant<1, 1>(ta, tb, p, num_sms, stream, status);

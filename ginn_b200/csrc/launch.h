@@ -40,7 +40,10 @@ cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t strea
 // --- fp16 kernel on CTA pairs, 256 x 256 tiles (hgemm_pair.cu) ---
 extern int g_pair_group_m;
 bool hgemm_pair_supported(const HgemmArgs& a);
-cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
+// `counter`: one int of device memory for the launch's tile queue (zeroed by the launcher on
+// `stream`); launches that may overlap on the GPU need different counters.
+cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int* counter, cudaStream_t stream,
+                              int* status);
 
 // --- tensor maps (defined in hgemm_tma.cu) ---
 bool encode_tmap(::CUtensorMap_st* out, int esize, const void* ptr, unsigned long long d0,

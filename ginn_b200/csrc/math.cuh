@@ -1,0 +1,58 @@
+// Scalar device helpers shared by every kernel: storage conversion, the fused nonlinearities
+// and the TF32 split.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "problem.h"
+
+namespace gb {
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+template <typename T>
+__device__ __forceinline__ T from_f(float x);
+template <>
+__device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+
+// Forward nonlinearities, following ginn/nonlin.h:93-95 (tanh), :116-118 (relu), :136-145 (sigmoid;
+// fp32 uses 0.5*tanh(0.5x)+0.5, Half the sign-split exponential form).  T is the storage type.
+template <typename T>
+__device__ __forceinline__ float act_forward(int act, float x) {
+  switch (act) {
+    case ACT_TANH: return tanhf(x);
+    case ACT_RELU: return fmaxf(x, 0.f);
+    case ACT_SIGMOID:
+      if (sizeof(T) == 2) {
+        if (x > 0.f) return 1.f / (1.f + expf(-x));
+        const float e = expf(x);
+        return e / (1.f + e);
+      }
+      return 0.5f * tanhf(0.5f * x) + 0.5f;
+    default: return x;
+  }
+}
+// Derivative times upstream gradient, expressed through the output y
+// (ginn/nonlin.h:96-106, :119-126, :146-152).
+template <typename T>
+__device__ __forceinline__ float act_backward(int act, float y, float dy) {
+  switch (act) {
+    case ACT_TANH: return sizeof(T) == 2 ? dy - y * y * dy : (1.f - y * y) * dy;
+    case ACT_RELU: return y > 0.f ? dy : 0.f;
+    case ACT_SIGMOID: return y * (1.f - y) * dy;
+    default: return dy;
+  }
+}
+
+// hi = round-to-nearest TF32 of x; lo = x - hi (exact in fp32; the tensor core keeps the top 11
+// significant bits of it).  Non-finite values stay in the hi plane only: inf - inf would poison
+// the lo plane.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  hi = __uint_as_float(u);
+  lo = ((u & 0x7f800000u) == 0x7f800000u) ? 0.f : x - hi;
+}
+
+}  // namespace gb

@@ -209,6 +209,36 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
 }
+// Bounded wait with cluster-scope acquire: for barriers whose arrival publishes plain stores made
+// by the peer CTA (mbar_arrive_remote releases at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status,
+                                                  int code, int detail) {
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      uint32_t ok;
+      asm volatile(
+          "{\n"
+          ".reg .pred P;\n"
+          "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n"
+          "selp.u32 %0, 1, 0, P;\n"
+          "}\n"
+          : "=r"(ok)
+          : "r"(bar), "r"(parity)
+          : "memory");
+      if (ok) return true;
+    }
+    if (clock64() - t0 > kWaitLimitCycles) {
+      record_error(status, code, detail);
+      return false;
+    }
+  }
+}
+// 32-bit store into another CTA's shared memory (address from mapa_shared).
+__device__ __forceinline__ void st_shared_remote(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 // TMA load into this CTA's shared memory whose completion is counted on an mbarrier that may
 // live in the peer CTA (cluster address).
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap,

@@ -19,6 +19,7 @@
 #include <cuda.h>
 #include <cstring>
 #include "ptx.cuh"
+#include "math.cuh"
 #include "launch.h"
 
 namespace gb {
@@ -57,32 +58,6 @@ struct SParams {
   int batches;
 };
 
-__device__ __forceinline__ float act_forward(int act, float x) {
-  switch (act) {
-    case ACT_TANH: return tanhf(x);
-    case ACT_RELU: return fmaxf(x, 0.f);
-    case ACT_SIGMOID: return 0.5f * tanhf(0.5f * x) + 0.5f;
-    default: return x;
-  }
-}
-__device__ __forceinline__ float act_backward(int act, float y, float dy) {
-  switch (act) {
-    case ACT_TANH: return (1.f - y * y) * dy;
-    case ACT_RELU: return y > 0.f ? dy : 0.f;
-    case ACT_SIGMOID: return y * (1.f - y) * dy;
-    default: return dy;
-  }
-}
-
-// hi = round-to-nearest TF32 of x; lo = x - hi (exact in fp32; the tensor core keeps its top
-// 11 significant bits).  Non-finite values stay in the hi plane only.
-__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  hi = __uint_as_float(u);
-  lo = ((u & 0x7f800000u) == 0x7f800000u) ? 0.f : x - hi;
-}
-
 // Transform of a k-contiguous raw slice: it already is K-major and swizzled (TMA box 32 k x 128
 // outer with the 128-byte swizzle), so hi and lo go to the same offsets of their planes.
 // 256 threads, 4 pieces of 16 bytes each.
@@ -95,10 +70,10 @@ __device__ __forceinline__ void transform_kc(const uint8_t* src, const uint8_t* 
     float4 x = *reinterpret_cast<const float4*>(src + off);
     if (HAS_Y) {
       const float4 y = *reinterpret_cast<const float4*>(ysrc + off);
-      x.x = act_backward(dact, y.x, x.x);
-      x.y = act_backward(dact, y.y, x.y);
-      x.z = act_backward(dact, y.z, x.z);
-      x.w = act_backward(dact, y.w, x.w);
+      x.x = act_backward<float>(dact, y.x, x.x);
+      x.y = act_backward<float>(dact, y.y, x.y);
+      x.z = act_backward<float>(dact, y.z, x.z);
+      x.w = act_backward<float>(dact, y.w, x.w);
     }
     float4 h, l;
     split_tf32(x.x, h.x, l.x);
@@ -128,7 +103,7 @@ __device__ __forceinline__ float transform_oc(const uint8_t* src, const uint8_t*
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       x[e] = col[(kbase + 4 * c + e) * 32];
-      if (HAS_Y) x[e] = act_backward(dact, ycol[(kbase + 4 * c + e) * 32], x[e]);
+      if (HAS_Y) x[e] = act_backward<float>(dact, ycol[(kbase + 4 * c + e) * 32], x[e]);
     }
     sum += (x[0] + x[1]) + (x[2] + x[3]);
     float4 h, l;
@@ -389,7 +364,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
               if (split_k)
                 atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
               else
-                *dst = act_forward(p.act, acc[j]);
+                *dst = act_forward<float>(p.act, acc[j]);
             }
           }
         }
@@ -724,7 +699,7 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
             if (split_k)
               atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
             else
-              *dst = act_forward(P.act, acc[j]);
+              *dst = act_forward<float>(P.act, acc[j]);
           }
         }
       }

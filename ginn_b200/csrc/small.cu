@@ -5,6 +5,7 @@
 //   * the bias gradient alone (row sums of dY (.) act'(Y)) when no weight gradient is wanted.
 // fp32 accumulation, one warp per output element, lanes strided along the contraction.
 #include <cuda_fp16.h>
+#include "math.cuh"
 #include "launch.h"
 
 namespace gb {
@@ -22,31 +23,6 @@ __device__ __forceinline__ void st_f(__half* p, float v) { *p = __float2half_rn(
 template <typename T>
 __device__ __forceinline__ float round_to(float v) {
   return sizeof(T) == 2 ? __half2float(__float2half_rn(v)) : v;
-}
-
-template <typename T>
-__device__ __forceinline__ float act_forward(int act, float x) {
-  switch (act) {
-    case ACT_TANH: return tanhf(x);
-    case ACT_RELU: return fmaxf(x, 0.f);
-    case ACT_SIGMOID:
-      if (sizeof(T) == 2) {
-        if (x > 0.f) return 1.f / (1.f + expf(-x));
-        const float e = expf(x);
-        return e / (1.f + e);
-      }
-      return 0.5f * tanhf(0.5f * x) + 0.5f;
-    default: return x;
-  }
-}
-template <typename T>
-__device__ __forceinline__ float act_backward(int act, float y, float dy) {
-  switch (act) {
-    case ACT_TANH: return sizeof(T) == 2 ? dy - y * y * dy : (1.f - y * y) * dy;
-    case ACT_RELU: return y > 0.f ? dy : 0.f;
-    case ACT_SIGMOID: return y * (1.f - y) * dy;
-    default: return dy;
-  }
 }
 
 template <typename T>

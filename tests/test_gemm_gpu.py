@@ -178,8 +178,10 @@ def test_large_half_product_by_linearity(gpu):
 def test_fp32_accuracy_holds_at_large_k(gpu):
     """dW of the MLP config contracts over the 4096-column batch."""
     rng = np.random.default_rng(18)
-    for (m, n, k, ta, tb) in [(128, 96, 4096, False, True), (256, 128, 8192, False, False)]:
-        run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, True)
+    for (m, n, k, ta, tb) in [(128, 96, 4096, False, True), (256, 128, 8192, False, False),
+                              (160, 64, 20000, True, False), (96, 130, 17001, False, True)]:
+        run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, True)   # > 8192: chained launches
+    run_gemm(gpu, rng, np.float32, 200, 72, 9000, False, False, False)
 
 
 def test_empty_and_degenerate_shapes(gpu):
