@@ -206,7 +206,7 @@ def run_gpu(args):
             dist.all_reduce(t.T)  # contiguous storage of the column-major matrix
         return lambda: main.wait_stream(comm_stream)
 
-    margin = args.sm_margin if args.sm_margin >= 0 else (24 if world > 1 else 0)
+    margin = args.sm_margin if args.sm_margin >= 0 else (8 if world > 1 else 0)
     gb.set_option("sm_margin", margin)
     prod = ShardedProd(lambda a, b, c, ta, tb, acc: gb.gemm(a, b, c, ta, tb, acc),
                        lambda t: t.zero_(), allreduce_async)
@@ -398,13 +398,14 @@ def run_affine(args):
     m, n, k = args.m, args.n, args.k
     g = torch.Generator(device="cuda").manual_seed(20241)
     a = (6 / (0.5 * (m + k))) ** 0.5
-    W = ((torch.rand(k, m, device="cuda", generator=g) * 2 - 1) * a).T
-    X = torch.randn(n, k, device="cuda", generator=g).T
-    b = (torch.rand(m, device="cuda", generator=g) * 2 - 1) * a
-    dY = torch.randn(n, m, device="cuda", generator=g).T
-    Y = B.colmajor(m, n, torch.float32, fill=0.0)
-    dW, dX = B.colmajor(m, k, torch.float32, fill=0.0), B.colmajor(k, n, torch.float32, fill=0.0)
-    db = torch.zeros(m, device="cuda")
+    tdt = torch.float16 if args.dtype == "f16" else torch.float32
+    W = ((torch.rand(k, m, device="cuda", generator=g) * 2 - 1) * a).to(tdt).T
+    X = torch.randn(n, k, device="cuda", generator=g).to(tdt).T
+    b = ((torch.rand(m, device="cuda", generator=g) * 2 - 1) * a).to(tdt)
+    dY = torch.randn(n, m, device="cuda", generator=g).to(tdt).T
+    Y = B.colmajor(m, n, tdt, fill=0.0)
+    dW, dX = B.colmajor(m, k, tdt, fill=0.0), B.colmajor(k, n, tdt, fill=0.0)
+    db = torch.zeros(m, device="cuda", dtype=tdt)
 
     def step():
         dW.zero_(); dX.zero_(); db.zero_()
@@ -424,7 +425,7 @@ def run_affine(args):
     assert gb.device_status(0, True) == 0
     print(json.dumps({"metric": "affine_fwd_bwd_tflops", "value": 3 * 2 * m * n * k / ms / 1e9,
                       "unit": UNIT, "n_gpus": 1, "steps": args.steps, "ms_per_step": ms,
-                      "dtype": "f32 (3xTF32)", "data": "synthetic",
+                      "dtype": "f16" if args.dtype == "f16" else "f32 (3xTF32)", "data": "synthetic",
                       "config": {"workload": f"Affine tanh fwd+bwd W {m}x{k}, X {k}x{n}"}}),
           flush=True)
 
@@ -523,10 +524,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--sm-margin", type=int, default=-1,
                     help="SMs left free for NCCL while the dB product overlaps the all-reduce "
-                         "(default: 0 on one GPU, 24 otherwise)")
+                         "(default: 0 on one GPU, 8 otherwise)")
     ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32", "attention_f32", "lstm_autobatch", "mlp_dp"])
     ap.add_argument("--cuda-graph", action="store_true",
                     help="lstm_autobatch: replay the level sequence from a CUDA graph")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f16"],
+                    help="affine_f32 workload only: run the same Affine in Half instead")
     ap.add_argument("--m", type=int, default=1024)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
