@@ -313,5 +313,12 @@ def launch_count() -> int:
     return int(lib().ginn_b200_launch_count())
 
 
+def selftest(device: int = 0) -> None:
+    """Bounded-wait self test (ginn_b200_selftest); raises if the time-out is not reported."""
+    fn = lib().ginn_b200_selftest
+    fn.argtypes, fn.restype = [C.c_int], C.c_int
+    _check(fn(device))
+
+
 def version() -> int:
     return lib().ginn_b200_version()

@@ -9,6 +9,7 @@
 
 #include "../../include/ginn_b200.h"
 #include "launch.h"
+#include "ptx.cuh"
 
 namespace {
 
@@ -109,7 +110,7 @@ int persistent_sms(const DevCtx* ctx) {
   return n < 2 ? 2 : n;
 }
 
-enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3, PATH_PAIR = 4 };
+enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3, PATH_PAIR = 4, PATH_GATHER = 5 };
 
 // Runs one Problem on the staged tcgen05 kernel or the CUDA-core kernel.
 int run_problem_once(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
@@ -127,10 +128,12 @@ int run_problem_once(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
              (gb::sgemm3x_supported(p) || gb::sgemm3x_gather_supported(p))) {
     const long long tiles = static_cast<long long>((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batches;
     p.split_k = gb::sgemm3x_pick_split(p, tiles, ctx->num_sms);
-    if (gb::sgemm3x_supported(p))
+    if (force != PATH_GATHER && gb::sgemm3x_supported(p))
       CU_TRY(gb::launch_sgemm3x(p, stream, ctx->d_status));
     else
       CU_TRY(gb::launch_sgemm3x_gather(p, stream, ctx->d_status));
+  } else if (dtype == GINN_B200_F16 && force != PATH_STAGED && gb::hgemm_gather_supported(p)) {
+    CU_TRY(gb::launch_hgemm_gather(p, stream, ctx->d_status));
   } else {
     const int bn = gb::staged_pick_bn(dtype, p.M, p.N, p.batches, ctx->num_sms);
     CU_TRY(gb::launch_staged(dtype, p, bn, stream, ctx->d_status));
@@ -346,9 +349,9 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
                              const LevelPlan& plan, int num_sms, unsigned char* h,
                              unsigned char* d) {
   LevelLaunch ll;
-  // fp32 levels run on the gather front end of the 3xTF32 kernel (128 x 128 tiles); fp16 levels
-  // on the staged kernel.
-  ll.use_gather = dtype == GINN_B200_F32 && g_force_path.load() != PATH_STAGED;
+  // Levels run on the gather kernels (128 x 128 tiles): the cp.async front end of the 3xTF32
+  // kernel for fp32, the cp.async fp16 kernel for Half; the staged kernel only when forced.
+  ll.use_gather = g_force_path.load() != PATH_STAGED;
   if (!ll.use_gather) {
     if (plan.max_n <= 32) ll.bn = 32;
     else if (plan.max_n <= 64 || plan.sum_tiles128 < num_sms) ll.bn = 64;
@@ -417,7 +420,8 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
     p.tiles_m = (p.M + 127) / 128;
     p.tiles_n = (p.N + ll.bn - 1) / ll.bn;
     p.tile_start = ll.tiles;
-    if (ll.use_gather) p.split_k = gb::sgemm3x_pick_split(p, plan.sum_tiles128, num_sms);
+    if (ll.use_gather && dtype == GINN_B200_F32)
+      p.split_k = gb::sgemm3x_pick_split(p, plan.sum_tiles128, num_sms);
     ll.tiles += p.tiles_m * p.tiles_n * (p.split_k > 1 ? p.split_k : 1);
     ++ll.nprobs;
   }
@@ -426,8 +430,10 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
 
 cudaError_t launch_level(int dtype, const LevelLaunch& ll, const Problem* dprobs,
                          cudaStream_t stream, int* status) {
-  if (ll.use_gather)
+  if (ll.use_gather && dtype == GINN_B200_F32)
     return gb::launch_sgemm3x_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
+  if (ll.use_gather)
+    return gb::launch_hgemm_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
   return gb::launch_staged_grouped(dtype, dprobs, ll.nprobs, ll.tiles, ll.bn, stream, status);
 }
 
@@ -670,11 +676,32 @@ int ginn_b200_device_status(int device, int reset) {
   return v;
 }
 
+int ginn_b200_selftest(int device) {
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  // Run on scratch words of our own so that the device status word keeps its meaning.
+  int* d = nullptr;
+  CU_TRY(cudaMalloc(&d, 2 * sizeof(int)));
+  CU_TRY(cudaMemset(d, 0, 2 * sizeof(int)));
+  cudaError_t e = gb::launch_wait_selftest(d, 200000, d + 1, nullptr);  // ~0.1 ms limit
+  int h[2] = {0, 0};
+  if (e == cudaSuccess) e = cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  if (e != cudaSuccess)
+    return fail(GINN_B200_CUDA_ERROR, "self test failed to run: %s", cudaGetErrorString(e));
+  const int want = (gb::DEV_TIMEOUT_SELFTEST << 16) | 0x5e1f;
+  if (h[0] != want || h[1] != 2)
+    return fail(GINN_B200_DEVICE_TIMEOUT,
+                "bounded wait did not report as expected: status %#x (want %#x), flag %d", h[0],
+                want, h[1]);
+  return GINN_B200_OK;
+}
+
 int ginn_b200_version(void) { return 100; }
 
 int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "force_path") == 0) {
-    if (value < 0 || value > 4) return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0..4");
+    if (value < 0 || value > 5) return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0..5");
     g_force_path.store(value);
     return GINN_B200_OK;
   }

@@ -569,10 +569,13 @@ cudaError_t launch_staged_grouped_static(int dtype, const void* host_image, size
   cudaError_t e = cudaMemcpyAsync(scratch, host_image, bytes, cudaMemcpyHostToDevice, stream);
   if (e != cudaSuccess) return e;
   // No status word: a wait that runs out still ends the kernel, it is just not recorded.
-  // fp32 levels use the same kernel as the allocating entry point (3xTF32 gather front end).
-  if (fp32_gather)
+  // Same kernels as the allocating entry point: the gather kernels unless the staged one is forced.
+  if (fp32_gather && dtype == 0)
     return launch_sgemm3x_gather_grouped(static_cast<const Problem*>(scratch), nprobs,
                                          total_tiles, stream, nullptr);
+  if (fp32_gather)
+    return launch_hgemm_gather_grouped(static_cast<const Problem*>(scratch), nprobs, total_tiles,
+                                       stream, nullptr);
   return launch_staged_grouped(dtype, static_cast<const Problem*>(scratch), nprobs, total_tiles,
                                bn, stream, nullptr);
 }

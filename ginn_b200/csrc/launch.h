@@ -45,6 +45,12 @@ bool hgemm_pair_supported(const HgemmArgs& a);
 cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int* counter, cudaStream_t stream,
                               int* status);
 
+// --- general fp16 kernel with a cp.async front end (hgemm_gather.cu) ---
+bool hgemm_gather_supported(const Problem& p);
+cudaError_t launch_hgemm_gather(Problem& p, cudaStream_t stream, int* status);
+cudaError_t launch_hgemm_gather_grouped(const Problem* dprobs, int nprobs, int total_tiles,
+                                        cudaStream_t stream, int* status);
+
 // --- tensor maps (defined in hgemm_tma.cu) ---
 bool encode_tmap(::CUtensorMap_st* out, int esize, const void* ptr, unsigned long long d0,
                  unsigned long long d1, unsigned long long d2, unsigned long long ld,
@@ -63,6 +69,11 @@ bool sgemm3x_gather_supported(const Problem& p);
 cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status);
 cudaError_t launch_sgemm3x_gather_grouped(const Problem* dprobs, int nprobs, int total_tiles,
                                           cudaStream_t stream, int* status);
+
+// One thread waits (bounded by limit_cycles) on a barrier nobody arrives on; writes 2 to *returned
+// and DEV_TIMEOUT_SELFTEST to *status when the wait ran out as it must.
+cudaError_t launch_wait_selftest(int* status, long long limit_cycles, int* returned,
+                                 cudaStream_t stream);
 
 // --- CUDA-core kernels for degenerate shapes and elementwise helpers (small.cu) ---
 // One warp per output element; used for tiny m*n (batched dot products) and k == 0.

@@ -17,7 +17,7 @@ enum DevErr : int {
   DEV_TIMEOUT_EMPTY = 2,   // producer waited for a free stage
   DEV_TIMEOUT_ACCUM = 3,   // epilogue waited for the accumulator
   DEV_TIMEOUT_TMEM_FREE = 4,  // MMA warp waited for a drained accumulator
-  DEV_TIMEOUT_SPLITK = 5,
+  DEV_TIMEOUT_SELFTEST = 5,  // the self test's deliberately unanswered wait
 };
 
 // Bound on one wait, in SM clock cycles (about one second at 2 GHz).
@@ -80,14 +80,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 // Bounded wait.  Returns false (and records `code`) when the bound expires.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code,
-                                          int detail) {
+                                          int detail, long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       record_error(status, code, detail);
       return false;
     }

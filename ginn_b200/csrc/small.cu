@@ -5,6 +5,7 @@
 //   * the bias gradient alone (row sums of dY (.) act'(Y)) when no weight gradient is wanted.
 // fp32 accumulation, one warp per output element, lanes strided along the contraction.
 #include <cuda_fp16.h>
+#include "ptx.cuh"
 #include "math.cuh"
 #include "launch.h"
 
@@ -96,7 +97,27 @@ __global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y,
   }
 }
 
+// Self test of the bounded-wait machinery: one thread waits on an mbarrier on which nothing ever
+// arrives, with a short limit, and must come back with DEV_TIMEOUT_SELFTEST in the status word.
+// Nothing faults and nothing hangs: the wait simply runs out.
+__global__ void wait_selftest_kernel(int* status, long long limit_cycles, int* returned) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, status, DEV_TIMEOUT_SELFTEST, 0x5e1f, limit_cycles);
+    *returned = ok ? 1 : 2;
+    mbar_inval(smem_u32(&bar));
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_wait_selftest(int* status, long long limit_cycles, int* returned,
+                                 cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit_cycles, returned);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream) {
   const long long total = static_cast<long long>(p.M) * p.N * p.batches;

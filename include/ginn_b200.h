@@ -171,12 +171,22 @@ const char* ginn_b200_last_error(void);
  * wait expires.  0 = healthy.  Synchronises the device. Returns -1 if the query itself fails. */
 int ginn_b200_device_status(int device, int reset);
 
+/* Exercises the kernels' bounded-wait machinery on `device`: a one-thread kernel waits, with a
+ * limit of about 0.1 ms, on a barrier nothing arrives on, and must come back with the time-out
+ * code in a status word (the library's own status word is not touched).  Returns GINN_B200_OK
+ * when the wait ran out and was reported as designed.  Nothing faults or hangs.
+ * Status word layout, also for ginn_b200_device_status: (code << 16) | detail with code
+ * 1 = a filled stage never came, 2 = a free stage never came, 3 = an accumulator never completed,
+ * 4 = an accumulator was never drained, 5 = self test. */
+int ginn_b200_selftest(int device);
+
 /* Library version: major * 10000 + minor * 100 + patch. */
 int ginn_b200_version(void);
 
 /* Test / benchmark knobs.  "force_path": 0 = automatic, 1 = staged tcgen05 kernel,
  * 2 = one-CTA TMA fp16 kernel, 4 = CTA-pair fp16 kernel (both fall back to automatic when not
- * applicable), 3 = CUDA-core kernel.
+ * applicable), 3 = CUDA-core kernel, 5 = cp.async gather kernels (the fallbacks for operands a
+ * tensor map cannot describe).
  * "sm_margin": number of SMs the persistent fp16 kernels leave unoccupied (default 0), so that a
  * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles.
  * Returns GINN_B200_UNSUPPORTED for unknown names. */

@@ -209,3 +209,11 @@ def test_argument_errors_are_reported(gpu):
     assert lib.ginn_b200_gemm(0, None, 0, 0, 0, 2, 2, 2, None, 2, p, 2, p, 2, 0) == 1   # null
     assert b"null" in lib.ginn_b200_last_error()
     assert lib.ginn_b200_gemm(999, None, 0, 0, 0, 2, 2, 2, p, 2, p, 2, p, 2, 0) == 1    # device
+
+
+def test_bounded_wait_reports_instead_of_hanging(gpu):
+    """A wait that nothing answers must end by itself and leave its code in a status word; the
+    context stays usable (the next product is correct) and the library's own status stays clean."""
+    gpu.selftest(0)
+    assert gpu.device_status(0, False) == 0
+    run_gemm(gpu, np.random.default_rng(23), np.float32, 64, 48, 80, False, False, False)

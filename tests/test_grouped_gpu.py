@@ -110,3 +110,26 @@ def test_prepared_level_equals_one_shot_call_and_survives_reuse(gpu):
         X, DY = np.stack(xs, 1), np.stack(dys, 1)
         check(B.to_host(dw), 2 * orc.gemm(DY, X, trans_b=True), np.float32, "dW")
         check(B.to_host(db), 2 * DY.astype(np.float64).sum(1), np.float32, "dbias")
+
+
+def test_half_level(gpu):
+    """Grouped launches in Half (fp16 gather kernel): forward, dX, dW against the oracle."""
+    rng = np.random.default_rng(45)
+    m, k, nc = 200, 72, 37
+    W, bias = randn(rng, (m, k), np.float16, 0.1), randn(rng, m, np.float16)
+    xs, dys = [randn(rng, k, np.float16) for _ in range(nc)], [randn(rng, m, np.float16) for _ in range(nc)]
+    Wd, bd = B.from_host(W), B.from_host(bias)
+    xd, dyd = [B.from_host(x) for x in xs], [B.from_host(d) for d in dys]
+    ys = [torch.zeros(m, device="cuda", dtype=torch.float16) for _ in range(nc)]
+    dxs = [torch.zeros(k, device="cuda", dtype=torch.float16) for _ in range(nc)]
+    dw = B.colmajor(m, k, torch.float16, fill=0.0)
+    db = torch.zeros(m, device="cuda", dtype=torch.float16)
+    gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=Wd, x_cols=xd, y_cols=ys, bias=bd)])
+    gpu.grouped(GROUPED_DX, [gpu.Group(w=Wd, y_cols=dyd, dx_cols=dxs)])
+    gpu.grouped(GROUPED_DW, [gpu.Group(w=Wd, x_cols=xd, y_cols=dyd, dw=dw, dbias=db)])
+    torch.cuda.synchronize()
+    X, DY = np.stack(xs, 1), np.stack(dys, 1)
+    check(np.stack([B.to_host(t) for t in ys], 1), orc.affine_forward([(W, X)], bias, 0), np.float16, "fwd")
+    check(np.stack([B.to_host(t) for t in dxs], 1), orc.gemm(W, DY, trans_a=True), np.float16, "dX")
+    check(B.to_host(dw), orc.gemm(DY, X, trans_b=True), np.float16, "dW")
+    check(B.to_host(db), DY.astype(np.float64).sum(1), np.float16, "dbias")
