@@ -533,7 +533,12 @@ def main():
     ap.add_argument("--m", type=int, default=1024)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--force-path", type=int, default=0,
+                    help="kernel choice override passed to the library (0 = automatic)")
     args = ap.parse_args()
+    if args.force_path and args.impl != "reference":
+        import ginn_b200
+        ginn_b200.set_option("force_path", args.force_path)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "affine_f32":

@@ -13,7 +13,6 @@
 //
 //   warp 0       TMEM allocation and MMA issue (kind::f16, M = 128, N = 128, K = 16)
 //   warps 1-4    producers of the A slice, warps 5-8 of the B slice; then the epilogue
-#include <cstdio>
 #include "ptx.cuh"
 #include "math.cuh"
 #include "launch.h"
@@ -23,10 +22,7 @@ namespace gb {
 namespace {
 
 constexpr int GBM = 128, GBN = 128, GBK = 64;
-#ifndef HG_STAGES
-#define HG_STAGES 3
-#endif
-constexpr int GSTAGES = HG_STAGES;
+constexpr int GSTAGES = 3;
 constexpr int GTILE = 128 * GBK * 2;  // 16 KiB per operand slice
 constexpr int GSTAGE = 2 * GTILE;
 constexpr int GPROD = 128;            // producer threads per operand
@@ -70,17 +66,41 @@ __device__ __noinline__ Piece2 load_piece_slow(const __half* p, const __half* y,
   return r;
 }
 
-// dY (.) act'(Y) on 8 halves, rounded to fp16.
-__device__ __noinline__ uint4 apply_dact(uint4 d, uint4 y, int dact) {
-  __half* dh = reinterpret_cast<__half*>(&d);
-  const __half* yh = reinterpret_cast<const __half*>(&y);
+// dY (.) act'(Y) on 8 halves in packed fp16 arithmetic, every operation rounded to fp16 as the
+// reference's Half expressions are (ginn/nonlin.h:96-106 tanh, :119-126 relu, :146-152 sigmoid).
+__device__ __forceinline__ uint4 apply_dact(uint4 d, uint4 y, int dact) {
+  __half2* dh = reinterpret_cast<__half2*>(&d);
+  const __half2* yh = reinterpret_cast<const __half2*>(&y);
+  const __half2 one = __float2half2_rn(1.f), zero = __float2half2_rn(0.f);
+  if (dact == ACT_TANH) {
 #pragma unroll
-  for (int e = 0; e < 8; ++e)
-    dh[e] = __float2half_rn(act_backward<__half>(dact, __half2float(yh[e]), __half2float(dh[e])));
+    for (int e = 0; e < 4; ++e) dh[e] = __hsub2(dh[e], __hmul2(__hmul2(yh[e], yh[e]), dh[e]));
+  } else if (dact == ACT_SIGMOID) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dh[e] = __hmul2(__hmul2(yh[e], __hsub2(one, yh[e])), dh[e]);
+  } else if (dact == ACT_RELU) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dh[e] = __hmul2(__hgt2(yh[e], zero), dh[e]);
+  }
   return d;
 }
 
-__device__ __noinline__ float act_forward_half(int act, float x) { return act_forward<__half>(act, x); }
+// Forward nonlinearity for fp16 outputs: hardware approximations (relative error about 2^-11,
+// below the rounding of the fp16 result) keep the epilogue a few instructions per element.
+__device__ __forceinline__ float act_forward_half(int act, float x) {
+  if (act == ACT_TANH) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  if (act == ACT_SIGMOID) {
+    const float e = __expf(-fabsf(x));
+    const float r = __fdividef(1.f, 1.f + e);
+    return x > 0.f ? r : e * r;
+  }
+  if (act == ACT_RELU) return fmaxf(x, 0.f);
+  return x;
+}
 
 // Raw 8 halves of a piece (and of Y at the same place): zero outside the matrix.
 __device__ __forceinline__ void load_raw(const PieceSrc& s, uint4& d, uint4& y) {
@@ -137,7 +157,7 @@ struct Feeder {
   // Fast path (plain operand, 16-byte aligned base, leading dimension and batch offset): the
   // eight sources are p0 + k-block * kadv + i * pstep (bytes) and only the edges need a test.
   bool fast;
-  long long pstep, kadv, qoff;
+  long long pstep, kadv, qoff, ydelta;
   uint32_t omask;     // k-contiguous: bit i set when piece i's row is inside the matrix
 
   __device__ __forceinline__ void init(const Operand& o, long long K_, long long boff, int o0,
@@ -152,9 +172,11 @@ struct Feeder {
     kc = o.k_contig != 0;
     has_y = o.dact != ACT_NONE;
     p0 = y0 = nullptr;
-    fast = o.cols == nullptr && !has_y &&
+    fast = o.cols == nullptr &&
            ((reinterpret_cast<uintptr_t>(o.base) | static_cast<uintptr_t>(o.ld * 2) |
-             static_cast<uintptr_t>(boff * 2)) & 15u) == 0;
+             static_cast<uintptr_t>(boff * 2) | (has_y ? reinterpret_cast<uintptr_t>(o.ybase) : 0)) &
+            15u) == 0;
+    ydelta = has_y ? static_cast<const char*>(o.ybase) - static_cast<const char*>(o.base) : 0;
     pstep = (o.k_contig ? 16 : 8) * o.ld * 2;
     kadv = o.k_contig ? GBK * 2 : GBK * o.ld * 2;
     omask = 0;
@@ -212,6 +234,31 @@ struct Feeder {
         d += 1024u;
         kg += 8;
       }
+    }
+  }
+
+  // Pieces h .. h+3 of the k-block starting at k0 into registers (and their Y values), fast path.
+  __device__ __forceinline__ void load4_fast(long long k0, int h, uint4* d, uint4* y) const {
+    const char* q = reinterpret_cast<const char*>(p0) + (k0 / GBK) * kadv + qoff + h * pstep;
+    const long long rem = K - (k0 + 8 * sub);
+    const int kv = rem >= 8 ? 8 : (rem > 0 ? static_cast<int>(rem) : 0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int valid;
+      if (kc) valid = ((omask >> (h + i)) & 1u) ? kv : 0;
+      else valid = (k0 + sub + 8 * (h + i) < K) ? valid_o : 0;
+      d[i] = make_uint4(0, 0, 0, 0);
+      y[i] = make_uint4(0, 0, 0, 0);
+      if (valid == 8) {
+        d[i] = __ldg(reinterpret_cast<const uint4*>(q));
+        if (has_y) y[i] = __ldg(reinterpret_cast<const uint4*>(q + ydelta));
+      } else if (valid > 0) {
+        const Piece2 r = load_piece_slow(reinterpret_cast<const __half*>(q),
+                                         has_y ? reinterpret_cast<const __half*>(q + ydelta) : nullptr, valid);
+        d[i] = r.d;
+        y[i] = r.y;
+      }
+      q += pstep;
     }
   }
 
@@ -308,17 +355,8 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
       int s = 0, pair = 0;
       uint32_t ph = 0;
       long long k0 = 0;
-#ifdef HG_TRACE
-      long long tw = 0, ti = 0, tt = clock64();
-#endif
       for (int it = 0; it < nkb; ++it) {
-#ifdef HG_TRACE
-        long long c0 = clock64();
-#endif
         if (!mbar_wait(smem_u32(&full_bar[s]), ph, status, DEV_TIMEOUT_FULL, it)) break;
-#ifdef HG_TRACE
-        tw += clock64() - c0;
-#endif
         // The slices were written through the generic proxy (cp.async or plain stores).
         fence_proxy_async_smem();
         tc_fence_after();
@@ -346,9 +384,6 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
         }
       }
       tc_commit(smem_u32(&acc_bar));
-#ifdef HG_TRACE
-      if (blockIdx.x == 0) printf("mma: total %lld wait_full %lld nkb %d\n", clock64() - tt, tw, nkb);
-#endif
     }
     __syncwarp();
   } else {
@@ -379,8 +414,12 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
 #pragma unroll
       for (int h = 0; h < GPIECES; h += 4) {  // four pieces at a time: their Y values need registers too
         uint4 y[4];
+        if (fd.fast) {
+          fd.load4_fast(kk0, h, &regs[h], y);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) load_raw(fd.src(h + i, kk0), regs[h + i], y[i]);
+          for (int i = 0; i < 4; ++i) load_raw(fd.src(h + i, kk0), regs[h + i], y[i]);
+        }
         if (fd.has_y) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) regs[h + i] = apply_dact(regs[h + i], y[i], fd.dact);
@@ -405,20 +444,11 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
         regs_loaded = true;
       }
     }
-#ifdef HG_TRACE
-    long long pw = 0, pi = 0, pg = 0, pa = 0, pt0 = clock64(), c1, c2;
-#endif
     for (int it = 0; it < nkb; ++it) {
-#ifdef HG_TRACE
-      c1 = clock64();
-#endif
       if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) {
         ok = false;
         break;
       }
-#ifdef HG_TRACE
-      c2 = clock64(); pw += c2 - c1; c1 = c2;
-#endif
       const uint32_t dst = tiles_base + s * GSTAGE + grp * GTILE;
       if (via_regs(pair)) {
 #pragma unroll
@@ -454,19 +484,10 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
       // The slice just issued is announced one k-block later, when its copies have landed;
       // the copies of the next slice are in flight meanwhile.
       asm volatile("cp.async.commit_group;" ::: "memory");
-#ifdef HG_TRACE
-      c2 = clock64(); pi += c2 - c1; c1 = c2;
-#endif
       if (it > 0) {
         asm volatile("cp.async.wait_group 1;" ::: "memory");
-#ifdef HG_TRACE
-        c2 = clock64(); pg += c2 - c1; c1 = c2;
-#endif
         announce(sig);
         if (++sig == GSTAGES) sig = 0;
-#ifdef HG_TRACE
-        c2 = clock64(); pa += c2 - c1; c1 = c2;
-#endif
       }
       if (++s == GSTAGES) {
         s = 0;
@@ -487,12 +508,6 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       announce(sig);
     }
-#ifdef HG_TRACE
-    if (blockIdx.x == 0 && (pt == 0 || pt == 128))
-      printf("prod %d: total %lld wait_empty %lld issue %lld wait_group %lld announce %lld\n", pt,
-             clock64() - pt0, pw, pi, pg, pa);
-    long long e0 = clock64();
-#endif
     if (want_rowsum && ok) {
       // Outer-contiguous A: every piece of this thread covers the same 8 rows.
       const int row = m0 + 8 * (t & 15);
@@ -553,9 +568,6 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
     }
   }
 
-#ifdef HG_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 32) printf("kernel end clock since tile start\n");
-#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {

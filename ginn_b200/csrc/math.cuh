@@ -45,14 +45,20 @@ __device__ __forceinline__ float act_backward(int act, float y, float dy) {
   }
 }
 
-// hi = round-to-nearest TF32 of x; lo = x - hi (exact in fp32; the tensor core keeps the top 11
-// significant bits of it).  Non-finite values stay in the hi plane only: inf - inf would poison
-// the lo plane.
+// hi = x rounded to TF32 (nearest, ties away from zero, what cvt.rna.tf32 gives); lo = x - hi
+// (exact in fp32; the tensor core keeps the top 11 significant bits of it).  The rounding is
+// done on the bit pattern with two integer instructions (add half an ulp of the 10-bit mantissa
+// to the magnitude, clear the 13 low bits) because the conversion instruction issues at a
+// sixteenth of the integer rate and would bound the split.  A carry out of the mantissa bumps
+// the exponent, as rounding should.  Values that are not finite, or so large that rounding
+// would reach inf (|x| >= 0x7f7ff000 as a bit pattern), go to the hi plane unchanged and leave
+// the lo plane zero: the integer add would wrap an all-ones NaN to zero, and inf - inf would
+// poison the lo plane.  One comparison covers all of it (NaN compares false).
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  hi = __uint_as_float(u);
-  lo = ((u & 0x7f800000u) == 0x7f800000u) ? 0.f : x - hi;
+  const float r = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+  const bool ok = fabsf(x) < __uint_as_float(0x7f7ff000u);
+  hi = ok ? r : x;
+  lo = ok ? x - r : 0.f;
 }
 
 }  // namespace gb

@@ -58,6 +58,10 @@ struct SParams {
   int batches;
 };
 
+// Out of line on purpose: thirty-two inlined copies of the precise tanh per epilogue would make
+// up most of the kernel's code.
+__device__ __noinline__ float act_forward_f32(int act, float x) { return act_forward<float>(act, x); }
+
 // Transform of a k-contiguous raw slice: it already is K-major and swizzled (TMA box 32 k x 128
 // outer with the 128-byte swizzle), so hi and lo go to the same offsets of their planes.
 // 256 threads, 4 pieces of 16 bytes each.
@@ -364,7 +368,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
               if (split_k)
                 atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
               else
-                *dst = act_forward<float>(p.act, acc[j]);
+                *dst = (p.act == ACT_NONE ? acc[j] : act_forward_f32(p.act, acc[j]));
             }
           }
         }
@@ -405,60 +409,93 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// A 16-byte piece whose source is only 4-byte aligned: element by element.  Out of line: the
+// fill loop has to stay short (its length is what bounds a k-block once the tensor core is fed).
+__device__ __noinline__ void fill_piece_slow(uint32_t dst, const float* src, int valid,
+                                             const void* safe) {
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    cp_async4(dst + 4 * e, e < valid ? static_cast<const void*>(src + e) : safe, e < valid ? 4 : 0);
+}
+
 // 16 bytes (4 floats) from src to dst, of which `valid` (0..4) elements exist; the rest is zero.
 __device__ __forceinline__ void fill_piece(uint32_t dst, const float* src, int valid,
                                            const void* safe) {
-  if (valid <= 0) {
-    cp_async16(dst, safe, 0);
-  } else if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
-    cp_async16(dst, src, valid * 4);
-  } else {
-#pragma unroll
-    for (int e = 0; e < 4; ++e)
-      cp_async4(dst + 4 * e, e < valid ? static_cast<const void*>(src + e) : safe, e < valid ? 4 : 0);
-  }
+  if (valid > 0 && (reinterpret_cast<uintptr_t>(src) & 15u) != 0)
+    fill_piece_slow(dst, src, valid, safe);
+  else
+    cp_async16(dst, valid > 0 ? static_cast<const void*>(src) : safe, valid * 4);
 }
 
-// Fills one raw slice (128 outer x 32 k) of operand `op` for k-block starting at k0, in the same
-// two layouts the TMA front end produces.  `y` selects the Y matrix of a derivative operand.
-__device__ __forceinline__ void fill_raw(const Operand& op, bool y, long long boff, int o0, int O,
-                                         long long k0, long long K, uint32_t dst_tile, int t) {
-  const float* base = static_cast<const float*>(y ? op.ybase : op.base);
-  const void* const* cols = y ? op.ycols : op.cols;
-  const void* safe = cols ? static_cast<const void*>(cols) : static_cast<const void*>(base);
-  if (op.k_contig) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int id = t + 256 * i;
-      const int row = id >> 3, c = id & 7;
-      const int o = o0 + row;
-      const long long kk = k0 + 4 * c;
-      int valid = 0;
-      const float* src = nullptr;
-      if (o < O && kk < K) {
-        const float* col = cols ? static_cast<const float*>(cols[o]) : base + boff + static_cast<long long>(o) * op.ld;
-        src = col + kk;
-        valid = K - kk >= 4 ? 4 : static_cast<int>(K - kk);
-      }
-      fill_piece(dst_tile + sw128_offset(row, c), src, valid, safe);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int id = t + 256 * i;
-      const int kk = id >> 5, oc = id & 31;
-      const int o = o0 + 4 * oc;
-      int valid = 0;
-      const float* src = nullptr;
-      if (k0 + kk < K && o < O) {
-        const float* col = cols ? static_cast<const float*>(cols[k0 + kk]) : base + boff + (k0 + kk) * op.ld;
-        src = col + o;
-        valid = O - o >= 4 ? 4 : O - o;
-      }
-      fill_piece(dst_tile + (oc >> 3) * 4096 + kk * 128 + (oc & 7) * 16, src, valid, safe);
+// Per-thread geometry of one raw slice (128 outer x 32 k) of an operand, in the two layouts the
+// TMA front end produces, worked out once per (tile, pair) and kept in registers: the copies'
+// "memory" clobbers would otherwise force every operand field to be re-read before each piece.
+//   k-contiguous : piece i = row (t/8 + 32 i), k offset 4 (t%8)    -> offset off0 + 4096 i
+//   outer-contig.: piece i = k (t/32 + 8 i), outer offset 4 (t%32) -> offset off0 + 1024 i
+struct RawFeeder {
+  const void* const* cols;
+  const float* p0;    // untabled: element of piece 0 at k = 0
+  const void* safe;
+  long long ld, K;
+  uint32_t off0;
+  int o_first, O, sub, valid_o;
+  bool kc;
+
+  __device__ __forceinline__ void init(const Operand& op, bool y, long long boff, int o0, int O_,
+                                       long long K_, int t) {
+    const float* base = static_cast<const float*>(y ? op.ybase : op.base);
+    cols = y ? op.ycols : op.cols;
+    safe = cols ? static_cast<const void*>(cols) : static_cast<const void*>(base);
+    ld = op.ld;
+    K = K_;
+    O = O_;
+    kc = op.k_contig != 0;
+    p0 = nullptr;
+    if (kc) {
+      sub = t & 7;
+      const int row0 = t >> 3;
+      off0 = sw128_offset(row0, sub);
+      o_first = o0 + row0;
+      valid_o = 4;
+      if (!cols) p0 = base + boff + static_cast<long long>(o_first) * ld + 4 * sub;
+    } else {
+      sub = t >> 5;
+      const int oc = t & 31;
+      off0 = (oc >> 3) * 4096u + sub * 128u + (oc & 7) * 16u;
+      o_first = o0 + 4 * oc;
+      valid_o = O_ - o_first >= 4 ? 4 : (O_ - o_first > 0 ? O_ - o_first : 0);
+      if (!cols) p0 = base + boff + o_first;
     }
   }
-}
+
+  __device__ __forceinline__ void fill(uint32_t dst_tile, long long k0) const {
+    uint32_t d = dst_tile + off0;
+    if (kc) {
+      const long long kk = k0 + 4 * sub;
+      const int kv = K - kk >= 4 ? 4 : (K - kk > 0 ? static_cast<int>(K - kk) : 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int o = o_first + 32 * i;
+        const int valid = o < O ? kv : 0;
+        const float* src = nullptr;
+        if (valid > 0)
+          src = cols ? static_cast<const float*>(cols[o]) + kk : p0 + static_cast<long long>(32 * i) * ld + k0;
+        fill_piece(d, src, valid, safe);
+        d += 4096u;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const long long kk = k0 + sub + 8 * i;
+        const int valid = kk < K ? valid_o : 0;
+        const float* src = nullptr;
+        if (valid > 0) src = cols ? static_cast<const float*>(cols[kk]) + o_first : p0 + kk * ld;
+        fill_piece(d, src, valid, safe);
+        d += 1024u;
+      }
+    }
+  }
+};
 
 template <bool GROUPED>
 __global__ void __launch_bounds__(GNTHREADS, 1)
@@ -581,36 +618,49 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
     float rs = 0.f;
     bool ok = true;
 
-    // k-block `j` of the whole contraction -> (pair, k0)
-    auto fill = [&](int j, int stage) -> bool {
-      // the (j / raw_stages)-th use of this stage: wait until its previous slice was consumed
-      const uint32_t use = static_cast<uint32_t>(j / raw_stages);
-      if (!mbar_wait(smem_u32(&raw_empty[grp][stage]), (use & 1u) ^ 1u, status, DEV_TIMEOUT_EMPTY,
-                     0x300 + j))
+    // Fill side of the pipeline: k-blocks are filled in order, raw_stages - 1 ahead of the
+    // transform; its position (pair, k0), ring stage and use count advance incrementally.
+    RawFeeder fx, fy;
+    int f_pair = 0, f_stage = 0;
+    uint32_t f_use = 0;  // how often the ring has wrapped
+    long long f_k0 = static_cast<long long>(kb_begin) * SBK;  // kb_begin > 0 only with one pair
+    auto f_setup = [&]() {
+      const Operand& op = grp ? P.b[f_pair] : P.a[f_pair];
+      fx.init(op, false, batch * op.batch_stride, o0, O, P.k[f_pair], t);
+      if (has_y) fy.init(op, true, batch * op.batch_stride, o0, O, P.k[f_pair], t);
+    };
+    if (nkb > 0) f_setup();
+    auto fill = [&](int j) -> bool {
+      if (!mbar_wait(smem_u32(&raw_empty[grp][f_stage]), (f_use & 1u) ^ 1u, status,
+                     DEV_TIMEOUT_EMPTY, 0x300 + j))
         return false;
-      int pair = 0;
-      long long k0 = static_cast<long long>(kb_begin + j) * SBK;
-      while (pair + 1 < P.npairs && k0 >= ((P.k[pair] + SBK - 1) / SBK) * SBK) {
-        k0 -= ((P.k[pair] + SBK - 1) / SBK) * SBK;
-        ++pair;
+      const uint32_t dst = raws_base + f_stage * raw_stage_bytes;
+      fx.fill(dst + grp * RAW_TILE, f_k0);
+      if (has_y) fy.fill(dst + 2 * RAW_TILE, f_k0);
+      cp_async_arrive(smem_u32(&raw_full[grp][f_stage]));
+      if (++f_stage == raw_stages) {
+        f_stage = 0;
+        ++f_use;
       }
-      const Operand& op = grp ? P.b[pair] : P.a[pair];
-      const uint32_t dst = raws_base + stage * raw_stage_bytes;
-      fill_raw(op, false, batch * op.batch_stride, o0, O, k0, P.k[pair], dst + grp * RAW_TILE, t);
-      if (has_y)
-        fill_raw(op, true, batch * op.batch_stride, o0, O, k0, P.k[pair], dst + 2 * RAW_TILE, t);
-      cp_async_arrive(smem_u32(&raw_full[grp][stage]));
+      f_k0 += SBK;
+      if (f_k0 >= P.k[f_pair] && f_pair + 1 < P.npairs) {
+        ++f_pair;
+        f_k0 = 0;
+        f_setup();
+      }
       return true;
     };
 
-    for (int j = 0; j < raw_stages - 1 && j < nkb; ++j) ok = ok && fill(j, j);
     int rs_i = 0, ps_i = 0;
     uint32_t rph = 0, pph = 0;
     int pair = 0;
     long long k0 = static_cast<long long>(kb_begin) * SBK;  // kb_begin > 0 only with one pair
-    for (int it = 0; it < nkb; ++it) {
+    // One loop, one copy of the fill code: step j fills k-block j and transforms k-block
+    // j - (raw_stages - 1).
+    for (int it = 1 - raw_stages; it < nkb; ++it) {
       const int ahead = it + raw_stages - 1;
-      if (ok && ahead < nkb) ok = fill(ahead, ahead % raw_stages);
+      if (ok && ahead < nkb) ok = fill(ahead);
+      if (it < 0) continue;
       if (!ok ||
           !mbar_wait(smem_u32(&raw_full[grp][rs_i]), rph, status, DEV_TIMEOUT_FULL, 0x200 + it) ||
           !mbar_wait(smem_u32(&plane_empty[ps_i]), pph ^ 1u, status, DEV_TIMEOUT_EMPTY,
@@ -699,7 +749,7 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
             if (split_k)
               atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
             else
-              *dst = act_forward<float>(P.act, acc[j]);
+              *dst = (P.act == ACT_NONE ? acc[j] : act_forward_f32(P.act, acc[j]));
           }
         }
       }

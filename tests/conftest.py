@@ -25,7 +25,9 @@ def gpu():
     import torch
     import ginn_b200 as gb
     assert torch.cuda.is_available()
-    gb.set_option("force_path", 0)
+    # GINN_B200_TEST_PATH reruns the whole suite with another kernel choice as the default
+    # (tests that pick a path themselves still override it).
+    gb.set_option("force_path", int(os.environ.get("GINN_B200_TEST_PATH", "0")))
     gb.device_status(0, True)
     yield gb
     torch.cuda.synchronize()
