@@ -430,6 +430,71 @@ def run_affine(args):
           flush=True)
 
 
+def run_step_ops(args):
+    """The step's elementwise neighbours on sizes well beyond the 126 MB L2: Adam on 2^26 fp32
+    parameters (32 algorithmic bytes per element: w, d, m, v read and written) and the picked
+    negative log softmax on a 1024 x 65536 fp32 score matrix (forward 8 bytes per element:
+    scores read, softmax written; backward 12: softmax read, gradient read and written).
+    One JSON line with the three bandwidths against the measured copy bandwidth."""
+    import torch
+    import ginn_b200 as gb
+    from ginn_b200 import binding as B
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, src = measured_peaks()
+    n = 1 << 26
+    w = torch.randn(n, device=dev)
+    d = torch.randn(n, device=dev)
+    m = torch.zeros(n, device=dev)
+    v = torch.zeros(n, device=dev)
+    rows, cols = 1024, 65536
+    x = B.colmajor(rows, cols, torch.float32, dev)
+    x.copy_(torch.randn(rows, cols, device=dev))
+    smax = B.colmajor(rows, cols, torch.float32, dev, fill=0.0)
+    dx = B.colmajor(rows, cols, torch.float32, dev, fill=0.0)
+    idx = torch.randint(0, rows, (cols,), device=dev, dtype=torch.int32)
+    val = torch.zeros(cols, device=dev)
+    g = torch.ones(cols, device=dev)
+    step = [0]
+
+    def adam():
+        step[0] += 1
+        gb.adam_update(w, d, m, v, step[0])
+
+    ops = {"adam": (adam, 32.0 * n),
+           "pick_nll_forward": (lambda: gb.pick_nll_forward(x, idx, smax, val), 8.0 * rows * cols),
+           "pick_nll_backward": (lambda: gb.pick_nll_backward(smax, idx, g, dx), 12.0 * rows * cols)}
+    sampler = ClockSampler(0)
+    sampler.start()
+    out = {}
+    launches0 = gb.launch_count()
+    for name, (fn, nbytes) in ops.items():
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / args.steps
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "bound": "hbm", "peak_source": src}
+    clocks = sampler.stop()
+    assert gb.device_status(0, True) == 0
+    print(json.dumps({"metric": "step_ops_adam_gbs", "value": out["adam"]["achieved"], "unit": "GB/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+                      "ms_per_step": out["adam"]["ms"], "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "Adam on 2^26 fp32 parameters; picked negative log softmax "
+                                             "on 1024 x 65536 fp32 scores", "l2": "every array exceeds the 126 MB L2"},
+                      "roofline": out["adam"], "ops": out, "clocks": clocks,
+                      "gpu_launches": int(gb.launch_count() - launches0)}), flush=True)
+
+
 def run_config_workload(args):
     """Secondary workloads: the other benchmark configurations (fp32), harnessed in
     ginn_b200/workloads.py.  Same timing rules as the main arm; one JSON line from rank 0."""
@@ -525,7 +590,7 @@ def main():
     ap.add_argument("--sm-margin", type=int, default=-1,
                     help="SMs left free for NCCL while the dB product overlaps the all-reduce "
                          "(default: 0 on one GPU, 8 otherwise)")
-    ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32", "attention_f32", "lstm_autobatch", "mlp_dp"])
+    ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32", "attention_f32", "lstm_autobatch", "mlp_dp", "step_ops"])
     ap.add_argument("--cuda-graph", action="store_true",
                     help="lstm_autobatch: replay the level sequence from a CUDA graph")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"],
@@ -543,6 +608,8 @@ def main():
         run_reference(args)
     elif args.workload == "affine_f32":
         run_affine(args)
+    elif args.workload == "step_ops":
+        run_step_ops(args)
     elif args.workload in ("attention_f32", "lstm_autobatch", "mlp_dp"):
         run_config_workload(args)
     else:

@@ -78,6 +78,13 @@ def lib():
     L.ginn_b200_level_destroy.argtypes = [vp]
     for name in ("ginn_b200_level_create", "ginn_b200_level_run", "ginn_b200_level_destroy"):
         getattr(L, name).restype = ci
+    cf, fp = C.c_float, C.POINTER(C.c_float)
+    L.ginn_b200_pick_nll_forward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, vp, i64, vp]
+    L.ginn_b200_pick_nll_backward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, vp, vp, i64]
+    L.ginn_b200_adam_update.argtypes = [ci, vp, ci, i64, vp, vp, vp, vp, cf, cf, cf, cf, cf, cf, cf]
+    for name in ("ginn_b200_pick_nll_forward", "ginn_b200_pick_nll_backward",
+                 "ginn_b200_adam_update"):
+        getattr(L, name).restype = ci
     L.ginn_b200_last_error.restype = C.c_char_p
     L.ginn_b200_device_status.argtypes = [ci, ci]
     L.ginn_b200_set_option.argtypes = [C.c_char_p, ci]
@@ -299,6 +306,37 @@ class GroupedCall:
         if getattr(self, "handle", None) is not None and _lib is not None:
             _lib.ginn_b200_level_destroy(self.handle)
             self.handle = None
+
+
+def pick_nll_forward(x: torch.Tensor, index: torch.Tensor, smax: torch.Tensor,
+                     value: torch.Tensor) -> None:
+    """smax = column softmax of x; value[j] = -log smax[index[j], j]  (ginn_b200_pick_nll_forward).
+    x, smax: column-major rows x cols; index: int32 (cols); value: cols elements."""
+    assert index.dtype == torch.int32 and index.is_contiguous() and value.is_contiguous()
+    rows, cols = x.shape
+    _check(lib().ginn_b200_pick_nll_forward(_dev(x), _stream(x), _dtype_of(x), rows, cols,
+                                            x.data_ptr(), _ld(x), index.data_ptr(),
+                                            smax.data_ptr(), _ld(smax), value.data_ptr()))
+
+
+def pick_nll_backward(smax: torch.Tensor, index: torch.Tensor, grad: torch.Tensor,
+                      dx: torch.Tensor) -> None:
+    """dx += (smax - onehot(index)) * grad  (ginn_b200_pick_nll_backward)."""
+    assert index.dtype == torch.int32 and index.is_contiguous() and grad.is_contiguous()
+    rows, cols = smax.shape
+    _check(lib().ginn_b200_pick_nll_backward(_dev(smax), _stream(smax), _dtype_of(smax), rows, cols,
+                                             smax.data_ptr(), _ld(smax), index.data_ptr(),
+                                             grad.data_ptr(), dx.data_ptr(), _ld(dx)))
+
+
+def adam_update(w: torch.Tensor, d: torch.Tensor, m: torch.Tensor, v: torch.Tensor, t: int,
+                lr=1e-3, clip=5.0, eps=1e-8, beta1=0.9, beta2=0.999) -> None:
+    """Step t (1-based) of Adam on flat contiguous tensors (ginn_b200_adam_update); m, v fp32."""
+    assert w.is_contiguous() and d.is_contiguous() and m.dtype == torch.float32 == v.dtype
+    assert w.numel() == d.numel() == m.numel() == v.numel()
+    _check(lib().ginn_b200_adam_update(_dev(w), _stream(w), _dtype_of(w), w.numel(), w.data_ptr(),
+                                       d.data_ptr(), m.data_ptr(), v.data_ptr(), lr, clip, eps,
+                                       beta1, beta2, beta1 ** t, beta2 ** t))
 
 
 def device_status(device: int = 0, reset: bool = True) -> int:

@@ -676,6 +676,58 @@ int ginn_b200_device_status(int device, int reset) {
   return v;
 }
 
+int ginn_b200_pick_nll_forward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                               const void* x, int64_t ldx, const int* index, void* smax,
+                               int64_t ldsmax, void* value) {
+  if (int s = check_common(dtype, rows, cols, 0)) return s;
+  if (rows == 0 || cols == 0) return GINN_B200_OK;
+  if (!x || !index || !smax || !value) return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  if (ldx < rows || ldsmax < rows)
+    return fail(GINN_B200_BAD_ARGUMENT, "leading dimension smaller than %lld rows", (long long)rows);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  CU_TRY(gb::launch_pick_nll_forward(dtype, x, ldx, index, smax, ldsmax, value, (int)rows, cols,
+                                     static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+int ginn_b200_pick_nll_backward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                                const void* smax, int64_t ldsmax, const int* index,
+                                const void* grad, void* dx, int64_t lddx) {
+  if (int s = check_common(dtype, rows, cols, 0)) return s;
+  if (rows == 0 || cols == 0) return GINN_B200_OK;
+  if (!smax || !index || !grad || !dx) return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  if (ldsmax < rows || lddx < rows)
+    return fail(GINN_B200_BAD_ARGUMENT, "leading dimension smaller than %lld rows", (long long)rows);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  CU_TRY(gb::launch_pick_nll_backward(dtype, smax, ldsmax, index, grad, dx, lddx, (int)rows, cols,
+                                      static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+int ginn_b200_adam_update(int device, void* stream, int dtype, int64_t n, void* w, void* d,
+                          float* m, float* v, float lr, float clip, float eps, float beta1,
+                          float beta2, float beta1_t, float beta2_t) {
+  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
+    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
+  if (n < 0) return fail(GINN_B200_BAD_ARGUMENT, "negative element count");
+  if (n == 0) return GINN_B200_OK;
+  if (!w || !d || !m || !v) return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  if (!(beta1_t < 1.f) || !(beta2_t < 1.f))
+    return fail(GINN_B200_BAD_ARGUMENT, "beta powers must be below 1 (got %g, %g)", beta1_t, beta2_t);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  const float step = -lr * (1.f / (1.f - beta1_t));
+  const float vscale = 1.f / (1.f - beta2_t);
+  CU_TRY(gb::launch_adam(dtype, w, d, m, v, n, clip, beta1, beta2, step, vscale, eps, ctx->num_sms,
+                         static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
 int ginn_b200_selftest(int device) {
   DevCtx* ctx;
   if (int s = get_ctx(device, &ctx)) return s;

@@ -82,4 +82,15 @@ cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream);
 cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
                           long long N, void* rowsum, cudaStream_t stream);
 
+// --- elementwise neighbours of the products on a training step (step_ops.cu) ---
+cudaError_t launch_pick_nll_forward(int dtype, const void* x, long long ldx, const int* index,
+                                    void* smax, long long lds, void* value, int rows,
+                                    long long cols, cudaStream_t stream);
+cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds, const int* index,
+                                     const void* grad, void* dx, long long lddx, int rows,
+                                     long long cols, cudaStream_t stream);
+cudaError_t launch_adam(int dtype, void* w, void* d, float* m, float* v, long long n, float clip,
+                        float b1, float b2, float step, float vscale, float eps, int num_sms,
+                        cudaStream_t stream);
+
 }  // namespace gb

@@ -1,0 +1,276 @@
+// The elementwise neighbours of the GEMMs on a training step: the picked negative log softmax
+// loss (forward and backward) and the Adam update.  All three are bound by HBM bandwidth; each
+// is one pass over its operands.
+//
+//   pick_nll_forward : per column j of X (rows x cols, column-major)
+//                        smax[:, j] = softmax(X[:, j]),  value[j] = -log(smax[index[j], j])
+//                      (SoftmaxOp::forward, ginn/nonlin.h:162-168: subtract the column maximum,
+//                      exponentiate, divide by the column sum; the pick of ginn/node/pick.h:60-84;
+//                      the -log of PickNegLogSoftmaxNode::forward_, pick.h:209-216)
+//   pick_nll_backward: dX[i, j] += (smax[i, j] - [i == index[j]]) * g[j]
+//                      (PickNegLogSoftmaxNode::backward_, pick.h:218-224, and pick_grad with
+//                      negate, pick.h:87-131, in one pass instead of gather + scatter + add)
+//   adam_update      : d = clip(d); m = b1 m + (1 - b1) d; v = b2 v + (1 - b2) d^2;
+//                      w += -lr / (1 - b1^t) * m / (eps + sqrt(v / (1 - b2^t)))
+//                      (Adam::update, ginn/update/update.h:115-133; m and v are always fp32)
+#include <cuda_fp16.h>
+#include "math.cuh"
+#include "launch.h"
+
+namespace gb {
+
+namespace {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Four consecutive elements of storage type T as floats.
+__device__ __forceinline__ void load4(const float* p, float (&x)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __half* p, float (&x)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&x)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+}
+__device__ __forceinline__ void store4(__half* p, const float (&x)[4]) {
+  uint2 v;
+  *reinterpret_cast<__half2*>(&v.x) = __floats2half2_rn(x[0], x[1]);
+  *reinterpret_cast<__half2*>(&v.y) = __floats2half2_rn(x[2], x[3]);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
+// One group of G threads (G = 32: a warp, G = blockDim.x: the whole CTA) per column.  Lanes run
+// along the column, which is contiguous in memory.
+template <typename T, bool BLOCK, bool VEC>
+__global__ void __launch_bounds__(256)
+pick_nll_forward_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ index,
+                        T* __restrict__ smax, long long lds, T* __restrict__ value, int rows,
+                        long long cols) {
+  __shared__ float red[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = BLOCK ? blockDim.x : 32;
+  const int g = BLOCK ? threadIdx.x : lane;
+  const long long j = BLOCK ? blockIdx.x : static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (j >= cols) return;  // BLOCK: uniform per CTA; warp mode: uniform per warp (no CTA barrier used)
+  const T* xc = x + j * ldx;
+  T* sc = smax + j * lds;
+
+  auto reduce = [&](float v, bool is_max) -> float {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    if (!BLOCK) return v;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < (blockDim.x >> 5); ++w) r = is_max ? fmaxf(r, red[w]) : r + red[w];
+    return r;
+  };
+
+  // VEC: columns start on 16-byte (fp16: 8-byte) boundaries; four elements per lane and pass,
+  // the last rows % 4 by the scalar tail.
+  const int rows4 = VEC ? rows / 4 : 0;
+  float m = -INFINITY;
+  for (int q = g; q < rows4; q += G) {
+    float v[4];
+    load4(xc + 4 * q, v);
+    m = fmaxf(fmaxf(m, fmaxf(v[0], v[1])), fmaxf(v[2], v[3]));
+  }
+  for (int i = 4 * rows4 + g; i < rows; i += G) m = fmaxf(m, to_f(xc[i]));
+  m = reduce(m, true);
+  float s = 0.f;
+  for (int q = g; q < rows4; q += G) {
+    float v[4];
+    load4(xc + 4 * q, v);
+    s += (expf(v[0] - m) + expf(v[1] - m)) + (expf(v[2] - m) + expf(v[3] - m));
+  }
+  for (int i = 4 * rows4 + g; i < rows; i += G) s += expf(to_f(xc[i]) - m);
+  s = reduce(s, false);
+  const float inv = 1.f / s;
+  for (int q = g; q < rows4; q += G) {
+    float v[4];
+    load4(xc + 4 * q, v);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = expf(v[e] - m) * inv;
+    store4(sc + 4 * q, v);
+  }
+  for (int i = 4 * rows4 + g; i < rows; i += G) sc[i] = from_f<T>(expf(to_f(xc[i]) - m) * inv);
+  if (g == 0) {
+    const int p = index[j];
+    // the reference takes the log of the stored (rounded) probability
+    const float picked = (p >= 0 && p < rows) ? to_f(from_f<T>(expf(to_f(xc[p]) - m) * inv)) : 0.f;
+    value[j] = from_f<T>(-logf(picked));
+  }
+}
+
+// One warp per column (eight columns per CTA), lanes along the column; no index arithmetic per
+// element.  VEC as above.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+pick_nll_backward_kernel(const T* __restrict__ smax, long long lds, const int* __restrict__ index,
+                         const T* __restrict__ grad, T* __restrict__ dx, long long lddx, int rows,
+                         long long cols) {
+  const int lane = threadIdx.x & 31;
+  const long long j = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (j >= cols) return;
+  const float g = to_f(grad[j]);
+  const int pick = index[j];
+  const T* sc = smax + j * lds;
+  T* dc = dx + j * lddx;
+  // two rounded steps, as the reference's two statements are: dX -= g at the pick, dX += y * g
+  auto one = [&](int i, float d, float y) {
+    if (i == pick) d = to_f(from_f<T>(d - g));
+    return to_f(from_f<T>(d + to_f(from_f<T>(y * g))));
+  };
+  const int rows4 = VEC ? rows / 4 : 0;
+  for (int q = lane; q < rows4; q += 32) {
+    float y[4], d[4];
+    load4(sc + 4 * q, y);
+    load4(dc + 4 * q, d);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) d[e] = one(4 * q + e, d[e], y[e]);
+    store4(dc + 4 * q, d);
+  }
+  for (int i = 4 * rows4 + lane; i < rows; i += 32) dc[i] = from_f<T>(one(i, to_f(dc[i]), to_f(sc[i])));
+}
+
+// One element of the update; returns the new weight and leaves d, m, v updated.
+template <typename T>
+__device__ __forceinline__ float adam_one(float w, float& d, float& m, float& v, float clip,
+                                          float b1, float b2, float step, float vscale, float eps) {
+  d = to_f(from_f<T>(fmaxf(fminf(d, clip), -clip)));  // the reference clips the gradient in place
+  m = b1 * m + (1.f - b1) * d;
+  v = b2 * v + (1.f - b2) * d * d;
+  // w += cast<Scalar>( step * m / (eps + sqrt(vscale * v)) ),  step = -lr / (1 - b1^t)
+  const float upd = to_f(from_f<T>(step * m / (eps + sqrtf(vscale * v))));
+  return to_f(from_f<T>(w + upd));
+}
+
+// VEC: all four arrays are 16-byte aligned (8-byte for fp16 w and d); four elements per thread and
+// pass, the last n % 4 elements by the scalar tail.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+adam_kernel(T* __restrict__ w, T* __restrict__ d, float* __restrict__ m, float* __restrict__ v,
+            long long n, float clip, float b1, float b2, float step, float vscale, float eps) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long n4 = VEC ? n / 4 : 0;
+  for (long long q = tid; q < n4; q += stride) {
+    float wi[4], di[4], mi[4], vi[4];
+    load4(w + 4 * q, wi);
+    load4(d + 4 * q, di);
+    load4(m + 4 * q, mi);
+    load4(v + 4 * q, vi);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      wi[e] = adam_one<T>(wi[e], di[e], mi[e], vi[e], clip, b1, b2, step, vscale, eps);
+    store4(w + 4 * q, wi);
+    store4(d + 4 * q, di);
+    store4(m + 4 * q, mi);
+    store4(v + 4 * q, vi);
+  }
+  for (long long i = 4 * n4 + tid; i < n; i += stride) {
+    float di = to_f(d[i]), mi = m[i], vi = v[i];
+    const float wn = adam_one<T>(to_f(w[i]), di, mi, vi, clip, b1, b2, step, vscale, eps);
+    w[i] = from_f<T>(wn);
+    d[i] = from_f<T>(di);
+    m[i] = mi;
+    v[i] = vi;
+  }
+}
+
+}  // namespace
+
+namespace {
+// Every column of a matrix with leading dimension ld starts on a boundary of `bytes`.
+bool cols_aligned(const void* p, long long ld, int esize, unsigned bytes) {
+  return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0 && (ld * esize) % bytes == 0;
+}
+
+template <typename T>
+void pick_forward_t(const void* x, long long ldx, const int* index, void* smax, long long lds,
+                    void* value, int rows, long long cols, cudaStream_t stream) {
+  const unsigned a = sizeof(T) * 4;
+  const bool vec = cols_aligned(x, ldx, sizeof(T), a) && cols_aligned(smax, lds, sizeof(T), a);
+  const bool block = rows > 2048;
+  const unsigned grid = block ? static_cast<unsigned>(cols) : static_cast<unsigned>((cols + 7) / 8);
+  const T* xp = static_cast<const T*>(x);
+  T* sp = static_cast<T*>(smax);
+  T* vp = static_cast<T*>(value);
+  if (block && vec) pick_nll_forward_kernel<T, true, true><<<grid, 256, 0, stream>>>(xp, ldx, index, sp, lds, vp, rows, cols);
+  else if (block) pick_nll_forward_kernel<T, true, false><<<grid, 256, 0, stream>>>(xp, ldx, index, sp, lds, vp, rows, cols);
+  else if (vec) pick_nll_forward_kernel<T, false, true><<<grid, 256, 0, stream>>>(xp, ldx, index, sp, lds, vp, rows, cols);
+  else pick_nll_forward_kernel<T, false, false><<<grid, 256, 0, stream>>>(xp, ldx, index, sp, lds, vp, rows, cols);
+}
+
+template <typename T>
+void pick_backward_t(const void* smax, long long lds, const int* index, const void* grad, void* dx,
+                     long long lddx, int rows, long long cols, cudaStream_t stream) {
+  const unsigned a = sizeof(T) * 4;
+  const bool vec = cols_aligned(smax, lds, sizeof(T), a) && cols_aligned(dx, lddx, sizeof(T), a);
+  const unsigned grid = static_cast<unsigned>((cols + 7) / 8);
+  const T* sp = static_cast<const T*>(smax);
+  const T* gp = static_cast<const T*>(grad);
+  T* dp = static_cast<T*>(dx);
+  if (vec) pick_nll_backward_kernel<T, true><<<grid, 256, 0, stream>>>(sp, lds, index, gp, dp, lddx, rows, cols);
+  else pick_nll_backward_kernel<T, false><<<grid, 256, 0, stream>>>(sp, lds, index, gp, dp, lddx, rows, cols);
+}
+}  // namespace
+
+cudaError_t launch_pick_nll_forward(int dtype, const void* x, long long ldx, const int* index,
+                                    void* smax, long long lds, void* value, int rows,
+                                    long long cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  if (cols > 0x7fffffffLL) return cudaErrorInvalidValue;
+  if (dtype == 0) pick_forward_t<float>(x, ldx, index, smax, lds, value, rows, cols, stream);
+  else pick_forward_t<__half>(x, ldx, index, smax, lds, value, rows, cols, stream);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds, const int* index,
+                                     const void* grad, void* dx, long long lddx, int rows,
+                                     long long cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  if (cols > 0x7fffffffLL) return cudaErrorInvalidValue;
+  if (dtype == 0) pick_backward_t<float>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
+  else pick_backward_t<__half>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_adam(int dtype, void* w, void* d, float* m, float* v, long long n, float clip,
+                        float b1, float b2, float step, float vscale, float eps, int num_sms,
+                        cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  auto al = [](const void* p, unsigned a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+  const bool vec = al(m, 16) && al(v, 16) && al(w, dtype == 0 ? 16 : 8) && al(d, dtype == 0 ? 16 : 8);
+  const long long work = vec ? (n + 3) / 4 : n;
+  long long blocks = (work + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms) * 8;  // grid-stride beyond eight CTAs per SM
+  if (blocks > cap) blocks = cap;
+  const unsigned g = static_cast<unsigned>(blocks);
+  if (dtype == 0) {
+    float *wf = static_cast<float*>(w), *df = static_cast<float*>(d);
+    if (vec) adam_kernel<float, true><<<g, 256, 0, stream>>>(wf, df, m, v, n, clip, b1, b2, step, vscale, eps);
+    else adam_kernel<float, false><<<g, 256, 0, stream>>>(wf, df, m, v, n, clip, b1, b2, step, vscale, eps);
+  } else {
+    __half *wh = static_cast<__half*>(w), *dh = static_cast<__half*>(d);
+    if (vec) adam_kernel<__half, true><<<g, 256, 0, stream>>>(wh, dh, m, v, n, clip, b1, b2, step, vscale, eps);
+    else adam_kernel<__half, false><<<g, 256, 0, stream>>>(wh, dh, m, v, n, clip, b1, b2, step, vscale, eps);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace gb

@@ -4,6 +4,8 @@
 #include <ginn/autobatch.h>
 #include <ginn/node/affine.h>
 #include <ginn/node/data.h>
+#include <ginn/node/pick.h>
 #include <ginn/node/prod.h>
 #include <ginn/prod.h>
+#include <ginn/update/update.h>
 #endif

@@ -211,6 +211,10 @@ class MlpDataParallel:
         self.x = B.colmajor(d[0], batch, torch.float32, device)
         self.x.copy_(torch.rand(d[0], batch, device=device, generator=gd))
         self.labels = torch.randint(0, 10, (batch,), device=device, generator=gd)
+        self.labels32 = self.labels.to(torch.int32)
+        self.smax = B.colmajor(d[3], batch, torch.float32, device, fill=0.0)
+        self.nll = torch.zeros(batch, device=device)
+        self.ones = torch.ones(batch, device=device)  # d(sum of the losses) / d(each loss)
         self.h = [self.x] + [B.colmajor(d[i + 1], batch, torch.float32, device, fill=0.0) for i in range(3)]
         self.dh = [None] + [B.colmajor(d[i + 1], batch, torch.float32, device, fill=0.0) for i in range(3)]
         self.acts = (B.ACT_RELU, B.ACT_RELU, B.ACT_NONE)
@@ -223,28 +227,20 @@ class MlpDataParallel:
     def step(self):
         gb = B
         self.grads.zero_()
-        for i in (1, 2):
+        for i in (1, 2, 3):
             self.dh[i].zero_()
         for i in range(3):
             gb.affine_forward([gb.Pair(self.W[i], self.h[i])], self.b[i], self.acts[i], self.h[i + 1])
-        logits = self.h[3]
-        logp = torch.log_softmax(logits, dim=0)
-        cols = torch.arange(self.batch, device=logits.device)
-        self.loss = -logp[self.labels, cols].sum()
-        dlog = torch.exp(logp)
-        dlog[self.labels, cols] -= 1.0
-        self.dh[3].copy_(dlog)
+        # loss = Sum(PickNegLogSoftmax(logits, labels)) (examples/mnist-dp.cu:141) and its gradient
+        gb.pick_nll_forward(self.h[3], self.labels32, self.smax, self.nll)
+        self.loss = self.nll.sum()
+        gb.pick_nll_backward(self.smax, self.labels32, self.ones, self.dh[3])
         for i in (2, 1, 0):
             gb.affine_backward([gb.PairGrad(self.W[i], self.h[i], self.dW[i],
                                             self.dh[i] if i > 0 else None)],
                                self.dh[i + 1], self.h[i + 1], self.acts[i], self.db[i])
         if self.allreduce is not None and self.world > 1:
             self.allreduce(self.grads)
-        # Adam on the flat buffers (glue)
+        # Adam on the flat buffers (ginn/update/update.h:115-133), one kernel
         self.t += 1
-        g = self.grads.clamp_(-5.0, 5.0)
-        self.m.mul_(0.9).add_(g, alpha=0.1)
-        self.v.mul_(0.999).addcmul_(g, g, value=0.001)
-        mhat = self.m / (1 - 0.9 ** self.t)
-        vhat = self.v / (1 - 0.999 ** self.t)
-        self.params.addcdiv_(mhat, vhat.sqrt_().add_(1e-8), value=-1e-3)
+        gb.adam_update(self.params, self.grads, self.m, self.v, self.t)

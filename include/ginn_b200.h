@@ -164,6 +164,36 @@ int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
 int ginn_b200_level_run(ginn_b200_level* level, void* stream);
 int ginn_b200_level_destroy(ginn_b200_level* level);
 
+/* ---- The elementwise neighbours of the products on a training step ------------------------ */
+
+/* Picked negative log softmax, forward: for every column j of x (rows x cols, column-major)
+ *   smax[:, j] = softmax(x[:, j]),   value[j] = -log(smax[index[j], j]).
+ * Replaces PickNegLogSoftmaxNode::forward_ (ginn/node/pick.h:209-216) with its SoftmaxOp::forward
+ * (ginn/nonlin.h:162-168: maximum, exp, sum, divide as four statements and two temporaries) and
+ * the thrust gather of PickNode::pick (pick.h:60-84).  `index` is a device array of `cols` ints;
+ * an index outside [0, rows) yields value = +inf (the reference asserts on the CPU only,
+ * pick.h:133-142).  smax is kept by the caller for the backward pass, as the node keeps smax_. */
+int ginn_b200_pick_nll_forward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                               const void* x, int64_t ldx, const int* index, void* smax,
+                               int64_t ldsmax, void* value);
+
+/* Backward of the above: dx[i, j] += (smax[i, j] - [i == index[j]]) * grad[j], one pass.
+ * Replaces PickNegLogSoftmaxNode::backward_ (pick.h:218-224) and pick_grad(negate) (pick.h:87-131:
+ * gather, subtract, scatter through a temporary). */
+int ginn_b200_pick_nll_backward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                                const void* smax, int64_t ldsmax, const int* index,
+                                const void* grad, void* dx, int64_t lddx);
+
+/* One Adam step on n elements: d is clipped to [-clip, clip] in place, then
+ *   m = beta1 m + (1 - beta1) d,  v = beta2 v + (1 - beta2) d^2,
+ *   w += -lr / (1 - beta1_t) * m / (eps + sqrt(v / (1 - beta2_t))),
+ * with beta1_t = beta1^t, beta2_t = beta2^t already advanced by the caller for this step.
+ * Replaces Adam::update (ginn/update/update.h:115-133: six tensor statements).  w and d have
+ * type `dtype`; m and v are always fp32, as the reference's History keeps them. */
+int ginn_b200_adam_update(int device, void* stream, int dtype, int64_t n, void* w, void* d,
+                          float* m, float* v, float lr, float clip, float eps, float beta1,
+                          float beta2, float beta1_t, float beta2_t);
+
 /* Text of the last failure on the calling thread ("" if none). */
 const char* ginn_b200_last_error(void);
 

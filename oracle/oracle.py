@@ -12,6 +12,10 @@ Reference lines followed (paths inside the ginn source tree):
   affine_forward         ginn/node/affine.h:35-77
   affine_backward        ginn/node/affine.h:79-129
   autobatch semantics    ginn/autobatch.h:80-183: a merged product equals the per-node products
+  pick_nll_forward       ginn/node/pick.h:60-84,177-182,209-216 with SoftmaxOp::forward,
+                         ginn/nonlin.h:162-168
+  pick_nll_backward      ginn/node/pick.h:87-131,218-224
+  adam_update            ginn/update/update.h:92-133
 
 Arithmetic: inputs exactly as handed to the GPU (fp32, or fp16-rounded), every product and sum
 in fp64, one rounding to the storage type where the reference materialises a tensor (node
@@ -119,6 +123,38 @@ def affine_backward(pairs, dout, out, act: int, store_dtype) -> dict:
         res["db"].append(f64(a).T @ dA)
         res["da"].append(dA @ f64(b).T)
     return res
+
+
+def pick_nll_forward(x, index):
+    """(smax, value): column softmax of x and -log of the entry index[j] of column j (fp64)."""
+    x = f64(x)
+    t = np.exp(x - x.max(axis=0, keepdims=True))
+    smax = t / t.sum(axis=0, keepdims=True)
+    idx = np.asarray(index, dtype=np.int64)
+    return smax, -np.log(smax[idx, np.arange(x.shape[1])])
+
+
+def pick_nll_backward(smax, index, grad, dx):
+    """dx + (smax - onehot(index)) * grad[None, :]  (fp64)."""
+    smax, g = f64(smax), f64(grad).reshape(1, -1)
+    out = f64(dx) + smax * g
+    idx = np.asarray(index, dtype=np.int64)
+    out[idx, np.arange(smax.shape[1])] -= g.ravel()
+    return out
+
+
+def adam_update(w, d, m, v, lr, clip, eps, beta1, beta2, beta1_t, beta2_t):
+    """One Adam step (fp64): returns (w, clipped d, m, v); beta*_t are beta^t for this step.
+    The hyper-parameters are the reference's `Real` members (ginn/update/update.h:92-97), i.e.
+    fp32 values: 1 - beta2 is 0.00099998713, not 0.001."""
+    lr, eps, beta1, beta2, beta1_t, beta2_t = (float(np.float32(x)) for x in
+                                               (lr, eps, beta1, beta2, beta1_t, beta2_t))
+    w, d, m, v = f64(w), f64(d), f64(m), f64(v)
+    d = np.clip(d, -clip, clip)
+    m = beta1 * m + (1.0 - beta1) * d
+    v = beta2 * v + (1.0 - beta2) * d * d
+    w = w + (-lr / (1.0 - beta1_t)) * m / (eps + np.sqrt(v / (1.0 - beta2_t)))
+    return w, d, m, v
 
 
 def rel_frobenius(x, ref) -> float:

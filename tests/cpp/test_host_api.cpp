@@ -330,6 +330,65 @@ static void test_errors() {
   CHECK(threw);  // CPU tensors are not served: no silent fallback
 }
 
+// test/nodes.cu.cpp:755-797 ("Pickles"): known picked negative log softmax, then the gradient
+// d/dW sum_j g_j * value_j = (softmax - onehot) * g against the closed form on the host.
+template <typename S>
+static void test_pick_nll(float eps) {
+  auto W = Values<S>(gpu(), {{-0.5, 0.55, -0.45}, {1., 2., -1.}, {0., 0., 0.}, {0.3, -0.33, 1.3}});
+  auto loss = PickNegLogSoftmax<S>(W, std::vector<Int>{3, 0, 1});
+  Graph g(loss);
+  g.forward();
+  CHECK((loss->shape() == Shape{1, 3}));
+  CHECK(close(loss->value().vector(), {1.43601264f, 1.8333567f, 2.73603603f}, eps));
+  g.reset_grad();
+  g.backward(2.);  // every column's loss weighted by 2
+  const std::vector<float> sm = floats(loss->softmax().vector());
+  std::vector<float> want(12);
+  const int idx[3] = {3, 0, 1};
+  for (int j = 0; j < 3; ++j)
+    for (int i = 0; i < 4; ++i) want[i + 4 * j] = 2.f * (sm[i + 4 * j] - (i == idx[j] ? 1.f : 0.f));
+  CHECK(close(W->grad().vector(), want, eps * 10, eps));
+  // index count must match the columns
+  bool threw = false;
+  try {
+    Graph(PickNegLogSoftmax<S>(W, std::vector<Int>{0, 1})).forward();
+  } catch (const RuntimeError&) {
+    threw = true;
+  }
+  CHECK(threw);
+}
+
+// ginn/update/update.h:115-133 restated on the host in double, two steps.
+static void test_adam() {
+  auto w = Random<Real>(gpu(), {7, 5}, 70);
+  update::Adam<Real> adam;  // lr 1e-3, clip 5, eps 1e-8, betas 0.9 / 0.999
+  adam.init(w);
+  std::vector<double> ref(35), m(35, 0.), v(35, 0.);
+  const std::vector<Real> w0 = w->value().vector();
+  for (int i = 0; i < 35; ++i) ref[i] = w0[i];
+  double b1t = 1, b2t = 1;
+  w->grad().resize(w->shape());
+  for (int t = 0; t < 2; ++t) {
+    std::vector<Real> d(35);
+    for (int i = 0; i < 35; ++i) d[i] = 0.9f * (i - 17) * (t + 1);  // some beyond the clip
+    w->grad().set(d);
+    adam.update(w);
+    b1t *= 0.9;
+    b2t *= 0.999;
+    for (int i = 0; i < 35; ++i) {
+      const double dc = std::fmin(std::fmax(double(d[i]), -5.), 5.);
+      m[i] = 0.9 * m[i] + 0.1 * dc;
+      v[i] = 0.999 * v[i] + 0.001 * dc * dc;
+      ref[i] += -1e-3 / (1 - b1t) * m[i] / (1e-8 + std::sqrt(v[i] / (1 - b2t)));
+    }
+    const std::vector<Real> dgot = w->grad().vector();
+    for (int i = 0; i < 35; ++i) CHECK(std::fabs(dgot[i]) <= 5.f);  // clipped in place
+  }
+  std::vector<float> want(35);
+  for (int i = 0; i < 35; ++i) want[i] = static_cast<float>(ref[i]);
+  CHECK(close(w->value().vector(), want, 1e-6f, 1e-6f));
+}
+
 int main() {
   if (gpus() < 1) {
     std::printf("no GPU\n");
@@ -350,6 +409,9 @@ int main() {
   test_autobatch();
   test_prealloc_accounting();
   test_errors();
+  test_pick_nll<Real>(1e-6f);
+  test_pick_nll<Half>(2e-3f);
+  test_adam();
   cudaDeviceSynchronize();
   const int status = ginn_b200_device_status(0, 1);
   CHECK(status == 0);

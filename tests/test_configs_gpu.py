@@ -172,3 +172,41 @@ def test_lstm_harness_matches_autograd(gpu):
     loss.backward()
     check(B.to_host(w.dW), W.grad.cpu().numpy(), np.float32, "dW")
     check(B.to_host(w.db), b.grad.cpu().numpy(), np.float32, "db")
+
+
+def test_mlp_harness_matches_autograd_and_adam(gpu):
+    """Config 5's training step (three fused Affines, picked negative log softmax, Adam in one
+    kernel each) against torch autograd in fp64 and a restatement of ginn's Adam
+    (ginn/update/update.h:115-133).  Each step starts the fp64 side from the GPU's current
+    parameters and feeds its Adam the GPU's (clipped) gradients: Adam's first steps move a weight
+    by about lr * sign(gradient), so a gradient that is zero to rounding would otherwise decide
+    the comparison."""
+    from ginn_b200.workloads import MlpDataParallel
+    w = MlpDataParallel(torch.device("cuda", 0), batch=256)
+    views = list(w.W) + list(w.b)
+    gviews = list(w.dW) + list(w.db)
+    m = [torch.zeros_like(p, dtype=torch.float64) for p in views]
+    v = [torch.zeros_like(p, dtype=torch.float64) for p in views]
+    x = w.x.double()
+    for t in (1, 2, 3):
+        params = [p.double().clone().requires_grad_(True) for p in views]
+        w.step()
+        torch.cuda.synchronize()
+        h = x
+        for i in range(3):
+            h = params[i] @ h + params[3 + i][:, None]
+            if i < 2:
+                h = torch.relu(h)
+        loss = torch.nn.functional.cross_entropy(h.T, w.labels, reduction="sum")
+        loss.backward()
+        assert abs(float(w.loss) - float(loss)) <= 1e-5 * abs(float(loss))
+        with torch.no_grad():
+            for i, p in enumerate(params):
+                g = p.grad.clamp(-5.0, 5.0)
+                got = gviews[i].double()
+                assert float((got - g).norm() / g.norm()) <= 1e-5, f"gradient {i} step {t}"
+                m[i] = 0.9 * m[i] + 0.1 * got
+                v[i] = 0.999 * v[i] + 0.001 * got * got
+                want = p + (-1e-3 / (1 - 0.9 ** t)) * m[i] / (1e-8 + (v[i] / (1 - 0.999 ** t)).sqrt())
+                now = views[i].double()
+                assert float((now - want).norm() / want.norm()) <= 1e-6, f"parameter {i} step {t}"

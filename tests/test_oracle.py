@@ -50,6 +50,36 @@ def test_affine_broadcast_and_high_rank(kat):
     np.testing.assert_allclose(out.reshape(h["WVb_shape"], order="F"), arr(h["WVb"]), rtol=1e-6)
 
 
+def test_pick_nll_known_answer_and_gradient(kat):
+    """test/nodes.cu.cpp:755-797: picked softmax and its negative log; the gradient restatement
+    against central differences, as the reference's CHECK_ does."""
+    k = kat["pick_nll"]
+    W, idx = arr(k["W"], np.float64), k["index"]
+    smax, val = orc.pick_nll_forward(W, idx)
+    np.testing.assert_allclose(smax[idx, np.arange(3)], k["psm"], rtol=1e-6)
+    np.testing.assert_allclose(val, k["pnlsm"], rtol=1e-6)
+    g = np.array([0.7, -1.3, 2.1])
+    dx = orc.pick_nll_backward(smax, idx, g, np.zeros_like(W))
+    num = np.zeros_like(W)
+    for i in range(W.shape[0]):
+        for j in range(W.shape[1]):
+            e = np.zeros_like(W)
+            e[i, j] = 1e-6
+            num[i, j] = ((orc.pick_nll_forward(W + e, idx)[1] - orc.pick_nll_forward(W - e, idx)[1]) * g).sum() / 2e-6
+    np.testing.assert_allclose(dx, num, rtol=1e-5, atol=1e-8)
+
+
+def test_adam_restatement_first_steps():
+    """ginn/update/update.h:115-133 by hand: with m = v = 0, step 1 moves every weight by
+    -lr * sign(d) (up to eps), whatever the size of d, and clips d in place."""
+    w, d = np.array([1.0, -2.0, 0.5]), np.array([0.3, -8.0, 0.0])
+    w1, d1, m1, v1 = orc.adam_update(w, d, np.zeros(3), np.zeros(3), 1e-3, 5.0, 1e-8, 0.9, 0.999, 0.9, 0.999)
+    np.testing.assert_allclose(d1, [0.3, -5.0, 0.0])
+    np.testing.assert_allclose(m1, 0.1 * d1, rtol=1e-6)  # betas are fp32 values, as in the reference
+    np.testing.assert_allclose(v1, 0.001 * d1 * d1, rtol=2e-5)
+    np.testing.assert_allclose(w1, w - 1e-3 * np.sign(d1), atol=1e-9)
+
+
 def test_lstm_five_steps_match_recorded_values():
     """test/model.cpp:22-66: five Lstm::step calls (ginn/model/lstm.h:90-105), values recorded
     from PyTorch.  Exercises multi-pair Affines with fused sigmoid/tanh."""

@@ -1,0 +1,92 @@
+"""GPU parity of the step neighbours (picked negative log softmax, Adam) against the oracle,
+through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from ginn_b200 import binding as B
+from oracle import oracle as orc
+from helpers import check, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def test_pick_nll_known_answer(gpu, kat):
+    """test/nodes.cu.cpp:755-797."""
+    k = kat["pick_nll"]
+    for dt in (np.float32, np.float16):
+        x = B.from_host(np.asarray(k["W"], dt))
+        idx = torch.tensor(k["index"], dtype=torch.int32, device="cuda")
+        smax = B.colmajor(4, 3, x.dtype, fill=0.0)
+        val = torch.zeros(3, dtype=x.dtype, device="cuda")
+        gpu.pick_nll_forward(x, idx, smax, val)
+        torch.cuda.synchronize()
+        eps = k["eps"]["f32" if dt == np.float32 else "f16"]
+        np.testing.assert_allclose(val.float().cpu().numpy(), k["pnlsm"], rtol=max(eps, 2e-6) * 2)
+        np.testing.assert_allclose(B.to_host(smax).astype(np.float64)[k["index"], np.arange(3)],
+                                   k["psm"], rtol=max(eps, 2e-6) * 2)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+@pytest.mark.parametrize("rows,cols,pad", [(10, 4096, 0), (1, 7, 0), (33, 100, 3), (1000, 37, 5), (5000, 9, 0)])
+def test_pick_nll_forward_backward(gpu, dt, rows, cols, pad):
+    """C5's 10 x 4096 logits, a single row, padded leading dimensions, and a vocabulary-sized
+    column (one CTA per column)."""
+    rng = np.random.default_rng(rows * 131 + cols)
+    # Half keeps the picked probability in fp16 before taking its log, as the reference does:
+    # logits are kept small enough that no probability falls into the subnormal range
+    x = (randn(rng, (rows, cols), dt) * (3 if dt == np.float32 else 0.5)).astype(dt)
+    idx = rng.integers(0, rows, cols).astype(np.int32)
+    g = randn(rng, (cols,), dt)
+    dx0 = randn(rng, (rows, cols), dt)
+    X, DX = B.from_host(x, ld=rows + pad), B.from_host(dx0, ld=rows + pad)
+    S = B.colmajor(rows, cols, X.dtype, ld=rows + pad, fill=0.0)
+    I = torch.from_numpy(idx).cuda()
+    V = torch.zeros(cols, dtype=X.dtype, device="cuda")
+    G = torch.from_numpy(g).cuda()
+    gpu.pick_nll_forward(X, I, S, V)
+    gpu.pick_nll_backward(S, I, G, DX)
+    torch.cuda.synchronize()
+    smax, val = orc.pick_nll_forward(x, idx)
+    check(B.to_host(S), smax, dt, "smax")
+    check(V.cpu().numpy(), val, dt, "value")
+    # backward from the stored (rounded) probabilities, as the node does
+    ref = orc.pick_nll_backward(B.to_host(S), idx, g, dx0)
+    check(B.to_host(DX), ref, dt, "dx")
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_adam_three_steps(gpu, dt):
+    """C5's flat parameter buffer size; three steps so that m, v and the bias corrections matter."""
+    n = 1_863_690 if dt == np.float32 else 100_003
+    rng = np.random.default_rng(77)
+    w = randn(rng, (n,), dt)
+    m, v = np.zeros(n), np.zeros(n)
+    W = torch.from_numpy(w).cuda()
+    M = torch.zeros(n, device="cuda")
+    Vv = torch.zeros(n, device="cuda")
+    wref = w.astype(np.float64)
+    for t in (1, 2, 3):
+        d = (randn(rng, (n,), dt) * 4).astype(dt)  # some elements beyond the clip of 5
+        D = torch.from_numpy(d).cuda()
+        gpu.adam_update(W, D, M, Vv, t)
+        torch.cuda.synchronize()
+        wref, dref, m, v = orc.adam_update(wref, d, m, v, 1e-3, 5.0, 1e-8, 0.9, 0.999, 0.9 ** t, 0.999 ** t)
+        wref = wref.astype(dt).astype(np.float64)  # the weight is stored in dt after every step
+        np.testing.assert_array_equal(D.cpu().numpy(), dref.astype(dt))
+        check(M.cpu().numpy(), m, np.float32, f"m step {t}")
+        check(Vv.cpu().numpy(), v, np.float32, f"v step {t}")
+        check(W.cpu().numpy(), wref, dt, f"w step {t}")
+    if dt == np.float32:
+        np.testing.assert_allclose(W.cpu().numpy(), wref, rtol=1e-6, atol=2e-6)  # a few ulp of the largest weights
+
+
+def test_step_ops_reject_bad_arguments(gpu):
+    x = B.colmajor(4, 3, torch.float32, fill=0.0)
+    idx = torch.zeros(3, dtype=torch.int32, device="cuda")
+    with pytest.raises(B.GinnB200Error):
+        B._check(B.lib().ginn_b200_pick_nll_forward(0, None, 0, 4, 3, x.data_ptr(), 2, idx.data_ptr(),
+                                                    x.data_ptr(), 4, x.data_ptr()))
+    with pytest.raises(B.GinnB200Error):
+        B._check(B.lib().ginn_b200_adam_update(0, None, 0, 4, x.data_ptr(), x.data_ptr(), x.data_ptr(),
+                                               x.data_ptr(), 1e-3, 5.0, 1e-8, 0.9, 0.999, 1.0, 0.999))
