@@ -82,8 +82,11 @@ def lib():
     L.ginn_b200_pick_nll_forward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, vp, i64, vp]
     L.ginn_b200_pick_nll_backward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, vp, vp, i64]
     L.ginn_b200_adam_update.argtypes = [ci, vp, ci, i64, vp, vp, vp, vp, cf, cf, cf, cf, cf, cf, cf]
+    L.ginn_b200_softmax_forward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, i64]
+    L.ginn_b200_softmax_backward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, ci]
     for name in ("ginn_b200_pick_nll_forward", "ginn_b200_pick_nll_backward",
-                 "ginn_b200_adam_update"):
+                 "ginn_b200_adam_update", "ginn_b200_softmax_forward",
+                 "ginn_b200_softmax_backward"):
         getattr(L, name).restype = ci
     L.ginn_b200_last_error.restype = C.c_char_p
     L.ginn_b200_device_status.argtypes = [ci, ci]
@@ -327,6 +330,27 @@ def pick_nll_backward(smax: torch.Tensor, index: torch.Tensor, grad: torch.Tenso
     _check(lib().ginn_b200_pick_nll_backward(_dev(smax), _stream(smax), _dtype_of(smax), rows, cols,
                                              smax.data_ptr(), _ld(smax), index.data_ptr(),
                                              grad.data_ptr(), dx.data_ptr(), _ld(dx)))
+
+
+def _fold_cols(t: torch.Tensor):
+    """(rows, cols) of a column-major tensor with its trailing dimensions folded into cols."""
+    assert t.stride(0) == 1 and (t.dim() < 3 or t.stride(2) == t.stride(1) * t.shape[1])
+    return t.shape[0], t.numel() // t.shape[0]
+
+
+def softmax_forward(x: torch.Tensor, y: torch.Tensor) -> None:
+    """y = softmax over dimension 0 of x (column-major, batches folded into the columns)."""
+    rows, cols = _fold_cols(x)
+    _check(lib().ginn_b200_softmax_forward(_dev(x), _stream(x), _dtype_of(x), rows, cols,
+                                           x.data_ptr(), _ld(x), y.data_ptr(), _ld(y)))
+
+
+def softmax_backward(y: torch.Tensor, dy: torch.Tensor, dx: torch.Tensor, accumulate=True) -> None:
+    """dx (+)= y * (dy - sum over dimension 0 of y * dy)."""
+    rows, cols = _fold_cols(y)
+    _check(lib().ginn_b200_softmax_backward(_dev(y), _stream(y), _dtype_of(y), rows, cols,
+                                            y.data_ptr(), _ld(y), dy.data_ptr(), _ld(dy),
+                                            dx.data_ptr(), _ld(dx), int(accumulate)))
 
 
 def adam_update(w: torch.Tensor, d: torch.Tensor, m: torch.Tensor, v: torch.Tensor, t: int,

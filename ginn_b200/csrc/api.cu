@@ -159,7 +159,35 @@ Operand shift_k(const Operand& o, int dtype, long long k0) {
 // launch, the activation with the last.
 constexpr long long kMaxChainK = 8192;
 
+// Products with one extent of at most 16 go to the CUDA-core kernels of small.cu (automatic
+// path choice only); a bias gradient riding on such a product is issued as its own launch.
+// Sets *done when the problem was taken.
+int try_skinny(int dtype, Problem& p, cudaStream_t stream, bool* done) {
+  *done = false;
+  if (p.M <= 0 || p.N <= 0 || p.batches <= 0) return GINN_B200_OK;
+  Problem q = p;
+  q.rowsum = nullptr;
+  const bool rowsum_ok = p.rowsum == nullptr || (p.a[0].cols == nullptr && p.a[0].ycols == nullptr &&
+                                                 p.batches == 1 && !p.a[0].k_contig);
+  const int kind = rowsum_ok ? gb::skinny_kind(dtype, q) : 0;
+  if (kind == 0) return GINN_B200_OK;
+  if (p.rowsum != nullptr) {
+    CU_TRY(gb::launch_rowsum(dtype, p.a[0].base, p.a[0].ybase, p.a[0].dact, p.a[0].ld, p.M, p.k[0],
+                             p.rowsum, stream));
+    g_launches.fetch_add(1);
+  }
+  CU_TRY(gb::launch_skinny(dtype, kind, q, stream));
+  g_launches.fetch_add(1);
+  *done = true;
+  return GINN_B200_OK;
+}
+
 int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
+  if (g_force_path.load() == PATH_AUTO) {
+    bool done = false;
+    if (int s = try_skinny(dtype, p, stream, &done)) return s;
+    if (done) return GINN_B200_OK;
+  }
   bool chain = dtype == GINN_B200_F32 && g_force_path.load() != PATH_SMALL;
   long long kmax = 0, ktot = 0;
   for (int i = 0; i < p.npairs; ++i) {
@@ -688,6 +716,37 @@ int ginn_b200_pick_nll_forward(int device, void* stream, int dtype, int64_t rows
   if (int s = get_ctx(device, &ctx)) return s;
   CU_TRY(gb::launch_pick_nll_forward(dtype, x, ldx, index, smax, ldsmax, value, (int)rows, cols,
                                      static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+int ginn_b200_softmax_forward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                              const void* x, int64_t ldx, void* y, int64_t ldy) {
+  if (int s = check_common(dtype, rows, cols, 0)) return s;
+  if (rows == 0 || cols == 0) return GINN_B200_OK;
+  if (!x || !y) return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  if (ldx < rows || ldy < rows)
+    return fail(GINN_B200_BAD_ARGUMENT, "leading dimension smaller than %lld rows", (long long)rows);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  CU_TRY(gb::launch_pick_nll_forward(dtype, x, ldx, nullptr, y, ldy, nullptr, (int)rows, cols,
+                                     static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+int ginn_b200_softmax_backward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                               const void* y, int64_t ldy, const void* dy, int64_t lddy, void* dx,
+                               int64_t lddx, int accumulate) {
+  if (int s = check_common(dtype, rows, cols, 0)) return s;
+  if (rows == 0 || cols == 0) return GINN_B200_OK;
+  if (!y || !dy || !dx) return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  if (ldy < rows || lddy < rows || lddx < rows)
+    return fail(GINN_B200_BAD_ARGUMENT, "leading dimension smaller than %lld rows", (long long)rows);
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  CU_TRY(gb::launch_softmax_backward(dtype, y, ldy, dy, lddy, dx, lddx, (int)rows, cols,
+                                     accumulate ? 1 : 0, static_cast<cudaStream_t>(stream)));
   g_launches.fetch_add(1);
   return GINN_B200_OK;
 }

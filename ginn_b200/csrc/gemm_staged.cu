@@ -118,8 +118,8 @@ struct TileLoader {
 #pragma unroll
             for (int e = 0; e < E; ++e) {
               if (kk + e < K) {
-                d[e] = __ldg(ptr[i] + kk + e);
-                if (has_y) y[e] = __ldg(yptr[i] + kk + e);
+                d[e] = ldg1(ptr[i] + kk + e);
+                if (has_y) y[e] = ldg1(yptr[i] + kk + e);
               }
             }
           }
@@ -145,11 +145,11 @@ struct TileLoader {
             if (kk + e < K) {
               float yv = 0.f;
               if (P.cols != nullptr) {
-                d[e] = __ldg(static_cast<const T*>(P.cols[kk + e]) + o);
-                if (has_y) yv = to_f(__ldg(static_cast<const T*>(P.ycols[kk + e]) + o));
+                d[e] = ldg1(static_cast<const T*>(P.cols[kk + e]) + o);
+                if (has_y) yv = to_f(ldg1(static_cast<const T*>(P.ycols[kk + e]) + o));
               } else {
-                d[e] = __ldg(rowp + (kk + e) * P.ld);
-                if (has_y) yv = to_f(__ldg(yrowp + (kk + e) * P.ld));
+                d[e] = ldg1(rowp + (kk + e) * P.ld);
+                if (has_y) yv = to_f(ldg1(yrowp + (kk + e) * P.ld));
               }
               if (has_y) d[e] = from_f<T>(act_backward<T>(P.dact, yv, to_f(d[e])));
             }

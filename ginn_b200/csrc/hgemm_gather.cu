@@ -60,8 +60,8 @@ __device__ __noinline__ Piece2 load_piece_slow(const __half* p, const __half* y,
 #pragma unroll
   for (int e = 0; e < 8; ++e)
     if (e < valid) {
-      dh[e] = __ldg(p + e);
-      if (y) yh[e] = __ldg(y + e);
+      dh[e] = ldg1(p + e);
+      if (y) yh[e] = ldg1(y + e);
     }
   return r;
 }

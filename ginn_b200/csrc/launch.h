@@ -78,6 +78,11 @@ cudaError_t launch_wait_selftest(int* status, long long limit_cycles, int* retur
 // --- CUDA-core kernels for degenerate shapes and elementwise helpers (small.cu) ---
 // One warp per output element; used for tiny m*n (batched dot products) and k == 0.
 cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream);
+// Products with one extent of at most 16 (or a total contraction of at most 32) on CUDA cores.
+// skinny_kind: 0 = not taken, else the mapping to pass to launch_skinny.  Problems with a bias
+// gradient are not taken: the caller issues launch_rowsum first and clears `rowsum`.
+int skinny_kind(int dtype, const Problem& p);
+cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t stream);
 // rowsum[o] += sum_n dY[o, n] * act'(Y[o, n])   (bias gradient when no weight gradient is wanted)
 cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
                           long long N, void* rowsum, cudaStream_t stream);
@@ -86,6 +91,10 @@ cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, lo
 cudaError_t launch_pick_nll_forward(int dtype, const void* x, long long ldx, const int* index,
                                     void* smax, long long lds, void* value, int rows,
                                     long long cols, cudaStream_t stream);
+// index == nullptr in launch_pick_nll_forward: plain column softmax, `value` unused.
+cudaError_t launch_softmax_backward(int dtype, const void* y, long long ldy, const void* dy,
+                                    long long lddy, void* dx, long long lddx, int rows,
+                                    long long cols, int accumulate, cudaStream_t stream);
 cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds, const int* index,
                                      const void* grad, void* dx, long long lddx, int rows,
                                      long long cols, cudaStream_t stream);

@@ -7,6 +7,16 @@
 
 namespace gb {
 
+// One element through the read-only path.  The fp16 overload of __ldg in cuda_fp16.hpp is a
+// non-volatile asm statement, which the compiler may hoist above the bounds test that guards it
+// (it did: a predicated loop over rows read past the end of a matrix); a volatile one stays put.
+__device__ __forceinline__ float ldg1(const float* p) { return __ldg(p); }
+__device__ __forceinline__ __half ldg1(const __half* p) {
+  unsigned short v;
+  asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(v) : "l"(p));
+  return __ushort_as_half(v);
+}
+
 __device__ __forceinline__ float to_f(float x) { return x; }
 __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
 template <typename T>

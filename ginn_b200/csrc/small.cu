@@ -3,7 +3,19 @@
 //     that SoftmaxOp::backward and LayerNormNode::backward send through gpu_batched_prod
 //     (ginn/nonlin.h:180-183, ginn/node/layernorm.h:61-64), and k == 0;
 //   * the bias gradient alone (row sums of dY (.) act'(Y)) when no weight gradient is wanted.
-// fp32 accumulation, one warp per output element, lanes strided along the contraction.
+//   * "skinny" products, where one extent is at most 16 (a 10-class output layer: W 10 x 1024 on
+//     4096 columns, and its two gradients).  A 128 x 128 tensor-core tile would be 8 % full and
+//     the product is bound by reading or writing the large operand once, so CUDA cores at HBM
+//     speed win by a wide margin.  Three mappings, chosen so that the large operand is read or
+//     written coalesced:
+//       skinny_m_kernel   m <= 16, B contraction-contiguous: one warp per column of C, lanes
+//                         along k, up to 16 running sums, warp reduction
+//       skinny_mt_kernel  m <= 16, B outer-contiguous (weight gradients): lanes along n, one
+//                         k-chunk per CTA row, partial sums added to C with atomics (fp32,
+//                         accumulating products only)
+//       skinny_k_kernel   k <= 32 in total: one thread per element of C, lanes along m
+// fp32 accumulation throughout; the tiny-result kernel uses one warp per output element, lanes
+// strided along the contraction.
 #include <cuda_fp16.h>
 #include "ptx.cuh"
 #include "math.cuh"
@@ -14,7 +26,7 @@ namespace gb {
 namespace {
 
 __device__ __forceinline__ float ld_f(const float* p) { return __ldg(p); }
-__device__ __forceinline__ float ld_f(const __half* p) { return __half2float(__ldg(p)); }
+__device__ __forceinline__ float ld_f(const __half* p) { return __half2float(ldg1(p)); }
 // Plain (coherent) loads for locations this kernel also writes.
 __device__ __forceinline__ float ld_rw(const float* p) { return *p; }
 __device__ __forceinline__ float ld_rw(const __half* p) { return __half2float(*p); }
@@ -69,6 +81,251 @@ __global__ void small_gemm_kernel(const __grid_constant__ Problem P) {
     if (P.bias) x += ld_f(static_cast<const T*>(P.bias) + row);
     if (P.accumulate) x += ld_rw(cp);
     st_f(cp, act_forward<T>(P.act, x));
+  }
+}
+
+constexpr int kSkinny = 16;
+
+// Writes one element of C: bias, previous value, activation, one rounding.
+template <typename T>
+__device__ __forceinline__ void finish(const Problem& P, long long batch, long long row,
+                                       long long col, float x) {
+  T* cp = (P.ccols ? static_cast<T*>(P.ccols[col])
+                   : static_cast<T*>(P.c) + batch * P.c_batch_stride + col * P.ldc) + row;
+  if (P.bias) x += ld_f(static_cast<const T*>(P.bias) + row);
+  if (P.accumulate) x += ld_rw(cp);
+  st_f(cp, act_forward<T>(P.act, x));
+}
+
+// m <= 16: one warp per (column, batch); lanes strided along the contraction.
+template <typename T>
+__global__ void __launch_bounds__(256) skinny_m_kernel(const __grid_constant__ Problem P) {
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_global >= static_cast<long long>(P.N) * P.batches) return;
+  const long long batch = warp_global / P.N;
+  const long long col = warp_global % P.N;
+  float acc[kSkinny];
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m) acc[m] = 0.f;
+  for (int p = 0; p < P.npairs; ++p) {
+    const long long ab = batch * P.a[p].batch_stride, bb = batch * P.b[p].batch_stride;
+    for (long long kk = lane; kk < P.k[p]; kk += 32) {
+      const float b = fetch<T>(P.b[p], bb, col, kk);
+#pragma unroll
+      for (int m = 0; m < kSkinny; ++m)
+        if (m < P.M) acc[m] += fetch<T>(P.a[p], ab, m, kk) * b;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], off);
+  }
+  // lane m keeps row m (every lane holds every sum after the butterfly)
+  float mine = 0.f;
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m)
+    if (lane == m) mine = acc[m];
+  if (lane < P.M) finish<T>(P, batch, lane, col, mine);
+}
+
+// m <= 16, accumulating, B outer-contiguous: thread = column n, blockIdx.y = k-chunk of 128.
+__global__ void __launch_bounds__(128) skinny_mt_kernel(const __grid_constant__ Problem P) {
+  const long long col = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long batch = blockIdx.z;
+  if (col >= P.N) return;
+  float acc[kSkinny];
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m) acc[m] = 0.f;
+  // chunks are numbered over the concatenated contraction of all pairs
+  long long chunk = blockIdx.y;
+  for (int p = 0; p < P.npairs; ++p) {
+    const long long nchunks = (P.k[p] + 127) / 128;
+    if (chunk >= nchunks) {
+      chunk -= nchunks;
+      continue;
+    }
+    const long long ab = batch * P.a[p].batch_stride, bb = batch * P.b[p].batch_stride;
+    const long long k1 = chunk * 128 + 128 < P.k[p] ? chunk * 128 + 128 : P.k[p];
+    for (long long kk = chunk * 128; kk < k1; ++kk) {
+      const float b = fetch<float>(P.b[p], bb, col, kk);
+#pragma unroll
+      for (int m = 0; m < kSkinny; ++m)
+        if (m < P.M) acc[m] += fetch<float>(P.a[p], ab, m, kk) * b;
+    }
+    break;
+  }
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m)
+    if (m < P.M) {
+      float* cp = (P.ccols ? static_cast<float*>(P.ccols[col])
+                           : static_cast<float*>(P.c) + batch * P.c_batch_stride + col * P.ldc) + m;
+      atomicAdd(cp, acc[m]);
+    }
+}
+
+// total k <= 32: one thread per element of C, consecutive threads along m.
+template <typename T>
+__global__ void __launch_bounds__(256) skinny_k_kernel(const __grid_constant__ Problem P) {
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long per_batch = static_cast<long long>(P.M) * P.N;
+  if (e >= per_batch * P.batches) return;
+  const long long batch = e / per_batch;
+  const long long rem = e - batch * per_batch;
+  const long long col = rem / P.M;
+  const long long row = rem - col * P.M;
+  float acc = 0.f;
+  for (int p = 0; p < P.npairs; ++p) {
+    const long long ab = batch * P.a[p].batch_stride, bb = batch * P.b[p].batch_stride;
+    for (long long kk = 0; kk < P.k[p]; ++kk)
+      acc += fetch<T>(P.a[p], ab, row, kk) * fetch<T>(P.b[p], bb, col, kk);
+  }
+  finish<T>(P, batch, row, col, acc);
+}
+
+// ---- lean variants for plain operands (no pointer tables, no fused derivative, one pair): the
+// generic fetch() above costs some thirty instructions per element, which would bound these
+// kernels; here an element is one load from base + o * so + k * sk. ----
+template <typename T>
+struct Plain {
+  const T* p;
+  long long so, sk;  // element strides along the outer index and along the contraction
+  __device__ __forceinline__ Plain(const Operand& op, long long batch)
+      : p(static_cast<const T*>(op.base) + batch * op.batch_stride),
+        so(op.k_contig ? op.ld : 1),
+        sk(op.k_contig ? 1 : op.ld) {}
+};
+
+// m <= 16, B contraction-contiguous.  A CTA owns 32 columns of C (four per warp).  The small
+// operand A is staged, 512 contraction indices at a time, in shared memory as [m][k], so that
+// lanes running along k read it without bank conflicts whatever its layout in memory is (read
+// straight from global memory, an outer-contiguous A costs ten cache lines per load: lanes are
+// 4 m bytes apart).  Every staged value is used for the four columns of the warp.
+constexpr int kSkinnyKC = 512;
+template <typename T>
+__global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_constant__ Problem P) {
+  __shared__ float As[kSkinny * kSkinnyKC];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long batch = blockIdx.y;
+  const Plain<T> A(P.a[0], batch), Bm(P.b[0], batch);
+  const int M = P.M;
+  const long long K = P.k[0];
+  const long long col0 = static_cast<long long>(blockIdx.x) * 32 + warp * 4;
+  const T* bp[4];
+  bool live[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    live[c] = col0 + c < P.N;
+    bp[c] = Bm.p + (live[c] ? col0 + c : 0) * Bm.so;  // contraction-contiguous: sk = 1
+  }
+  float acc[4][kSkinny];
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int m = 0; m < kSkinny; ++m) acc[c][m] = 0.f;
+  for (long long k0 = 0; k0 < K; k0 += kSkinnyKC) {
+    const int kc = K - k0 < kSkinnyKC ? static_cast<int>(K - k0) : kSkinnyKC;
+    __syncthreads();
+    for (int kk = threadIdx.x; kk < kc; kk += 256) {
+      const T* ak = A.p + (k0 + kk) * A.sk;
+#pragma unroll
+      for (int m = 0; m < kSkinny; ++m)
+        if (m < M) As[m * kSkinnyKC + kk] = ld_f(ak + m * A.so);
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int kk = lane; kk < kc; kk += 32) {
+      float b[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) b[c] = live[c] ? ld_f(bp[c] + k0 + kk) : 0.f;
+#pragma unroll
+      for (int m = 0; m < kSkinny; ++m)
+        if (m < M) {
+          const float a = As[m * kSkinnyKC + kk];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[c][m] += a * b[c];
+        }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float mine = 0.f;
+#pragma unroll
+    for (int m = 0; m < kSkinny; ++m) {
+      float v = acc[c][m];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if (lane == m) mine = v;
+    }
+    if (live[c] && lane < M) finish<T>(P, batch, lane, col0 + c, mine);
+  }
+}
+
+__global__ void __launch_bounds__(128) skinny_mt_plain_kernel(const __grid_constant__ Problem P) {
+  const long long col = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long batch = blockIdx.z;
+  if (col >= P.N) return;
+  const Plain<float> A(P.a[0], batch), Bm(P.b[0], batch);
+  const float* bp = Bm.p + col * Bm.so;
+  const int M = P.M;
+  const long long k0 = static_cast<long long>(blockIdx.y) * 128;
+  const long long k1 = k0 + 128 < P.k[0] ? k0 + 128 : P.k[0];
+  float acc[kSkinny];
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m) acc[m] = 0.f;
+#pragma unroll 4
+  for (long long kk = k0; kk < k1; ++kk) {
+    const float b = __ldg(bp + kk * Bm.sk);
+    const float* ak = A.p + kk * A.sk;  // the same address in every lane: a broadcast load
+#pragma unroll
+    for (int m = 0; m < kSkinny; ++m)
+      if (m < M) acc[m] += __ldg(ak + m * A.so) * b;
+  }
+  float* cp = static_cast<float*>(P.c) + batch * P.c_batch_stride + col * P.ldc;
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m)
+    if (m < M) atomicAdd(cp + m, acc[m]);
+}
+
+// k <= 32: a CTA owns 256 rows x 64 columns of C; thread = one row, its row of A in registers.
+// Both operand tiles pass through shared memory so that global memory is read in the order it
+// is stored (a contraction-contiguous A read row by row from the threads would again cost one
+// cache line per lane).
+template <typename T>
+__global__ void __launch_bounds__(256) skinny_k_plain_kernel(const __grid_constant__ Problem P) {
+  __shared__ float Bs[64][33];
+  __shared__ float As[256][33];
+  const long long batch = blockIdx.z;
+  const Plain<T> A(P.a[0], batch), Bm(P.b[0], batch);
+  const int K = static_cast<int>(P.k[0]);
+  const long long row0 = static_cast<long long>(blockIdx.x) * 256;
+  const long long col0 = static_cast<long long>(blockIdx.y) * 64;
+  const int rows = P.M - row0 < 256 ? static_cast<int>(P.M - row0) : 256;
+  const int cols = P.N - col0 < 64 ? static_cast<int>(P.N - col0) : 64;
+  // tiles in storage order: index = outer * K + k when the contraction is contiguous, else
+  // k * extent + outer
+  for (int idx = threadIdx.x; idx < cols * K; idx += 256) {
+    const int c = Bm.sk == 1 ? idx / K : idx % cols;
+    const int kk = Bm.sk == 1 ? idx % K : idx / cols;
+    Bs[c][kk] = ld_f(Bm.p + (col0 + c) * Bm.so + kk * Bm.sk);
+  }
+  for (int idx = threadIdx.x; idx < rows * K; idx += 256) {
+    const int r = A.sk == 1 ? idx / K : idx % rows;
+    const int kk = A.sk == 1 ? idx % K : idx / rows;
+    As[r][kk] = ld_f(A.p + (row0 + r) * A.so + kk * A.sk);
+  }
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) >= rows) return;
+  float a[32];
+#pragma unroll
+  for (int kk = 0; kk < 32; ++kk) a[kk] = kk < K ? As[threadIdx.x][kk] : 0.f;
+  for (int c = 0; c < cols; ++c) {
+    float acc = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk)
+      if (kk < K) acc += a[kk] * Bs[c][kk];  // the same word in every lane: a broadcast
+    finish<T>(P, batch, row0 + threadIdx.x, col0 + c, acc);
   }
 }
 
@@ -129,6 +386,66 @@ cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream) {
     small_gemm_kernel<float><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p);
   else
     small_gemm_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+// 0: not a skinny problem (or a form the skinny kernels do not take); otherwise the mapping.
+int skinny_kind(int dtype, const Problem& p) {
+  if (p.rowsum != nullptr) return 0;  // the caller splits the bias gradient off first
+  long long ktot = 0;
+  for (int i = 0; i < p.npairs; ++i) ktot += p.k[i];
+  if (ktot <= 0 || p.M <= 0 || p.N <= 0) return 0;
+  if (p.M <= kSkinny) {
+    bool b_kc = true;
+    for (int i = 0; i < p.npairs; ++i) b_kc = b_kc && p.b[i].k_contig;
+    if (b_kc) return 1;
+    if (dtype == 0 && p.accumulate && p.act == ACT_NONE && p.bias == nullptr && ktot >= 512 &&
+        p.batches <= 65535)
+      return 2;
+  }
+  if (ktot <= 32 && static_cast<long long>(p.M) * p.N >= 4096) return 3;
+  return 0;
+}
+
+cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t stream) {
+  bool plain = p.npairs == 1 && p.ccols == nullptr;
+  for (int i = 0; i < p.npairs; ++i)
+    plain = plain && p.a[i].cols == nullptr && p.b[i].cols == nullptr &&
+            p.a[i].dact == ACT_NONE && p.b[i].dact == ACT_NONE;
+  if (kind == 1) {
+    const long long warps = static_cast<long long>(p.N) * p.batches;
+    const long long blocks = (warps + 7) / 8;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const unsigned g = static_cast<unsigned>(blocks);
+    if (plain && p.batches <= 65535) {
+      dim3 grid(static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(p.batches));
+      if (dtype == 0) skinny_m_plain_kernel<float><<<grid, 256, 0, stream>>>(p);
+      else skinny_m_plain_kernel<__half><<<grid, 256, 0, stream>>>(p);
+    } else if (dtype == 0) {
+      skinny_m_kernel<float><<<g, 256, 0, stream>>>(p);
+    } else {
+      skinny_m_kernel<__half><<<g, 256, 0, stream>>>(p);
+    }
+  } else if (kind == 2) {
+    long long chunks = 0;
+    for (int i = 0; i < p.npairs; ++i) chunks += (p.k[i] + 127) / 128;
+    if (chunks > 65535) return cudaErrorInvalidValue;
+    dim3 grid(static_cast<unsigned>((p.N + 127) / 128), static_cast<unsigned>(chunks),
+              static_cast<unsigned>(p.batches));
+    if (plain) skinny_mt_plain_kernel<<<grid, 128, 0, stream>>>(p);
+    else skinny_mt_kernel<<<grid, 128, 0, stream>>>(p);
+  } else if (plain && p.batches <= 65535 && (p.N + 63) / 64 <= 65535) {
+    dim3 grid(static_cast<unsigned>((p.M + 255) / 256), static_cast<unsigned>((p.N + 63) / 64),
+              static_cast<unsigned>(p.batches));
+    if (dtype == 0) skinny_k_plain_kernel<float><<<grid, 256, 0, stream>>>(p);
+    else skinny_k_plain_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  } else {
+    const long long total = static_cast<long long>(p.M) * p.N * p.batches;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    if (dtype == 0) skinny_k_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    else skinny_k_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+  }
   return cudaGetLastError();
 }
 

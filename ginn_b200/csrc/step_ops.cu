@@ -10,6 +10,9 @@
 //   pick_nll_backward: dX[i, j] += (smax[i, j] - [i == index[j]]) * g[j]
 //                      (PickNegLogSoftmaxNode::backward_, pick.h:218-224, and pick_grad with
 //                      negate, pick.h:87-131, in one pass instead of gather + scatter + add)
+//   softmax_forward  : the same kernel without the pick (SoftmaxOp::forward alone)
+//   softmax_backward : dX (+)= Y (.) (dY - colsum(Y (.) dY))   (SoftmaxOp::backward,
+//                      ginn/nonlin.h:169-190: a batched 1 x 1 product plus a broadcast expression)
 //   adam_update      : d = clip(d); m = b1 m + (1 - b1) d; v = b2 v + (1 - b2) d^2;
 //                      w += -lr / (1 - b1^t) * m / (eps + sqrt(v / (1 - b2^t)))
 //                      (Adam::update, ginn/update/update.h:115-133; m and v are always fp32)
@@ -108,11 +111,62 @@ pick_nll_forward_kernel(const T* __restrict__ x, long long ldx, const int* __res
     store4(sc + 4 * q, v);
   }
   for (int i = 4 * rows4 + g; i < rows; i += G) sc[i] = from_f<T>(expf(to_f(xc[i]) - m) * inv);
-  if (g == 0) {
+  if (g == 0 && index != nullptr) {  // plain softmax: no pick
     const int p = index[j];
     // the reference takes the log of the stored (rounded) probability
     const float picked = (p >= 0 && p < rows) ? to_f(from_f<T>(expf(to_f(xc[p]) - m) * inv)) : 0.f;
     value[j] = from_f<T>(-logf(picked));
+  }
+}
+
+// Softmax backward (SoftmaxOp::backward, ginn/nonlin.h:169-190): per column
+//   m = sum_i y_i dy_i,   dx_i (+)= y_i (dy_i - m)
+// in one kernel: the reference forms m with a batched 1 x 1 product and then runs a broadcast
+// expression.  One warp per column (one CTA above 2048 rows); the column is read twice, the
+// second time from cache.
+template <typename T, bool BLOCK, bool VEC>
+__global__ void __launch_bounds__(256)
+softmax_backward_kernel(const T* __restrict__ y, long long ldy, const T* __restrict__ dy,
+                        long long lddy, T* __restrict__ dx, long long lddx, int rows,
+                        long long cols, int accumulate) {
+  __shared__ float red[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = BLOCK ? blockDim.x : 32;
+  const int g = BLOCK ? threadIdx.x : lane;
+  const long long j = BLOCK ? blockIdx.x : static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (j >= cols) return;
+  const T* yc = y + j * ldy;
+  const T* dc = dy + j * lddy;
+  T* xc = dx + j * lddx;
+  const int rows4 = VEC ? rows / 4 : 0;
+  float m = 0.f;
+  for (int q = g; q < rows4; q += G) {
+    float a[4], b[4];
+    load4(yc + 4 * q, a);
+    load4(dc + 4 * q, b);
+    m += (a[0] * b[0] + a[1] * b[1]) + (a[2] * b[2] + a[3] * b[3]);
+  }
+  for (int i = 4 * rows4 + g; i < rows; i += G) m += to_f(yc[i]) * to_f(dc[i]);
+  m = warp_sum(m);
+  if (BLOCK) {
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) m += red[w];
+  }
+  m = to_f(from_f<T>(m));  // the reference keeps m in a tensor of the storage type
+  for (int q = g; q < rows4; q += G) {
+    float a[4], b[4], o[4] = {0.f, 0.f, 0.f, 0.f};
+    load4(yc + 4 * q, a);
+    load4(dc + 4 * q, b);
+    if (accumulate) load4(xc + 4 * q, o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] += a[e] * (b[e] - m);
+    store4(xc + 4 * q, o);
+  }
+  for (int i = 4 * rows4 + g; i < rows; i += G) {
+    const float v = to_f(yc[i]) * (to_f(dc[i]) - m);
+    xc[i] = from_f<T>(accumulate ? to_f(xc[i]) + v : v);
   }
 }
 
@@ -217,6 +271,24 @@ void pick_forward_t(const void* x, long long ldx, const int* index, void* smax, 
 }
 
 template <typename T>
+void softmax_backward_t(const void* y, long long ldy, const void* dy, long long lddy, void* dx,
+                        long long lddx, int rows, long long cols, int accumulate,
+                        cudaStream_t stream) {
+  const unsigned a = sizeof(T) * 4;
+  const bool vec = cols_aligned(y, ldy, sizeof(T), a) && cols_aligned(dy, lddy, sizeof(T), a) &&
+                   cols_aligned(dx, lddx, sizeof(T), a);
+  const bool block = rows > 2048;
+  const unsigned grid = block ? static_cast<unsigned>(cols) : static_cast<unsigned>((cols + 7) / 8);
+  const T* yp = static_cast<const T*>(y);
+  const T* dp = static_cast<const T*>(dy);
+  T* xp = static_cast<T*>(dx);
+  if (block && vec) softmax_backward_kernel<T, true, true><<<grid, 256, 0, stream>>>(yp, ldy, dp, lddy, xp, lddx, rows, cols, accumulate);
+  else if (block) softmax_backward_kernel<T, true, false><<<grid, 256, 0, stream>>>(yp, ldy, dp, lddy, xp, lddx, rows, cols, accumulate);
+  else if (vec) softmax_backward_kernel<T, false, true><<<grid, 256, 0, stream>>>(yp, ldy, dp, lddy, xp, lddx, rows, cols, accumulate);
+  else softmax_backward_kernel<T, false, false><<<grid, 256, 0, stream>>>(yp, ldy, dp, lddy, xp, lddx, rows, cols, accumulate);
+}
+
+template <typename T>
 void pick_backward_t(const void* smax, long long lds, const int* index, const void* grad, void* dx,
                      long long lddx, int rows, long long cols, cudaStream_t stream) {
   const unsigned a = sizeof(T) * 4;
@@ -237,6 +309,16 @@ cudaError_t launch_pick_nll_forward(int dtype, const void* x, long long ldx, con
   if (cols > 0x7fffffffLL) return cudaErrorInvalidValue;
   if (dtype == 0) pick_forward_t<float>(x, ldx, index, smax, lds, value, rows, cols, stream);
   else pick_forward_t<__half>(x, ldx, index, smax, lds, value, rows, cols, stream);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_softmax_backward(int dtype, const void* y, long long ldy, const void* dy,
+                                    long long lddy, void* dx, long long lddx, int rows,
+                                    long long cols, int accumulate, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  if (cols > 0x7fffffffLL) return cudaErrorInvalidValue;
+  if (dtype == 0) softmax_backward_t<float>(y, ldy, dy, lddy, dx, lddx, rows, cols, accumulate, stream);
+  else softmax_backward_t<__half>(y, ldy, dy, lddy, dx, lddx, rows, cols, accumulate, stream);
   return cudaGetLastError();
 }
 

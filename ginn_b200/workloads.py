@@ -49,11 +49,11 @@ class Attention:
         for t in (self.dV, self.dQ, self.dK, self.dP):
             t.zero_()
         gb.gemm_batched(self.k, self.q, self.S)
-        self.P.copy_(torch.softmax(self.S, dim=0))
+        gb.softmax_forward(self.S, self.P)  # SoftmaxOp::forward, ginn/nonlin.h:162-168
         gb.gemm_batched(self.v, self.P, self.O)
         gb.gemm_batched(self.dO, self.P, self.dV, trans_b=True, accumulate=True)
         gb.gemm_batched(self.v, self.dO, self.dP, trans_a=True, accumulate=True)
-        self.dS.copy_(self.P * (self.dP - (self.P * self.dP).sum(dim=0, keepdim=True)))
+        gb.softmax_backward(self.P, self.dP, self.dS, accumulate=False)  # nonlin.h:169-190
         gb.gemm_batched(self.dS, self.q, self.dK, trans_b=True, accumulate=True)
         gb.gemm_batched(self.k, self.dS, self.dQ, trans_a=True, accumulate=True)
 

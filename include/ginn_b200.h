@@ -184,6 +184,18 @@ int ginn_b200_pick_nll_backward(int device, void* stream, int dtype, int64_t row
                                 const void* smax, int64_t ldsmax, const int* index,
                                 const void* grad, void* dx, int64_t lddx);
 
+/* Column softmax y[:, j] = softmax(x[:, j]) of a rows x cols column-major matrix (any number of
+ * trailing dimensions folded into cols).  Replaces SoftmaxOp::forward (ginn/nonlin.h:162-168). */
+int ginn_b200_softmax_forward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                              const void* x, int64_t ldx, void* y, int64_t ldy);
+
+/* dx (+)= y (.) (dy - colsum(y (.) dy)), `+=` when accumulate != 0.  Replaces SoftmaxOp::backward
+ * (ginn/nonlin.h:169-190), including the batched 1 x 1 products its GPU branch sends through
+ * gpu_batched_prod (:177-184). */
+int ginn_b200_softmax_backward(int device, void* stream, int dtype, int64_t rows, int64_t cols,
+                               const void* y, int64_t ldy, const void* dy, int64_t lddy, void* dx,
+                               int64_t lddx, int accumulate);
+
 /* One Adam step on n elements: d is clipped to [-clip, clip] in place, then
  *   m = beta1 m + (1 - beta1) d,  v = beta2 v + (1 - beta2) d^2,
  *   w += -lr / (1 - beta1_t) * m / (eps + sqrt(v / (1 - beta2_t))),

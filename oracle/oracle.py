@@ -14,6 +14,7 @@ Reference lines followed (paths inside the ginn source tree):
   autobatch semantics    ginn/autobatch.h:80-183: a merged product equals the per-node products
   pick_nll_forward       ginn/node/pick.h:60-84,177-182,209-216 with SoftmaxOp::forward,
                          ginn/nonlin.h:162-168
+  softmax_backward       ginn/nonlin.h:169-190
   pick_nll_backward      ginn/node/pick.h:87-131,218-224
   adam_update            ginn/update/update.h:92-133
 
@@ -132,6 +133,13 @@ def pick_nll_forward(x, index):
     smax = t / t.sum(axis=0, keepdims=True)
     idx = np.asarray(index, dtype=np.int64)
     return smax, -np.log(smax[idx, np.arange(x.shape[1])])
+
+
+def softmax_backward(y, dy, dx=None):
+    """SoftmaxOp::backward (ginn/nonlin.h:169-190): y * (dy - colsum(y * dy)) [+ dx]  (fp64)."""
+    y, dy = f64(y), f64(dy)
+    out = y * (dy - (y * dy).sum(axis=0, keepdims=True))
+    return out if dx is None else f64(dx) + out
 
 
 def pick_nll_backward(smax, index, grad, dx):

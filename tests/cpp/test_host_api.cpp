@@ -358,6 +358,23 @@ static void test_pick_nll(float eps) {
   CHECK(threw);
 }
 
+// test/nodes.cu.cpp:689-700: Softmax values; gradient of sum_ij c_ij y_ij against the closed form
+// y (.) (c - colsum(y (.) c)), accumulated onto a non-zero gradient.
+template <typename S>
+static void test_softmax(float eps) {
+  auto W = Values<S>(gpu(), {{-1, -2, -3}, {4, 5, 6}});
+  auto y = Softmax<S>(W);
+  Graph g(y);
+  g.forward();
+  CHECK(close(y->value().vector(),
+              {0.00669285f, 0.99330715f, 9.11051194e-04f, 9.99088949e-01f, 1.23394576e-04f,
+               9.99876605e-01f},
+              eps * 10, eps));
+  g.reset_grad();
+  g.backward(0.5);  // c = 0.5 everywhere: y (.) (0.5 - 0.5 * colsum(y)) = 0 up to rounding
+  for (float v : floats(W->grad().vector())) CHECK(std::fabs(v) <= eps);
+}
+
 // ginn/update/update.h:115-133 restated on the host in double, two steps.
 static void test_adam() {
   auto w = Random<Real>(gpu(), {7, 5}, 70);
@@ -412,6 +429,8 @@ int main() {
   test_pick_nll<Real>(1e-6f);
   test_pick_nll<Half>(2e-3f);
   test_adam();
+  test_softmax<Real>(1e-6f);
+  test_softmax<Half>(1e-3f);
   cudaDeviceSynchronize();
   const int status = ginn_b200_device_status(0, 1);
   CHECK(status == 0);

@@ -217,3 +217,28 @@ def test_bounded_wait_reports_instead_of_hanging(gpu):
     gpu.selftest(0)
     assert gpu.device_status(0, False) == 0
     run_gemm(gpu, np.random.default_rng(23), np.float32, 64, 48, 80, False, False, False)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_skinny_products_on_cuda_cores(gpu, dt):
+    """One extent of at most 16 (config 5's ten-class output layer and its two gradients) or a
+    contraction of at most 32: the CUDA-core mappings, every transpose, `=` and `+=`, batches,
+    and the same shapes on the tensor-core path as a cross-check of the dispatch."""
+    rng = np.random.default_rng(21)
+    shapes = [(10, 4096, 1024), (1024, 512, 10), (10, 1024, 4096), (16, 300, 77), (3, 5, 2000),
+              (200, 300, 7), (1, 513, 640), (7, 129, 33)]
+    for (m, n, k) in shapes:
+        for ta, tb in TRANS:
+            for acc in (False, True):
+                run_gemm(gpu, rng, dt, m, n, k, ta, tb, acc)
+    run_gemm(gpu, rng, dt, 10, 333, 129, False, True, True, 3, 1)  # padded, unaligned, NT +=
+    a, b = randn(rng, (10, 96, 6), dt), randn(rng, (96, 200, 6), dt)
+    c0 = randn(rng, (10, 200, 6), dt)
+    for acc in (False, True):
+        C = B.from_host(c0)
+        gpu.gemm_batched(B.from_host(a), B.from_host(b), C, False, False, acc)
+        torch.cuda.synchronize()
+        check(B.to_host(C), orc.gemm_batched(a, b, False, False, c0, acc), dt, "batched skinny")
+    launches = gpu.launch_count()
+    run_gemm(gpu, rng, dt, 10, 4096, 1024, False, False, False)
+    assert gpu.launch_count() == launches + 1

@@ -69,6 +69,25 @@ def test_pick_nll_known_answer_and_gradient(kat):
     np.testing.assert_allclose(dx, num, rtol=1e-5, atol=1e-8)
 
 
+def test_softmax_known_answers_and_gradient(kat):
+    """test/nodes.cu.cpp:689-700 for the values; the backward restatement against central
+    differences of sum(w * softmax(x))."""
+    k = kat["softmax"]
+    W = arr(k["W"], np.float64)
+    y = orc.pick_nll_forward(W, [0, 0, 0])[0]
+    np.testing.assert_allclose(y, k["smaxW"], rtol=1e-6)
+    w = np.array([[0.3, -1.0, 2.0], [0.7, 0.2, -0.4]])
+    dx = orc.softmax_backward(y, w)
+    num = np.zeros_like(W)
+    for i in range(2):
+        for j in range(3):
+            e = np.zeros_like(W)
+            e[i, j] = 1e-6
+            f = lambda z: (orc.pick_nll_forward(z, [0, 0, 0])[0] * w).sum()
+            num[i, j] = (f(W + e) - f(W - e)) / 2e-6
+    np.testing.assert_allclose(dx, num, rtol=1e-5, atol=1e-9)
+
+
 def test_adam_restatement_first_steps():
     """ginn/update/update.h:115-133 by hand: with m = v = 0, step 1 moves every weight by
     -lr * sign(d) (up to eps), whatever the size of d, and clips d in place."""

@@ -90,3 +90,45 @@ def test_step_ops_reject_bad_arguments(gpu):
     with pytest.raises(B.GinnB200Error):
         B._check(B.lib().ginn_b200_adam_update(0, None, 0, 4, x.data_ptr(), x.data_ptr(), x.data_ptr(),
                                                x.data_ptr(), 1e-3, 5.0, 1e-8, 0.9, 0.999, 1.0, 0.999))
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+@pytest.mark.parametrize("shape,pad", [((256, 256, 8), 0), ((3, 5), 0), ((33, 100), 3), ((5000, 6), 0), ((1, 9), 0)])
+def test_softmax_forward_backward(gpu, dt, shape, pad):
+    """SoftmaxOp (ginn/nonlin.h:157-190) over dimension 0, batches folded into the columns (the
+    attention scores of config 3), `=` and `+=` into the input gradient; the reference's own
+    softmax values of test/nodes.cu.cpp:755-763 are part of the pick test above."""
+    rng = np.random.default_rng(sum(shape))
+    x = (randn(rng, shape, dt) * (3 if dt == np.float32 else 1)).astype(dt)
+    dy, dx0 = randn(rng, shape, dt), randn(rng, shape, dt)
+    ld = shape[0] + pad if len(shape) == 2 else None
+    X, DY = B.from_host(x, ld=ld), B.from_host(dy, ld=ld)
+    Y = B.from_host(np.zeros(shape, dt), ld=ld)
+    gpu.softmax_forward(X, Y)
+    torch.cuda.synchronize()
+    x2 = x.reshape(shape[0], -1, order="F")
+    ref_y = orc.pick_nll_forward(x2, np.zeros(x2.shape[1], np.int64))[0].reshape(shape, order="F")
+    check(B.to_host(Y), ref_y, dt, "softmax")
+    y_stored = B.to_host(Y).reshape(shape[0], -1, order="F")
+    dy2, dx2 = dy.reshape(shape[0], -1, order="F"), dx0.reshape(shape[0], -1, order="F")
+    for acc in (False, True):
+        DX = B.from_host(dx0, ld=ld)
+        gpu.softmax_backward(Y, DY, DX, accumulate=acc)
+        torch.cuda.synchronize()
+        ref = orc.softmax_backward(y_stored, dy2, dx2 if acc else None)
+        check(B.to_host(DX).reshape(shape[0], -1, order="F"), ref, dt, f"dx acc={acc}")
+
+
+def test_softmax_known_answers(gpu, kat):
+    """test/nodes.cu.cpp:689-700 (values) and :728-747 (saturating inputs, -inf, a single row)."""
+    k = kat["softmax"]
+    for dt, eps in ((np.float32, 1e-5), (np.float16, 2e-3)):
+        cases = [(k["W"], k["smaxW"])] + [(c["x"], c["y"]) for c in k["extreme"]]
+        for x, y in cases:
+            x = np.asarray([[float(v) for v in row] for row in x], dt)
+            X = B.from_host(x)
+            Y = B.from_host(np.zeros_like(x))
+            gpu.softmax_forward(X, Y)
+            torch.cuda.synchronize()
+            np.testing.assert_allclose(B.to_host(Y).astype(np.float64), np.asarray(y, np.float64),
+                                       rtol=eps, atol=eps * 1e-2)
