@@ -171,7 +171,13 @@ int try_skinny(int dtype, Problem& p, cudaStream_t stream, bool* done) {
                                                  p.batches == 1 && !p.a[0].k_contig);
   const int kind = rowsum_ok ? gb::skinny_kind(dtype, q) : 0;
   if (kind == 0) return GINN_B200_OK;
-  if (p.rowsum != nullptr) {
+  // The weight-gradient mapping (2) of plain operands sums the rows of A on the way; otherwise
+  // the bias gradient is a launch of its own.
+  const bool fold = kind == 2 && p.rowsum != nullptr && p.npairs == 1 && p.a[0].dact == gb::ACT_NONE &&
+                    p.b[0].cols == nullptr && p.b[0].dact == gb::ACT_NONE && p.ccols == nullptr;
+  if (fold) {
+    q.rowsum = p.rowsum;
+  } else if (p.rowsum != nullptr) {
     CU_TRY(gb::launch_rowsum(dtype, p.a[0].base, p.a[0].ybase, p.a[0].dact, p.a[0].ld, p.M, p.k[0],
                              p.rowsum, stream));
     g_launches.fetch_add(1);

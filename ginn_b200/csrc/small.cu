@@ -197,12 +197,13 @@ struct Plain {
         sk(op.k_contig ? 1 : op.ld) {}
 };
 
-// m <= 16, B contraction-contiguous.  A CTA owns 32 columns of C (four per warp).  The small
+// m <= 16, B contraction-contiguous.  A CTA owns 16 columns of C (two per warp).  The small
 // operand A is staged, 512 contraction indices at a time, in shared memory as [m][k], so that
 // lanes running along k read it without bank conflicts whatever its layout in memory is (read
 // straight from global memory, an outer-contiguous A costs ten cache lines per load: lanes are
-// 4 m bytes apart).  Every staged value is used for the four columns of the warp.
+// 4 m bytes apart).  Every staged value is used for both columns of the warp.
 constexpr int kSkinnyKC = 512;
+constexpr int kSkinnyCols = 2;  // columns of C per warp
 template <typename T>
 __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_constant__ Problem P) {
   __shared__ float As[kSkinny * kSkinnyKC];
@@ -211,17 +212,17 @@ __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_consta
   const Plain<T> A(P.a[0], batch), Bm(P.b[0], batch);
   const int M = P.M;
   const long long K = P.k[0];
-  const long long col0 = static_cast<long long>(blockIdx.x) * 32 + warp * 4;
-  const T* bp[4];
-  bool live[4];
+  const long long col0 = static_cast<long long>(blockIdx.x) * (8 * kSkinnyCols) + warp * kSkinnyCols;
+  const T* bp[kSkinnyCols];
+  bool live[kSkinnyCols];
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < kSkinnyCols; ++c) {
     live[c] = col0 + c < P.N;
     bp[c] = Bm.p + (live[c] ? col0 + c : 0) * Bm.so;  // contraction-contiguous: sk = 1
   }
-  float acc[4][kSkinny];
+  float acc[kSkinnyCols][kSkinny];
 #pragma unroll
-  for (int c = 0; c < 4; ++c)
+  for (int c = 0; c < kSkinnyCols; ++c)
 #pragma unroll
     for (int m = 0; m < kSkinny; ++m) acc[c][m] = 0.f;
   for (long long k0 = 0; k0 < K; k0 += kSkinnyKC) {
@@ -234,22 +235,22 @@ __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_consta
         if (m < M) As[m * kSkinnyKC + kk] = ld_f(ak + m * A.so);
     }
     __syncthreads();
-#pragma unroll 2
+#pragma unroll 4
     for (int kk = lane; kk < kc; kk += 32) {
-      float b[4];
+      float b[kSkinnyCols];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) b[c] = live[c] ? ld_f(bp[c] + k0 + kk) : 0.f;
+      for (int c = 0; c < kSkinnyCols; ++c) b[c] = live[c] ? ld_f(bp[c] + k0 + kk) : 0.f;
 #pragma unroll
       for (int m = 0; m < kSkinny; ++m)
         if (m < M) {
           const float a = As[m * kSkinnyKC + kk];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) acc[c][m] += a * b[c];
+          for (int c = 0; c < kSkinnyCols; ++c) acc[c][m] += a * b[c];
         }
     }
   }
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < kSkinnyCols; ++c) {
     float mine = 0.f;
 #pragma unroll
     for (int m = 0; m < kSkinny; ++m) {
@@ -262,6 +263,7 @@ __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_consta
   }
 }
 
+constexpr int kSkinnyMtChunk = 32;  // contraction indices per CTA row: short, so that many CTAs run
 __global__ void __launch_bounds__(128) skinny_mt_plain_kernel(const __grid_constant__ Problem P) {
   const long long col = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long batch = blockIdx.z;
@@ -269,33 +271,42 @@ __global__ void __launch_bounds__(128) skinny_mt_plain_kernel(const __grid_const
   const Plain<float> A(P.a[0], batch), Bm(P.b[0], batch);
   const float* bp = Bm.p + col * Bm.so;
   const int M = P.M;
-  const long long k0 = static_cast<long long>(blockIdx.y) * 128;
-  const long long k1 = k0 + 128 < P.k[0] ? k0 + 128 : P.k[0];
-  float acc[kSkinny];
+  const long long k0 = static_cast<long long>(blockIdx.y) * kSkinnyMtChunk;
+  const long long k1 = k0 + kSkinnyMtChunk < P.k[0] ? k0 + kSkinnyMtChunk : P.k[0];
+  // the thread of column 0 also sums A along the contraction: the bias gradient, for free
+  const bool sums = P.rowsum != nullptr && col == 0;
+  float acc[kSkinny], rs[kSkinny];
 #pragma unroll
-  for (int m = 0; m < kSkinny; ++m) acc[m] = 0.f;
-#pragma unroll 4
+  for (int m = 0; m < kSkinny; ++m) acc[m] = rs[m] = 0.f;
+#pragma unroll 8
   for (long long kk = k0; kk < k1; ++kk) {
     const float b = __ldg(bp + kk * Bm.sk);
     const float* ak = A.p + kk * A.sk;  // the same address in every lane: a broadcast load
 #pragma unroll
     for (int m = 0; m < kSkinny; ++m)
-      if (m < M) acc[m] += __ldg(ak + m * A.so) * b;
+      if (m < M) {
+        const float a = __ldg(ak + m * A.so);
+        acc[m] += a * b;
+        rs[m] += a;
+      }
   }
   float* cp = static_cast<float*>(P.c) + batch * P.c_batch_stride + col * P.ldc;
 #pragma unroll
   for (int m = 0; m < kSkinny; ++m)
-    if (m < M) atomicAdd(cp + m, acc[m]);
+    if (m < M) {
+      atomicAdd(cp + m, acc[m]);
+      if (sums) atomicAdd(static_cast<float*>(P.rowsum) + m, rs[m]);
+    }
 }
 
 // k <= 32: a CTA owns 256 rows x 64 columns of C; thread = one row, its row of A in registers.
 // Both operand tiles pass through shared memory so that global memory is read in the order it
 // is stored (a contraction-contiguous A read row by row from the threads would again cost one
 // cache line per lane).
-template <typename T>
+template <typename T, int KMAX>
 __global__ void __launch_bounds__(256) skinny_k_plain_kernel(const __grid_constant__ Problem P) {
-  __shared__ float Bs[64][33];
-  __shared__ float As[256][33];
+  __shared__ float Bs[64][KMAX + 1];
+  __shared__ float As[256][KMAX + 1];
   const long long batch = blockIdx.z;
   const Plain<T> A(P.a[0], batch), Bm(P.b[0], batch);
   const int K = static_cast<int>(P.k[0]);
@@ -317,29 +328,52 @@ __global__ void __launch_bounds__(256) skinny_k_plain_kernel(const __grid_consta
   }
   __syncthreads();
   if (static_cast<int>(threadIdx.x) >= rows) return;
-  float a[32];
+  float a[KMAX];
 #pragma unroll
-  for (int kk = 0; kk < 32; ++kk) a[kk] = kk < K ? As[threadIdx.x][kk] : 0.f;
-  for (int c = 0; c < cols; ++c) {
-    float acc = 0.f;
+  for (int kk = 0; kk < KMAX; ++kk) a[kk] = kk < K ? As[threadIdx.x][kk] : 0.f;
+  const long long row = row0 + threadIdx.x;
+  const float bias = P.bias ? ld_f(static_cast<const T*>(P.bias) + row) : 0.f;
+  T* crow = static_cast<T*>(P.c) + batch * P.c_batch_stride + row;
+  // eight columns at a time: the previous values of C (for +=) are requested together, so that
+  // their latency is paid once per eight elements and not once per element
+  for (int c0 = 0; c0 < cols; c0 += 8) {
+    float x[8];
 #pragma unroll
-    for (int kk = 0; kk < 32; ++kk)
-      if (kk < K) acc += a[kk] * Bs[c][kk];  // the same word in every lane: a broadcast
-    finish<T>(P, batch, row0 + threadIdx.x, col0 + c, acc);
+    for (int j = 0; j < 8; ++j)
+      x[j] = (P.accumulate && c0 + j < cols) ? ld_rw(crow + (col0 + c0 + j) * P.ldc) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float acc = 0.f;
+      const int c = c0 + j < cols ? c0 + j : 0;
+#pragma unroll
+      for (int kk = 0; kk < KMAX; ++kk)
+        if (kk < K) acc += a[kk] * Bs[c][kk];  // the same word in every lane: a broadcast
+      x[j] += acc + bias;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j < cols) st_f(crow + (col0 + c0 + j) * P.ldc, act_forward<T>(P.act, x[j]));
   }
 }
 
-// One warp per row: rowsum[o] += sum_n dY[o,n] * act'(Y[o,n]).
+__device__ __forceinline__ void atomic_add_t(float* p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add_t(__half* p, float v) { atomicAdd(p, __float2half_rn(v)); }
+
+// rowsum[o] += sum_n dY[o,n] * act'(Y[o,n]).  Threads of a block cover 32 consecutive rows
+// (coalesced along a column) and blockDim.y slices of the block's range of columns (blockIdx.y);
+// the slices meet in shared memory, the blocks in an atomic add.
 template <typename T>
 __global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y, int dact,
                               long long ld, int M, long long N, T* __restrict__ rowsum) {
-  // Threads of a block cover 32 consecutive rows (coalesced along the column) and
-  // blockDim.y slices of the columns; partial sums meet in shared memory.
   __shared__ float part[8][33];
   const int row = blockIdx.x * 32 + threadIdx.x;
+  const long long per = (N + gridDim.y - 1) / gridDim.y;
+  const long long n0 = blockIdx.y * per;
+  const long long n1 = n0 + per < N ? n0 + per : N;
   float acc = 0.f;
   if (row < M) {
-    for (long long n = threadIdx.y; n < N; n += blockDim.y) {
+#pragma unroll 4
+    for (long long n = n0 + threadIdx.y; n < n1; n += blockDim.y) {
       float v = ld_f(dy + n * ld + row);
       if (dact != ACT_NONE) v = round_to<T>(act_backward<T>(dact, ld_f(y + n * ld + row), v));
       acc += v;
@@ -350,7 +384,7 @@ __global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y,
   if (threadIdx.y == 0 && row < M) {
     float s = 0.f;
     for (int j = 0; j < blockDim.y; ++j) s += part[j][threadIdx.x];
-    st_f(rowsum + row, ld_rw(rowsum + row) + s);
+    atomic_add_t(rowsum + row, s);
   }
 }
 
@@ -391,7 +425,7 @@ cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream) {
 
 // 0: not a skinny problem (or a form the skinny kernels do not take); otherwise the mapping.
 int skinny_kind(int dtype, const Problem& p) {
-  if (p.rowsum != nullptr) return 0;  // the caller splits the bias gradient off first
+  if (p.rowsum != nullptr) return 0;  // the caller decides how the bias gradient is formed
   long long ktot = 0;
   for (int i = 0; i < p.npairs; ++i) ktot += p.k[i];
   if (ktot <= 0 || p.M <= 0 || p.N <= 0) return 0;
@@ -400,7 +434,7 @@ int skinny_kind(int dtype, const Problem& p) {
     for (int i = 0; i < p.npairs; ++i) b_kc = b_kc && p.b[i].k_contig;
     if (b_kc) return 1;
     if (dtype == 0 && p.accumulate && p.act == ACT_NONE && p.bias == nullptr && ktot >= 512 &&
-        p.batches <= 65535)
+        ktot <= 2000000 && p.batches <= 65535)
       return 2;
   }
   if (ktot <= 32 && static_cast<long long>(p.M) * p.N >= 4096) return 3;
@@ -418,7 +452,7 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
     const unsigned g = static_cast<unsigned>(blocks);
     if (plain && p.batches <= 65535) {
-      dim3 grid(static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(p.batches));
+      dim3 grid(static_cast<unsigned>((p.N + 15) / 16), static_cast<unsigned>(p.batches));
       if (dtype == 0) skinny_m_plain_kernel<float><<<grid, 256, 0, stream>>>(p);
       else skinny_m_plain_kernel<__half><<<grid, 256, 0, stream>>>(p);
     } else if (dtype == 0) {
@@ -427,8 +461,9 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
       skinny_m_kernel<__half><<<g, 256, 0, stream>>>(p);
     }
   } else if (kind == 2) {
+    const int chunk = plain ? kSkinnyMtChunk : 128;
     long long chunks = 0;
-    for (int i = 0; i < p.npairs; ++i) chunks += (p.k[i] + 127) / 128;
+    for (int i = 0; i < p.npairs; ++i) chunks += (p.k[i] + chunk - 1) / chunk;
     if (chunks > 65535) return cudaErrorInvalidValue;
     dim3 grid(static_cast<unsigned>((p.N + 127) / 128), static_cast<unsigned>(chunks),
               static_cast<unsigned>(p.batches));
@@ -437,8 +472,14 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
   } else if (plain && p.batches <= 65535 && (p.N + 63) / 64 <= 65535) {
     dim3 grid(static_cast<unsigned>((p.M + 255) / 256), static_cast<unsigned>((p.N + 63) / 64),
               static_cast<unsigned>(p.batches));
-    if (dtype == 0) skinny_k_plain_kernel<float><<<grid, 256, 0, stream>>>(p);
-    else skinny_k_plain_kernel<__half><<<grid, 256, 0, stream>>>(p);
+    const bool k16 = p.k[0] <= 16;
+    if (dtype == 0) {
+      if (k16) skinny_k_plain_kernel<float, 16><<<grid, 256, 0, stream>>>(p);
+      else skinny_k_plain_kernel<float, 32><<<grid, 256, 0, stream>>>(p);
+    } else {
+      if (k16) skinny_k_plain_kernel<__half, 16><<<grid, 256, 0, stream>>>(p);
+      else skinny_k_plain_kernel<__half, 32><<<grid, 256, 0, stream>>>(p);
+    }
   } else {
     const long long total = static_cast<long long>(p.M) * p.N * p.batches;
     const long long blocks = (total + 255) / 256;
@@ -453,7 +494,13 @@ cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, lo
                           long long N, void* rowsum, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return cudaSuccess;
   dim3 block(32, 8);
-  dim3 grid((M + 31) / 32);
+  // enough blocks along the columns to fill the GPU when there are few rows (at least 64
+  // columns per block)
+  long long chunks = 1184 / ((M + 31) / 32);
+  if (chunks > (N + 63) / 64) chunks = (N + 63) / 64;
+  if (chunks < 1) chunks = 1;
+  if (chunks > 65535) chunks = 65535;
+  dim3 grid((M + 31) / 32, static_cast<unsigned>(chunks));
   if (dtype == 0)
     rowsum_kernel<float><<<grid, block, 0, stream>>>(static_cast<const float*>(dy),
                                                      static_cast<const float*>(y), dact, ld, M, N,
