@@ -202,11 +202,22 @@ struct Plain {
 // lanes running along k read it without bank conflicts whatever its layout in memory is (read
 // straight from global memory, an outer-contiguous A costs ten cache lines per load: lanes are
 // 4 m bytes apart).  Every staged value is used for both columns of the warp.
+__device__ __forceinline__ void ld4(const float* p, float (&x)[4]) {
+  const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+  x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+__device__ __forceinline__ void ld4(const __half* p, float (&x)[4]) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+
 constexpr int kSkinnyKC = 512;
 constexpr int kSkinnyCols = 2;  // columns of C per warp
 template <typename T>
 __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_constant__ Problem P) {
-  __shared__ float As[kSkinny * kSkinnyKC];
+  __shared__ __align__(16) float As[kSkinny * kSkinnyKC];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long batch = blockIdx.y;
   const Plain<T> A(P.a[0], batch), Bm(P.b[0], batch);
@@ -225,6 +236,9 @@ __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_consta
   for (int c = 0; c < kSkinnyCols; ++c)
 #pragma unroll
     for (int m = 0; m < kSkinny; ++m) acc[c][m] = 0.f;
+  // every column of B starts on a boundary of four elements
+  const unsigned va = sizeof(T) * 4;
+  const bool vec = (reinterpret_cast<uintptr_t>(Bm.p) & (va - 1)) == 0 && (Bm.so * sizeof(T)) % va == 0;
   for (long long k0 = 0; k0 < K; k0 += kSkinnyKC) {
     const int kc = K - k0 < kSkinnyKC ? static_cast<int>(K - k0) : kSkinnyKC;
     __syncthreads();
@@ -235,8 +249,31 @@ __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_consta
         if (m < M) As[m * kSkinnyKC + kk] = ld_f(ak + m * A.so);
     }
     __syncthreads();
-#pragma unroll 4
-    for (int kk = lane; kk < kc; kk += 32) {
+    if (vec) {
+      // four consecutive contraction indices per lane: 16-byte loads of B and of the staged A
+#pragma unroll 2
+      for (int kk = 4 * lane; kk + 3 < kc; kk += 128) {
+        float b[kSkinnyCols][4];
+#pragma unroll
+        for (int c = 0; c < kSkinnyCols; ++c) {
+          if (live[c]) {
+            ld4(bp[c] + k0 + kk, b[c]);
+          } else {
+            b[c][0] = b[c][1] = b[c][2] = b[c][3] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < kSkinny; ++m)
+          if (m < M) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[m * kSkinnyKC + kk]);
+#pragma unroll
+            for (int c = 0; c < kSkinnyCols; ++c)
+              acc[c][m] += (a.x * b[c][0] + a.y * b[c][1]) + (a.z * b[c][2] + a.w * b[c][3]);
+          }
+      }
+    }
+    // scalar path: everything when unaligned, else the last kc % 4 indices of the chunk
+    for (int kk = (vec ? (kc & ~3) : 0) + lane; kk < kc; kk += 32) {
       float b[kSkinnyCols];
 #pragma unroll
       for (int c = 0; c < kSkinnyCols; ++c) b[c] = live[c] ? ld_f(bp[c] + k0 + kk) : 0.f;
@@ -263,57 +300,97 @@ __global__ void __launch_bounds__(256) skinny_m_plain_kernel(const __grid_consta
   }
 }
 
-constexpr int kSkinnyMtChunk = 32;  // contraction indices per CTA row: short, so that many CTAs run
-__global__ void __launch_bounds__(128) skinny_mt_plain_kernel(const __grid_constant__ Problem P) {
-  const long long col = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+// m <= 16, accumulating, B outer-contiguous (weight gradients), plain operands.  A CTA of 32 x 8
+// threads owns 32 columns of C and 256 contraction indices: warp ty sums its 32 indices for the
+// 32 columns (lanes along n: coalesced reads of B; A is a broadcast), the eight warps meet in
+// shared memory and one atomic add per element and CTA goes to memory.  (Atomics on the same
+// cache line serialise in L2 at some 30 cycles each: one per thread and chunk, as a first version
+// did, made 1.3 M of them the whole run time.)  The thread of column 0 also sums A along the
+// contraction: the bias gradient, for free.
+constexpr int kSkinnyMtChunk = 256;
+__global__ void __launch_bounds__(256) skinny_mt_plain_kernel(const __grid_constant__ Problem P) {
+  __shared__ float red[8][kSkinny][33];
+  __shared__ float rsred[8][kSkinny];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const long long col = static_cast<long long>(blockIdx.x) * 32 + tx;
   const long long batch = blockIdx.z;
-  if (col >= P.N) return;
+  const bool live = col < P.N;
   const Plain<float> A(P.a[0], batch), Bm(P.b[0], batch);
-  const float* bp = Bm.p + col * Bm.so;
+  const float* bp = Bm.p + (live ? col : 0) * Bm.so;
   const int M = P.M;
-  const long long k0 = static_cast<long long>(blockIdx.y) * kSkinnyMtChunk;
-  const long long k1 = k0 + kSkinnyMtChunk < P.k[0] ? k0 + kSkinnyMtChunk : P.k[0];
-  // the thread of column 0 also sums A along the contraction: the bias gradient, for free
-  const bool sums = P.rowsum != nullptr && col == 0;
+  const long long k0 = static_cast<long long>(blockIdx.y) * kSkinnyMtChunk + ty * 32;
+  const long long k1 = k0 + 32 < P.k[0] ? k0 + 32 : P.k[0];
+  // the CTA's slice of A (256 contraction indices x m) through shared memory: every thread
+  // needs every value of it
+  __shared__ float As[kSkinnyMtChunk][kSkinny + 1];
+  {
+    const long long kb = static_cast<long long>(blockIdx.y) * kSkinnyMtChunk;
+    const int tid = ty * 32 + tx;
+    const int kn = P.k[0] - kb < kSkinnyMtChunk ? static_cast<int>(P.k[0] - kb) : kSkinnyMtChunk;
+    // storage order: index = k * M + m when m is contiguous, else m * kn + k
+    for (int idx = tid; idx < kn * M; idx += 256) {
+      const int kl = A.so == 1 ? idx / M : idx % kn;
+      const int m = A.so == 1 ? idx % M : idx / kn;
+      As[kl][m] = __ldg(A.p + (kb + kl) * A.sk + m * A.so);
+    }
+  }
+  __syncthreads();
   float acc[kSkinny], rs[kSkinny];
 #pragma unroll
   for (int m = 0; m < kSkinny; ++m) acc[m] = rs[m] = 0.f;
 #pragma unroll 8
   for (long long kk = k0; kk < k1; ++kk) {
-    const float b = __ldg(bp + kk * Bm.sk);
-    const float* ak = A.p + kk * A.sk;  // the same address in every lane: a broadcast load
+    const float b = live ? __ldg(bp + kk * Bm.sk) : 0.f;
+    const float* ak = As[ty * 32 + static_cast<int>(kk - k0)];  // the same word in every lane
 #pragma unroll
     for (int m = 0; m < kSkinny; ++m)
       if (m < M) {
-        const float a = __ldg(ak + m * A.so);
+        const float a = ak[m];
         acc[m] += a * b;
         rs[m] += a;
       }
   }
-  float* cp = static_cast<float*>(P.c) + batch * P.c_batch_stride + col * P.ldc;
 #pragma unroll
-  for (int m = 0; m < kSkinny; ++m)
-    if (m < M) {
-      atomicAdd(cp + m, acc[m]);
-      if (sums) atomicAdd(static_cast<float*>(P.rowsum) + m, rs[m]);
-    }
+  for (int m = 0; m < kSkinny; ++m) {
+    red[ty][m][tx] = acc[m];
+    if (tx == 0) rsred[ty][m] = rs[m];
+  }
+  __syncthreads();
+  if (ty == 0 && live) {
+    float* cp = static_cast<float*>(P.c) + batch * P.c_batch_stride + col * P.ldc;
+    const bool sums = P.rowsum != nullptr && blockIdx.x == 0 && tx == 0;
+#pragma unroll
+    for (int m = 0; m < kSkinny; ++m)
+      if (m < M) {
+        float v = 0.f, r = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+          v += red[w][m][tx];
+          r += rsred[w][m];
+        }
+        atomicAdd(cp + m, v);
+        if (sums) atomicAdd(static_cast<float*>(P.rowsum) + m, r);
+      }
+  }
 }
 
-// k <= 32: a CTA owns 256 rows x 64 columns of C; thread = one row, its row of A in registers.
+// k <= 32: a CTA owns 256 rows x 16 columns of C (small tiles: many CTAs, so that enough loads
+// and stores are in flight); thread = one row, its row of A in registers.
 // Both operand tiles pass through shared memory so that global memory is read in the order it
 // is stored (a contraction-contiguous A read row by row from the threads would again cost one
 // cache line per lane).
+constexpr int kSkinnyKCols = 16;
 template <typename T, int KMAX>
 __global__ void __launch_bounds__(256) skinny_k_plain_kernel(const __grid_constant__ Problem P) {
-  __shared__ float Bs[64][KMAX + 1];
+  __shared__ float Bs[kSkinnyKCols][KMAX + 1];
   __shared__ float As[256][KMAX + 1];
   const long long batch = blockIdx.z;
   const Plain<T> A(P.a[0], batch), Bm(P.b[0], batch);
   const int K = static_cast<int>(P.k[0]);
   const long long row0 = static_cast<long long>(blockIdx.x) * 256;
-  const long long col0 = static_cast<long long>(blockIdx.y) * 64;
+  const long long col0 = static_cast<long long>(blockIdx.y) * kSkinnyKCols;
   const int rows = P.M - row0 < 256 ? static_cast<int>(P.M - row0) : 256;
-  const int cols = P.N - col0 < 64 ? static_cast<int>(P.N - col0) : 64;
+  const int cols = P.N - col0 < kSkinnyKCols ? static_cast<int>(P.N - col0) : kSkinnyKCols;
   // tiles in storage order: index = outer * K + k when the contraction is contiguous, else
   // k * extent + outer
   for (int idx = threadIdx.x; idx < cols * K; idx += 256) {
@@ -465,12 +542,18 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
     long long chunks = 0;
     for (int i = 0; i < p.npairs; ++i) chunks += (p.k[i] + chunk - 1) / chunk;
     if (chunks > 65535) return cudaErrorInvalidValue;
-    dim3 grid(static_cast<unsigned>((p.N + 127) / 128), static_cast<unsigned>(chunks),
-              static_cast<unsigned>(p.batches));
-    if (plain) skinny_mt_plain_kernel<<<grid, 128, 0, stream>>>(p);
-    else skinny_mt_kernel<<<grid, 128, 0, stream>>>(p);
-  } else if (plain && p.batches <= 65535 && (p.N + 63) / 64 <= 65535) {
-    dim3 grid(static_cast<unsigned>((p.M + 255) / 256), static_cast<unsigned>((p.N + 63) / 64),
+    if (plain) {
+      dim3 grid(static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(chunks),
+                static_cast<unsigned>(p.batches));
+      skinny_mt_plain_kernel<<<grid, dim3(32, 8), 0, stream>>>(p);
+    } else {
+      dim3 grid(static_cast<unsigned>((p.N + 127) / 128), static_cast<unsigned>(chunks),
+                static_cast<unsigned>(p.batches));
+      skinny_mt_kernel<<<grid, 128, 0, stream>>>(p);
+    }
+  } else if (plain && p.batches <= 65535 && (p.N + kSkinnyKCols - 1) / kSkinnyKCols <= 65535) {
+    dim3 grid(static_cast<unsigned>((p.M + 255) / 256),
+              static_cast<unsigned>((p.N + kSkinnyKCols - 1) / kSkinnyKCols),
               static_cast<unsigned>(p.batches));
     const bool k16 = p.k[0] <= 16;
     if (dtype == 0) {
