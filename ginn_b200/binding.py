@@ -84,6 +84,11 @@ def lib():
     L.ginn_b200_adam_update.argtypes = [ci, vp, ci, i64, vp, vp, vp, vp, cf, cf, cf, cf, cf, cf, cf]
     L.ginn_b200_softmax_forward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, i64]
     L.ginn_b200_softmax_backward.argtypes = [ci, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, ci]
+    L.ginn_b200_lstm_cell_forward.argtypes = [ci, vp, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp,
+                                              i64, vp, i64]
+    L.ginn_b200_lstm_cell_backward.argtypes = [ci, vp, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp,
+                                               i64, vp, i64, cf, vp, i64, vp, i64]
+    L.ginn_b200_lstm_cell_forward.restype = L.ginn_b200_lstm_cell_backward.restype = ci
     for name in ("ginn_b200_pick_nll_forward", "ginn_b200_pick_nll_backward",
                  "ginn_b200_adam_update", "ginn_b200_softmax_forward",
                  "ginn_b200_softmax_backward"):
@@ -351,6 +356,27 @@ def softmax_backward(y: torch.Tensor, dy: torch.Tensor, dx: torch.Tensor, accumu
     _check(lib().ginn_b200_softmax_backward(_dev(y), _stream(y), _dtype_of(y), rows, cols,
                                             y.data_ptr(), _ld(y), dy.data_ptr(), _ld(dy),
                                             dx.data_ptr(), _ld(dx), int(accumulate)))
+
+
+def lstm_cell_forward(gates, c_prev, c, h, xh_next=None, n_next=0) -> None:
+    """Cell update of one level (ginn_b200_lstm_cell_forward): gates (4H x n) are replaced by
+    their activations; c_prev may be None; xh_next: the next level's h block (H x n_next view)."""
+    H, n = c.shape
+    _check(lib().ginn_b200_lstm_cell_forward(
+        _dev(c), _stream(c), H, n, n_next if xh_next is not None else 0, gates.data_ptr(),
+        _ld(gates), _ptr(c_prev), _ld(c_prev) if c_prev is not None else 0, c.data_ptr(), _ld(c),
+        h.data_ptr(), _ld(h), _ptr(xh_next), _ld(xh_next) if xh_next is not None else 0))
+
+
+def lstm_cell_backward(gates, c, c_prev, dh_next, dc_next, n_next, dgates, dc_out, dh_end=1.0) -> None:
+    """Gradients of one level's cell update (ginn_b200_lstm_cell_backward)."""
+    H, n = c.shape
+    _check(lib().ginn_b200_lstm_cell_backward(
+        _dev(c), _stream(c), H, n, n_next, gates.data_ptr(), _ld(gates), c.data_ptr(), _ld(c),
+        _ptr(c_prev), _ld(c_prev) if c_prev is not None else 0, _ptr(dh_next),
+        _ld(dh_next) if dh_next is not None else 0, _ptr(dc_next),
+        _ld(dc_next) if dc_next is not None else 0, dh_end, dgates.data_ptr(), _ld(dgates),
+        dc_out.data_ptr(), _ld(dc_out)))
 
 
 def adam_update(w: torch.Tensor, d: torch.Tensor, m: torch.Tensor, v: torch.Tensor, t: int,

@@ -773,6 +773,52 @@ int ginn_b200_pick_nll_backward(int device, void* stream, int dtype, int64_t row
   return GINN_B200_OK;
 }
 
+int ginn_b200_lstm_cell_forward(int device, void* stream, int64_t hidden, int64_t n, int64_t n_next,
+                                float* gates, int64_t ldg, const float* c_prev, int64_t ldcp,
+                                float* c, int64_t ldc, float* h, int64_t ldh, float* xh_next,
+                                int64_t ldx) {
+  if (hidden < 0 || n < 0 || n_next < 0 || n_next > n || hidden > 0x7fffffffLL)
+    return fail(GINN_B200_BAD_ARGUMENT, "bad extents hidden=%lld n=%lld n_next=%lld",
+                (long long)hidden, (long long)n, (long long)n_next);
+  if (hidden == 0 || n == 0) return GINN_B200_OK;
+  if (!gates || !c || !h || (n_next > 0 && xh_next == nullptr && ldx != 0))
+    return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  if (ldg < 4 * hidden || ldc < hidden || ldh < hidden || (c_prev && ldcp < hidden) ||
+      (xh_next && ldx < hidden))
+    return fail(GINN_B200_BAD_ARGUMENT, "leading dimension too small");
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  CU_TRY(gb::launch_lstm_cell_forward(gates, ldg, c_prev, ldcp, c, ldc, h, ldh, xh_next, ldx,
+                                      (int)hidden, n, xh_next ? n_next : 0,
+                                      static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+int ginn_b200_lstm_cell_backward(int device, void* stream, int64_t hidden, int64_t n,
+                                 int64_t n_next, const float* gates, int64_t ldg, const float* c,
+                                 int64_t ldc, const float* c_prev, int64_t ldcp,
+                                 const float* dh_next, int64_t lddh, const float* dc_next,
+                                 int64_t lddc, float dh_end, float* dgates, int64_t lddg,
+                                 float* dc_out, int64_t lddo) {
+  if (hidden < 0 || n < 0 || n_next < 0 || n_next > n || hidden > 0x7fffffffLL)
+    return fail(GINN_B200_BAD_ARGUMENT, "bad extents hidden=%lld n=%lld n_next=%lld",
+                (long long)hidden, (long long)n, (long long)n_next);
+  if (hidden == 0 || n == 0) return GINN_B200_OK;
+  if (!gates || !c || !dgates || !dc_out || (n_next > 0 && (!dh_next || !dc_next)))
+    return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  if (ldg < 4 * hidden || lddg < 4 * hidden || ldc < hidden || lddo < hidden ||
+      (c_prev && ldcp < hidden) || (n_next > 0 && (lddh < hidden || lddc < hidden)))
+    return fail(GINN_B200_BAD_ARGUMENT, "leading dimension too small");
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  CU_TRY(gb::launch_lstm_cell_backward(gates, ldg, c, ldc, c_prev, ldcp, dh_next, lddh, dc_next,
+                                       lddc, dh_end, dgates, lddg, dc_out, lddo, (int)hidden, n,
+                                       n_next, static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
 int ginn_b200_adam_update(int device, void* stream, int dtype, int64_t n, void* w, void* d,
                           float* m, float* v, float lr, float clip, float eps, float beta1,
                           float beta2, float beta1_t, float beta2_t) {

@@ -98,6 +98,16 @@ cudaError_t launch_softmax_backward(int dtype, const void* y, long long ldy, con
 cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds, const int* index,
                                      const void* grad, void* dx, long long lddx, int rows,
                                      long long cols, cudaStream_t stream);
+cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c_prev,
+                                     long long ldcp, float* c, long long ldc, float* h,
+                                     long long ldh, float* xh_next, long long ldx, int H,
+                                     long long n, long long n_next, cudaStream_t stream);
+cudaError_t launch_lstm_cell_backward(const float* gates, long long ldg, const float* c,
+                                      long long ldc, const float* c_prev, long long ldcp,
+                                      const float* dh_next, long long lddh, const float* dc_next,
+                                      long long lddc, float dh_end, float* dgates, long long lddg,
+                                      float* dc_out, long long lddo, int H, long long n,
+                                      long long n_next, cudaStream_t stream);
 cudaError_t launch_adam(int dtype, void* w, void* d, float* m, float* v, long long n, float clip,
                         float b1, float b2, float step, float vscale, float eps, int num_sms,
                         cudaStream_t stream);

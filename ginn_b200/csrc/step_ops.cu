@@ -201,6 +201,67 @@ pick_nll_backward_kernel(const T* __restrict__ smax, long long lds, const int* _
   for (int i = 4 * rows4 + lane; i < rows; i += 32) dc[i] = from_f<T>(one(i, to_f(dc[i]), to_f(sc[i])));
 }
 
+// ---- LSTM cell glue of the autobatch benchmark -------------------------------------------
+// The gates of one level arrive as one 4H x n matrix (rows i | f | g | o, the order of the
+// benchmark's shared gate weight); the cell update the reference composes from CwiseProd, Tanh
+// and Add nodes (ginn/model/lstm.h:97-100) is one pass here.  fp32 only.
+//   forward : i, f, o = sigmoid, g = tanh (written back over the pre-activations, the backward
+//             pass needs them), c = f c_prev + i g, h = o tanh(c); h of the columns that live on
+//             is also copied into the next level's input block.
+//   backward: dh = upstream (next level's input gradient for columns that live on, `dh_end` for
+//             those that end here), dc = dc_next + dh o (1 - tanh(c)^2), the four gate gradients
+//             through their nonlinearities, and dc f carried to the previous level.
+__device__ __forceinline__ float sigmoid_f(float x) { return 0.5f * tanhf(0.5f * x) + 0.5f; }
+
+__global__ void __launch_bounds__(256)
+lstm_cell_forward_kernel(float* __restrict__ gates, long long ldg, const float* __restrict__ c_prev,
+                         long long ldcp, float* __restrict__ c, long long ldc, float* __restrict__ h,
+                         long long ldh, float* __restrict__ xh_next, long long ldx, int H,
+                         long long n, long long n_next) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long col = blockIdx.y;
+  if (r >= H || col >= n) return;
+  float* g = gates + col * ldg + r;
+  const float i = sigmoid_f(g[0]), f = sigmoid_f(g[H]), gg = tanhf(g[2 * static_cast<long long>(H)]),
+              o = sigmoid_f(g[3 * static_cast<long long>(H)]);
+  g[0] = i;
+  g[H] = f;
+  g[2 * static_cast<long long>(H)] = gg;
+  g[3 * static_cast<long long>(H)] = o;
+  const float cp = c_prev ? c_prev[col * ldcp + r] : 0.f;
+  const float cv = f * cp + i * gg;
+  const float hv = o * tanhf(cv);
+  c[col * ldc + r] = cv;
+  h[col * ldh + r] = hv;
+  if (xh_next != nullptr && col < n_next) xh_next[col * ldx + r] = hv;
+}
+
+__global__ void __launch_bounds__(256)
+lstm_cell_backward_kernel(const float* __restrict__ gates, long long ldg, const float* __restrict__ c,
+                          long long ldc, const float* __restrict__ c_prev, long long ldcp,
+                          const float* __restrict__ dh_next, long long lddh,
+                          const float* __restrict__ dc_next, long long lddc, float dh_end,
+                          float* __restrict__ dgates, long long lddg, float* __restrict__ dc_out,
+                          long long lddo, int H, long long n, long long n_next) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long col = blockIdx.y;
+  if (r >= H || col >= n) return;
+  const float* g = gates + col * ldg + r;
+  const long long Hl = H;
+  const float i = g[0], f = g[Hl], gg = g[2 * Hl], o = g[3 * Hl];
+  const float tc = tanhf(c[col * ldc + r]);
+  const float cp = c_prev ? c_prev[col * ldcp + r] : 0.f;
+  const bool lives = col < n_next;
+  const float dh = lives ? dh_next[col * lddh + r] : dh_end;
+  const float dc = (lives ? dc_next[col * lddc + r] : 0.f) + dh * o * (1.f - tc * tc);
+  float* dg = dgates + col * lddg + r;
+  dg[0] = dc * gg * i * (1.f - i);
+  dg[Hl] = dc * cp * f * (1.f - f);
+  dg[2 * Hl] = dc * i * (1.f - gg * gg);
+  dg[3 * Hl] = dh * tc * o * (1.f - o);
+  dc_out[col * lddo + r] = dc * f;
+}
+
 // One element of the update; returns the new weight and leaves d, m, v updated.
 template <typename T>
 __device__ __forceinline__ float adam_one(float w, float& d, float& m, float& v, float clip,
@@ -329,6 +390,33 @@ cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds,
   if (cols > 0x7fffffffLL) return cudaErrorInvalidValue;
   if (dtype == 0) pick_backward_t<float>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
   else pick_backward_t<__half>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c_prev,
+                                     long long ldcp, float* c, long long ldc, float* h,
+                                     long long ldh, float* xh_next, long long ldx, int H,
+                                     long long n, long long n_next, cudaStream_t stream) {
+  if (H <= 0 || n <= 0) return cudaSuccess;
+  if (n > 65535) return cudaErrorInvalidValue;
+  dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
+  lstm_cell_forward_kernel<<<grid, 256, 0, stream>>>(gates, ldg, c_prev, ldcp, c, ldc, h, ldh,
+                                                     xh_next, ldx, H, n, n_next);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_lstm_cell_backward(const float* gates, long long ldg, const float* c,
+                                      long long ldc, const float* c_prev, long long ldcp,
+                                      const float* dh_next, long long lddh, const float* dc_next,
+                                      long long lddc, float dh_end, float* dgates, long long lddg,
+                                      float* dc_out, long long lddo, int H, long long n,
+                                      long long n_next, cudaStream_t stream) {
+  if (H <= 0 || n <= 0) return cudaSuccess;
+  if (n > 65535) return cudaErrorInvalidValue;
+  dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
+  lstm_cell_backward_kernel<<<grid, 256, 0, stream>>>(gates, ldg, c, ldc, c_prev, ldcp, dh_next,
+                                                      lddh, dc_next, lddc, dh_end, dgates, lddg,
+                                                      dc_out, lddo, H, n, n_next);
   return cudaGetLastError();
 }
 

@@ -65,7 +65,7 @@ class LstmAutobatch:
     grouped launch (forward, dX, dW); every column is addressed through the pointer tables, as the
     nodes' own tensors would be.  Loss = sum of the final hidden states."""
 
-    def __init__(self, device, nseq=256, H=256, E=128, seed=20242, static=False):
+    def __init__(self, device, nseq=256, H=256, E=128, seed=20242, static=False, fused_cell=True):
         g = torch.Generator(device=device).manual_seed(seed)
         cpu_g = torch.Generator().manual_seed(seed)
         lens = torch.randint(5, 41, (nseq,), generator=cpu_g).sort(descending=True).values
@@ -90,6 +90,11 @@ class LstmAutobatch:
         self.flops = 3 * 2 * 4 * H * (E + H) * self.nodes
         self.units = self.nodes
         self.static = static
+        # The elementwise cell update between the levels: one kernel per level and pass, or the
+        # same arithmetic as a sequence of torch ops (kept as a cross-check of the kernel).
+        self.fused_cell = fused_cell
+        self.dc = [cm(H, n) for n in self.n]
+        self.side = None
         self.fwd = self.dx = self.dw = None
         self.graph = None
 
@@ -108,6 +113,13 @@ class LstmAutobatch:
     def forward(self):
         H, E = self.H, self.E
         self.gates = []
+        if self.fused_cell:
+            for t in range(self.T):
+                self.fwd[t]()
+                nxt = self.n[t + 1] if t + 1 < self.T else 0
+                B.lstm_cell_forward(self.G[t], self.c[t - 1] if t > 0 else None, self.c[t], self.h[t],
+                                    self.XH[t + 1][E:] if nxt else None, nxt)
+            return
         for t in range(self.T):
             self.fwd[t]()
             G, n = self.G[t], self.n[t]
@@ -129,6 +141,27 @@ class LstmAutobatch:
 
     def backward(self):
         H, E = self.H, self.E
+        if self.fused_cell:
+            # The weight-gradient product of a level is needed by nothing before the end of the
+            # pass: it runs on a side stream (a parallel branch when captured in a CUDA graph),
+            # off the chain cell update -> input gradient -> previous level.  The side stream
+            # keeps the accumulations into dW in order.
+            main = torch.cuda.current_stream()
+            if self.side is None:
+                self.side = torch.cuda.Stream(device=self.W.device)
+            for t in reversed(range(self.T)):
+                nxt = self.n[t + 1] if t + 1 < self.T else 0
+                B.lstm_cell_backward(self.G[t], self.c[t], self.c[t - 1] if t > 0 else None,
+                                     self.dXH[t + 1][E:] if nxt else None,
+                                     self.dc[t + 1] if nxt else None, nxt, self.dG[t], self.dc[t])
+                ready = torch.cuda.Event()
+                ready.record(main)
+                self.dx[t]()
+                with torch.cuda.stream(self.side):
+                    self.side.wait_event(ready)
+                    self.dw[t]()
+            main.wait_stream(self.side)
+            return
         dh_next = dc_next = None  # gradients flowing from step t+1 (a prefix of the columns)
         for t in reversed(range(self.T)):
             n = self.n[t]

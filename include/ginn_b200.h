@@ -196,6 +196,27 @@ int ginn_b200_softmax_backward(int device, void* stream, int dtype, int64_t rows
                                const void* y, int64_t ldy, const void* dy, int64_t lddy, void* dx,
                                int64_t lddx, int accumulate);
 
+/* LSTM cell glue for the autobatch benchmark (fp32).  No single reference counterpart: ginn
+ * composes the cell from CwiseProd, Tanh and Add nodes (ginn/model/lstm.h:97-100), i.e. several
+ * elementwise kernels per step; with one merged gate product per level (rows i | f | g | o of a
+ * 4*hidden x n matrix) the whole update is one pass.
+ * forward: gates are replaced by their activations (sigmoid, sigmoid, tanh, sigmoid);
+ *   c = f c_prev + i g (c_prev NULL: zeros), h = o tanh(c); when xh_next is not NULL the first
+ *   n_next columns of h are also written there (the next level's input block, leading dim ldx). */
+int ginn_b200_lstm_cell_forward(int device, void* stream, int64_t hidden, int64_t n, int64_t n_next,
+                                float* gates, int64_t ldg, const float* c_prev, int64_t ldcp,
+                                float* c, int64_t ldc, float* h, int64_t ldh, float* xh_next,
+                                int64_t ldx);
+/* backward: columns < n_next take dh from dh_next and dc from dc_next (the next level's results),
+ * the others end here and take dh = dh_end, dc = 0;  dc += dh o (1 - tanh(c)^2);
+ *   dgates = [dc g i(1-i) | dc c_prev f(1-f) | dc i (1-g^2) | dh tanh(c) o(1-o)],  dc_out = dc f. */
+int ginn_b200_lstm_cell_backward(int device, void* stream, int64_t hidden, int64_t n,
+                                 int64_t n_next, const float* gates, int64_t ldg, const float* c,
+                                 int64_t ldc, const float* c_prev, int64_t ldcp,
+                                 const float* dh_next, int64_t lddh, const float* dc_next,
+                                 int64_t lddc, float dh_end, float* dgates, int64_t lddg,
+                                 float* dc_out, int64_t lddo);
+
 /* One Adam step on n elements: d is clipped to [-clip, clip] in place, then
  *   m = beta1 m + (1 - beta1) d,  v = beta2 v + (1 - beta2) d^2,
  *   w += -lr / (1 - beta1_t) * m / (eps + sqrt(v / (1 - beta2_t))),

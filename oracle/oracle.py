@@ -16,6 +16,7 @@ Reference lines followed (paths inside the ginn source tree):
                          ginn/nonlin.h:162-168
   softmax_backward       ginn/nonlin.h:169-190
   pick_nll_backward      ginn/node/pick.h:87-131,218-224
+  lstm_cell_*            ginn/model/lstm.h:97-100 (the elementwise part of the cell)
   adam_update            ginn/update/update.h:92-133
 
 Arithmetic: inputs exactly as handed to the GPU (fp32, or fp16-rounded), every product and sum
@@ -149,6 +150,36 @@ def pick_nll_backward(smax, index, grad, dx):
     idx = np.asarray(index, dtype=np.int64)
     out[idx, np.arange(smax.shape[1])] -= g.ravel()
     return out
+
+
+def lstm_cell_forward(gates, c_prev):
+    """Cell update from one level's merged gate pre-activations (rows i | f | g | o), fp64:
+    the composition of ginn/model/lstm.h:97-100.  Returns (activated gates, c, h)."""
+    G = f64(gates)
+    H = G.shape[0] // 4
+    sig = lambda x: 0.5 * np.tanh(0.5 * x) + 0.5
+    i, f, g, o = sig(G[:H]), sig(G[H:2 * H]), np.tanh(G[2 * H:3 * H]), sig(G[3 * H:])
+    cp = np.zeros_like(i) if c_prev is None else f64(c_prev)[:, :G.shape[1]]
+    c = f * cp + i * g
+    return np.concatenate([i, f, g, o], 0), c, o * np.tanh(c)
+
+
+def lstm_cell_backward(act, c, c_prev, dh_next, dc_next, n_next, dh_end=1.0):
+    """Gradients of the same update: returns (dgates, dc carried to the previous level)."""
+    A, c = f64(act), f64(c)
+    H, n = c.shape
+    i, f, g, o = A[:H], A[H:2 * H], A[2 * H:3 * H], A[3 * H:]
+    cp = np.zeros_like(c) if c_prev is None else f64(c_prev)[:, :n]
+    dh = np.full((H, n), float(dh_end))
+    dc = np.zeros((H, n))
+    if n_next:
+        dh[:, :n_next] = f64(dh_next)[:, :n_next]
+        dc[:, :n_next] = f64(dc_next)[:, :n_next]
+    tc = np.tanh(c)
+    dc = dc + dh * o * (1 - tc * tc)
+    dG = np.concatenate([dc * g * i * (1 - i), dc * cp * f * (1 - f), dc * i * (1 - g * g),
+                         dh * tc * o * (1 - o)], 0)
+    return dG, dc * f
 
 
 def adam_update(w, d, m, v, lr, clip, eps, beta1, beta2, beta1_t, beta2_t):

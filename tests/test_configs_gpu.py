@@ -146,11 +146,13 @@ def test_config2_lstm_gate_levels(gpu):
     check(B.to_host(db), db_ref, np.float32, "db over levels")
 
 
-def test_lstm_harness_matches_autograd(gpu):
-    """The benchmark's autobatched LSTM harness (grouped launches + elementwise glue) against
-    torch autograd in fp64 on the same small problem: dW and db of the shared gate weights."""
+@pytest.mark.parametrize("fused_cell", [True, False])
+def test_lstm_harness_matches_autograd(gpu, fused_cell):
+    """The benchmark's autobatched LSTM harness (grouped launches + the cell update, as one
+    kernel per level or as torch ops) against torch autograd in fp64 on the same small problem:
+    dW and db of the shared gate weights."""
     from ginn_b200.workloads import LstmAutobatch
-    w = LstmAutobatch(torch.device("cuda", 0), nseq=9, H=32, E=16, seed=3)
+    w = LstmAutobatch(torch.device("cuda", 0), nseq=9, H=32, E=16, seed=3, fused_cell=fused_cell)
     w.rewrite()
     w.step()
     torch.cuda.synchronize()

@@ -132,3 +132,41 @@ def test_softmax_known_answers(gpu, kat):
             torch.cuda.synchronize()
             np.testing.assert_allclose(B.to_host(Y).astype(np.float64), np.asarray(y, np.float64),
                                        rtol=eps, atol=eps * 1e-2)
+
+
+def test_lstm_cell_forward_backward(gpu):
+    """The cell update between two autobatch levels: a level with 7 columns of which 4 live on,
+    padded leading dimensions, against the fp64 restatement."""
+    rng = np.random.default_rng(91)
+    H, n, n_next, E = 24, 7, 4, 5
+    f32 = np.float32
+    G, cp = randn(rng, (4 * H, n), f32), randn(rng, (H, n + 2), f32)
+    Gd, CP = B.from_host(G, ld=4 * H + 3), B.from_host(cp)
+    C, Hh = B.colmajor(H, n, torch.float32, fill=0.0), B.colmajor(H, n, torch.float32, ld=H + 1, fill=0.0)
+    XH = B.colmajor(E + H, n_next, torch.float32, fill=7.0)
+    gpu.lstm_cell_forward(Gd, CP, C, Hh, XH[E:], n_next)
+    torch.cuda.synchronize()
+    act, c, h = orc.lstm_cell_forward(G, cp)
+    check(B.to_host(Gd), act, f32, "activations")
+    check(B.to_host(C), c, f32, "c")
+    check(B.to_host(Hh), h, f32, "h")
+    np.testing.assert_array_equal(B.to_host(XH)[:E], 7.0)       # the x block is not touched
+    check(B.to_host(XH)[E:], h[:, :n_next], f32, "h copied into the next level's input")
+    dhn, dcn = randn(rng, (E + H, n_next), f32), randn(rng, (H, n_next), f32)
+    DHN, DCN = B.from_host(dhn), B.from_host(dcn)
+    dG, dC = B.colmajor(4 * H, n, torch.float32, fill=0.0), B.colmajor(H, n, torch.float32, fill=0.0)
+    gpu.lstm_cell_backward(Gd, C, CP, DHN[E:], DCN, n_next, dG, dC, dh_end=1.0)
+    torch.cuda.synchronize()
+    rg, rc = orc.lstm_cell_backward(B.to_host(Gd), B.to_host(C), cp, dhn[E:], dcn, n_next, 1.0)
+    check(B.to_host(dG), rg, f32, "dgates")
+    check(B.to_host(dC), rc, f32, "dc")
+    # first level (no previous cell state) and last level (no column lives on)
+    C0 = B.colmajor(H, n, torch.float32, fill=0.0)
+    G0 = B.from_host(G)
+    gpu.lstm_cell_forward(G0, None, C0, Hh, None, 0)
+    gpu.lstm_cell_backward(G0, C0, None, None, None, 0, dG, dC, dh_end=0.5)
+    torch.cuda.synchronize()
+    act0, c0, _ = orc.lstm_cell_forward(G, None)
+    rg0, rc0 = orc.lstm_cell_backward(act0, c0, None, None, None, 0, 0.5)
+    check(B.to_host(dG), rg0, f32, "dgates, no neighbours")
+    check(B.to_host(dC), rc0, f32, "dc, no neighbours")
