@@ -53,8 +53,8 @@ struct Problem {
   int tiles_m, tiles_n;
   int tile_start;         // first linear tile index of this problem inside a grouped launch
   // Split of the contraction over `split_k` CTAs per output tile (fp32 tensor-core kernels only;
-  // needs accumulate = 1, no activation, no bias, one pair): every CTA adds its partial sum to C
-  // with atomic adds.  0 or 1 = no split.
+  // needs accumulate = 1, no activation, one pair): every CTA adds its partial sum to C with
+  // atomic adds, the first one of a tile also the bias.  0 or 1 = no split.
   int split_k;
 };
 

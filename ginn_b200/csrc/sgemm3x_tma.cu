@@ -54,7 +54,7 @@ struct SParams {
   float* rowsum;
   int act;
   int accumulate;
-  int split_k;  // CTAs per output tile along K (1 = none); > 1 only with accumulate, no bias/act
+  int split_k;  // CTAs per output tile along K (1 = none); > 1 only with accumulate and no act
   int batches;
 };
 
@@ -332,7 +332,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       const int cgrp = (warp - 2) >> 2;  // 0..3
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const float bias = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
+      const float bias = (p.bias != nullptr && row_ok && split == 0) ? p.bias[row] : 0.f;  // once per tile
       float* crow = p.C + static_cast<long long>(batch) * p.strideC + row;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
       {
@@ -711,7 +711,8 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
       const int c0 = ((warp - 1) >> 2) * 32;
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < P.M;
-      const float bias = (P.bias != nullptr && row_ok) ? static_cast<const float*>(P.bias)[row] : 0.f;
+      const float bias = (P.bias != nullptr && row_ok && split == 0)
+                             ? static_cast<const float*>(P.bias)[row] : 0.f;  // once per tile
       float* cbase = static_cast<float*>(P.c) + batch * P.c_batch_stride;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
       float acc[32];
@@ -856,10 +857,10 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
 }
 
 // Number of K splits for a problem of `tiles` output tiles: only where partial sums can simply be
-// added to C (accumulate, no bias, no activation, one pair), when the tiles alone leave most SMs
+// added to C (accumulate, no activation, one pair; a bias is added by the first CTA of a tile), when the tiles alone leave most SMs
 // idle, and never below four k-blocks per CTA.
 int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms) {
-  if (!p.accumulate || p.act != ACT_NONE || p.bias != nullptr || p.npairs != 1) return 1;
+  if (!p.accumulate || p.act != ACT_NONE || p.npairs != 1) return 1;
   const long long nkb = (p.k[0] + SBK - 1) / SBK;
   if (tiles <= 0 || tiles * 2 > num_sms || nkb < 8) return 1;
   long long s = num_sms / tiles;

@@ -80,7 +80,14 @@ class LstmAutobatch:
         cm = lambda r, c: B.colmajor(r, c, torch.float32, device, fill=0.0)
         self.XH = [cm(E + H, n) for n in self.n]
         self.dXH = [cm(E + H, n) for n in self.n]
-        self.G = [cm(4 * H, n) for n in self.n]
+        # The gate matrices of all levels share one buffer that is zeroed once per step: the
+        # forward products then accumulate (y += W x + b), which lets the library split their
+        # contraction over several CTAs (a level has only 16 output tiles and 12 k-blocks).
+        self.Gflat = torch.zeros(4 * H * sum(self.n), device=device)
+        self.G, off = [], 0
+        for n in self.n:
+            self.G.append(torch.as_strided(self.Gflat, (4 * H, n), (1, 4 * H), off))
+            off += 4 * H * n
         self.dG = [cm(4 * H, n) for n in self.n]
         self.c = [cm(H, n) for n in self.n]
         self.h = [cm(H, n) for n in self.n]
@@ -105,7 +112,8 @@ class LstmAutobatch:
         self.fwd, self.dx, self.dw = [], [], []
         for t in range(self.T):
             x, y, dy, dx = cols(self.XH[t]), cols(self.G[t]), cols(self.dG[t]), cols(self.dXH[t])
-            self.fwd.append(mk(GROUPED_FORWARD, B.Group(w=self.W, x_cols=x, y_cols=y, bias=self.b)))
+            self.fwd.append(mk(GROUPED_FORWARD, B.Group(w=self.W, x_cols=x, y_cols=y, bias=self.b,
+                                                        accumulate=True)))
             self.dx.append(mk(GROUPED_DX, B.Group(w=self.W, y_cols=dy, dx_cols=dx)))
             self.dw.append(mk(GROUPED_DW, B.Group(w=self.W, x_cols=x, y_cols=dy, dw=self.dW,
                                                   dbias=self.db)))
@@ -113,6 +121,7 @@ class LstmAutobatch:
     def forward(self):
         H, E = self.H, self.E
         self.gates = []
+        self.Gflat.zero_()
         if self.fused_cell:
             for t in range(self.T):
                 self.fwd[t]()

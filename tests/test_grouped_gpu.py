@@ -133,3 +133,20 @@ def test_half_level(gpu):
     check(np.stack([B.to_host(t) for t in dxs], 1), orc.gemm(W, DY, trans_a=True), np.float16, "dX")
     check(B.to_host(dw), orc.gemm(DY, X, trans_b=True), np.float16, "dW")
     check(B.to_host(db), DY.astype(np.float64).sum(1), np.float16, "dbias")
+
+
+def test_accumulating_forward_level_with_bias(gpu):
+    """y += W x + b into non-zero outputs: the form whose contraction the library may split over
+    several CTAs (each adds its partial sum, the first one of a tile also the bias)."""
+    rng = np.random.default_rng(46)
+    for specs in ([(1024, 384, 256)], [(256, 2048, 40), (128, 96, 7)]):
+        groups, host = make_level(rng, specs)
+        y0 = [[randn(rng, g["w"].shape[0], np.float32) for _ in g["x"]] for g in groups]
+        ys = [[B.from_host(v) for v in col] for col in y0]
+        gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=y, bias=g["bias"],
+                                                accumulate=True) for g, y in zip(groups, ys)])
+        torch.cuda.synchronize()
+        for (W, bias, xs, _), y, base in zip(host, ys, y0):
+            X = np.stack(xs, 1)
+            ref = np.stack(base, 1).astype(np.float64) + orc.affine_forward([(W, X)], bias, 0)
+            check(np.stack([B.to_host(t) for t in y], 1), ref, np.float32, "y += W x + b")
