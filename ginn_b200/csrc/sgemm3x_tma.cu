@@ -864,7 +864,7 @@ int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms) {
   const long long nkb = (p.k[0] + SBK - 1) / SBK;
   if (tiles <= 0 || tiles * 2 > num_sms || nkb < 8) return 1;
   long long s = num_sms / tiles;
-  if (s > nkb / 4) s = nkb / 4;
+  if (s > nkb / 2) s = nkb / 2;
   if (s > 32) s = 32;
   return s < 1 ? 1 : static_cast<int>(s);
 }
