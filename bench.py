@@ -528,7 +528,14 @@ def run_config_workload(args):
         comm = torch.cuda.Stream(device=dev) if world > 1 else None
 
         def allreduce(t):
-            dist.all_reduce(t)
+            """Sum over ranks on the communication stream; returns the wait for its result."""
+            main = torch.cuda.current_stream(dev)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            comm.wait_event(ready)
+            with torch.cuda.stream(comm):
+                dist.all_reduce(t)
+            return lambda: main.wait_stream(comm)
         w = wl.MlpDataParallel(dev, rank, world, allreduce=allreduce if world > 1 else None)
         metric, name = "mlp_dp_tflops", "C5 data-parallel MLP 784-1024-1024-10, fp32, batch 4096 per GPU, Adam"
 

@@ -232,7 +232,9 @@ class MlpDataParallel:
         gw = torch.Generator(device=device).manual_seed(123457)          # same weights everywhere
         gd = torch.Generator(device=device).manual_seed(123457 + 1 + rank)  # own data per rank
         d = self.DIMS
-        sizes = [d[i + 1] * d[i] for i in range(3)] + [d[i + 1] for i in range(3)]
+        # flat layout W1 b1 | W2 b2 W3 b3: the gradients of layers 2 and 3 are complete before
+        # layer 1's weight gradient starts and form one contiguous bucket for the all-reduce
+        sizes = [d[1] * d[0], d[1], d[2] * d[1], d[2], d[3] * d[2], d[3]]
         total = sum(sizes)
         self.params = torch.empty(total, device=device)
         self.grads = torch.zeros(total, device=device)
@@ -243,10 +245,12 @@ class MlpDataParallel:
             views.append(self.params[off:off + n])
             gviews.append(self.grads[off:off + n])
             off += n
+        self.bucket_late = self.grads[:sizes[0] + sizes[1]]    # layer 1: ready last
+        self.bucket_early = self.grads[sizes[0] + sizes[1]:]   # layers 2 and 3
         cmv = lambda flat, r, c: torch.as_strided(flat, (r, c), (1, r))
-        self.W = [cmv(views[i], d[i + 1], d[i]) for i in range(3)]
-        self.dW = [cmv(gviews[i], d[i + 1], d[i]) for i in range(3)]
-        self.b, self.db = views[3:], gviews[3:]
+        self.W = [cmv(views[2 * i], d[i + 1], d[i]) for i in range(3)]
+        self.dW = [cmv(gviews[2 * i], d[i + 1], d[i]) for i in range(3)]
+        self.b, self.db = [views[2 * i + 1] for i in range(3)], [gviews[2 * i + 1] for i in range(3)]
         for i in range(3):
             self.W[i].copy_(_xavier(d[i + 1], d[i], gw, device))
             self.b[i].copy_(_xavier(d[i + 1], 1, gw, device).reshape(-1))
@@ -277,12 +281,19 @@ class MlpDataParallel:
         gb.pick_nll_forward(self.h[3], self.labels32, self.smax, self.nll)
         self.loss = self.nll.sum()
         gb.pick_nll_backward(self.smax, self.labels32, self.ones, self.dh[3])
+        wait = []
         for i in (2, 1, 0):
             gb.affine_backward([gb.PairGrad(self.W[i], self.h[i], self.dW[i],
                                             self.dh[i] if i > 0 else None)],
                                self.dh[i + 1], self.h[i + 1], self.acts[i], self.db[i])
+            # data parallel: the all-reduce of layers 2 and 3 runs beside layer 1's backward
+            # product; `allreduce` returns a function that makes this stream wait for the result
+            if self.allreduce is not None and self.world > 1 and i == 1:
+                wait.append(self.allreduce(self.bucket_early))
         if self.allreduce is not None and self.world > 1:
-            self.allreduce(self.grads)
+            wait.append(self.allreduce(self.bucket_late))
+            for w in wait:
+                w()
         # Adam on the flat buffers (ginn/update/update.h:115-133), one kernel
         self.t += 1
         gb.adam_update(self.params, self.grads, self.m, self.v, self.t)
