@@ -528,40 +528,42 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
                              ? __half2float(static_cast<const __half*>(P.bias)[row]) : 0.f;
       __half* cbase = static_cast<__half*>(P.c) + batch * P.c_batch_stride;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
+      void* const* ccols = P.ccols;
+      const long long ldc = P.ldc;
+      const int N = P.N, act = P.act;
+      const bool load_c = P.accumulate && row_ok;
+      // eight columns per pass, not unrolled: the epilogue runs once per CTA, so its code size
+      // is pure instruction-fetch time
 #pragma unroll 1
-      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
-        float acc[32];
+      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 8) {
+        float acc[8];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 8; ++j) {
           const int col = n0 + c0 + j;
           float v = bias;
-          if (P.accumulate && row_ok && col < P.N) {
-            const __half* src = (P.ccols ? static_cast<const __half*>(P.ccols[col])
-                                         : cbase + static_cast<long long>(col) * P.ldc) + row;
-            v += __half2float(*src);
-          }
+          if (load_c && col < N)
+            v += __half2float((ccols ? static_cast<const __half*>(ccols[col])
+                                     : cbase + static_cast<long long>(col) * ldc)[row]);
           acc[j] = v;
         }
         if (nkb > 0) {
-          uint32_t v[32];
-          tmem_ld32(tbase + c0, v);
+          uint32_t v[8];
+          tmem_ld8(tbase + c0, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+          for (int j = 0; j < 8; ++j) acc[j] += __uint_as_float(v[j]);
         }
-        if (P.act != ACT_NONE) {
+        if (act != ACT_NONE) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] = act_forward_half(P.act, acc[j]);
+          for (int j = 0; j < 8; ++j) acc[j] = act_forward_half(act, acc[j]);
         }
         if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
+          for (int j = 0; j < 8; ++j) {
             const int col = n0 + c0 + j;
-            if (col < P.N) {
-              __half* dst = (P.ccols ? static_cast<__half*>(P.ccols[col])
-                                     : cbase + static_cast<long long>(col) * P.ldc) + row;
-              *dst = __float2half_rn(acc[j]);
-            }
+            if (col < N)
+              (ccols ? static_cast<__half*>(ccols[col]) : cbase + static_cast<long long>(col) * ldc)[row] =
+                  __float2half_rn(acc[j]);
           }
         }
       }

@@ -335,34 +335,36 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       const float bias = (p.bias != nullptr && row_ok && split == 0) ? p.bias[row] : 0.f;  // once per tile
       float* crow = p.C + static_cast<long long>(batch) * p.strideC + row;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
-      {
-        const int c0 = cgrp * 32;
-        float acc[32];
-        const bool split_k = p.split_k > 1;
-        const bool load_c = p.accumulate && row_ok && !split_k;
+      const int c0 = cgrp * 32;
+      const bool split_k = p.split_k > 1;
+      const bool load_c = p.accumulate && row_ok && !split_k;
+      // eight columns per pass, not unrolled (code size: see the gather kernel's epilogue)
+#pragma unroll 1
+      for (int c = 0; c < 32; c += 8) {
+        float acc[8];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = n0 + c0 + j;
-          acc[j] = (load_c && col < p.N) ? crow[static_cast<long long>(col) * p.ldc] : 0.f;
+        for (int j = 0; j < 8; ++j) {
+          const int col = n0 + c0 + c + j;
+          acc[j] = bias + ((load_c && col < p.N) ? crow[static_cast<long long>(col) * p.ldc] : 0.f);
         }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] += bias;
-        uint32_t v[32];
-        tmem_ld32(tbase + CROSS_COL + c0, v);
+        uint32_t v0[8], v1[8], v2[8], v3[8];
+        if (nkb > 0) tmem_ld8(tbase + CROSS_COL + c0 + c, v0);
+        if (nkb > 0) tmem_ld8(tbase + c0 + c, v1);
+        if (nkb > 1) tmem_ld8(tbase + SBN + c0 + c, v2);
+        if (nkb > 2) tmem_ld8(tbase + 2 * SBN + c0 + c, v3);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
-#pragma unroll 1
-        for (int a = 0; a < 3 && a < nkb; ++a) {
-          tmem_ld32(tbase + a * SBN + c0, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+        for (int j = 0; j < 8; ++j) {
+          float t = 0.f;
+          if (nkb > 0) t = __uint_as_float(v0[j]) + __uint_as_float(v1[j]);
+          if (nkb > 1) t += __uint_as_float(v2[j]);
+          if (nkb > 2) t += __uint_as_float(v3[j]);
+          acc[j] += t;
         }
         if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = n0 + c0 + j;
+          for (int j = 0; j < 8; ++j) {
+            const int col = n0 + c0 + c + j;
             if (col < p.N) {
               float* dst = crow + static_cast<long long>(col) * p.ldc;
               if (split_k)
@@ -715,42 +717,50 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
                              ? static_cast<const float*>(P.bias)[row] : 0.f;  // once per tile
       float* cbase = static_cast<float*>(P.c) + batch * P.c_batch_stride;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
-      float acc[32];
       const bool split_k = nsplit > 1;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = n0 + c0 + j;
-        float v = bias;
-        if (P.accumulate && !split_k && row_ok && col < P.N) {
-          const float* src = (P.ccols ? static_cast<const float*>(P.ccols[col])
-                                      : cbase + static_cast<long long>(col) * P.ldc) + row;
-          v += *src;
-        }
-        acc[j] = v;
-      }
-      uint32_t v[32];
-      tmem_ld32(tbase + CROSS_COL + c0, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
+      const bool load_c = P.accumulate && !split_k && row_ok;
+      void* const* ccols = P.ccols;
+      const long long ldc = P.ldc;
+      const int N = P.N, act = P.act;
+      // Eight columns per pass, not unrolled: a kernel that serves 2-k-block tiles runs its code
+      // once per CTA, from a cold instruction cache, and a 32-fold unrolled epilogue was more
+      // than half of it.
 #pragma unroll 1
-      for (int a = 0; a < 3 && a < nkb; ++a) {
-        tmem_ld32(tbase + a * SBN + c0, v);
+      for (int c = 0; c < 32; c += 8) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int col = n0 + c0 + c + j;
+          float v = bias;
+          if (load_c && col < N)
+            v += (ccols ? static_cast<const float*>(ccols[col]) : cbase + static_cast<long long>(col) * ldc)[row];
+          acc[j] = v;
+        }
+        uint32_t v0[8], v1[8], v2[8], v3[8];
+        if (nkb > 0) tmem_ld8(tbase + CROSS_COL + c0 + c, v0);
+        if (nkb > 0) tmem_ld8(tbase + c0 + c, v1);
+        if (nkb > 1) tmem_ld8(tbase + SBN + c0 + c, v2);
+        if (nkb > 2) tmem_ld8(tbase + 2 * SBN + c0 + c, v3);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(v[j]);
-      }
-      if (row_ok) {
+        for (int j = 0; j < 8; ++j) {
+          float t = 0.f;
+          if (nkb > 0) t = __uint_as_float(v0[j]) + __uint_as_float(v1[j]);
+          if (nkb > 1) t += __uint_as_float(v2[j]);
+          if (nkb > 2) t += __uint_as_float(v3[j]);
+          acc[j] += t;
+        }
+        if (row_ok) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = n0 + c0 + j;
-          if (col < P.N) {
-            float* dst = (P.ccols ? static_cast<float*>(P.ccols[col])
-                                  : cbase + static_cast<long long>(col) * P.ldc) + row;
-            if (split_k)
-              atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
-            else
-              *dst = (P.act == ACT_NONE ? acc[j] : act_forward_f32(P.act, acc[j]));
+          for (int j = 0; j < 8; ++j) {
+            const int col = n0 + c0 + c + j;
+            if (col < N) {
+              float* dst = (ccols ? static_cast<float*>(ccols[col]) : cbase + static_cast<long long>(col) * ldc) + row;
+              if (split_k)
+                atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
+              else
+                *dst = (act == ACT_NONE ? acc[j] : act_forward_f32(act, acc[j]));
+            }
           }
         }
       }
