@@ -499,7 +499,11 @@ struct RawFeeder {
   }
 };
 
-template <bool GROUPED>
+// WITH_Y: the instantiation that can take a derivative operand.  Grouped levels never have one
+// (autobatch merges identity Affines only) and most single products do not either; leaving the
+// second feeder and the derivative transforms out makes their kernel a fifth smaller, which is
+// run time for tiles of a few k-blocks (the code is fetched once per CTA, cold).
+template <bool GROUPED, bool WITH_Y>
 __global__ void __launch_bounds__(GNTHREADS, 1)
 sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restrict__ probs,
                       int nprobs, int* __restrict__ status) {
@@ -546,7 +550,7 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
   const int kb_begin = static_cast<int>(static_cast<long long>(nkb_total) * split / nsplit);
   const int nkb =
       static_cast<int>(static_cast<long long>(nkb_total) * (split + 1) / nsplit) - kb_begin;
-  const int dop = P.a[0].dact != ACT_NONE ? 1 : (P.b[0].dact != ACT_NONE ? 2 : 0);
+  const int dop = !WITH_Y ? 0 : (P.a[0].dact != ACT_NONE ? 1 : (P.b[0].dact != ACT_NONE ? 2 : 0));
   const int dact = dop == 1 ? P.a[0].dact : (dop == 2 ? P.b[0].dact : ACT_NONE);
   const int raw_stages = dop ? 2 : 3;
   const int raw_stage_bytes = dop ? 3 * RAW_TILE : 2 * RAW_TILE;
@@ -615,7 +619,7 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
     const int t = xt & 255;
     const int o0 = grp ? n0 : m0;
     const int O = grp ? P.N : P.M;
-    const bool has_y = dop == grp + 1;
+    const bool has_y = WITH_Y && dop == grp + 1;
     const bool want_rowsum = grp == 0 && P.rowsum != nullptr && n_tile == 0;
     float rs = 0.f;
     bool ok = true;
@@ -775,10 +779,10 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
   }
 }
 
-template <bool GROUPED>
+template <bool GROUPED, bool WITH_Y>
 cudaError_t launch_gather(const Problem& p, const Problem* dprobs, int nprobs, int total_tiles,
                           cudaStream_t stream, int* status) {
-  auto kern = sgemm3x_gather_kernel<GROUPED>;
+  auto kern = sgemm3x_gather_kernel<GROUPED, WITH_Y>;
   const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
@@ -901,7 +905,9 @@ cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status) 
                           (p.split_k > 1 ? p.split_k : 1);
   if (total <= 0) return cudaSuccess;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
-  return launch_gather<false>(p, nullptr, 1, static_cast<int>(total), stream, status);
+  const bool with_y = p.a[0].dact != ACT_NONE || p.b[0].dact != ACT_NONE;
+  return with_y ? launch_gather<false, true>(p, nullptr, 1, static_cast<int>(total), stream, status)
+                : launch_gather<false, false>(p, nullptr, 1, static_cast<int>(total), stream, status);
 }
 
 // Descriptors in device memory, tiles_m / tiles_n / tile_start filled for 128 x 128 tiles.
@@ -909,7 +915,7 @@ cudaError_t launch_sgemm3x_gather_grouped(const Problem* dprobs, int nprobs, int
                                           cudaStream_t stream, int* status) {
   if (total_tiles <= 0) return cudaSuccess;
   Problem dummy{};
-  return launch_gather<true>(dummy, dprobs, nprobs, total_tiles, stream, status);
+  return launch_gather<true, false>(dummy, dprobs, nprobs, total_tiles, stream, status);
 }
 
 }  // namespace gb
