@@ -310,6 +310,15 @@ class GroupedCall:
         else:
             _check(lib().ginn_b200_level_run(self.handle, _stream(self.w0)))
 
+    def run(self, stream: int):
+        """Same as calling the object, on an explicit stream handle (saves the per-call lookup
+        of torch's current stream in launch-bound loops)."""
+        if self.static:
+            _check(lib().ginn_b200_grouped_static(self.dev, stream, self.dtype, self.mode, self.n,
+                                                  self.arr))
+        else:
+            _check(_lib.ginn_b200_level_run(self.handle, stream))
+
     def __del__(self):
         if getattr(self, "handle", None) is not None and _lib is not None:
             _lib.ginn_b200_level_destroy(self.handle)

@@ -294,7 +294,10 @@ struct Feeder {
   }
 };
 
-template <bool GROUPED>
+// WITH_REGS: the instantiation that can route an operand through registers (fused derivative,
+// bias-gradient sums).  That machinery is 60 % of the kernel's code; products that need none of
+// it (plain products, Affine forward) run an instantiation without it.
+template <bool GROUPED, bool WITH_REGS>
 __global__ void __launch_bounds__(GTHREADS, 2)
 hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restrict__ probs,
                     int nprobs, int* __restrict__ status) {
@@ -393,7 +396,7 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
     const int t = pt & (GPROD - 1);
     const int o0 = grp ? n0 : m0;
     const int O = grp ? P.N : P.M;
-    const bool want_rowsum = grp == 0 && P.rowsum != nullptr && n_tile == 0;
+    const bool want_rowsum = WITH_REGS && grp == 0 && P.rowsum != nullptr && n_tile == 0;
     float rs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     bool ok = true;
     int s = 0, pair = 0;
@@ -404,7 +407,9 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
 
     auto operand = [&](int pr) -> const Operand& { return grp ? P.b[pr] : P.a[pr]; };
     // Register path: this operand carries a derivative or feeds the bias gradient.
-    auto via_regs = [&](int pr) { return operand(pr).dact != ACT_NONE || (want_rowsum && pr == 0); };
+    auto via_regs = [&](int pr) {
+      return WITH_REGS && (operand(pr).dact != ACT_NONE || (want_rowsum && pr == 0));
+    };
     Feeder fd;
     auto setup = [&](int pr) {
       const Operand& op = operand(pr);
@@ -578,10 +583,10 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
   }
 }
 
-template <bool GROUPED>
+template <bool GROUPED, bool WITH_REGS>
 cudaError_t launch_hgather(const Problem& p, const Problem* dprobs, int nprobs, int total_tiles,
                            cudaStream_t stream, int* status) {
-  auto kern = hgemm_gather_kernel<GROUPED>;
+  auto kern = hgemm_gather_kernel<GROUPED, WITH_REGS>;
   const int smem = GSTAGES * GSTAGE + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
@@ -607,14 +612,17 @@ cudaError_t launch_hgemm_gather(Problem& p, cudaStream_t stream, int* status) {
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   if (total <= 0) return cudaSuccess;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
-  return launch_hgather<false>(p, nullptr, 1, static_cast<int>(total), stream, status);
+  bool regs = p.rowsum != nullptr;
+  for (int i = 0; i < p.npairs; ++i) regs = regs || p.a[i].dact != ACT_NONE || p.b[i].dact != ACT_NONE;
+  return regs ? launch_hgather<false, true>(p, nullptr, 1, static_cast<int>(total), stream, status)
+              : launch_hgather<false, false>(p, nullptr, 1, static_cast<int>(total), stream, status);
 }
 
 cudaError_t launch_hgemm_gather_grouped(const Problem* dprobs, int nprobs, int total_tiles,
                                         cudaStream_t stream, int* status) {
   if (total_tiles <= 0) return cudaSuccess;
   Problem dummy{};
-  return launch_hgather<true>(dummy, dprobs, nprobs, total_tiles, stream, status);
+  return launch_hgather<true, true>(dummy, dprobs, nprobs, total_tiles, stream, status);
 }
 
 }  // namespace gb

@@ -117,17 +117,37 @@ class LstmAutobatch:
             self.dx.append(mk(GROUPED_DX, B.Group(w=self.W, y_cols=dy, dx_cols=dx)))
             self.dw.append(mk(GROUPED_DW, B.Group(w=self.W, x_cols=x, y_cols=dy, dw=self.dW,
                                                   dbias=self.db)))
+        # Argument lists of the cell-update calls, built once (slot 1 is the stream): a step
+        # launched from Python is bound by host time per call.
+        H, E, dev = self.H, self.E, B._dev(self.W)
+        ptr = lambda t: None if t is None else t.data_ptr()
+        ld = lambda t: 0 if t is None else B._ld(t)
+        self.cf_args, self.cb_args = [], []
+        for t in range(self.T):
+            nxt = self.n[t + 1] if t + 1 < self.T else 0
+            cp = self.c[t - 1] if t > 0 else None
+            xh = self.XH[t + 1][E:] if nxt else None
+            self.cf_args.append([dev, None, H, self.n[t], nxt, ptr(self.G[t]), ld(self.G[t]), ptr(cp), ld(cp),
+                                 ptr(self.c[t]), ld(self.c[t]), ptr(self.h[t]), ld(self.h[t]), ptr(xh), ld(xh)])
+            dhn = self.dXH[t + 1][E:] if nxt else None
+            dcn = self.dc[t + 1] if nxt else None
+            self.cb_args.append([dev, None, H, self.n[t], nxt, ptr(self.G[t]), ld(self.G[t]), ptr(self.c[t]),
+                                 ld(self.c[t]), ptr(cp), ld(cp), ptr(dhn), ld(dhn), ptr(dcn), ld(dcn), 1.0,
+                                 ptr(self.dG[t]), ld(self.dG[t]), ptr(self.dc[t]), ld(self.dc[t])])
+        self.events = [torch.cuda.Event() for _ in range(self.T)]
 
     def forward(self):
         H, E = self.H, self.E
         self.gates = []
         self.Gflat.zero_()
         if self.fused_cell:
+            st = torch.cuda.current_stream().cuda_stream
+            cell, check = B.lib().ginn_b200_lstm_cell_forward, B._check
             for t in range(self.T):
-                self.fwd[t]()
-                nxt = self.n[t + 1] if t + 1 < self.T else 0
-                B.lstm_cell_forward(self.G[t], self.c[t - 1] if t > 0 else None, self.c[t], self.h[t],
-                                    self.XH[t + 1][E:] if nxt else None, nxt)
+                self.fwd[t].run(st)
+                a = self.cf_args[t]
+                a[1] = st
+                check(cell(*a))
             return
         for t in range(self.T):
             self.fwd[t]()
@@ -158,17 +178,17 @@ class LstmAutobatch:
             main = torch.cuda.current_stream()
             if self.side is None:
                 self.side = torch.cuda.Stream(device=self.W.device)
+            st, side_st = main.cuda_stream, self.side.cuda_stream
+            cell, check = B.lib().ginn_b200_lstm_cell_backward, B._check
             for t in reversed(range(self.T)):
-                nxt = self.n[t + 1] if t + 1 < self.T else 0
-                B.lstm_cell_backward(self.G[t], self.c[t], self.c[t - 1] if t > 0 else None,
-                                     self.dXH[t + 1][E:] if nxt else None,
-                                     self.dc[t + 1] if nxt else None, nxt, self.dG[t], self.dc[t])
-                ready = torch.cuda.Event()
+                a = self.cb_args[t]
+                a[1] = st
+                check(cell(*a))
+                ready = self.events[t]
                 ready.record(main)
-                self.dx[t]()
-                with torch.cuda.stream(self.side):
-                    self.side.wait_event(ready)
-                    self.dw[t]()
+                self.dx[t].run(st)
+                self.side.wait_event(ready)
+                self.dw[t].run(side_st)
             main.wait_stream(self.side)
             return
         dh_next = dc_next = None  # gradients flowing from step t+1 (a prefix of the columns)
