@@ -102,22 +102,6 @@ __device__ __forceinline__ float act_forward_half(int act, float x) {
   return x;
 }
 
-// Raw 8 halves of a piece (and of Y at the same place): zero outside the matrix.
-__device__ __forceinline__ void load_raw(const PieceSrc& s, uint4& d, uint4& y) {
-  d = make_uint4(0, 0, 0, 0);
-  y = make_uint4(0, 0, 0, 0);
-  if (s.valid <= 0) return;
-  const uintptr_t both = reinterpret_cast<uintptr_t>(s.p) | reinterpret_cast<uintptr_t>(s.y);
-  if (s.valid == 8 && (both & 15u) == 0) {
-    d = __ldg(reinterpret_cast<const uint4*>(s.p));
-    if (s.y) y = __ldg(reinterpret_cast<const uint4*>(s.y));
-  } else {
-    const Piece2 r = load_piece_slow(s.p, s.y, s.valid);
-    d = r.d;
-    y = r.y;
-  }
-}
-
 // A piece whose source is not 16-byte aligned: 4-byte asynchronous copies, or through registers
 // when even those are impossible.
 __device__ __noinline__ void copy_piece_slow(uint32_t d, const __half* p, int valid, const void* safe) {
@@ -423,7 +407,16 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
           fd.load4_fast(kk0, h, &regs[h], y);
         } else {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) load_raw(fd.src(h + i, kk0), regs[h + i], y[i]);
+          for (int i = 0; i < 4; ++i) {  // tables or unaligned operands: element by element
+            const PieceSrc ps = fd.src(h + i, kk0);
+            regs[h + i] = make_uint4(0, 0, 0, 0);
+            y[i] = make_uint4(0, 0, 0, 0);
+            if (ps.valid > 0) {
+              const Piece2 r = load_piece_slow(ps.p, ps.y, ps.valid);
+              regs[h + i] = r.d;
+              y[i] = r.y;
+            }
+          }
         }
         if (fd.has_y) {
 #pragma unroll
@@ -442,14 +435,10 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
       if (lane == 0) mbar_arrive(smem_u32(&full_bar[stage]));
     };
 
-    if (nkb > 0) {
-      setup(0);
-      if (via_regs(0)) {
-        load_regs(0);
-        regs_loaded = true;
-      }
-    }
-    for (int it = 0; it < nkb; ++it) {
+    if (nkb > 0) setup(0);
+    // The pass it = -1 only prefetches (one copy of the register loads in the code, not two).
+    for (int it = -1; it < nkb; ++it) {
+      if (it >= 0) {
       if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) {
         ok = false;
         break;
@@ -504,6 +493,7 @@ hgemm_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restric
         k0 = 0;
         if (it + 1 < nkb) setup(pair);
       }
+      }  // it >= 0
       if (it + 1 < nkb && via_regs(pair)) {  // prefetch the next slice while this one is consumed
         load_regs(k0);
         regs_loaded = true;

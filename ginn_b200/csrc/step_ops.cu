@@ -201,6 +201,43 @@ pick_nll_backward_kernel(const T* __restrict__ smax, long long lds, const int* _
   for (int i = 4 * rows4 + lane; i < rows; i += 32) dc[i] = from_f<T>(one(i, to_f(dc[i]), to_f(sc[i])));
 }
 
+// dA = dY (.) act'(Y) in fp16, every operation rounded to fp16 as the reference's Half expressions
+// are (ginn/nonlin.h:96-106 tanh, :119-126 relu, :146-152 sigmoid): the tensor AffineNode::backward_
+// calls dpreactiv_ (ginn/node/affine.h:82-88), materialised once so that both gradient products
+// can run on the TMA-fed kernels.  dA is m x n with leading dimension m.
+__device__ __forceinline__ __half2 dact_h2(int act, __half2 y, __half2 d) {
+  const __half2 one = __float2half2_rn(1.f), zero = __float2half2_rn(0.f);
+  if (act == ACT_TANH) return __hsub2(d, __hmul2(__hmul2(y, y), d));
+  if (act == ACT_SIGMOID) return __hmul2(__hmul2(y, __hsub2(one, y)), d);
+  if (act == ACT_RELU) return __hmul2(__hgt2(y, zero), d);
+  return d;
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+dact_half_kernel(const __half* __restrict__ dy, long long lddy, const __half* __restrict__ y,
+                 long long ldy, int act, __half* __restrict__ da, int m, long long n) {
+  const long long col = blockIdx.y;
+  const int per = VEC ? 8 : 1;
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) * per;
+  if (r >= m || col >= n) return;
+  const __half* dp = dy + col * lddy + r;
+  const __half* yp = y + col * ldy + r;
+  __half* op = da + col * static_cast<long long>(m) + r;
+  if (VEC) {
+    uint4 dv = *reinterpret_cast<const uint4*>(dp);
+    const uint4 yv = *reinterpret_cast<const uint4*>(yp);
+    __half2* d2 = reinterpret_cast<__half2*>(&dv);
+    const __half2* y2 = reinterpret_cast<const __half2*>(&yv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) d2[e] = dact_h2(act, y2[e], d2[e]);
+    *reinterpret_cast<uint4*>(op) = dv;
+  } else {
+    const __half2 v = dact_h2(act, __half2half2(*yp), __half2half2(*dp));
+    *op = __low2half(v);
+  }
+}
+
 // ---- LSTM cell glue of the autobatch benchmark -------------------------------------------
 // The gates of one level arrive as one 4H x n matrix (rows i | f | g | o, the order of the
 // benchmark's shared gate weight); the cell update the reference composes from CwiseProd, Tanh
@@ -390,6 +427,20 @@ cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds,
   if (cols > 0x7fffffffLL) return cudaErrorInvalidValue;
   if (dtype == 0) pick_backward_t<float>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
   else pick_backward_t<__half>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dact_half(const void* dy, long long lddy, const void* y, long long ldy, int act,
+                             void* da, int m, long long n, cudaStream_t stream) {
+  if (m <= 0 || n <= 0) return cudaSuccess;
+  if (n > 65535) return cudaErrorInvalidValue;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const bool vec = m % 8 == 0 && lddy % 8 == 0 && ldy % 8 == 0 && al(dy) && al(y) && al(da);
+  const int per = vec ? 8 : 1;
+  dim3 grid(((m + per - 1) / per + 255) / 256, static_cast<unsigned>(n));
+  const __half *d = static_cast<const __half*>(dy), *yy = static_cast<const __half*>(y);
+  if (vec) dact_half_kernel<true><<<grid, 256, 0, stream>>>(d, lddy, yy, ldy, act, static_cast<__half*>(da), m, n);
+  else dact_half_kernel<false><<<grid, 256, 0, stream>>>(d, lddy, yy, ldy, act, static_cast<__half*>(da), m, n);
   return cudaGetLastError();
 }
 

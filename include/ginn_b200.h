@@ -83,9 +83,12 @@ typedef struct {
   int64_t lddb;
 } ginn_b200_pair_grad;
 
-/* Backward of the Affine node, with dA = dout (.) act'(out) formed on the fly inside the
- * operand loaders (no dpreactiv_ tensor is written):
+/* Backward of the Affine node, with dA = dout (.) act'(out):
  *   dbias += rowsum(dA);   db_i += A_i^T * dA;   da_i += dA * B_i^T.
+ * fp32: dA is formed on the fly inside the operand loaders (no dpreactiv_ tensor is written).
+ * fp16 with m * n >= 65536: dA is materialised once in a stream-ordered scratch allocation of the
+ * library's own (cudaMallocAsync / cudaFreeAsync on `stream`), as the reference materialises
+ * dpreactiv_, so that both products run on the TMA-fed kernels.
  * Replaces the GPU branch of AffineNode::backward_ (ginn/node/affine.h:79-87,103-125).
  * `out` is the node's value (needed for tanh/sigmoid/relu derivatives; may be NULL for
  * ACT_NONE); dbias may be NULL. */
