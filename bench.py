@@ -514,6 +514,10 @@ def run_config_workload(args):
     if args.workload == "attention_f32":
         w = wl.Attention(dev)
         metric, name = "attention_fwd_bwd_tflops", "C3 min-GPT attention via BatchedProd, fp32, 256 x (256x64x256)"
+    elif args.workload == "lstm_flat":
+        w = wl.LstmFlat(dev)
+        extra["levels"], extra["nodes"] = 1, w.nodes
+        metric, name = "autobatch_nodes_per_s", "C2 flat variant: one merged level, W 1024x384 on sum(len) gathered columns, fp32"
     elif args.workload == "lstm_autobatch":
         w = wl.LstmAutobatch(dev)
         t0 = time.perf_counter()
@@ -570,9 +574,10 @@ def run_config_workload(args):
     assert gb.device_status(local, True) == 0
     if rank == 0:
         tflops = world * w.flops / (ms * 1e-3) / 1e12
-        value = world * w.units / (ms * 1e-3) if args.workload == "lstm_autobatch" else tflops
+        per_unit = args.workload in ("lstm_autobatch", "lstm_flat")
+        value = world * w.units / (ms * 1e-3) if per_unit else tflops
         line = {"metric": metric, "value": value,
-                "unit": "nodes/s" if args.workload == "lstm_autobatch" else UNIT,
+                "unit": "nodes/s" if per_unit else UNIT,
                 "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
                 "ms_per_step": ms, "wall_ms_per_step": wall_ms, "tflops": tflops,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -597,7 +602,7 @@ def main():
     ap.add_argument("--sm-margin", type=int, default=-1,
                     help="SMs left free for NCCL while the dB product overlaps the all-reduce "
                          "(default: 0 on one GPU, 8 otherwise)")
-    ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32", "attention_f32", "lstm_autobatch", "mlp_dp", "step_ops"])
+    ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32", "attention_f32", "lstm_autobatch", "lstm_flat", "mlp_dp", "step_ops"])
     ap.add_argument("--cuda-graph", action="store_true",
                     help="lstm_autobatch: replay the level sequence from a CUDA graph")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"],
@@ -617,7 +622,7 @@ def main():
         run_affine(args)
     elif args.workload == "step_ops":
         run_step_ops(args)
-    elif args.workload in ("attention_f32", "lstm_autobatch", "mlp_dp"):
+    elif args.workload in ("attention_f32", "lstm_autobatch", "lstm_flat", "mlp_dp"):
         run_config_workload(args)
     else:
         run_gpu(args)

@@ -239,6 +239,45 @@ class LstmAutobatch:
         self.graph = g
 
 
+class LstmFlat:
+    """Config 2, flat variant: the hidden states are independent data too, so all sum(len) gate
+    Affines share one height and autobatch merges them into a single level: one grouped launch per
+    pass with sum(len) gathered columns.  Isolates the grouped kernel's throughput from the
+    latency of 40 dependent levels."""
+
+    def __init__(self, device, nseq=256, H=256, E=128, seed=20242):
+        g = torch.Generator(device=device).manual_seed(seed)
+        cpu_g = torch.Generator().manual_seed(seed)
+        lens = torch.randint(5, 41, (nseq,), generator=cpu_g)
+        self.nodes = n = int(lens.sum())
+        self.W = _xavier(4 * H, E + H, g, device)
+        self.b = _xavier(4 * H, 1, g, device).reshape(-1).contiguous()
+        self.dW = B.colmajor(4 * H, E + H, torch.float32, device, fill=0.0)
+        self.db = torch.zeros(4 * H, device=device)
+        self.XH = B.colmajor(E + H, n, torch.float32, device)
+        self.XH.copy_(torch.randn(E + H, n, device=device, generator=g))
+        self.dG = B.colmajor(4 * H, n, torch.float32, device)
+        self.dG.copy_(torch.randn(4 * H, n, device=device, generator=g))
+        self.G = B.colmajor(4 * H, n, torch.float32, device, fill=0.0)
+        self.dXH = B.colmajor(E + H, n, torch.float32, device, fill=0.0)
+        cols = lambda m: [m[:, j] for j in range(m.shape[1])]
+        x, y, dy, dx = cols(self.XH), cols(self.G), cols(self.dG), cols(self.dXH)
+        self.fwd = B.GroupedCall(GROUPED_FORWARD, [B.Group(w=self.W, x_cols=x, y_cols=y, bias=self.b)])
+        self.dx = B.GroupedCall(GROUPED_DX, [B.Group(w=self.W, y_cols=dy, dx_cols=dx)])
+        self.dw = B.GroupedCall(GROUPED_DW, [B.Group(w=self.W, x_cols=x, y_cols=dy, dw=self.dW,
+                                                     dbias=self.db)])
+        self.flops = 3 * 2 * 4 * H * (E + H) * n
+        self.units = n
+
+    def step(self):
+        self.dW.zero_()
+        self.db.zero_()
+        self.dXH.zero_()
+        self.fwd()
+        self.dx()
+        self.dw()
+
+
 class MlpDataParallel:
     """Config 5: Affine+ReLU 784 -> 1024 -> 1024 -> 10, softmax cross-entropy summed over the
     batch, Adam (lr 1e-3, per-element clip 5, eps 1e-8, betas 0.9/0.999: ginn/update/update.h:
