@@ -85,23 +85,6 @@ __device__ __forceinline__ uint4 apply_dact(uint4 d, uint4 y, int dact) {
   return d;
 }
 
-// Forward nonlinearity for fp16 outputs: hardware approximations (relative error about 2^-11,
-// below the rounding of the fp16 result) keep the epilogue a few instructions per element.
-__device__ __forceinline__ float act_forward_half(int act, float x) {
-  if (act == ACT_TANH) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-  }
-  if (act == ACT_SIGMOID) {
-    const float e = __expf(-fabsf(x));
-    const float r = __fdividef(1.f, 1.f + e);
-    return x > 0.f ? r : e * r;
-  }
-  if (act == ACT_RELU) return fmaxf(x, 0.f);
-  return x;
-}
-
 // A piece whose source is not 16-byte aligned: 4-byte asynchronous copies, or through registers
 // when even those are impossible.
 __device__ __noinline__ void copy_piece_slow(uint32_t d, const __half* p, int valid, const void* safe) {

@@ -98,6 +98,9 @@ cudaError_t launch_softmax_backward(int dtype, const void* y, long long ldy, con
 cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds, const int* index,
                                      const void* grad, void* dx, long long lddx, int rows,
                                      long long cols, cudaStream_t stream);
+// y = act(y + bias) in place, fp16, n <= 65535.
+cudaError_t launch_bias_act_half(void* y, long long ldy, const void* bias, int act, int m,
+                                 long long n, cudaStream_t stream);
 // da (m x n, leading dimension m) = dy (.) act'(y), fp16, n <= 65535.
 cudaError_t launch_dact_half(const void* dy, long long lddy, const void* y, long long ldy, int act,
                              void* da, int m, long long n, cudaStream_t stream);

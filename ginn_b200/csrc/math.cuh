@@ -55,6 +55,23 @@ __device__ __forceinline__ float act_backward(int act, float y, float dy) {
   }
 }
 
+// Forward nonlinearity for fp16 outputs: hardware approximations (relative error about 2^-11,
+// below the rounding of the fp16 result) keep the epilogue a few instructions per element.
+__device__ __forceinline__ float act_forward_half(int act, float x) {
+  if (act == ACT_TANH) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  if (act == ACT_SIGMOID) {
+    const float e = __expf(-fabsf(x));
+    const float r = __fdividef(1.f, 1.f + e);
+    return x > 0.f ? r : e * r;
+  }
+  if (act == ACT_RELU) return fmaxf(x, 0.f);
+  return x;
+}
+
 // hi = x rounded to TF32 (nearest, ties away from zero, what cvt.rna.tf32 gives); lo = x - hi
 // (exact in fp32; the tensor core keeps the top 11 significant bits of it).  The rounding is
 // done on the bit pattern with two integer instructions (add half an ulp of the 10-bit mantissa

@@ -238,6 +238,35 @@ dact_half_kernel(const __half* __restrict__ dy, long long lddy, const __half* __
   }
 }
 
+// Y = act(Y + bias) in place, fp16 (bias per row, broadcast over columns): the epilogue of a large
+// Half Affine whose product ran on a TMA-fed kernel that has no fused epilogue of its own.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+bias_act_half_kernel(__half* __restrict__ y, long long ldy, const __half* __restrict__ bias, int act,
+                     int m, long long n) {
+  const long long col = blockIdx.y;
+  const int per = VEC ? 8 : 1;
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) * per;
+  if (r >= m || col >= n) return;
+  __half* yp = y + col * ldy + r;
+  if (VEC) {
+    uint4 v = *reinterpret_cast<const uint4*>(yp);
+    uint4 bv = make_uint4(0, 0, 0, 0);
+    if (bias) bv = *reinterpret_cast<const uint4*>(bias + r);
+    __half2* v2 = reinterpret_cast<__half2*>(&v);
+    const __half2* b2 = reinterpret_cast<const __half2*>(&bv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __half22float2(v2[e]), b = __half22float2(b2[e]);
+      v2[e] = __floats2half2_rn(act_forward_half(act, x.x + b.x), act_forward_half(act, x.y + b.y));
+    }
+    *reinterpret_cast<uint4*>(yp) = v;
+  } else {
+    const float b = bias ? __half2float(bias[r]) : 0.f;
+    *yp = __float2half_rn(act_forward_half(act, __half2float(*yp) + b));
+  }
+}
+
 // ---- LSTM cell glue of the autobatch benchmark -------------------------------------------
 // The gates of one level arrive as one 4H x n matrix (rows i | f | g | o, the order of the
 // benchmark's shared gate weight); the cell update the reference composes from CwiseProd, Tanh
@@ -427,6 +456,19 @@ cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds,
   if (cols > 0x7fffffffLL) return cudaErrorInvalidValue;
   if (dtype == 0) pick_backward_t<float>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
   else pick_backward_t<__half>(smax, lds, index, grad, dx, lddx, rows, cols, stream);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bias_act_half(void* y, long long ldy, const void* bias, int act, int m,
+                                 long long n, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || (bias == nullptr && act == ACT_NONE)) return cudaSuccess;
+  if (n > 65535) return cudaErrorInvalidValue;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const bool vec = m % 8 == 0 && ldy % 8 == 0 && al(y) && (bias == nullptr || al(bias));
+  const int per = vec ? 8 : 1;
+  dim3 grid(((m + per - 1) / per + 255) / 256, static_cast<unsigned>(n));
+  if (vec) bias_act_half_kernel<true><<<grid, 256, 0, stream>>>(static_cast<__half*>(y), ldy, static_cast<const __half*>(bias), act, m, n);
+  else bias_act_half_kernel<false><<<grid, 256, 0, stream>>>(static_cast<__half*>(y), ldy, static_cast<const __half*>(bias), act, m, n);
   return cudaGetLastError();
 }
 
