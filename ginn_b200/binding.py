@@ -73,6 +73,8 @@ def lib():
     L.ginn_b200_grouped.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
     L.ginn_b200_grouped_static.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
     L.ginn_b200_grouped_static.restype = ci
+    L.ginn_b200_grouped_static_status.argtypes = [ci, ci]
+    L.ginn_b200_grouped_static_status.restype = ci
     L.ginn_b200_level_create.argtypes = [ci, ci, ci, ci, C.POINTER(_Group), C.POINTER(vp)]
     L.ginn_b200_level_run.argtypes = [vp, vp]
     L.ginn_b200_level_destroy.argtypes = [vp]
@@ -400,6 +402,11 @@ def adam_update(w: torch.Tensor, d: torch.Tensor, m: torch.Tensor, v: torch.Tens
 
 def device_status(device: int = 0, reset: bool = True) -> int:
     return lib().ginn_b200_device_status(device, int(reset))
+
+
+def grouped_static_status(device: int = 0, reset: bool = True) -> int:
+    """Status word of the kernels launched through `grouped_static` (0 = healthy)."""
+    return lib().ginn_b200_grouped_static_status(device, int(reset))
 
 
 def set_option(name: str, value: int) -> None:

@@ -18,8 +18,12 @@ using gb::Problem;
 
 thread_local std::string t_error;
 std::atomic<long long> g_launches{0};
-std::atomic<int> g_force_path{0};
-std::atomic<int> g_sm_margin{0};  // SMs the persistent kernels leave free (e.g. for NCCL)
+// Options set through ginn_b200_set_option belong to the calling host thread (ginn's model is
+// one thread per GPU, or several threads that share one): a margin set by the thread that
+// overlaps a collective with a product does not slow the products of another thread.
+thread_local int t_force_path = 0;
+thread_local int t_sm_margin = 0;     // SMs the persistent kernels leave free (e.g. for NCCL)
+thread_local int t_pair_group_m = 0;  // rasterisation group of the CTA-pair kernel (0 = default)
 
 int fail(int status, const char* fmt, ...) {
   char buf[512];
@@ -41,19 +45,27 @@ int fail(int status, const char* fmt, ...) {
 
 constexpr int kMaxDevices = 64;
 constexpr size_t kStageBytes = 8u << 20;
-constexpr unsigned kCounters = 64;  // launches in flight at once that need their own counter
+constexpr unsigned kCounters = 64;  // tile queues (two ints each) handed out round robin
 
 struct DevCtx {
   std::mutex mu;
   bool ready = false;
   int num_sms = 0;
   int* d_status = nullptr;
-  int* d_counters = nullptr;     // tile-queue counters of the persistent fp16 kernel, round robin
+  int* d_counters = nullptr;     // tile queues of the CTA-pair kernel: zero between launches
   unsigned next_counter = 0;
-  // staging ring for grouped launches (problem descriptors + pointer tables)
+  // Staging ring for grouped launches (problem descriptors + pointer tables), used in two
+  // halves.  A half is reused only after the launches that read it have finished: every stream
+  // that used a half leaves an event behind, and the host waits for those before it writes
+  // into that half again.
   unsigned char* h_stage = nullptr;
   unsigned char* d_stage = nullptr;
   size_t stage_off = 0;
+  struct StageUser {
+    cudaStream_t stream;
+    cudaEvent_t done;
+  };
+  std::vector<StageUser> stage_users[2];
 };
 DevCtx g_ctx[kMaxDevices];
 
@@ -73,8 +85,8 @@ int get_ctx(int device, DevCtx** out) {
     CU_TRY(cudaDeviceGetAttribute(&c.num_sms, cudaDevAttrMultiProcessorCount, device));
     CU_TRY(cudaMalloc(&c.d_status, sizeof(int)));
     CU_TRY(cudaMemset(c.d_status, 0, sizeof(int)));
-    CU_TRY(cudaMalloc(&c.d_counters, kCounters * sizeof(int)));
-    CU_TRY(cudaMemset(c.d_counters, 0, kCounters * sizeof(int)));
+    CU_TRY(cudaMalloc(&c.d_counters, 2 * kCounters * sizeof(int)));
+    CU_TRY(cudaMemset(c.d_counters, 0, 2 * kCounters * sizeof(int)));
     c.ready = true;
   }
   *out = &c;
@@ -106,25 +118,25 @@ Operand make_operand(int dtype, const void* base, long long ld, long long batch_
 
 // SMs a persistent kernel may occupy: all of them minus the margin the host asked to keep free.
 int persistent_sms(const DevCtx* ctx) {
-  const int n = ctx->num_sms - g_sm_margin.load();
+  const int n = ctx->num_sms - t_sm_margin;
   return n < 2 ? 2 : n;
 }
 
-enum Path { PATH_AUTO = 0, PATH_STAGED = 1, PATH_TMA = 2, PATH_SMALL = 3, PATH_PAIR = 4, PATH_GATHER = 5 };
+// Value 1 named a kernel that no longer exists.
+enum Path { PATH_AUTO = 0, PATH_TMA = 2, PATH_SMALL = 3, PATH_PAIR = 4, PATH_GATHER = 5 };
 
-// Runs one Problem on the staged tcgen05 kernel or the CUDA-core kernel.
+// Runs one Problem on a tensor-core kernel or the CUDA-core kernel.
 int run_problem_once(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
   if (p.M <= 0 || p.N <= 0 || p.batches <= 0) return GINN_B200_OK;
   long long ktot = 0;
   for (int i = 0; i < p.npairs; ++i) ktot += p.k[i];
-  const int force = g_force_path.load();
+  const int force = t_force_path;
   bool small = (static_cast<long long>(p.M) * p.N <= 16) || ktot == 0;
   if (force == PATH_SMALL) small = true;
-  if (force == PATH_STAGED && ktot > 0) small = false;
   if (p.rowsum != nullptr && ktot > 0) small = false;
   if (small) {
     CU_TRY(gb::launch_small(dtype, p, stream));
-  } else if (dtype == GINN_B200_F32 && force != PATH_STAGED &&
+  } else if (dtype == GINN_B200_F32 &&
              (gb::sgemm3x_supported(p) || gb::sgemm3x_gather_supported(p))) {
     const long long tiles = static_cast<long long>((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batches;
     p.split_k = gb::sgemm3x_pick_split(p, tiles, ctx->num_sms);
@@ -132,11 +144,12 @@ int run_problem_once(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
       CU_TRY(gb::launch_sgemm3x(p, stream, ctx->d_status));
     else
       CU_TRY(gb::launch_sgemm3x_gather(p, stream, ctx->d_status));
-  } else if (dtype == GINN_B200_F16 && force != PATH_STAGED && gb::hgemm_gather_supported(p)) {
+  } else if (dtype == GINN_B200_F16 && gb::hgemm_gather_supported(p)) {
     CU_TRY(gb::launch_hgemm_gather(p, stream, ctx->d_status));
   } else {
-    const int bn = gb::staged_pick_bn(dtype, p.M, p.N, p.batches, ctx->num_sms);
-    CU_TRY(gb::launch_staged(dtype, p, bn, stream, ctx->d_status));
+    // Not reachable through the entry points of this file: they build one pair per gradient
+    // product and hang the bias gradient on an outer-contiguous operand.
+    return fail(GINN_B200_UNSUPPORTED, "no kernel takes this combination of operands");
   }
   g_launches.fetch_add(1);
   return GINN_B200_OK;
@@ -189,12 +202,12 @@ int try_skinny(int dtype, Problem& p, cudaStream_t stream, bool* done) {
 }
 
 int run_problem(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
-  if (g_force_path.load() == PATH_AUTO) {
+  if (t_force_path == PATH_AUTO) {
     bool done = false;
     if (int s = try_skinny(dtype, p, stream, &done)) return s;
     if (done) return GINN_B200_OK;
   }
-  bool chain = dtype == GINN_B200_F32 && g_force_path.load() != PATH_SMALL;
+  bool chain = dtype == GINN_B200_F32 && t_force_path != PATH_SMALL;
   long long kmax = 0, ktot = 0;
   for (int i = 0; i < p.npairs; ++i) {
     kmax = p.k[i] > kmax ? p.k[i] : kmax;
@@ -265,7 +278,7 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
   DevCtx* ctx;
   if (int s = get_ctx(device, &ctx)) return s;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const int force = g_force_path.load();
+  const int force = t_force_path;
 
   if (dtype == GINN_B200_F16 && k > 0 &&
       (force == PATH_AUTO || force == PATH_TMA || force == PATH_PAIR)) {
@@ -288,9 +301,10 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
       int* counter;
       {
         std::lock_guard<std::mutex> g(ctx->mu);
-        counter = ctx->d_counters + (ctx->next_counter++ % kCounters);
+        counter = ctx->d_counters + 2 * (ctx->next_counter++ % kCounters);
       }
-      CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), counter, stream, ctx->d_status));
+      CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), t_pair_group_m, counter, stream,
+                                   ctx->d_status));
       g_launches.fetch_add(1);
       return GINN_B200_OK;
     }
@@ -314,25 +328,62 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
   return run_problem(ctx, dtype, p, stream);
 }
 
-// Reserves `bytes` in the staging ring; returns host and device addresses of the slot.
-int stage_alloc(DevCtx* ctx, size_t bytes, unsigned char** h, unsigned char** d) {
+// Reserves `bytes` in the staging ring for a launch on `stream`; returns host and device
+// addresses of the slot.  Call stage_mark after the launch has been queued.
+int stage_alloc(DevCtx* ctx, size_t bytes, cudaStream_t stream, unsigned char** h,
+                unsigned char** d, int* half_out) {
   bytes = (bytes + 255) & ~size_t(255);
-  if (bytes > kStageBytes)
+  constexpr size_t kHalf = kStageBytes / 2;
+  if (bytes > kHalf)
     return fail(GINN_B200_BAD_ARGUMENT, "grouped launch needs %zu staging bytes (limit %zu)",
-                bytes, kStageBytes);
+                bytes, kHalf);
   std::lock_guard<std::mutex> g(ctx->mu);
   if (!ctx->h_stage) {
     CU_TRY(cudaMallocHost(&ctx->h_stage, kStageBytes));
     CU_TRY(cudaMalloc(&ctx->d_stage, kStageBytes));
   }
-  if (ctx->stage_off + bytes > kStageBytes) {
-    // Wrapping: earlier launches may still be reading their slots.
-    CU_TRY(cudaDeviceSynchronize());
-    ctx->stage_off = 0;
+  int half = ctx->stage_off < kHalf ? 0 : 1;
+  if (ctx->stage_off + bytes > static_cast<size_t>(half + 1) * kHalf) {
+    // Moving on to the other half: the launches that read it last time round must be done.
+    // The host waits for their events only -- other work on the device is left alone.
+    half ^= 1;
+    for (const DevCtx::StageUser& u : ctx->stage_users[half]) CU_TRY(cudaEventSynchronize(u.done));
+    ctx->stage_off = half * kHalf;
   }
   *h = ctx->h_stage + ctx->stage_off;
   *d = ctx->d_stage + ctx->stage_off;
+  *half_out = half;
   ctx->stage_off += bytes;
+  (void)stream;
+  return GINN_B200_OK;
+}
+
+// Leaves (or moves) the event that tells when `stream` is done with `half` of the ring.
+int stage_mark(DevCtx* ctx, int half, cudaStream_t stream) {
+  std::lock_guard<std::mutex> g(ctx->mu);
+  for (DevCtx::StageUser& u : ctx->stage_users[half])
+    if (u.stream == stream) {
+      CU_TRY(cudaEventRecord(u.done, stream));
+      return GINN_B200_OK;
+    }
+  cudaEvent_t ev;
+  CU_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  CU_TRY(cudaEventRecord(ev, stream));
+  ctx->stage_users[half].push_back({stream, ev});
+  return GINN_B200_OK;
+}
+
+// Entry points that copy descriptors from a host buffer they reuse cannot be recorded into a
+// CUDA graph: a replay would copy whatever the buffer holds by then.
+int refuse_capture(cudaStream_t stream, const char* who) {
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  CU_TRY(cudaStreamIsCapturing(stream, &cs));
+  if (cs != cudaStreamCaptureStatusNone)
+    return fail(GINN_B200_UNSUPPORTED,
+                "%s was called on a stream that is being captured; its descriptors are copied "
+                "from a host buffer that later calls overwrite.  Prepare the level with "
+                "ginn_b200_level_create and capture ginn_b200_level_run instead",
+                who);
   return GINN_B200_OK;
 }
 
@@ -345,8 +396,7 @@ struct LevelPlan {
   long long max_n = 0, sum_tiles128 = 0;
 };
 struct LevelLaunch {
-  int nprobs = 0, tiles = 0, bn = 128;
-  bool use_gather = false;
+  int nprobs = 0, tiles = 0;
 };
 
 int plan_level(int dtype, int mode, int ngroups, const ginn_b200_group* groups, LevelPlan* plan) {
@@ -388,12 +438,7 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
                              unsigned char* d) {
   LevelLaunch ll;
   // Levels run on the gather kernels (128 x 128 tiles): the cp.async front end of the 3xTF32
-  // kernel for fp32, the cp.async fp16 kernel for Half; the staged kernel only when forced.
-  ll.use_gather = g_force_path.load() != PATH_STAGED;
-  if (!ll.use_gather) {
-    if (plan.max_n <= 32) ll.bn = 32;
-    else if (plan.max_n <= 64 || plan.sum_tiles128 < num_sms) ll.bn = 64;
-  }
+  // kernel for fp32, the cp.async fp16 kernel for Half.
   Problem* hp = reinterpret_cast<Problem*>(h);
   size_t off = plan.desc_bytes;
   for (int g = 0; g < ngroups; ++g) {
@@ -456,9 +501,9 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
       p.accumulate = 1;
     }
     p.tiles_m = (p.M + 127) / 128;
-    p.tiles_n = (p.N + ll.bn - 1) / ll.bn;
+    p.tiles_n = (p.N + 127) / 128;
     p.tile_start = ll.tiles;
-    if (ll.use_gather && dtype == GINN_B200_F32)
+    if (dtype == GINN_B200_F32)
       p.split_k = gb::sgemm3x_pick_split(p, plan.sum_tiles128, num_sms);
     ll.tiles += p.tiles_m * p.tiles_n * (p.split_k > 1 ? p.split_k : 1);
     ++ll.nprobs;
@@ -468,11 +513,9 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
 
 cudaError_t launch_level(int dtype, const LevelLaunch& ll, const Problem* dprobs,
                          cudaStream_t stream, int* status) {
-  if (ll.use_gather && dtype == GINN_B200_F32)
+  if (dtype == GINN_B200_F32)
     return gb::launch_sgemm3x_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
-  if (ll.use_gather)
-    return gb::launch_hgemm_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
-  return gb::launch_staged_grouped(dtype, dprobs, ll.nprobs, ll.tiles, ll.bn, stream, status);
+  return gb::launch_hgemm_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
 }
 
 }  // namespace
@@ -530,7 +573,7 @@ int ginn_b200_affine_forward(int device, void* stream_, int dtype, int npairs,
   // the others accumulate), then one elementwise pass for bias and activation -- 16 + 4 us
   // against 29 us for the fused cp.async kernel on a 1024 x 1024 layer with 4096 columns.  The
   // product is rounded to fp16 before the nonlinearity, as the reference's is.
-  if (dtype == GINN_B200_F16 && g_force_path.load() == PATH_AUTO && np > 0 && m > 16 && n > 16 &&
+  if (dtype == GINN_B200_F16 && t_force_path == PATH_AUTO && np > 0 && m > 16 && n > 16 &&
       n <= 65535) {
     bool tma = true;
     for (int i = 0; i < np && tma; ++i) {
@@ -583,7 +626,7 @@ int ginn_b200_affine_backward(int device, void* stream_, int dtype, int npairs,
   // once per output tile that reads the element and keeps those products on the register path
   // of the general kernel: 82 + 239 us against about 90 us for a 1024 x 1024 layer on 4096
   // columns.  The scratch is a stream-ordered allocation of the library's own.
-  if (dtype == GINN_B200_F16 && g_force_path.load() == PATH_AUTO && m * n >= 65536 && n <= 65535) {
+  if (dtype == GINN_B200_F16 && t_force_path == PATH_AUTO && m * n >= 65536 && n <= 65535) {
     void* scratch = nullptr;
     const void* dA = dout;
     int64_t ldA = lddout;
@@ -680,19 +723,21 @@ int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroup
   DevCtx* ctx;
   if (int s = get_ctx(device, &ctx)) return s;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int s = refuse_capture(stream, "ginn_b200_grouped")) return s;
   unsigned char *h, *d;
-  if (int s = stage_alloc(ctx, plan.bytes, &h, &d)) return s;
+  int half = 0;
+  if (int s = stage_alloc(ctx, plan.bytes, stream, &h, &d, &half)) return s;
   LevelLaunch ll = fill_level_image(dtype, mode, ngroups, groups, plan, ctx->num_sms, h, d);
   CU_TRY(cudaMemcpyAsync(d, h, plan.bytes, cudaMemcpyHostToDevice, stream));
   CU_TRY(launch_level(dtype, ll, reinterpret_cast<const Problem*>(d), stream, ctx->d_status));
   g_launches.fetch_add(1);
-  return GINN_B200_OK;
+  return stage_mark(ctx, half, stream);
 }
 
 // Same work as ginn_b200_grouped, for callers that may not allocate (see include/ginn_b200.h).
 // Nothing here calls cudaMalloc, cudaMallocHost, cudaFree or any allocating library routine:
 // the device-side descriptors go into a fixed array inside the library image
-// (gemm_staged.cu), the host-side image is assembled in a fixed buffer below.
+// (grouped_static.cu), the host-side image is assembled in a fixed buffer below.
 int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int ngroups,
                              const ginn_b200_group* groups) {
   static std::mutex image_mu;
@@ -714,13 +759,18 @@ int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int
                 "and column tables, limit %zu (%d groups, 16 bytes per column); split the level "
                 "or use ginn_b200_grouped",
                 plan.bytes, gb::kGroupedStaticBytes, plan.live);
+  // The host image below is one buffer shared by all calls: a captured copy would read it at
+  // replay time, after later calls have overwritten it.
+  if (int s = refuse_capture(static_cast<cudaStream_t>(stream_), "ginn_b200_grouped_static"))
+    return s;
   void* scratch = nullptr;
-  CU_TRY(gb::grouped_static_scratch(device, &scratch));
+  int* status = nullptr;
+  CU_TRY(gb::grouped_static_scratch(device, &scratch, &status));
   std::lock_guard<std::mutex> lock(image_mu);
   LevelLaunch ll = fill_level_image(dtype, mode, ngroups, groups, plan, num_sms, image,
                                     static_cast<unsigned char*>(scratch));
-  CU_TRY(gb::launch_staged_grouped_static(dtype, image, plan.bytes, scratch, ll.nprobs, ll.tiles,
-                                          ll.bn, ll.use_gather, static_cast<cudaStream_t>(stream_)));
+  CU_TRY(gb::launch_grouped_static(dtype, image, plan.bytes, scratch, status, ll.nprobs, ll.tiles,
+                                   static_cast<cudaStream_t>(stream_)));
   g_launches.fetch_add(1);
   return GINN_B200_OK;
 }
@@ -789,7 +839,24 @@ int ginn_b200_device_status(int device, int reset) {
   int v = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
   if (cudaMemcpy(&v, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (reset && v != 0) cudaMemset(ctx->d_status, 0, sizeof(int));
+  if (reset && v != 0) {
+    cudaMemset(ctx->d_status, 0, sizeof(int));
+    // a kernel that gave up may have left its tile queue half used
+    cudaMemset(ctx->d_counters, 0, 2 * kCounters * sizeof(int));
+  }
+  return v;
+}
+
+int ginn_b200_grouped_static_status(int device, int reset) {
+  if (device < 0 || device >= kMaxDevices) return -1;
+  if (cudaSetDevice(device) != cudaSuccess) return -1;
+  void* scratch = nullptr;
+  int* status = nullptr;
+  if (gb::grouped_static_scratch(device, &scratch, &status) != cudaSuccess) return -1;
+  int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpy(&v, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (reset && v != 0) cudaMemset(status, 0, sizeof(int));
   return v;
 }
 
@@ -947,18 +1014,19 @@ int ginn_b200_version(void) { return 100; }
 
 int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "force_path") == 0) {
-    if (value < 0 || value > 5) return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0..5");
-    g_force_path.store(value);
+    if (value < 0 || value > 5 || value == 1)
+      return fail(GINN_B200_BAD_ARGUMENT, "force_path must be 0, 2, 3, 4 or 5");
+    t_force_path = value;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "pair_group_m") == 0) {
     if (value < 0 || value > 1024) return fail(GINN_B200_BAD_ARGUMENT, "pair_group_m must be 0..1024");
-    gb::g_pair_group_m = value;
+    t_pair_group_m = value;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "sm_margin") == 0) {
     if (value < 0 || value > 128) return fail(GINN_B200_BAD_ARGUMENT, "sm_margin must be 0..128");
-    g_sm_margin.store(value);
+    t_sm_margin = value;
     return GINN_B200_OK;
   }
   return fail(GINN_B200_UNSUPPORTED, "unknown option '%s'", name ? name : "(null)");

@@ -33,9 +33,10 @@ constexpr int PEPI_PITCH = 36;
 constexpr int PEPI_WARP_BYTES = 32 * PEPI_PITCH * 4;
 constexpr int PEPI_BYTES = 4 * PEPI_WARP_BYTES;
 // Ring through which the even CTA's producer announces tile numbers to every other role of the
-// pair.  Depth: the producer is never more than three tiles ahead of the slowest reader (the
-// six-stage ring holds less than one tile, the MMA warp runs at most two accumulators ahead
-// of the epilogues), so eight slots cannot be overrun.
+// pair.  Depth: with at least two k-blocks per tile (K > 64, which hgemm_pair_supported requires)
+// the six-stage ring holds at most three tiles, and the MMA warp runs at most two accumulators
+// ahead of the epilogues, so the producer is never more than five tiles ahead of the slowest
+// reader and eight slots cannot be overrun.
 constexpr int PSCHED = 8;
 
 struct PParams {
@@ -47,9 +48,11 @@ struct PParams {
   int tiles_m, tiles_n, total_tiles;
   int group_m;  // m-tiles per rasterisation group (L2 reuse of the A rows across waves)
   // Work queue: tiles [0, #pairs) are taken statically, every further tile is claimed with an
-  // atomic add on *counter (zeroed before the launch).  A pair that starts late -- because
-  // another kernel, e.g. an NCCL collective, holds its SMs for a while -- then simply finds
-  // fewer tiles left instead of delaying the end of the launch.
+  // atomic add on counter[0].  A pair that starts late -- because another kernel, e.g. an NCCL
+  // collective, holds its SMs for a while -- then simply finds fewer tiles left instead of
+  // delaying the end of the launch.  counter[1] counts the pairs that have finished; the last
+  // one puts both words back to zero, so the next launch needs no memset of its own (a memset
+  // queued on another stream could otherwise clear the counter of a launch that is running).
   int* counter;
 };
 
@@ -319,6 +322,16 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tc_fence_after();
     tmem_dealloc_pair(tmem, 512);
   }
+  // This pair has made its last claim (the even CTA's producer left its loop before the
+  // barriers above).  The last pair to get here re-arms the queue for the next launch.
+  if (rank == 0 && threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.counter + 1, 1) == nclusters - 1) {
+      p.counter[0] = 0;
+      p.counter[1] = 0;
+      __threadfence();
+    }
+  }
 }
 
 template <int A_MN, int B_MN>
@@ -353,17 +366,17 @@ cudaError_t launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, co
 
 }  // namespace
 
-int g_pair_group_m = 0;  // tuning knob (0 = default)
-
 bool hgemm_pair_supported(const HgemmArgs& a) {
   if (!hgemm_tma_supported(a)) return false;
+  // At least two k-blocks per tile: the tile-announcement ring's depth is sized for that.
+  if (a.K <= PBK) return false;
   // 16-byte accesses to C keep the two epilogues cheap; fall back to the one-CTA kernel otherwise.
   return (reinterpret_cast<uintptr_t>(a.C) & 15u) == 0 && a.ldc % 8 == 0 &&
          (a.batches == 1 || a.strideC % 8 == 0);
 }
 
-cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int* counter, cudaStream_t stream,
-                              int* status) {
+cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int* counter,
+                              cudaStream_t stream, int* status) {
   const unsigned long long a_rows = a.transA ? a.K : a.M, a_cols = a.transA ? a.M : a.K;
   const unsigned long long b_rows = a.transB ? a.N : a.K, b_cols = a.transB ? a.K : a.N;
   const unsigned long long sa = a.batches > 1 ? a.strideA : a.lda * a_cols;
@@ -386,10 +399,8 @@ cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int* counter, cud
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batches;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   p.total_tiles = static_cast<int>(total);
-  p.group_m = g_pair_group_m > 0 ? g_pair_group_m : 8;
+  p.group_m = group_m > 0 ? group_m : 8;
   p.counter = counter;
-  cudaError_t ce = cudaMemsetAsync(counter, 0, sizeof(int), stream);
-  if (ce != cudaSuccess) return ce;
   if (!a.transA && !a.transB) return launch_pair_variant<1, 0>(ta, tb, p, num_sms, stream, status);
   if (a.transA && !a.transB) return launch_pair_variant<0, 0>(ta, tb, p, num_sms, stream, status);
   return launch_pair_variant<1, 1>(ta, tb, p, num_sms, stream, status);

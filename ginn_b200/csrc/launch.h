@@ -9,18 +9,12 @@ struct CUtensorMap_st;  // CUDA driver tensor-map descriptor (cuda.h)
 
 namespace gb {
 
-// --- staged tcgen05 kernel (gemm_staged.cu); dtype 0 = fp32 (3xTF32), 1 = fp16 ---
-int staged_pick_bn(int dtype, long long M, long long N, long long batches, int num_sms);
-cudaError_t launch_staged(int dtype, Problem& p, int bn, cudaStream_t stream, int* status);
-cudaError_t launch_staged_grouped(int dtype, const Problem* dprobs, int nprobs, int total_tiles,
-                                  int bn, cudaStream_t stream, int* status);
-
-// Allocation-free grouped launch: descriptors live in a fixed array inside the library image.
+// Allocation-free grouped launch (grouped_static.cu): descriptors live in a fixed array inside
+// the library image, and so does the status word its kernels report to.
 constexpr size_t kGroupedStaticBytes = 256 * 1024;
-cudaError_t grouped_static_scratch(int device, void** ptr);
-cudaError_t launch_staged_grouped_static(int dtype, const void* host_image, size_t bytes,
-                                         void* scratch, int nprobs, int total_tiles, int bn,
-                                         bool fp32_gather, cudaStream_t stream);
+cudaError_t grouped_static_scratch(int device, void** scratch, int** status);
+cudaError_t launch_grouped_static(int dtype, const void* host_image, size_t bytes, void* scratch,
+                                  int* status, int nprobs, int total_tiles, cudaStream_t stream);
 
 // --- TMA-fed persistent fp16 kernel (hgemm_tma.cu) ---
 struct HgemmArgs {
@@ -38,12 +32,12 @@ bool hgemm_tma_supported(const HgemmArgs& a);
 cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t stream, int* status);
 
 // --- fp16 kernel on CTA pairs, 256 x 256 tiles (hgemm_pair.cu) ---
-extern int g_pair_group_m;
 bool hgemm_pair_supported(const HgemmArgs& a);
-// `counter`: one int of device memory for the launch's tile queue (zeroed by the launcher on
-// `stream`); launches that may overlap on the GPU need different counters.
-cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int* counter, cudaStream_t stream,
-                              int* status);
+// `counter`: two ints of device memory for the launch's tile queue, zero when the kernel starts;
+// the kernel leaves them zero again.  Launches that may run at the same time need different
+// counters.  group_m: m-tiles per rasterisation group (0 = default).
+cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int* counter,
+                              cudaStream_t stream, int* status);
 
 // --- general fp16 kernel with a cp.async front end (hgemm_gather.cu) ---
 bool hgemm_gather_supported(const Problem& p);

@@ -224,6 +224,7 @@ class LstmAutobatch:
         """Records one forward + reset_grad + backward pass (prepared levels and glue) into a CUDA
         graph; later steps replay it.  The prepared levels make no host-to-device copies, so
         the capture holds only kernel launches."""
+        assert not self.static, "the allocation-free grouped entry point refuses stream capture"
         self.graph = None
         side = torch.cuda.Stream(device=self.W.device)
         side.wait_stream(torch.cuda.current_stream())

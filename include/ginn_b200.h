@@ -2,9 +2,11 @@
  *
  * All matrices are column-major, as in ginn (ginn/tensor.h).  Pointers are device pointers on
  * GPU `device`; `stream` is a cudaStream_t (NULL = legacy default stream).  Calls enqueue work
- * and return; they never synchronise and never allocate from a ginn Device (the library keeps
- * small internal buffers of its own).  Every function returns a ginn_b200_status; on a non-zero
- * status ginn_b200_last_error() describes the failure for the calling thread.
+ * and return; they never synchronise the device and never allocate from a ginn Device (the
+ * library keeps small internal buffers of its own).  The one host-side wait: ginn_b200_grouped
+ * recycles an 8 MiB descriptor ring in halves and, before it reuses a half, waits for its own
+ * earlier launches that read that half.  Every function returns a ginn_b200_status; on a
+ * non-zero status ginn_b200_last_error() describes the failure for the calling thread.
  *
  * dtype: GINN_B200_F32 computes with three TF32 tensor-core products per term (fp32-level
  * accuracy, fp32 accumulation); GINN_B200_F16 uses fp16 inputs/outputs with fp32 accumulation.
@@ -124,7 +126,10 @@ typedef enum {
   GINN_B200_GROUPED_DW = 2       /* dW  += sum_j dy_j x_j^T, dbias += sum_j dy_j */
 } ginn_b200_grouped_mode;
 
-/* All groups of one autobatch level in ONE launch (device-side tile table lookup). */
+/* All groups of one autobatch level in ONE launch (device-side tile table lookup).
+ * The descriptors travel through a host ring that later calls reuse, so the call refuses
+ * (GINN_B200_UNSUPPORTED) a stream that is being captured into a CUDA graph; prepared levels
+ * (ginn_b200_level_*) are the form to capture. */
 int ginn_b200_grouped(int device, void* stream, int dtype, int mode, int ngroups,
                       const ginn_b200_group* groups);
 
@@ -144,14 +149,21 @@ int ginn_b200_grouped(int device, void* stream, int dtype, int mode, int ngroups
  * and 16 bytes per column, e.g. 32 groups with 15000 columns in total.  Larger levels are
  * refused with GINN_B200_BAD_ARGUMENT; split them or use ginn_b200_grouped.
  * The first call on each device looks up the array's device address; make that first call
- * outside any stream capture.  Because the descriptors are copied from ordinary host memory,
- * the call may wait for work already queued on `stream`.  All calls on a GPU share the one
- * array, and it keeps what the last call wrote; the part a call uses is rewritten in full, so
- * nothing has to be cleared, but two calls whose GPU work overlaps (different streams without
- * an event between them) would corrupt each other -- keep these calls on one stream.  A kernel
- * that gives up on a bounded wait is not recorded in the device status word by this variant. */
+ * outside any stream capture.  Every call copies its descriptors from one host buffer that the
+ * next call overwrites, so a call on a stream that is being captured is refused with
+ * GINN_B200_UNSUPPORTED.  Because that buffer is ordinary host memory, the call may wait for
+ * work already queued on `stream`.  All calls on a GPU share the one array, and it keeps what
+ * the last call wrote; the part a call uses is rewritten in full, so nothing has to be
+ * cleared, but two calls whose GPU work overlaps (different streams without an event between
+ * them) would corrupt each other -- keep these calls on one stream.  A kernel that gives up on
+ * a bounded wait records it in a status word that also lives inside the library image; read
+ * it with ginn_b200_grouped_static_status (ginn_b200_device_status does not see it). */
 int ginn_b200_grouped_static(int device, void* stream, int dtype, int mode, int ngroups,
                              const ginn_b200_group* groups);
+
+/* Status word of the kernels launched by ginn_b200_grouped_static on `device` (same layout as
+ * ginn_b200_device_status; 0 = healthy).  Allocates nothing; synchronises the device. */
+int ginn_b200_grouped_static_status(int device, int reset);
 
 /* A level prepared once and launched many times -- the schedule cache ginn's Autobatch lacks: the
  * reference rebuilds RowwiseCat / Prod / RowwiseUncat nodes and re-copies every column on each
@@ -249,12 +261,15 @@ int ginn_b200_selftest(int device);
 /* Library version: major * 10000 + minor * 100 + patch. */
 int ginn_b200_version(void);
 
-/* Test / benchmark knobs.  "force_path": 0 = automatic, 1 = staged tcgen05 kernel,
- * 2 = one-CTA TMA fp16 kernel, 4 = CTA-pair fp16 kernel (both fall back to automatic when not
- * applicable), 3 = CUDA-core kernel, 5 = cp.async gather kernels (the fallbacks for operands a
- * tensor map cannot describe).
+/* Test / benchmark knobs.  They belong to the calling host thread: a value set here affects
+ * the calls this thread makes afterwards and nobody else's.
+ * "force_path": 0 = automatic, 2 = one-CTA TMA fp16 kernel, 4 = CTA-pair fp16 kernel (both fall
+ * back to automatic when not applicable), 3 = CUDA-core kernel, 5 = cp.async gather kernels
+ * (the fallbacks for operands a tensor map cannot describe).
  * "sm_margin": number of SMs the persistent fp16 kernels leave unoccupied (default 0), so that a
- * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles.
+ * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles; set
+ * it around the one product that overlaps the collective and back to 0 afterwards.
+ * "pair_group_m": m-tiles per rasterisation group of the CTA-pair kernel (0 = default).
  * Returns GINN_B200_UNSUPPORTED for unknown names. */
 int ginn_b200_set_option(const char* name, int value);
 

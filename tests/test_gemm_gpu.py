@@ -42,7 +42,7 @@ def run_gemm(gb, rng, dt, m, n, k, ta, tb, acc, ld_pad=0, offset=0):
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float16])
-@pytest.mark.parametrize("path", [1, 0, 5])
+@pytest.mark.parametrize("path", [0, 5])
 def test_shape_sweep_all_transposes(gpu, dt, path):
     gpu.set_option("force_path", path)
     rng = np.random.default_rng(11)
@@ -54,7 +54,7 @@ def test_shape_sweep_all_transposes(gpu, dt, path):
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float16])
-@pytest.mark.parametrize("path", [1, 0, 5])
+@pytest.mark.parametrize("path", [0, 5])
 def test_padded_leading_dimension_and_unaligned_base(gpu, dt, path):
     """ginn's PreallocGpu hands out unaligned bump pointers (ginn/dev.h:237-245) and
     RowwiseUncat views start at arbitrary column offsets (ginn/node/layout.h:283-289)."""
@@ -82,7 +82,7 @@ def test_prod_known_answer(gpu, kat):
     """test/nodes.cu.cpp:1023-1041 through every path that accepts the shape."""
     p = kat["prod"]
     for dt, eps in [(np.float32, kat["eps"]["f32"]), (np.float16, kat["eps"]["f16_prod"])]:
-        for path in (0, 1, 3):
+        for path in (0, 3, 5):
             gpu.set_option("force_path", path)
             W, V = np.asarray(p["W"], dt), np.asarray(p["V"], dt)
             C = B.colmajor(2, 2, B.from_host(W).dtype, fill=0.0)
