@@ -1,18 +1,25 @@
 #!/usr/bin/env python
-"""Benchmark of the Prod fwd+bwd hot path (large dense ProdNode, Half) on 1..N B200s.
+"""Benchmark of ginn's dense-contraction hot path on 1..N B200s.
 
-One step = what ProdNode does for one forward + backward pass (ginn/node/prod.h:28-66) with the
-gradients zeroed first, as Graph::reset_grad does (ginn/node.h:261-264):
+Headline workload (config 4): what ProdNode does for one forward + backward pass
+(ginn/node/prod.h:28-66) with the gradients zeroed first, as Graph::reset_grad does
+(ginn/node.h:261-264):
     dA = 0; dB = 0;  C = A*B;  dA += dC*B^T;  dB += A^T*dC
 A, B, dC are 8192 x 8192 fp16 (~N(0,1)), fp32 accumulation, column-major.
 
-Multi-GPU (weak scaling): every rank owns an 8192-column shard of B, C and dC and a replica of A
-(global B is 8192 x 8192*N).  Forward and dB need no exchange; dA is a sum over the sharded
-columns, so the dA contributions are all-reduced (NCCL) on a side stream while the dB product
-runs.
+Multi-GPU: ONE 8192^3 product, column-sharded (strong scaling).  Rank r owns columns
+[r*8192/N, (r+1)*8192/N) of B, C and dC and a replica of A.  Forward and dB need no exchange; dA
+is a sum over the sharded columns, so it is all-reduced (NCCL), panel by panel, while the later
+panels and the dB product are computed.  The same line carries, under "secondary", the weak
+variant (8192 columns per rank) and the data-parallel MLP of config 5, so that one record holds
+all three scaling series.
+
+On one GPU the line also carries "configs": the other benchmark configurations (Affine fp32,
+autobatched LSTM gates, attention through BatchedProd, data-parallel MLP step), each with its own
+timing, roofline fraction and CPU baseline.
 
 Prints ONE JSON line (rank 0).  `--impl reference` instead times the CPU restatement of the
-reference's Eigen path (oracle/cpu_path.c) on the host cores, on a bounded sample.
+reference's Eigen path (oracle/cpu_path.c) on the host cores, on the same configuration.
 """
 from __future__ import annotations
 
@@ -30,13 +37,10 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one hgemm_pair_kernel launch at 8192^3, from the
-# ncu capture summarised in profiles/hgemm_pair_prod8192.md (mean of the three captured launches).
-NCU_TRAFFIC_BYTES = {8192: 1.551e9}
-
 METRIC = "prod_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 SIZE = 8192
+PARITY_TOL_F16 = 5e-3   # relative Frobenius error against fp64, fp16 storage (the stated bound)
 
 
 def measured_peaks():
@@ -45,6 +49,27 @@ def measured_peaks():
             return json.load(f), "measured"
     except Exception:
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def dram_traffic(kernel: str, size: int):
+    """DRAM bytes per launch from the committed table of ncu captures (one entry per kernel and
+    size, each with the command that produced it); None when the size was never captured."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            table = json.load(f)
+        return table[kernel]["bytes_per_launch"].get(str(size))
+    except Exception:
+        return None
+
+
+def c4_config(n: int, world: int) -> dict:
+    """The configuration both arms are measured on (identical dictionaries)."""
+    return {"workload": f"C4 large dense ProdNode Half fwd+bwd, one {n}^3 product "
+                        "(C=A*B, dA+=dC*B^T, dB+=A^T*dC, grads zeroed each step)",
+            "size": n, "gpus": world,
+            "l2": "inputs and outputs (768 MiB) exceed the 126 MB L2",
+            "sharding": (f"columns of B/C/dC split over {world} ranks; dA all-reduced over NCCL"
+                         if world > 1 else "single GPU")}
 
 
 class ClockSampler:
@@ -105,58 +130,181 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 # CPU arm: the restated reference path on the host cores
 # ------------------------------------------------------------------------------------------
-def cpu_fwd_bwd(size: int, threads: int, steps: int, warmup: int):
-    """Times `steps` fwd+bwd passes of the CPU port at size^3, fp16 storage.  Returns
-    (TFLOP/s, seconds per step)."""
+def cpu_threads() -> int:
     from oracle import oracle as orc
-    rng = np.random.default_rng(20244)
-    a = np.asfortranarray(rng.standard_normal((size, size)).astype(np.float16))
-    b = np.asfortranarray(rng.standard_normal((size, size)).astype(np.float16))
-    dc = np.asfortranarray(rng.standard_normal((size, size)).astype(np.float16))
-    L = orc.cpu_path()
-    c = np.zeros((size, size), np.float16, order="F")
-    da = np.zeros((size, size), np.float16, order="F")
-    db = np.zeros((size, size), np.float16, order="F")
+    return max(orc.cpu_path().cpu_max_threads(), os.cpu_count() or 1)
 
-    def step():
-        da.fill(0)
-        db.fill(0)
-        L.cpu_gemm(1, 0, 0, size, size, size, a.ctypes.data, size, b.ctypes.data, size,
-                   c.ctypes.data, size, 0, threads)
-        L.cpu_gemm(1, 0, 1, size, size, size, dc.ctypes.data, size, b.ctypes.data, size,
-                   da.ctypes.data, size, 1, threads)
-        L.cpu_gemm(1, 1, 0, size, size, size, a.ctypes.data, size, dc.ctypes.data, size,
-                   db.ctypes.data, size, 1, threads)
 
+class CpuMat:
+    """Column-major host matrix for the C port (which takes pointers and leading dimensions)."""
+
+    def __init__(self, rows, cols, dtype, rng=None, scale=1.0, lo=None):
+        if rng is None:
+            self.a = np.zeros((rows, cols), dtype, order="F")
+        elif lo is not None:
+            self.a = np.asfortranarray(rng.uniform(lo, -lo, (rows, cols)).astype(dtype))
+        else:
+            self.a = np.asfortranarray((rng.standard_normal((rows, cols)) * scale).astype(dtype))
+        self.rows, self.cols = rows, cols
+
+    @property
+    def p(self):
+        return self.a.ctypes.data
+
+
+def cpu_gemm(L, dt, ta, tb, m, n, k, A, B, C, acc, threads, a_off=0, b_off=0, c_off=0):
+    """C (+)= op(A) op(B) with the port; offsets are in elements (column blocks of a matrix)."""
+    es = 4 if dt == 0 else 2
+    L.cpu_gemm(dt, ta, tb, m, n, k, A.p + a_off * es, A.rows, B.p + b_off * es, B.rows,
+               C.p + c_off * es, C.rows, acc, threads)
+
+
+def timed(fn, steps, warmup):
     for _ in range(warmup):
-        step()
+        fn()
     t0 = time.perf_counter()
     for _ in range(steps):
-        step()
-    dt = (time.perf_counter() - t0) / steps
+        fn()
+    return (time.perf_counter() - t0) / steps
+
+
+def cpu_c4(size: int, threads: int, steps: int, warmup: int):
+    """`steps` fwd+bwd passes of the CPU port at size^3, fp16 storage: (TFLOP/s, s per step)."""
+    from oracle import oracle as orc
+    L = orc.cpu_path()
+    rng = np.random.default_rng(20244)
+    a, b, dc = (CpuMat(size, size, np.float16, rng) for _ in range(3))
+    c, da, db = (CpuMat(size, size, np.float16) for _ in range(3))
+
+    def step():
+        da.a.fill(0)
+        db.a.fill(0)
+        cpu_gemm(L, 1, 0, 0, size, size, size, a, b, c, 0, threads)
+        cpu_gemm(L, 1, 0, 1, size, size, size, dc, b, da, 1, threads)
+        cpu_gemm(L, 1, 1, 0, size, size, size, a, dc, db, 1, threads)
+
+    dt = timed(step, steps, warmup)
     return 3 * 2 * size ** 3 / dt / 1e12, dt
+
+
+def cpu_config_baselines(threads: int) -> dict:
+    """The C port on the shapes of configs 1, 2 (recurrent and flat), 3 and 5, one to a few
+    passes each (a few seconds in total).  Products only, as in the GPU flop counts."""
+    from oracle import oracle as orc
+    L = orc.cpu_path()
+    rng = np.random.default_rng(20240)
+    out = {}
+
+    def affine_layer(m, k, n, need_dx=True):
+        W, X, dY = CpuMat(m, k, np.float32, rng, 0.05), CpuMat(k, n, np.float32, rng), CpuMat(m, n, np.float32, rng)
+        Y, dW, dX = CpuMat(m, n, np.float32), CpuMat(m, k, np.float32), CpuMat(k, n, np.float32)
+
+        def run():
+            cpu_gemm(L, 0, 0, 0, m, n, k, W, X, Y, 0, threads)
+            cpu_gemm(L, 0, 0, 1, m, k, n, dY, X, dW, 1, threads)
+            if need_dx:
+                cpu_gemm(L, 0, 1, 0, k, n, m, W, dY, dX, 1, threads)
+        return run
+
+    # C1: one Affine 512 x 784 on 128 columns
+    f = affine_layer(512, 784, 128)
+    dt = timed(f, 20, 2)
+    out["C1"] = {"value": 3 * 2 * 512 * 784 * 128 / dt / 1e12, "unit": UNIT, "ms_per_step": dt * 1e3,
+                 "cores": threads, "kind": "port", "sample": "20 fwd+bwd passes, products only"}
+    # C2: 40 levels of W 1024 x 384 on the live columns; flat: one level on all columns
+    import torch
+    lens = torch.randint(5, 41, (256,), generator=torch.Generator().manual_seed(20242)).numpy()
+    live = [int((lens > t).sum()) for t in range(int(lens.max()))]   # the GPU harness's levels
+    total = int(lens.sum())
+    W = CpuMat(1024, 384, np.float32, rng, 0.05)
+    X, dY = CpuMat(384, total, np.float32, rng), CpuMat(1024, total, np.float32, rng)
+    Y, dX, dW = CpuMat(1024, total, np.float32), CpuMat(384, total, np.float32), CpuMat(1024, 384, np.float32)
+
+    def levels():
+        off = 0
+        for n in live:
+            cpu_gemm(L, 0, 0, 0, 1024, n, 384, W, X, Y, 0, threads, b_off=off * 384, c_off=off * 1024)
+            cpu_gemm(L, 0, 1, 0, 384, n, 1024, W, dY, dX, 1, threads, b_off=off * 1024, c_off=off * 384)
+            cpu_gemm(L, 0, 0, 1, 1024, 384, n, dY, X, dW, 1, threads, a_off=off * 1024, b_off=off * 384)
+            off += n
+
+    def flat():
+        cpu_gemm(L, 0, 0, 0, 1024, total, 384, W, X, Y, 0, threads)
+        cpu_gemm(L, 0, 1, 0, 384, total, 1024, W, dY, dX, 1, threads)
+        cpu_gemm(L, 0, 0, 1, 1024, 384, total, dY, X, dW, 1, threads)
+
+    for key, fn in (("C2", levels), ("C2_flat", flat)):
+        dt = timed(fn, 2, 1)
+        out[key] = {"value": total / dt, "unit": "nodes/s", "ms_per_step": dt * 1e3,
+                    "tflops": 3 * 2 * 1024 * 384 * total / dt / 1e12, "cores": threads,
+                    "kind": "port", "sample": "2 passes over the same level sizes, products only "
+                                              "(no graph rewrite, no cell update)"}
+    # C3: six batched products, 256 x (256 x 64 x 256)
+    T, hs, nb = 256, 64, 256
+    K_, Q, V, dO = (CpuMat(T, hs * nb, np.float32, rng, 0.35), CpuMat(hs, T * nb, np.float32, rng, 0.35),
+                    CpuMat(hs, T * nb, np.float32, rng, 0.35), CpuMat(hs, T * nb, np.float32, rng))
+    S, dS = CpuMat(T, T * nb, np.float32), CpuMat(T, T * nb, np.float32)
+    O, dV, dQ, dK = (CpuMat(hs, T * nb, np.float32), CpuMat(hs, T * nb, np.float32),
+                     CpuMat(hs, T * nb, np.float32), CpuMat(T, hs * nb, np.float32))
+
+    def bg(ta, tb, m, n, k, A, B, C, acc):
+        L.cpu_gemm_batched(0, ta, tb, m, n, k, A.p, A.rows, A.rows * (A.cols // nb), B.p, B.rows,
+                           B.rows * (B.cols // nb), C.p, C.rows, C.rows * (C.cols // nb), nb, acc,
+                           threads)
+
+    def attention():
+        bg(0, 0, T, T, hs, K_, Q, S, 0)
+        bg(0, 0, hs, T, T, V, S, O, 0)
+        bg(0, 1, hs, T, T, dO, S, dV, 1)
+        bg(1, 0, T, T, hs, V, dO, dS, 1)
+        bg(0, 1, T, hs, T, dS, Q, dK, 1)
+        bg(1, 0, hs, T, T, K_, dS, dQ, 1)
+
+    dt = timed(attention, 2, 1)
+    out["C3"] = {"value": 6 * nb * 2 * T * hs * T / dt / 1e12, "unit": UNIT, "ms_per_step": dt * 1e3,
+                 "cores": threads, "kind": "port",
+                 "sample": "2 passes of the six batched products (softmax excluded, as in the flop count)"}
+    # C5: the three layers of the MLP on 4096 columns
+    layers = [affine_layer(1024, 784, 4096, False), affine_layer(1024, 1024, 4096),
+              affine_layer(10, 1024, 4096)]
+
+    def mlp():
+        for f in layers:
+            f()
+    dt = timed(mlp, 2, 1)
+    flops = 2 * sum(2 * a * b * 4096 for a, b in ((1024, 784), (1024, 1024), (10, 1024))) + \
+        sum(2 * a * b * 4096 for a, b in ((1024, 1024), (10, 1024)))
+    out["C5"] = {"value": flops / dt / 1e12, "unit": UNIT, "ms_per_step": dt * 1e3, "cores": threads,
+                 "kind": "port", "sample": "2 passes of the eight products of a step (loss and Adam excluded)"}
+    return out
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle as orc
-    threads = orc.cpu_path().cpu_max_threads()
-    threads = max(threads, os.cpu_count() or 1)
-    size = args.cpu_size
-    val, dt = cpu_fwd_bwd(size, threads, max(args.steps, 1), min(args.warmup, 1))
-    sample = (f"{size}^3 fp16 fwd+bwd (3 GEMMs) per step instead of {SIZE}^3; same operation "
-              f"sequence, CPU port of the Eigen path (oracle/cpu_path.c), {threads} threads")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    threads = cpu_threads()
+    size = args.size
+    steps, warmup = max(args.steps, 1), min(args.warmup, 1)
+    val, dt = cpu_c4(size, threads, steps, warmup)
+    single = None
+    if not args.no_single_thread:
+        # what the reference's own Makefile build does (no OpenMP): one thread, on a bounded
+        # sample of the same operation sequence
+        v1, dt1 = cpu_c4(args.cpu_size, 1, 1, 0)
+        single = {"value": v1, "unit": UNIT, "cores": 1,
+                  "sample": f"one fwd+bwd pass at {args.cpu_size}^3 ({dt1:.2f} s)"}
+    sample = (f"{steps} fwd+bwd passes (3 GEMMs each) at the full {size}^3, CPU port of the Eigen "
+              f"path (oracle/cpu_path.c, fp32 arithmetic on fp16 storage), {threads} threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic",
-        "config": {"workload": "C4 large dense ProdNode Half fwd+bwd 8192^3 (bounded CPU sample)",
-                   "sample_size": size},
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": c4_config(size, world),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": sample},
+                         "sample": sample, "single_thread": single},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -165,268 +313,458 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
-def run_gpu(args):
-    import torch
-    import torch.distributed as dist
-    import ginn_b200 as gb
-    from ginn_b200 import binding as B
-    from ginn_b200.parallel import ShardedProd
+class Dist:
+    """Rank bookkeeping and the collectives the harness needs (none on one GPU)."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    n = args.size
-    g = torch.Generator(device=dev)
-    g.manual_seed(20244 + rank)
-    ga = torch.Generator(device=dev)
-    ga.manual_seed(20244)  # A is replicated: same seed on every rank
+    def __init__(self):
+        import torch
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.comm = torch.cuda.Stream(device=self.dev) if self.world > 1 else None
 
-    def randn_cm(gen):  # column-major n x n fp16
-        return torch.randn(n, n, device=dev, dtype=torch.float32, generator=gen).half().T
+    def barrier(self):
+        import torch
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize(self.dev)
 
-    A, Bm, dC = randn_cm(ga), randn_cm(g), randn_cm(g)
-    Cm = torch.empty(n, n, device=dev, dtype=torch.float16).T
-    dA = torch.empty(n, n, device=dev, dtype=torch.float16).T
-    dB = torch.empty(n, n, device=dev, dtype=torch.float16).T
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    main = torch.cuda.current_stream(dev)
-    gemm_events = []
+    def max_over_ranks(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([x], device=self.dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-    def allreduce_async(t):
-        if world == 1:
+    def sum_f64(self, t):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t)
+        return t
+
+    def allreduce_async(self, t):
+        """Sum of a contiguous tensor over ranks on the communication stream; returns the
+        function that makes the current stream wait for the result."""
+        import torch
+        import torch.distributed as dist
+        main = torch.cuda.current_stream(self.dev)
+        if self.world == 1:
             return lambda: None
         ready = torch.cuda.Event()
         ready.record(main)
-        comm_stream.wait_event(ready)
-        with torch.cuda.stream(comm_stream):
-            dist.all_reduce(t.T)  # contiguous storage of the column-major matrix
-        return lambda: main.wait_stream(comm_stream)
+        self.comm.wait_event(ready)
+        with torch.cuda.stream(self.comm):
+            dist.all_reduce(t)
+        return lambda: main.wait_stream(self.comm)
 
-    margin = args.sm_margin if args.sm_margin >= 0 else (8 if world > 1 else 0)
-    gb.set_option("sm_margin", margin)
-    prod = ShardedProd(lambda a, b, c, ta, tb, acc: gb.gemm(a, b, c, ta, tb, acc),
-                       lambda t: t.zero_(), allreduce_async)
+    def close(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
 
-    def step(record=False):
-        if not record:
-            prod.step(A, Bm, dC, Cm, dA, dB)
-            return
-        # CUDA events around each of the three products, on the stream they are launched on
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-        state = {"first": True}
 
-        def gemm_timed(a, b, c, ta, tb, acc):
-            if state["first"]:
-                evs[0].record()
-                state["first"] = False
+class ProdShard:
+    """Tensors and step of the sharded Prod pass on one rank: `ncols` columns of B, C, dC."""
+
+    def __init__(self, D: Dist, n: int, first_col: int, ncols: int, panels: int, margin: int):
+        import torch
+        import ginn_b200 as gb
+        from ginn_b200.parallel import ShardedProd
+        self.D, self.n, self.first_col, self.ncols = D, n, first_col, ncols
+        dev = D.dev
+        ga = torch.Generator(device=dev).manual_seed(20244)       # A is replicated
+        g = torch.Generator(device=dev).manual_seed(20245 + D.rank)
+
+        def randn_cm(rows, cols, gen):  # column-major rows x cols fp16
+            return torch.randn(cols, rows, device=dev, dtype=torch.float32, generator=gen).half().T
+
+        self.A = randn_cm(n, n, ga)
+        self.B, self.dC = randn_cm(n, ncols, g), randn_cm(n, ncols, g)
+        empty = lambda cols: torch.empty(cols, n, device=dev, dtype=torch.float16).T
+        self.C, self.dA, self.dB = empty(ncols), empty(n), empty(ncols)
+        self.events = None
+
+        def gemm(a, b, c, ta, tb, acc):
+            if self.events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                self.events.append(ev)
             gb.gemm(a, b, c, ta, tb, acc)
 
-        timed = ShardedProd(gemm_timed, lambda t: t.zero_(), allreduce_async)
-        timed.step(A, Bm, dC, Cm, dA, dB, between=lambda i: evs[i + 1].record())
-        gemm_events.append(evs)
+        def overlapped(on):
+            # SMs are kept free only for the products that run beside a reduction
+            if D.world > 1 and margin > 0:
+                gb.set_option("sm_margin", margin if on else 0)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
+        self.prod = ShardedProd(gemm, lambda t: t.zero_(),
+                                lambda t: D.allreduce_async(t.T),  # contiguous storage of a panel
+                                panels=panels if D.world > 1 else 1, overlapped=overlapped)
+        self.flops = 3 * 2 * n * n * ncols
 
-    for _ in range(max(args.warmup, 3)):
+    def step(self, between=None):
+        self.prod.step(self.A, self.B, self.dC, self.C, self.dA, self.dB, between=between)
+
+    def step_timed(self):
+        """One step with a CUDA event before every product and one after the last; returns the
+        events (durations are read after the timed region)."""
+        import torch
+        self.events = []
+        self.step()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        evs, self.events = self.events + [ev], None
+        return evs
+
+    def parity(self) -> dict:
+        """Sampled entries of C, dB (local) and the reduced dA against an fp64 recomputation on
+        the host from the very operands the GPU used (untimed).  Relative Frobenius error over
+        each sampled block; the maximum over blocks and ranks is returned."""
+        import torch
+        D, n = self.D, self.n
+        self.step()
+        torch.cuda.synchronize(D.dev)
+        rs = np.random.default_rng(99)                      # same samples on every rank
+        rows = np.sort(rs.choice(n, 32, replace=False))
+        gcols = np.sort(rs.choice(n, 64, replace=False))    # columns of dA = rows of B
+        lcols = np.sort(rs.choice(self.ncols, min(64, self.ncols), replace=False))
+        ti = lambda idx: torch.as_tensor(idx, device=D.dev)
+        f64 = lambda t: t.double().cpu().numpy()
+        A_rows, A_cols = f64(self.A[ti(rows)]), f64(self.A[:, ti(rows)])
+        B_lc, dC_lc = f64(self.B[:, ti(lcols)]), f64(self.dC[:, ti(lcols)])
+        errs = {}
+
+        def rel(got, ref):
+            return float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-300))
+
+        errs["C"] = rel(f64(self.C[ti(rows)][:, ti(lcols)]), A_rows @ B_lc)
+        errs["dB"] = rel(f64(self.dB[ti(rows)][:, ti(lcols)]), A_cols.T @ dC_lc)
+        part = f64(self.dC[ti(rows)]) @ f64(self.B[ti(gcols)]).T   # this rank's share of dA
+        ref = D.sum_f64(torch.as_tensor(part, device=D.dev)).cpu().numpy()
+        errs["dA"] = rel(f64(self.dA[ti(rows)][:, ti(gcols)]), ref)
+        worst = D.max_over_ranks(max(errs.values()))
+        return {"checked": True, "max_rel": worst, "tol": PARITY_TOL_F16,
+                "what": "32 x 64 sampled entries each of C, dB (per rank) and the all-reduced dA "
+                        "against an fp64 host recomputation, relative Frobenius error, max over ranks",
+                "rank0": errs, "ok": bool(worst <= PARITY_TOL_F16)}
+
+
+def time_steps(D: Dist, step, steps: int, warmup: int):
+    """Barrier + synchronize on both sides, CUDA events on the current stream, max over ranks."""
+    import torch
+    for _ in range(warmup):
         step()
-    barrier()
-    status = gb.device_status(local, True)
-    if status != 0:
-        raise RuntimeError(f"device status {status:#x} after warm-up")
-
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
-    launches0 = gb.launch_count()
-    barrier()
+    D.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        step(record=True)
+    for _ in range(steps):
+        step()
     e1.record()
-    barrier()
-    launches = gb.launch_count() - launches0
-    clocks = sampler.stop() if sampler else None
-    ms = e0.elapsed_time(e1) / args.steps
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
-    kern_ms = []
-    for evs in gemm_events:
-        kern_ms += [evs[i].elapsed_time(evs[i + 1]) for i in range(3)]
-    status = gb.device_status(local, True)
-    if status != 0:
-        raise RuntimeError(f"device status {status:#x} after the timed region")
-
-    flops_step = 3 * 2 * n ** 3
-    value = world * flops_step / (ms * 1e-3) / 1e12
-
-    # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
-    e2e = None
-    if not args.no_e2e:
-        hA, hB, hdC = (torch.empty(n * n, dtype=torch.float16).pin_memory() for _ in range(3))
-        hC, hdA, hdB = (torch.empty(n * n, dtype=torch.float16).pin_memory() for _ in range(3))
-        hA.copy_(A.T.reshape(-1).cpu()); hB.copy_(Bm.T.reshape(-1).cpu()); hdC.copy_(dC.T.reshape(-1).cpu())
-
-        # Copies run on their own streams so that they overlap the products inside a step:
-        # dC arrives while C = A*B runs, C leaves while the two backward products run.
-        h2d, d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-
-        def e2e_step():
-            start = torch.cuda.Event()
-            start.record(main)                      # previous step's products and copies are queued
-            h2d.wait_event(start)
-            d2h_prev = torch.cuda.Event()
-            d2h_prev.record(d2h)
-            main.wait_event(d2h_prev)               # results of the previous step have left
-            ev_ab, ev_dc, ev_c = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
-            with torch.cuda.stream(h2d):
-                A.T.reshape(-1).copy_(hA, non_blocking=True)
-                Bm.T.reshape(-1).copy_(hB, non_blocking=True)
-                ev_ab.record(h2d)
-                dC.T.reshape(-1).copy_(hdC, non_blocking=True)
-                ev_dc.record(h2d)
-            main.wait_event(ev_ab)
-
-            def after(i):
-                if i == 0:
-                    ev_c.record(main)
-                    main.wait_event(ev_dc)
-                    d2h.wait_event(ev_c)
-                    with torch.cuda.stream(d2h):
-                        hC.copy_(Cm.T.reshape(-1), non_blocking=True)
-
-            prod.step(A, Bm, dC, Cm, dA, dB, between=after)
-            done = torch.cuda.Event()
-            done.record(main)
-            d2h.wait_event(done)
-            with torch.cuda.stream(d2h):
-                hdA.copy_(dA.T.reshape(-1), non_blocking=True)
-                hdB.copy_(dB.T.reshape(-1), non_blocking=True)
-
-        def e2e_finish():
-            main.wait_stream(d2h)
-            main.wait_stream(h2d)
-
-        e2e_step()
-        e2e_finish()
-        barrier()
-        k = max(1, min(args.steps, 5))
-        e0.record()
-        for _ in range(k):
-            e2e_step()
-        e2e_finish()
-        e1.record()
-        barrier()
-        ms_e = e0.elapsed_time(e1) / k
-        if world > 1:
-            t = torch.tensor([ms_e], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_e = t.item()
-        nbytes = 3 * n * n * 2
-        e2e = {"value": world * flops_step / (ms_e * 1e-3) / 1e12, "unit": UNIT,
-               "ms_per_step": ms_e, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    peaks, peak_src = measured_peaks()
-    timed_s = ms * args.steps * 1e-3
-    # Which measured cuBLAS figure is the fair denominator: the burst one for a short, cool run, the
-    # sustained one when the board ran power-capped (clock well below maximum under sw_power_cap)
-    # or the timed region is long.  Both fractions are reported.
-    capped = bool(clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz")
-                  and "sw_power_cap" in clocks.get("reasons", [])
-                  and clocks["sm_mhz"] < 0.8 * clocks["sm_max_mhz"])
-    sustained = timed_s >= 1.0 or capped
-    peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
-    avg_kernel_ms = sum(kern_ms) / len(kern_ms)
-    achieved = 2 * n ** 3 / (avg_kernel_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(n),
-                "frac_of_burst": achieved / peaks["bf16_tflops"],
-                "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
-                "kernel": "hgemm_pair_kernel (tcgen05 cta_group::2; three transpose variants, "
-                          "one launch each per step)",
-                "avg_launch_ms": avg_kernel_ms,
-                "peak_kind": f"{'sustained' if sustained else 'burst'} cuBLAS bf16, of {peak_src}"
-                             + (" (board power-capped during the timed region)" if capped else "")}
-
-    cpu_baseline = None
-    if world == 1 and not args.no_cpu:
-        from oracle import oracle as orc
-        threads = max(orc.cpu_path().cpu_max_threads(), os.cpu_count() or 1)
-        v, dt = cpu_fwd_bwd(args.cpu_size, threads, 1, 1)
-        cpu_baseline = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                        "sample": f"one fwd+bwd pass at {args.cpu_size}^3 fp16 ({dt:.2f} s), "
-                                  f"CPU port of the Eigen path (oracle/cpu_path.c)"}
-
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"C4 large dense ProdNode Half fwd+bwd {n}^3 per GPU "
-                               "(C=A*B, dA+=dC*B^T, dB+=A^T*dC, grads zeroed each step)",
-                   "size": n, "l2": "inputs and outputs (768 MiB) exceed the 126 MB L2",
-                   "sharding": "columns of B/C/dC per rank; dA all-reduced over NCCL" if world > 1
-                   else "single GPU"},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-        "roofline": roofline, "cpu_baseline": cpu_baseline,
-    }
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    D.barrier()
+    return D.max_over_ranks(e0.elapsed_time(e1) / steps)
 
 
-def run_affine(args):
-    """Secondary workload (profiling aid): one fp32 AffineNode fwd+bwd, tanh, through the fused
-    entry points.  Shapes default to config 5's hidden layer (1024 x 1024, batch 4096)."""
+def e2e_prod(D: Dist, P: ProdShard, steps: int):
+    """The same pass through the C ABI with HOST buffers: every step copies this rank's operands
+    in from pinned memory and its results out (C and dB shards, and this rank's slice of the
+    reduced dA), copies overlapped with the products on their own streams."""
+    import torch
+    from ginn_b200.parallel import column_shard
+    dev, n = D.dev, P.n
+    main = torch.cuda.current_stream(dev)
+    flat = lambda t: t.T.reshape(-1)
+    pin = lambda t: torch.empty(t.numel(), dtype=torch.float16).pin_memory()
+    hA, hB, hdC = pin(P.A), pin(P.B), pin(P.dC)
+    hA.copy_(flat(P.A).cpu()); hB.copy_(flat(P.B).cpu()); hdC.copy_(flat(P.dC).cpu())
+    s, c = column_shard(n, D.world, D.rank)
+    dA_slice = P.dA[:, s:s + c]
+    hC, hdB, hdA = pin(P.C), pin(P.dB), pin(dA_slice)
+    h2d, d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def step():
+        start = torch.cuda.Event()
+        start.record(main)                      # previous step's products and copies are queued
+        h2d.wait_event(start)
+        d2h_prev = torch.cuda.Event()
+        d2h_prev.record(d2h)
+        main.wait_event(d2h_prev)               # results of the previous step have left
+        ev_ab, ev_dc, ev_c = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+        with torch.cuda.stream(h2d):
+            flat(P.A).copy_(hA, non_blocking=True)
+            flat(P.B).copy_(hB, non_blocking=True)
+            ev_ab.record(h2d)
+            flat(P.dC).copy_(hdC, non_blocking=True)
+            ev_dc.record(h2d)
+        main.wait_event(ev_ab)
+
+        def after(i):
+            if i == 0:      # dC must have arrived before the backward products; C may leave now
+                ev_c.record(main)
+                main.wait_event(ev_dc)
+                d2h.wait_event(ev_c)
+                with torch.cuda.stream(d2h):
+                    hC.copy_(flat(P.C), non_blocking=True)
+
+        P.step(between=after)
+        done = torch.cuda.Event()
+        done.record(main)
+        d2h.wait_event(done)
+        with torch.cuda.stream(d2h):
+            hdA.copy_(flat(dA_slice), non_blocking=True)
+            hdB.copy_(flat(P.dB), non_blocking=True)
+
+    def finish():
+        main.wait_stream(d2h)
+        main.wait_stream(h2d)
+
+    for _ in range(3):
+        step()
+    finish()
+    D.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    finish()
+    e1.record()
+    D.barrier()
+    ms = D.max_over_ranks(e0.elapsed_time(e1) / steps)
+    h2d_b = 2 * (P.A.numel() + P.B.numel() + P.dC.numel())
+    d2h_b = 2 * (P.C.numel() + P.dB.numel() + dA_slice.numel())
+    return ms, h2d_b, d2h_b
+
+
+def fp32_ceiling(peaks):
+    """Ceiling of a 3xTF32 kernel in useful fp32 flops: the measured bf16 burst rate, halved for
+    TF32 operands, divided by the three tensor-core products every term costs."""
+    return peaks["bf16_tflops"] / 2.0 / 3.0
+
+
+def run_mlp_dp(D: Dist, steps: int, warmup: int) -> dict:
+    """Config 5 step (fwd, loss, bwd, bucketed all-reduce, Adam); replicas must stay identical."""
+    import torch
+    from ginn_b200 import workloads as wl
+    w = wl.MlpDataParallel(D.dev, D.rank, D.world,
+                           allreduce=D.allreduce_async if D.world > 1 else None)
+    ms = time_steps(D, w.step, steps, max(warmup, 3))
+    out = {"ms_per_step": ms, "tflops": D.world * w.flops / (ms * 1e-3) / 1e12,
+           "flops_per_step_per_gpu": w.flops, "loss": float(w.loss)}
+    if D.world > 1:
+        import torch.distributed as dist
+        ref = w.params.clone()
+        dist.broadcast(ref, 0)
+        out["replica_max_abs_diff"] = D.max_over_ranks(float((w.params - ref).abs().max()))
+    return out
+
+
+def run_configs(D: Dist, args, peaks) -> dict:
+    """Configs 1, 2 (recurrent and flat), 3 and 5 on one GPU: ms per step, useful TFLOP/s or
+    nodes/s, fraction of the 3xTF32 ceiling, and the CPU port on the same shapes."""
     import torch
     import ginn_b200 as gb
     from ginn_b200 import binding as B
-    torch.cuda.set_device(0)
-    m, n, k = args.m, args.n, args.k
-    g = torch.Generator(device="cuda").manual_seed(20241)
-    a = (6 / (0.5 * (m + k))) ** 0.5
-    tdt = torch.float16 if args.dtype == "f16" else torch.float32
-    W = ((torch.rand(k, m, device="cuda", generator=g) * 2 - 1) * a).to(tdt).T
-    X = torch.randn(n, k, device="cuda", generator=g).to(tdt).T
-    b = ((torch.rand(m, device="cuda", generator=g) * 2 - 1) * a).to(tdt)
-    dY = torch.randn(n, m, device="cuda", generator=g).to(tdt).T
-    Y = B.colmajor(m, n, tdt, fill=0.0)
-    dW, dX = B.colmajor(m, k, tdt, fill=0.0), B.colmajor(k, n, tdt, fill=0.0)
-    db = torch.zeros(m, device="cuda", dtype=tdt)
+    from ginn_b200 import workloads as wl
+    dev = D.dev
+    ceil = fp32_ceiling(peaks)
+    steps, warmup = max(args.config_steps, 1), 3
+    cpu = cpu_config_baselines(cpu_threads()) if not args.no_cpu else {}
+    out = {}
 
-    def step():
-        dW.zero_(); dX.zero_(); db.zero_()
-        gb.affine_forward([gb.Pair(W, X)], b, gb.ACT_TANH, Y)
-        gb.affine_backward([gb.PairGrad(W, X, dW, dX)], dY, Y, gb.ACT_TANH, db)
+    def entry(key, name, ms, flops, extra=None):
+        tf = flops / (ms * 1e-3) / 1e12
+        e = {"workload": name, "ms_per_step": ms, "tflops": tf, "dtype": "f32 (3xTF32)",
+             "roofline": {"bound": "tensor", "achieved": tf, "peak": ceil, "unit": UNIT,
+                          "frac": tf / ceil,
+                          "peak_kind": "measured bf16 burst / 2 (TF32) / 3 (products per term)"},
+             "cpu_baseline": cpu.get(key)}
+        e.update(extra or {})
+        out[key] = e
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
+    # C1
+    w = wl.AffineLayer(dev, 512, 128, 784)
+    launches0 = gb.launch_count()
+    ms = time_steps(D, w.step, steps, warmup)
+    entry("C1", "Affine tanh fwd+bwd fp32: W 512x784, X 784x128", ms, w.flops,
+          {"us_per_step": ms * 1e3, "launches_per_step": (gb.launch_count() - launches0) // (steps + warmup)})
+    # C2 recurrent: prepared levels replayed from a CUDA graph; the rewrite (host grouping +
+    # descriptor upload) timed separately and added for the with-rewrite figure
+    w = wl.LstmAutobatch(dev)
+    t0 = time.perf_counter()
+    w.rewrite()
+    torch.cuda.synchronize(dev)
+    rewrite_ms = (time.perf_counter() - t0) * 1e3
+    ms_launch = time_steps(D, w.step, max(steps // 4, 2), 2)
+    w.capture()
+    ms = time_steps(D, w.step, steps, warmup)
+    entry("C2", "autobatched LSTM gates fp32: 256 seqs len 5..40, W 1024x384, 40 dependent levels",
+          ms, w.flops,
+          {"nodes": w.nodes, "levels": w.T, "nodes_per_s": w.nodes / (ms * 1e-3),
+           "nodes_per_s_launched_from_python": w.nodes / (ms_launch * 1e-3),
+           "rewrite_ms": rewrite_ms,
+           "nodes_per_s_with_rewrite": w.nodes / ((ms_launch + rewrite_ms) * 1e-3),
+           "note": "replayed from a CUDA graph; with_rewrite = one rewrite + one pass launched "
+                   "level by level, as a graph built anew for every batch needs"})
+    del w
+    # C2 flat
+    w = wl.LstmFlat(dev)
+    ms = time_steps(D, w.step, steps, warmup)
+    entry("C2_flat", "C2 flat variant: one merged level, W 1024x384 on sum(len) gathered columns",
+          ms, w.flops, {"nodes": w.nodes, "nodes_per_s": w.nodes / (ms * 1e-3)})
+    del w
+    # C3
+    w = wl.Attention(dev)
+    ms = time_steps(D, w.step, steps, warmup)
+    entry("C3", "min-GPT attention via BatchedProd fp32: 256 x (256x64x256), fwd+bwd", ms, w.flops)
+    del w
+    # C5
+    r = run_mlp_dp(D, steps, warmup)
+    entry("C5", "data-parallel MLP 784-1024-1024-10 fp32, batch 4096 per GPU, softmax-CE, Adam",
+          r["ms_per_step"], r["flops_per_step_per_gpu"], {"loss": r["loss"]})
+    assert gb.device_status(D.local, True) == 0
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_gpu(args):
+    import torch
+    import ginn_b200 as gb
+    from ginn_b200.parallel import column_shard
+
+    D = Dist()
+    world, rank = D.world, D.rank
+    n = args.size
+    margin = args.sm_margin if args.sm_margin >= 0 else (8 if world > 1 else 0)
+    first, ncols = column_shard(n, world, rank)
+    P = ProdShard(D, n, first, ncols, args.panels, margin)
+    warmup = max(args.warmup, 3)
+
+    for _ in range(warmup):
+        P.step()
+    D.barrier()
+    status = gb.device_status(D.local, True)
+    if status != 0:
+        raise RuntimeError(f"device status {status:#x} after warm-up")
+
+    sampler = ClockSampler(D.local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = gb.launch_count()
+    gemm_events = []
+    D.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step()
+        gemm_events.append(P.step_timed())
     e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+    D.barrier()
+    launches = gb.launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    ms = D.max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    gemm_ms = sum(evs[0].elapsed_time(evs[-1]) for evs in gemm_events) / len(gemm_events)
+    launches_per_step = len(gemm_events[0]) - 1
+    status = gb.device_status(D.local, True)
+    if status != 0:
+        raise RuntimeError(f"device status {status:#x} after the timed region")
+
+    total_flops = 3 * 2 * n ** 3                     # the whole job, however it is sharded
+    value = total_flops / (ms * 1e-3) / 1e12
+    flops_launches = P.flops                         # this rank's three products
+    parity = P.parity()
+
+    e2e = None
+    if not args.no_e2e:
+        ms_e, h2d_b, d2h_b = e2e_prod(D, P, args.steps)
+        e2e = {"value": total_flops / (ms_e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e,
+               "h2d_bytes_per_step": h2d_b, "d2h_bytes_per_step": d2h_b,
+               "bytes_are": "per rank" if world > 1 else "total"}
+
+    secondary = {}
+    if world > 1:
+        del P
+        torch.cuda.empty_cache()
+        Pw = ProdShard(D, n, rank * n, n, args.panels, margin)     # weak: n columns per rank
+        ms_w = time_steps(D, Pw.step, args.steps, warmup)
+        secondary["c4_weak"] = {
+            "scaling": "weak", "ms_per_step": ms_w, "value": world * Pw.flops / (ms_w * 1e-3) / 1e12,
+            "unit": UNIT, "workload": f"{n}^3 per rank (global B is {n} x {n * world})",
+            "parity": Pw.parity()}
+        del Pw
+        torch.cuda.empty_cache()
+        r = run_mlp_dp(D, args.steps, warmup)
+        secondary["c5_mlp_dp"] = {"scaling": "weak", "unit": UNIT, "value": r["tflops"], **r,
+                                  "workload": "C5 data-parallel MLP, 4096 columns per rank, "
+                                              "bucketed NCCL all-reduce overlapped with backward"}
+
+    if rank != 0:
+        D.close()
+        return
+
+    peaks, peak_src = measured_peaks()
+    achieved = flops_launches / (gemm_ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"]
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT,
+                "frac": achieved / peak,
+                "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                "traffic": dram_traffic("hgemm_pair_kernel", n) if world == 1 else None,
+                "kernel": "hgemm_pair_kernel (tcgen05 cta_group::2; NN, NT, TN variants)",
+                "launches_per_step": launches_per_step,
+                "avg_launch_ms": gemm_ms / launches_per_step,
+                "peak_kind": f"burst cuBLAS bf16, of {peak_src}; frac_of_sustained = against the "
+                             "seconds-long power-capped figure"}
+
+    cpu_baseline, configs = None, None
+    if world == 1:
+        if not args.no_cpu:
+            threads = cpu_threads()
+            v, dt = cpu_c4(args.cpu_size, threads, 1, 1)
+            cpu_baseline = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                            "sample": f"one fwd+bwd pass at {args.cpu_size}^3 fp16 ({dt:.2f} s), CPU "
+                                      "port of the Eigen path (oracle/cpu_path.c); the reference "
+                                      "arm times the full size"}
+        if not args.no_configs:
+            configs = run_configs(D, args, peaks)
+            c5 = configs["C5"]
+            secondary["c5_mlp_dp"] = {"scaling": "weak", "unit": UNIT, "value": c5["tflops"],
+                                      "ms_per_step": c5["ms_per_step"], "tflops": c5["tflops"]}
+            secondary["c4_weak"] = {"scaling": "weak", "ms_per_step": ms, "value": value, "unit": UNIT}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": c4_config(n, world),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "parity": parity,
+        "secondary": secondary or None, "configs": configs,
+        "dA_panels": args.panels if world > 1 else 1, "sm_margin_beside_collectives": margin,
+    }
+    print(json.dumps(line), flush=True)
+    D.close()
+    if not parity["ok"] or any(not s.get("parity", {"ok": True})["ok"] for s in secondary.values()):
+        sys.exit(4)
+
+
+def run_affine(args):
+    """Profiling aid: one AffineNode fwd+bwd, tanh, through the fused entry points.  Shapes
+    default to config 5's hidden layer (1024 x 1024, batch 4096)."""
+    import torch
+    import ginn_b200 as gb
+    from ginn_b200 import workloads as wl
+    D = Dist()
+    w = wl.AffineLayer(D.dev, args.m, args.n, args.k, half=args.dtype == "f16")
+    ms = time_steps(D, w.step, args.steps, max(args.warmup, 3))
     assert gb.device_status(0, True) == 0
-    print(json.dumps({"metric": "affine_fwd_bwd_tflops", "value": 3 * 2 * m * n * k / ms / 1e9,
+    print(json.dumps({"metric": "affine_fwd_bwd_tflops", "value": w.flops / ms / 1e9,
                       "unit": UNIT, "n_gpus": 1, "steps": args.steps, "ms_per_step": ms,
                       "dtype": "f16" if args.dtype == "f16" else "f32 (3xTF32)", "data": "synthetic",
-                      "config": {"workload": f"Affine tanh fwd+bwd W {m}x{k}, X {k}x{n}"}}),
+                      "config": {"workload": f"Affine tanh fwd+bwd W {args.m}x{args.k}, X {args.k}x{args.n}"}}),
           flush=True)
 
 
@@ -496,20 +834,14 @@ def run_step_ops(args):
 
 
 def run_config_workload(args):
-    """Secondary workloads: the other benchmark configurations (fp32), harnessed in
-    ginn_b200/workloads.py.  Same timing rules as the main arm; one JSON line from rank 0."""
+    """One of the other configurations alone (profiling aid; the default run reports them all in
+    its "configs" block).  Same timing rules as the main arm; one JSON line from rank 0."""
     import torch
-    import torch.distributed as dist
     import ginn_b200 as gb
     from ginn_b200 import workloads as wl
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    D = Dist()
+    dev, world, rank = D.dev, D.world, D.rank
     extra = {}
     if args.workload == "attention_f32":
         w = wl.Attention(dev)
@@ -529,49 +861,29 @@ def run_config_workload(args):
         extra["cuda_graph"] = bool(args.cuda_graph)
         metric, name = "autobatch_nodes_per_s", "C2 autobatched LSTM gates, fp32, 256 seqs len 5..40, W 1024x384"
     else:
-        comm = torch.cuda.Stream(device=dev) if world > 1 else None
-
-        def allreduce(t):
-            """Sum over ranks on the communication stream; returns the wait for its result."""
-            main = torch.cuda.current_stream(dev)
-            ready = torch.cuda.Event()
-            ready.record(main)
-            comm.wait_event(ready)
-            with torch.cuda.stream(comm):
-                dist.all_reduce(t)
-            return lambda: main.wait_stream(comm)
-        w = wl.MlpDataParallel(dev, rank, world, allreduce=allreduce if world > 1 else None)
+        w = wl.MlpDataParallel(dev, rank, world, allreduce=D.allreduce_async if world > 1 else None)
         metric, name = "mlp_dp_tflops", "C5 data-parallel MLP 784-1024-1024-10, fp32, batch 4096 per GPU, Adam"
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
 
     for _ in range(max(args.warmup, 3)):
         w.step()
-    barrier()
-    assert gb.device_status(local, True) == 0
-    sampler = ClockSampler(local) if rank == 0 else None
+    D.barrier()
+    assert gb.device_status(D.local, True) == 0
+    sampler = ClockSampler(D.local) if rank == 0 else None
     if sampler:
         sampler.start()
     launches0 = gb.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    D.barrier()
     t0 = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
         w.step()
     e1.record()
-    barrier()
+    D.barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    ms = e0.elapsed_time(e1) / args.steps
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
+    ms = D.max_over_ranks(e0.elapsed_time(e1) / args.steps)
     clocks = sampler.stop() if sampler else None
-    assert gb.device_status(local, True) == 0
+    assert gb.device_status(D.local, True) == 0
     if rank == 0:
         tflops = world * w.flops / (ms * 1e-3) / 1e12
         per_unit = args.workload in ("lstm_autobatch", "lstm_flat")
@@ -585,22 +897,29 @@ def run_config_workload(args):
                 "clocks": clocks, "gpu_launches": int(gb.launch_count() - launches0)}
         line.update(extra)
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    D.close()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=SIZE, help="matrix extent (default: the C4 config)")
-    ap.add_argument("--cpu-size", type=int, default=3072, help="extent of the bounded CPU sample")
+    ap.add_argument("--cpu-size", type=int, default=3072,
+                    help="extent of the bounded CPU samples (cpu_baseline of the GPU arm, "
+                         "single-thread figure of the reference arm)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the configs block (1 GPU)")
+    ap.add_argument("--no-single-thread", action="store_true",
+                    help="reference arm: skip the single-thread sample")
+    ap.add_argument("--config-steps", type=int, default=20, help="timed steps per configs entry")
+    ap.add_argument("--panels", type=int, default=4,
+                    help="column panels of dA, each all-reduced as soon as it is computed (N > 1)")
     ap.add_argument("--sm-margin", type=int, default=-1,
-                    help="SMs left free for NCCL while the dB product overlaps the all-reduce "
+                    help="SMs left free for NCCL by the products that run beside a reduction "
                          "(default: 0 on one GPU, 8 otherwise)")
     ap.add_argument("--workload", default="prod_f16", choices=["prod_f16", "affine_f32", "attention_f32", "lstm_autobatch", "lstm_flat", "mlp_dp", "step_ops"])
     ap.add_argument("--cuda-graph", action="store_true",

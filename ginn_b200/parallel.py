@@ -23,12 +23,27 @@ def column_shard(n_total: int, world: int, rank: int) -> Tuple[int, int]:
 
 
 class ShardedProd:
-    """One forward+backward pass of ProdNode (ginn/node/prod.h:28-66) on a column shard."""
+    """One forward+backward pass of ProdNode (ginn/node/prod.h:28-66) on a column shard.
 
-    def __init__(self, gemm: Callable, zero: Callable, allreduce_async: Callable):
+    `panels` > 1 splits dA = dC * B^T into that many column panels of dA (row blocks of the
+    local B shard, i.e. pointer offsets into column-major storage, no copy): the reduction of a
+    finished panel starts while the later panels and the dB product are still being computed,
+    so only the last panel's reduction is exposed.  `col_block(x, first, count)` must return the
+    view of columns [first, first+count) of x, `row_block` the same for rows.
+    """
+
+    def __init__(self, gemm: Callable, zero: Callable, allreduce_async: Callable, panels: int = 1,
+                 col_block: Callable = None, row_block: Callable = None,
+                 overlapped: Callable = None):
         self.gemm = gemm
         self.zero = zero
         self.allreduce_async = allreduce_async
+        self.panels = max(1, panels)
+        self.col_block = col_block or (lambda x, s, c: x[:, s:s + c])
+        self.row_block = row_block or (lambda x, s, c: x[s:s + c])
+        # called with True before the first product that runs beside a reduction and with
+        # False after the last one (the GPU harness reserves SMs for the collective there)
+        self.overlapped = overlapped or (lambda on: None)
 
     def step(self, A, B_shard, dC_shard, C_shard, dA, dB_shard, between: Callable = None):
         """C = A*B; dA += dC*B^T (all-reduced); dB += A^T*dC.  Gradients are zeroed first, as
@@ -38,11 +53,24 @@ class ShardedProd:
         self.gemm(A, B_shard, C_shard, False, False, False)
         if between:
             between(0)
-        self.gemm(dC_shard, B_shard, dA, False, True, True)
+        waits = []
+        k = dA.shape[1]
+        for p in range(self.panels):
+            s, c = column_shard(k, self.panels, p)
+            if c == 0:
+                continue
+            if waits:
+                self.overlapped(True)
+            # columns [s, s+c) of dA = dC * (rows [s, s+c) of B)^T
+            self.gemm(dC_shard, self.row_block(B_shard, s, c), self.col_block(dA, s, c), False,
+                      True, True)
+            waits.append(self.allreduce_async(self.col_block(dA, s, c)))
         if between:
             between(1)
-        wait = self.allreduce_async(dA)
+        self.overlapped(True)
         self.gemm(A, dC_shard, dB_shard, True, False, True)
+        self.overlapped(False)
         if between:
             between(2)
-        wait()
+        for w in waits:
+            w()

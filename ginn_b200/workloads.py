@@ -22,6 +22,33 @@ def _xavier(rows, cols, gen, device):
     return buf.T  # column-major rows x cols
 
 
+class AffineLayer:
+    """One AffineNode forward + backward with tanh through the fused entry points (config 1 at
+    m, n, k = 512, 128, 784; config 5's hidden layer at 1024, 4096, 1024).  Gradients are zeroed
+    every step, as Graph::reset_grad does."""
+
+    def __init__(self, device, m, n, k, half=False, seed=20241):
+        g = torch.Generator(device=device).manual_seed(seed)
+        tdt = torch.float16 if half else torch.float32
+        self.W = _xavier(m, k, g, device).to(tdt)
+        self.X = torch.randn(n, k, device=device, generator=g).to(tdt).T
+        self.b = _xavier(m, 1, g, device).reshape(-1).contiguous().to(tdt)
+        self.dY = torch.randn(n, m, device=device, generator=g).to(tdt).T
+        self.Y = B.colmajor(m, n, tdt, device, fill=0.0)
+        self.dW, self.dX = B.colmajor(m, k, tdt, device, fill=0.0), B.colmajor(k, n, tdt, device, fill=0.0)
+        self.db = torch.zeros(m, device=device, dtype=tdt)
+        self.flops = 3 * 2 * m * n * k
+        self.units = 1
+
+    def step(self):
+        self.dW.zero_()
+        self.dX.zero_()
+        self.db.zero_()
+        B.affine_forward([B.Pair(self.W, self.X)], self.b, B.ACT_TANH, self.Y)
+        B.affine_backward([B.PairGrad(self.W, self.X, self.dW, self.dX)], self.dY, self.Y,
+                          B.ACT_TANH, self.db)
+
+
 class Attention:
     """Config 3: min-GPT attention through BatchedProd (examples/min-gpt.cu.cpp:108-157):
     S = K' * Q, column softmax, O = V * P, and the four backward products; 256 (batch, head)

@@ -5,7 +5,7 @@ import torch
 
 from oracle import oracle as orc
 from ginn_b200 import binding as B
-from helpers import check, randn
+from helpers import check, check_elementwise, randn
 
 pytestmark = pytest.mark.gpu
 ACTS = [orc.ACT_NONE, orc.ACT_TANH, orc.ACT_SIGMOID, orc.ACT_RELU]
@@ -104,6 +104,33 @@ def test_forward_backward_config1_shape(gpu, dt, act):
     check(B.to_host(dX), tw(g["db"][0]), dt, "dX")
     check(B.to_host(dV), tw(g["da"][1]), dt, "dV")
     check(B.to_host(db), tw(g["dbias"]), dt, "db")
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+@pytest.mark.parametrize("act", [orc.ACT_NONE, orc.ACT_SIGMOID])
+def test_reference_elementwise_rule_on_affine(gpu, dt, act):
+    """The reference compares every element of the value and of every gradient between its CPU
+    and GPU runs (test/check_node.h:104-119: within eps relatively, or both near zero) on
+    well-scaled inputs; the same rule on a two-pair Affine with positive operands, so that no
+    element is a difference of large numbers."""
+    rng = np.random.default_rng(41 + act)
+    m, n, k1, k2 = 130, 70, 96, 40
+    pos = lambda shape, s: (np.abs(rng.standard_normal(shape)) * s + 0.1 * s).astype(dt)
+    W, V, X, H, b = pos((m, k1), 0.02), pos((m, k2), 0.02), pos((k1, n), 1), pos((k2, n), 1), pos(m, 0.1)
+    dY = pos((m, n), 1)
+    Wd, Vd, Xd, Hd, bd, dYd = map(B.from_host, (W, V, X, H, b, dY))
+    Y = B.colmajor(m, n, Wd.dtype, fill=0.0)
+    gpu.affine_forward([gpu.Pair(Wd, Xd), gpu.Pair(Vd, Hd)], bd, act, Y)
+    dW, dX, dV, dH = zeros_like_cm(Wd), zeros_like_cm(Xd), zeros_like_cm(Vd), zeros_like_cm(Hd)
+    db = torch.zeros(m, device="cuda", dtype=Wd.dtype)
+    gpu.affine_backward([gpu.PairGrad(Wd, Xd, dW, dX), gpu.PairGrad(Vd, Hd, dV, dH)], dYd, Y, act, db)
+    torch.cuda.synchronize()
+    y = B.to_host(Y)
+    check_elementwise(y, orc.affine_forward([(W, X), (V, H)], b, act), dt, "value")
+    g = orc.affine_backward([(W, X), (V, H)], dY, y, act, dt)
+    for got, ref, what in [(dW, g["da"][0], "dW"), (dX, g["db"][0], "dX"), (dV, g["da"][1], "dV"),
+                           (dH, g["db"][1], "dH"), (db, g["dbias"], "db")]:
+        check_elementwise(B.to_host(got), np.asarray(ref), dt, what)
 
 
 def test_bias_gradient_alone(gpu):

@@ -175,6 +175,35 @@ def test_large_half_product_by_linearity(gpu):
     assert ((lhs - rhs).norm() / rhs.norm()).item() < 5e-3
 
 
+def test_large_half_products_against_sampled_oracle(gpu):
+    """C4 size (8192^3), all three products of the pass: 32 sampled rows x 64 sampled columns of
+    every result against the fp64 oracle on exactly the operands the GPU used (the full fp64
+    product would be hours of host time; a sampled block is a few GFLOP)."""
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(6)
+    A = torch.randn(n, n, device="cuda", generator=g).half().T
+    Bm = torch.randn(n, n, device="cuda", generator=g).half().T
+    dC = torch.randn(n, n, device="cuda", generator=g).half().T
+    rs = np.random.default_rng(7)
+    rows = torch.as_tensor(np.sort(rs.choice(n, 32, replace=False)), device="cuda")
+    cols = torch.as_tensor(np.sort(rs.choice(n, 64, replace=False)), device="cuda")
+    host = lambda t: t.cpu().numpy()
+    out = torch.empty(n, n, device="cuda", dtype=torch.float16).T
+    gpu.gemm(A, Bm, out)                                         # C = A B
+    torch.cuda.synchronize()
+    check(host(out[rows][:, cols]), orc.gemm(host(A[rows]), host(Bm[:, cols])), np.float16, "C")
+    out.zero_()
+    gpu.gemm(dC, Bm, out, trans_b=True, accumulate=True)         # dA += dC B^T
+    torch.cuda.synchronize()
+    check(host(out[rows][:, cols]), orc.gemm(host(dC[rows]), host(Bm[cols]), trans_b=True),
+          np.float16, "dA")
+    out.zero_()
+    gpu.gemm(A, dC, out, trans_a=True, accumulate=True)          # dB += A^T dC
+    torch.cuda.synchronize()
+    check(host(out[rows][:, cols]), orc.gemm(host(A[:, rows]), host(dC[:, cols]), trans_a=True),
+          np.float16, "dB")
+
+
 def test_fp32_accuracy_holds_at_large_k(gpu):
     """dW of the MLP config contracts over the 4096-column batch."""
     rng = np.random.default_rng(18)

@@ -8,7 +8,7 @@ import torch
 from oracle import oracle as orc
 from ginn_b200 import binding as B
 from ginn_b200.binding import GROUPED_DW, GROUPED_DX, GROUPED_FORWARD
-from helpers import check, randn
+from helpers import check, check_elementwise, randn
 
 pytestmark = pytest.mark.gpu
 
@@ -50,6 +50,40 @@ def test_level_equals_per_node_products(gpu, specs):
         check(np.stack([B.to_host(t) for t in dx], 1), 1 + orc.gemm(W, DY, trans_a=True), np.float32, "dX")
         check(B.to_host(dw), 1 + orc.gemm(DY, X, trans_b=True), np.float32, "dW")
         check(B.to_host(db), 1 + DY.astype(np.float64).sum(1), np.float32, "dbias")
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_reference_elementwise_rule_on_a_level(gpu, dt):
+    """Every element of every result of a level within the reference's per-element rule
+    (test/check_node.h:104-119), on positive, well-scaled operands as in its own tests."""
+    rng = np.random.default_rng(43)
+    tdt = torch.float32 if dt == np.float32 else torch.float16
+    pos = lambda shape, s: (np.abs(rng.standard_normal(shape)) * s + 0.1 * s).astype(dt)
+    specs = [(200, 96, 37), (64, 40, 130)]
+    groups, host = [], []
+    for m, k, nc in specs:
+        W, bias = pos((m, k), 0.02), pos(m, 0.1)
+        xs, dys = [pos(k, 1) for _ in range(nc)], [pos(m, 1) for _ in range(nc)]
+        host.append((W, bias, xs, dys))
+        groups.append(dict(w=B.from_host(W), bias=B.from_host(bias),
+                           x=[B.from_host(x) for x in xs], dy=[B.from_host(d) for d in dys]))
+    ys = [[torch.zeros(g["w"].shape[0], device="cuda", dtype=tdt) for _ in g["x"]] for g in groups]
+    dxs = [[torch.zeros(g["w"].shape[1], device="cuda", dtype=tdt) for _ in g["x"]] for g in groups]
+    dws = [B.colmajor(*g["w"].shape, tdt, fill=0.0) for g in groups]
+    dbs = [torch.zeros(g["w"].shape[0], device="cuda", dtype=tdt) for g in groups]
+    gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=y, bias=g["bias"])
+                                  for g, y in zip(groups, ys)])
+    gpu.grouped(GROUPED_DX, [gpu.Group(w=g["w"], y_cols=g["dy"], dx_cols=dx)
+                             for g, dx in zip(groups, dxs)])
+    gpu.grouped(GROUPED_DW, [gpu.Group(w=g["w"], x_cols=g["x"], y_cols=g["dy"], dw=dw, dbias=db)
+                             for g, dw, db in zip(groups, dws, dbs)])
+    torch.cuda.synchronize()
+    for (W, bias, xs, dys), y, dx, dw, db in zip(host, ys, dxs, dws, dbs):
+        X, DY = np.stack(xs, 1), np.stack(dys, 1)
+        check_elementwise(np.stack([B.to_host(t) for t in y], 1), orc.affine_forward([(W, X)], bias, 0), dt, "fwd")
+        check_elementwise(np.stack([B.to_host(t) for t in dx], 1), orc.gemm(W, DY, trans_a=True), dt, "dX")
+        check_elementwise(B.to_host(dw), orc.gemm(DY, X, trans_b=True), dt, "dW")
+        check_elementwise(B.to_host(db), DY.astype(np.float64).sum(1).astype(dt), dt, "dbias")
 
 
 def test_unaligned_column_vectors(gpu):

@@ -3,6 +3,7 @@ for the GPU products: the sharded pass must reproduce the unsharded one."""
 import os
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -20,7 +21,7 @@ def test_column_shard_covers_everything():
         assert cols == list(range(n))
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, panels=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     rng = np.random.default_rng(3)                      # same stream on every rank: global data
@@ -38,14 +39,18 @@ def _worker(rank, world, port, q):
         x[...] = 0
 
     def allreduce_async(x):
-        t = torch.from_numpy(x)
+        t = torch.from_numpy(np.ascontiguousarray(x))   # a column panel is a strided view here
         work = dist.all_reduce(t, async_op=True)
-        return work.wait
+
+        def wait():
+            work.wait()
+            x[...] = t.numpy()
+        return wait
 
     C = np.empty((m, c), np.float32)
     dA = np.full((m, k), 7.0, np.float32)               # stale values must be zeroed by the step
     dB = np.full((k, c), 7.0, np.float32)
-    ShardedProd(gemm, zero, allreduce_async).step(A, Bs, dCs, C, dA, dB)
+    ShardedProd(gemm, zero, allreduce_async, panels=panels).step(A, Bs, dCs, C, dA, dB)
     ok = (np.allclose(C, A @ Bs, rtol=1e-5, atol=1e-5)
           and np.allclose(dA, dCf @ Bf.T, rtol=1e-4, atol=1e-4)
           and np.allclose(dB, A.T @ dCs, rtol=1e-5, atol=1e-5))
@@ -53,11 +58,12 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_sharded_prod_matches_unsharded_on_two_ranks():
+@pytest.mark.parametrize("panels", [1, 3])
+def test_sharded_prod_matches_unsharded_on_two_ranks(panels):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    port = 29500 + (os.getpid() + 7 * panels) % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, panels)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in procs]
