@@ -417,10 +417,11 @@ class ProdShard:
         events (durations are read after the timed region)."""
         import torch
         self.events = []
-        self.step()
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record()
-        evs, self.events = self.events + [ev], None
+        after_gemms = torch.cuda.Event(enable_timing=True)
+        self.step(between=lambda i: after_gemms.record() if i == 2 else None)
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()                      # after the waits for the reductions
+        evs, self.events = self.events + [after_gemms, end], None
         return evs
 
     def parity(self) -> dict:
@@ -667,8 +668,12 @@ def run_gpu(args):
     launches = gb.launch_count() - launches0
     clocks = sampler.stop() if sampler else None
     ms = D.max_over_ranks(e0.elapsed_time(e1) / args.steps)
-    gemm_ms = sum(evs[0].elapsed_time(evs[-1]) for evs in gemm_events) / len(gemm_events)
-    launches_per_step = len(gemm_events[0]) - 1
+    gemm_ms = sum(evs[0].elapsed_time(evs[-2]) for evs in gemm_events) / len(gemm_events)
+    launches_per_step = len(gemm_events[0]) - 2
+    # mean duration of every product of a step, in launch order, and of the wait for the
+    # reductions that is left after the last product
+    breakdown = [sum(evs[i].elapsed_time(evs[i + 1]) for evs in gemm_events) / len(gemm_events)
+                 for i in range(launches_per_step + 1)]
     status = gb.device_status(D.local, True)
     if status != 0:
         raise RuntimeError(f"device status {status:#x} after the timed region")
@@ -744,6 +749,8 @@ def run_gpu(args):
         "roofline": roofline, "cpu_baseline": cpu_baseline, "parity": parity,
         "secondary": secondary or None, "configs": configs,
         "dA_panels": args.panels if world > 1 else 1, "sm_margin_beside_collectives": margin,
+        "step_breakdown_ms": {"products_in_launch_order": breakdown[:-1],
+                              "exposed_wait_for_reductions": breakdown[-1]},
     }
     print(json.dumps(line), flush=True)
     D.close()

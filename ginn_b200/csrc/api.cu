@@ -511,6 +511,78 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
   return ll;
 }
 
+// Stride (in elements) of a column table whose entries are equally spaced, i.e. the columns of
+// one strided matrix; -1 otherwise.  A single column fits any stride.
+long long table_stride(const void* const* t, int64_t n, int es, int64_t rows) {
+  if (n <= 1) return rows;
+  const char* p0 = static_cast<const char*>(t[0]);
+  const long long step = static_cast<const char*>(t[1]) - p0;
+  if (step < rows * es || step % es != 0) return -1;
+  for (int64_t j = 2; j < n; ++j)
+    if (static_cast<const char*>(t[j]) - p0 != step * j) return -1;
+  return step / es;
+}
+
+// A level whose column tables all describe plain strided matrices -- the nodes' tensors happen
+// to be the columns of one allocation, as with a bump allocator or a batched input -- needs no
+// tables at all: each group is an ordinary product, and an fp32 one whose operands a tensor map
+// can describe runs on the TMA-fed kernel (about twice the throughput of the cp.async front
+// end).  Returns true and the per-group problems when the whole level qualifies.
+bool direct_level(int dtype, int mode, int ngroups, const ginn_b200_group* groups, int num_sms,
+                  std::vector<Problem>* out) {
+  if (dtype != GINN_B200_F32 || t_force_path != PATH_AUTO) return false;
+  out->clear();
+  for (int g = 0; g < ngroups; ++g) {
+    const ginn_b200_group& q = groups[g];
+    if (q.m == 0 || q.k == 0 || q.ncols == 0) continue;
+    if (out->size() == 4) return false;  // many groups: one grouped launch serves them better
+    Problem p;
+    std::memset(&p, 0, sizeof(p));
+    p.npairs = 1;
+    p.batches = 1;
+    if (mode == GINN_B200_GROUPED_FORWARD || mode == GINN_B200_GROUPED_DX) {
+      const bool fwd = mode == GINN_B200_GROUPED_FORWARD;
+      const void* const* in = fwd ? q.x_cols : reinterpret_cast<const void* const*>(q.y_cols);
+      void* const* outc = fwd ? q.y_cols : q.dx_cols;
+      const int64_t in_rows = fwd ? q.k : q.m, out_rows = fwd ? q.m : q.k;
+      const long long ldi = table_stride(in, q.ncols, 4, in_rows);
+      const long long ldo = table_stride(reinterpret_cast<const void* const*>(outc), q.ncols, 4, out_rows);
+      if (ldi < 0 || ldo < 0) return false;
+      p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, fwd ? 0 : 1);
+      p.b[0] = make_operand(dtype, in[0], ldi, 0, 1, 1);
+      p.k[0] = in_rows;
+      p.M = (int)out_rows; p.N = (int)q.ncols;
+      p.c = outc[0]; p.ldc = ldo;
+      p.bias = fwd ? q.bias : nullptr;
+      p.accumulate = fwd ? (q.accumulate ? 1 : 0) : 1;
+    } else {
+      const long long ldy = table_stride(reinterpret_cast<const void* const*>(q.y_cols), q.ncols, 4, q.m);
+      const long long ldx = table_stride(q.x_cols, q.ncols, 4, q.k);
+      if (ldy < 0 || ldx < 0) return false;
+      p.a[0] = make_operand(dtype, q.y_cols[0], ldy, 0, 1, 0);
+      p.b[0] = make_operand(dtype, q.x_cols[0], ldx, 0, 1, 0);
+      p.k[0] = q.ncols;
+      p.M = (int)q.m; p.N = (int)q.k;
+      p.c = q.dw; p.ldc = q.lddw;
+      p.rowsum = q.dbias;
+      p.accumulate = 1;
+    }
+    if (p.k[0] > kMaxChainK || !gb::sgemm3x_supported(p)) return false;
+    const long long tiles = static_cast<long long>((p.M + 127) / 128) * ((p.N + 127) / 128);
+    p.split_k = gb::sgemm3x_pick_split(p, tiles, num_sms);
+    out->push_back(p);
+  }
+  return !out->empty();
+}
+
+int launch_direct_level(const std::vector<Problem>& probs, cudaStream_t stream, int* status) {
+  for (const Problem& p : probs) {
+    CU_TRY(gb::launch_sgemm3x(p, stream, status));
+    g_launches.fetch_add(1);
+  }
+  return GINN_B200_OK;
+}
+
 cudaError_t launch_level(int dtype, const LevelLaunch& ll, const Problem* dprobs,
                          cudaStream_t stream, int* status) {
   if (dtype == GINN_B200_F32)
@@ -723,6 +795,9 @@ int ginn_b200_grouped(int device, void* stream_, int dtype, int mode, int ngroup
   DevCtx* ctx;
   if (int s = get_ctx(device, &ctx)) return s;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  std::vector<Problem> direct;
+  if (direct_level(dtype, mode, ngroups, groups, ctx->num_sms, &direct))
+    return launch_direct_level(direct, stream, ctx->d_status);
   if (int s = refuse_capture(stream, "ginn_b200_grouped")) return s;
   unsigned char *h, *d;
   int half = 0;
@@ -781,6 +856,7 @@ struct ginn_b200_level {
   int dtype;
   LevelLaunch ll;
   unsigned char* d_image;
+  std::vector<Problem> direct;  // table-free form of the level (then d_image is null)
 };
 
 int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
@@ -791,8 +867,11 @@ int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
   if (int s = plan_level(dtype, mode, ngroups, groups, &plan)) return s;
   DevCtx* ctx;
   if (int s = get_ctx(device, &ctx)) return s;
-  ginn_b200_level* lv = new ginn_b200_level{device, dtype, LevelLaunch{}, nullptr};
-  if (plan.live > 0) {
+  ginn_b200_level* lv = new ginn_b200_level{device, dtype, LevelLaunch{}, nullptr, {}};
+  const bool direct =
+      plan.live > 0 && direct_level(dtype, mode, ngroups, groups, ctx->num_sms, &lv->direct);
+  if (!direct) lv->direct.clear();
+  if (plan.live > 0 && !direct) {
     std::vector<unsigned char> h(plan.bytes);
     cudaError_t e = cudaMalloc(&lv->d_image, plan.bytes);
     if (e == cudaSuccess) {
@@ -812,9 +891,11 @@ int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
 
 int ginn_b200_level_run(ginn_b200_level* level, void* stream) {
   if (level == nullptr) return fail(GINN_B200_BAD_ARGUMENT, "null level");
-  if (level->d_image == nullptr) return GINN_B200_OK;
+  if (level->d_image == nullptr && level->direct.empty()) return GINN_B200_OK;
   DevCtx* ctx;
   if (int s = get_ctx(level->device, &ctx)) return s;
+  if (!level->direct.empty())
+    return launch_direct_level(level->direct, static_cast<cudaStream_t>(stream), ctx->d_status);
   CU_TRY(launch_level(level->dtype, level->ll, reinterpret_cast<const Problem*>(level->d_image),
                       static_cast<cudaStream_t>(stream), ctx->d_status));
   g_launches.fetch_add(1);

@@ -30,7 +30,11 @@ def make_level(rng, specs):
     [(8, 5, 1)], [(1024, 384, 7)], [(1024, 384, 256)], [(96, 40, 100), (200, 64, 3), (33, 17, 45)],
     [(1024, 384, 150), (256, 256, 31)],
 ])
-def test_level_equals_per_node_products(gpu, specs):
+@pytest.mark.parametrize("path", [0, 5])
+def test_level_equals_per_node_products(gpu, specs, path):
+    """path 0: automatic (equally spaced columns collapse to a strided matrix and may run on
+    the TMA-fed kernel); path 5: always through the column tables."""
+    gpu.set_option("force_path", path)
     rng = np.random.default_rng(41)
     groups, host = make_level(rng, specs)
     ys = [[torch.zeros(g["w"].shape[0], device="cuda") for _ in g["x"]] for g in groups]
@@ -84,6 +88,43 @@ def test_reference_elementwise_rule_on_a_level(gpu, dt):
         check_elementwise(np.stack([B.to_host(t) for t in dx], 1), orc.gemm(W, DY, trans_a=True), dt, "dX")
         check_elementwise(B.to_host(dw), orc.gemm(DY, X, trans_b=True), dt, "dW")
         check_elementwise(B.to_host(db), DY.astype(np.float64).sum(1).astype(dt), dt, "dbias")
+
+
+@pytest.mark.parametrize("prepared", [False, True])
+def test_columns_of_one_matrix_need_no_tables(gpu, prepared):
+    """The nodes' vectors are the columns of one padded matrix (a batched input, or tensors
+    handed out back to back by a bump allocator): the level is then run as plain products.
+    Same results as through the tables; both the immediate and the prepared form."""
+    rng = np.random.default_rng(47)
+    m, k, n, ldx, ldy = 1024, 384, 300, 388, 1024
+    W, bias = randn(rng, (m, k), np.float32, 0.05), randn(rng, m, np.float32)
+    X, DY = randn(rng, (k, n), np.float32), randn(rng, (m, n), np.float32)
+    Wd, bd = B.from_host(W), B.from_host(bias)
+    Xd, DYd = B.from_host(X, ld=ldx), B.from_host(DY, ld=ldy)
+    cols = lambda t: [t[:, j] for j in range(t.shape[1])]
+    results = []
+    for path in (0, 5):
+        gpu.set_option("force_path", path)
+        Y = B.colmajor(m, n, torch.float32, ld=ldy, fill=0.0)
+        dX = B.colmajor(k, n, torch.float32, ld=ldx, fill=1.0)
+        dW, db = B.colmajor(m, k, torch.float32, fill=1.0), torch.ones(m, device="cuda")
+        calls = [(GROUPED_FORWARD, gpu.Group(w=Wd, x_cols=cols(Xd), y_cols=cols(Y), bias=bd)),
+                 (GROUPED_DX, gpu.Group(w=Wd, y_cols=cols(DYd), dx_cols=cols(dX))),
+                 (GROUPED_DW, gpu.Group(w=Wd, x_cols=cols(Xd), y_cols=cols(DYd), dw=dW, dbias=db))]
+        launches = gpu.launch_count()
+        for mode, grp in calls:
+            if prepared:
+                gpu.GroupedCall(mode, [grp])()
+            else:
+                gpu.grouped(mode, [grp])
+        torch.cuda.synchronize()
+        assert gpu.launch_count() == launches + 3
+        results.append([B.to_host(t) for t in (Y, dX, dW, db)])
+    for got in results:
+        check(got[0], orc.affine_forward([(W, X)], bias, 0), np.float32, "fwd")
+        check(got[1], 1 + orc.gemm(W, DY, trans_a=True), np.float32, "dX")
+        check(got[2], 1 + orc.gemm(DY, X, trans_b=True), np.float32, "dW")
+        check(got[3], 1 + DY.astype(np.float64).sum(1), np.float32, "dbias")
 
 
 def test_unaligned_column_vectors(gpu):
