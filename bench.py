@@ -938,10 +938,15 @@ def main():
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--force-path", type=int, default=0,
                     help="kernel choice override passed to the library (0 = automatic)")
+    ap.add_argument("--pdl", type=int, default=1,
+                    help="0: launch without programmatic dependent launch (A/B aid)")
     args = ap.parse_args()
     if args.force_path and args.impl != "reference":
         import ginn_b200
         ginn_b200.set_option("force_path", args.force_path)
+    if not args.pdl and args.impl != "reference":
+        import ginn_b200
+        ginn_b200.set_option("pdl", 0)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "affine_f32":

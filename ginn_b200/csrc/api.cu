@@ -24,6 +24,11 @@ std::atomic<long long> g_launches{0};
 thread_local int t_force_path = 0;
 thread_local int t_sm_margin = 0;     // SMs the persistent kernels leave free (e.g. for NCCL)
 thread_local int t_pair_group_m = 0;  // rasterisation group of the CTA-pair kernel (0 = default)
+thread_local int t_pdl = 1;           // programmatic dependent launch for the kernels that support it
+
+}  // namespace
+bool gb::pdl_enabled() { return t_pdl != 0; }
+namespace {
 
 int fail(int status, const char* fmt, ...) {
   char buf[512];
@@ -1103,6 +1108,10 @@ int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "pair_group_m") == 0) {
     if (value < 0 || value > 1024) return fail(GINN_B200_BAD_ARGUMENT, "pair_group_m must be 0..1024");
     t_pair_group_m = value;
+    return GINN_B200_OK;
+  }
+  if (name && std::strcmp(name, "pdl") == 0) {
+    t_pdl = value != 0;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "sm_margin") == 0) {

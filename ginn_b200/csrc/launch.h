@@ -9,6 +9,29 @@ struct CUtensorMap_st;  // CUDA driver tensor-map descriptor (cuda.h)
 
 namespace gb {
 
+// Whether kernels that support it are launched with programmatic dependent launch (option
+// "pdl" of the calling thread, default on).
+bool pdl_enabled();
+
+// Launch with the programmatic-stream-serialization attribute when `pdl` is set: the kernel may
+// begin while its predecessor in the stream drains; it must call pdl_wait() before it touches
+// global memory.  Kernel arguments must have the kernel's exact parameter types.
+template <typename... KArgs>
+cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, bool pdl, KArgs... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 // Allocation-free grouped launch (grouped_static.cu): descriptors live in a fixed array inside
 // the library image, and so does the status word its kernels report to.
 constexpr size_t kGroupedStaticBytes = 256 * 1024;

@@ -27,6 +27,17 @@ __device__ __forceinline__ void record_error(int* status, int code, int detail) 
   if (status) atomicCAS(status, 0, (code << 16) | (detail & 0xffff));
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running.  pdl_wait() blocks until that kernel has
+// completed and its writes are visible, so everything above it (barrier set-up, TMEM allocation)
+// overlaps the predecessor's tail; pdl_launch_dependents() lets the next kernel in the stream
+// begin its own prologue.  Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- addresses --------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -185,6 +185,10 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  // Everything above touched only shared and tensor memory; from here on the kernel reads what
+  // its predecessor in the stream may have written.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ===================== TMA producer =====================
@@ -523,6 +527,30 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
   const uint32_t planes_base = base;
   const uint32_t raws_base = base + PLANE_STAGES * PLANE_STAGE;
 
+  // Barrier set-up and the TMEM allocation need nothing from global memory: they run before
+  // the wait for the preceding kernel.
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int g = 0; g < 2; ++g)
+        for (int s = 0; s < 3; ++s) {
+          mbar_init(smem_u32(&raw_full[g][s]), 256);
+          mbar_init(smem_u32(&raw_empty[g][s]), 256);
+        }
+      for (int s = 0; s < PLANE_STAGES; ++s) {
+        mbar_init(smem_u32(&plane_full[s]), XFORM_THREADS);
+        mbar_init(smem_u32(&plane_empty[s]), 1);
+      }
+      mbar_init(smem_u32(&acc_full), 1);
+      fence_mbar_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+
   int tile = blockIdx.x;
   if (GROUPED) {
     int g = 0;
@@ -555,25 +583,6 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
   const int raw_stages = dop ? 2 : 3;
   const int raw_stage_bytes = dop ? 3 * RAW_TILE : 2 * RAW_TILE;
 
-  if (warp == 0) {
-    if (lane == 0) {
-      for (int g = 0; g < 2; ++g)
-        for (int s = 0; s < 3; ++s) {
-          mbar_init(smem_u32(&raw_full[g][s]), 256);
-          mbar_init(smem_u32(&raw_empty[g][s]), 256);
-        }
-      for (int s = 0; s < PLANE_STAGES; ++s) {
-        mbar_init(smem_u32(&plane_full[s]), XFORM_THREADS);
-        mbar_init(smem_u32(&plane_empty[s]), 1);
-      }
-      mbar_init(smem_u32(&acc_full), 1);
-      fence_mbar_init();
-    }
-    __syncwarp();
-    tmem_alloc(smem_u32(&tmem_slot), 512);
-    tmem_relinquish();
-    tc_fence_before();
-  }
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
@@ -786,8 +795,8 @@ cudaError_t launch_gather(const Problem& p, const Problem* dprobs, int nprobs, i
   const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  kern<<<total_tiles, GNTHREADS, smem, stream>>>(p, dprobs, nprobs, status);
-  return cudaGetLastError();
+  return launch_kernel(kern, dim3(total_tiles), dim3(GNTHREADS), smem, stream, pdl_enabled(), p,
+                       dprobs, nprobs, status);
 }
 
 bool operand_tma_ok(const Operand& o, int batches) {
@@ -866,8 +875,8 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   cudaError_t e = cudaFuncSetAttribute(sgemm3x_tma_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  sgemm3x_tma_kernel<<<static_cast<unsigned>(total), NTHREADS, smem, stream>>>(sp, status);
-  return cudaGetLastError();
+  return launch_kernel(sgemm3x_tma_kernel, dim3(static_cast<unsigned>(total)), dim3(NTHREADS), smem,
+                       stream, pdl_enabled(), sp, status);
 }
 
 // Number of K splits for a problem of `tiles` output tiles: only where partial sums can simply be

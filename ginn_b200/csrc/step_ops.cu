@@ -18,6 +18,7 @@
 //                      (Adam::update, ginn/update/update.h:115-133; m and v are always fp32)
 #include <cuda_fp16.h>
 #include "math.cuh"
+#include "ptx.cuh"
 #include "launch.h"
 
 namespace gb {
@@ -284,6 +285,8 @@ lstm_cell_forward_kernel(float* __restrict__ gates, long long ldg, const float* 
                          long long ldcp, float* __restrict__ c, long long ldc, float* __restrict__ h,
                          long long ldh, float* __restrict__ xh_next, long long ldx, int H,
                          long long n, long long n_next) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   const long long col = blockIdx.y;
   if (r >= H || col >= n) return;
@@ -309,6 +312,8 @@ lstm_cell_backward_kernel(const float* __restrict__ gates, long long ldg, const 
                           const float* __restrict__ dc_next, long long lddc, float dh_end,
                           float* __restrict__ dgates, long long lddg, float* __restrict__ dc_out,
                           long long lddo, int H, long long n, long long n_next) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   const long long col = blockIdx.y;
   if (r >= H || col >= n) return;
@@ -493,9 +498,8 @@ cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c
   if (H <= 0 || n <= 0) return cudaSuccess;
   if (n > 65535) return cudaErrorInvalidValue;
   dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
-  lstm_cell_forward_kernel<<<grid, 256, 0, stream>>>(gates, ldg, c_prev, ldcp, c, ldc, h, ldh,
-                                                     xh_next, ldx, H, n, n_next);
-  return cudaGetLastError();
+  return launch_kernel(lstm_cell_forward_kernel, grid, dim3(256), 0, stream, pdl_enabled(), gates,
+                       ldg, c_prev, ldcp, c, ldc, h, ldh, xh_next, ldx, H, n, n_next);
 }
 
 cudaError_t launch_lstm_cell_backward(const float* gates, long long ldg, const float* c,
@@ -507,10 +511,9 @@ cudaError_t launch_lstm_cell_backward(const float* gates, long long ldg, const f
   if (H <= 0 || n <= 0) return cudaSuccess;
   if (n > 65535) return cudaErrorInvalidValue;
   dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
-  lstm_cell_backward_kernel<<<grid, 256, 0, stream>>>(gates, ldg, c, ldc, c_prev, ldcp, dh_next,
-                                                      lddh, dc_next, lddc, dh_end, dgates, lddg,
-                                                      dc_out, lddo, H, n, n_next);
-  return cudaGetLastError();
+  return launch_kernel(lstm_cell_backward_kernel, grid, dim3(256), 0, stream, pdl_enabled(), gates,
+                       ldg, c, ldc, c_prev, ldcp, dh_next, lddh, dc_next, lddc, dh_end, dgates, lddg,
+                       dc_out, lddo, H, n, n_next);
 }
 
 cudaError_t launch_adam(int dtype, void* w, void* d, float* m, float* v, long long n, float clip,
