@@ -24,10 +24,12 @@ std::atomic<long long> g_launches{0};
 thread_local int t_force_path = 0;
 thread_local int t_sm_margin = 0;     // SMs the persistent kernels leave free (e.g. for NCCL)
 thread_local int t_pair_group_m = 0;  // rasterisation group of the CTA-pair kernel (0 = default)
+thread_local int t_max_split = 0;     // cap on the K split of fp32 products (0 = none, 1 = no split)
 thread_local int t_pdl = 1;           // programmatic dependent launch for the kernels that support it
 
 }  // namespace
 bool gb::pdl_enabled() { return t_pdl != 0; }
+int gb::max_split() { return t_max_split; }
 namespace {
 
 int fail(int status, const char* fmt, ...) {
@@ -144,11 +146,16 @@ int run_problem_once(DevCtx* ctx, int dtype, Problem& p, cudaStream_t stream) {
   } else if (dtype == GINN_B200_F32 &&
              (gb::sgemm3x_supported(p) || gb::sgemm3x_gather_supported(p))) {
     const long long tiles = static_cast<long long>((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batches;
-    p.split_k = gb::sgemm3x_pick_split(p, tiles, ctx->num_sms);
-    if (force != PATH_GATHER && gb::sgemm3x_supported(p))
+    if (force != PATH_GATHER && gb::sgemm3x_supported(p)) {
+      // The TMA-fed launcher can split any single-pair product: it zeroes C for an assignment
+      // and applies an activation in a pass of its own.
+      p.split_k = gb::sgemm3x_pick_split(p, tiles, ctx->num_sms, true);
       CU_TRY(gb::launch_sgemm3x(p, stream, ctx->d_status));
-    else
+      if (p.split_k > 1 && p.act != gb::ACT_NONE) g_launches.fetch_add(1);
+    } else {
+      p.split_k = gb::sgemm3x_pick_split(p, tiles, ctx->num_sms);
       CU_TRY(gb::launch_sgemm3x_gather(p, stream, ctx->d_status));
+    }
   } else if (dtype == GINN_B200_F16 && gb::hgemm_gather_supported(p)) {
     CU_TRY(gb::launch_hgemm_gather(p, stream, ctx->d_status));
   } else {
@@ -1108,6 +1115,11 @@ int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "pair_group_m") == 0) {
     if (value < 0 || value > 1024) return fail(GINN_B200_BAD_ARGUMENT, "pair_group_m must be 0..1024");
     t_pair_group_m = value;
+    return GINN_B200_OK;
+  }
+  if (name && std::strcmp(name, "max_split") == 0) {
+    if (value < 0 || value > 32) return fail(GINN_B200_BAD_ARGUMENT, "max_split must be 0..32");
+    t_max_split = value;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "pdl") == 0) {

@@ -12,6 +12,8 @@ namespace gb {
 // Whether kernels that support it are launched with programmatic dependent launch (option
 // "pdl" of the calling thread, default on).
 bool pdl_enabled();
+// Cap on the K split of fp32 products (option "max_split" of the calling thread; 0 = no cap).
+int max_split();
 
 // Launch with the programmatic-stream-serialization attribute when `pdl` is set: the kernel may
 // begin while its predecessor in the stream drains; it must call pdl_wait() before it touches
@@ -80,7 +82,8 @@ bool tmap_encoder_available();
 bool sgemm3x_supported(const Problem& p);
 cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status);
 
-int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms);
+// K split for a problem with `tiles` output tiles (see the definition for the rules).
+int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms, bool tma_path = false);
 // Same pipeline with a cp.async gather front end: any alignment, column tables, grouped launches.
 bool sgemm3x_gather_supported(const Problem& p);
 cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status);
@@ -115,6 +118,10 @@ cudaError_t launch_softmax_backward(int dtype, const void* y, long long ldy, con
 cudaError_t launch_pick_nll_backward(int dtype, const void* smax, long long lds, const int* index,
                                      const void* grad, void* dx, long long lddx, int rows,
                                      long long cols, cudaStream_t stream);
+// c = act(c) in place, fp32, every matrix of a strided batch (the activation of a product whose
+// contraction was split over CTAs).
+cudaError_t launch_act_inplace_f32(float* c, long long ldc, long long stride, int act, int m, int n,
+                                   int batches, cudaStream_t stream);
 // y = act(y + bias) in place, fp16, n <= 65535.
 cudaError_t launch_bias_act_half(void* y, long long ldy, const void* bias, int act, int m,
                                  long long n, cudaStream_t stream);

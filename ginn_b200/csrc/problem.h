@@ -52,9 +52,10 @@ struct Problem {
   // tile bookkeeping (filled by the launcher)
   int tiles_m, tiles_n;
   int tile_start;         // first linear tile index of this problem inside a grouped launch
-  // Split of the contraction over `split_k` CTAs per output tile (fp32 tensor-core kernels only;
-  // needs accumulate = 1, no activation, one pair): every CTA adds its partial sum to C with
-  // atomic adds, the first one of a tile also the bias.  0 or 1 = no split.
+  // Split of the contraction over `split_k` CTAs per output tile (fp32 tensor-core kernels only,
+  // one pair): every CTA adds its partial sum to C with atomic adds, the first one of a tile
+  // also the bias.  0 or 1 = no split.  The gather kernels split only products that add and have
+  // no activation; the TMA-fed launcher handles the rest around the kernel.
   int split_k;
 };
 

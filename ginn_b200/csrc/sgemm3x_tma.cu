@@ -17,6 +17,8 @@
 // three accumulators (k-block j goes to accumulator j mod 3), the small cross terms use a
 // fourth, and the epilogue adds the four in fp32 with round-to-nearest.
 #include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include "ptx.cuh"
 #include "math.cuh"
@@ -54,13 +56,61 @@ struct SParams {
   float* rowsum;
   int act;
   int accumulate;
-  int split_k;  // CTAs per output tile along K (1 = none); > 1 only with accumulate and no act
+  int split_k;  // CTAs per output tile along K (1 = none): partial sums are added atomically
   int batches;
+#ifdef GB_PHASE_TIMES
+  int dbg;  // instrumented build only: 1 = skip the stores, 2 = skip the tensor-memory loads
+#endif
 };
 
-// Out of line on purpose: thirty-two inlined copies of the precise tanh per epilogue would make
-// up most of the kernel's code.
-__device__ __noinline__ float act_forward_f32(int act, float x) { return act_forward<float>(act, x); }
+// Inline: with the short tanh of math.cuh eight copies per pass are cheaper than eight calls
+// (measured on a 128 x 128 tile: 7.5 against 11.4 thousand cycles for the tanh epilogue).
+__device__ __forceinline__ float act_forward_f32(int act, float x) { return act_forward<float>(act, x); }
+
+// Sum of the four accumulators for eight consecutive columns of this thread's row (warp
+// collective: every lane takes part in the tensor-memory loads).
+__device__ __forceinline__ void load_acc8(uint32_t taddr, int nkb, float (&acc)[8]) {
+  uint32_t v0[8], v1[8], v2[8], v3[8];
+  if (nkb > 0) tmem_ld8(taddr + CROSS_COL, v0);
+  if (nkb > 0) tmem_ld8(taddr, v1);
+  if (nkb > 1) tmem_ld8(taddr + SBN, v2);
+  if (nkb > 2) tmem_ld8(taddr + 2 * SBN, v3);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float t = 0.f;
+    if (nkb > 0) t = __uint_as_float(v0[j]) + __uint_as_float(v1[j]);
+    if (nkb > 1) t += __uint_as_float(v2[j]);
+    if (nkb > 2) t += __uint_as_float(v3[j]);
+    acc[j] = t;
+  }
+}
+
+// Eight results of one row into C: `dst` addresses the first, consecutive columns are `ldc`
+// elements apart, the first `nvalid` exist.  mode 0: store, 1: add to the previous C, 2: atomic
+// add (partial sum of a split contraction).  The bounds test is compiled out for full groups.
+template <bool FULL>
+__device__ __forceinline__ void store_acc8(float* dst, long long ldc, int nvalid, float (&acc)[8],
+                                           float bias, int mode, int act) {
+  if (mode == 1) {
+    float old[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) old[j] = (FULL || j < nvalid) ? dst[j * ldc] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += old[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float v = acc[j] + bias;
+    if (mode != 2 && act != ACT_NONE) v = act_forward_f32(act, v);
+    if (FULL || j < nvalid) {
+      if (mode == 2)
+        atomicAdd(dst + j * ldc, v);
+      else
+        dst[j * ldc] = v;
+    }
+  }
+}
 
 // Transform of a k-contiguous raw slice: it already is K-major and swizzled (TMA box 32 k x 128
 // outer with the 128-byte swizzle), so hi and lo go to the same offsets of their planes.
@@ -131,6 +181,13 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   __shared__ __align__(8) uint64_t plane_empty[PLANE_STAGES];
   __shared__ __align__(8) uint64_t acc_full;
   __shared__ uint32_t tmem_slot;
+#ifdef GB_PHASE_TIMES
+  __shared__ long long ph_t[12];
+  if (threadIdx.x == 0) ph_t[0] = clock64();
+#define PH(i) do { ph_t[i] = clock64(); } while (0)
+#else
+#define PH(i) do { } while (0)
+#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -187,8 +244,10 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   const uint32_t tmem = tmem_slot;
   // Everything above touched only shared and tensor memory; from here on the kernel reads what
   // its predecessor in the stream may have written.
+  if (threadIdx.x == 0) PH(1);
   pdl_wait();
   pdl_launch_dependents();
+  if (threadIdx.x == 0) PH(2);
 
   if (warp == 0) {
     // ===================== TMA producer =====================
@@ -248,6 +307,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       uint32_t ph = 0;
       for (int it = 0; it < nkb; ++it) {
         if (!mbar_wait(smem_u32(&plane_full[s]), ph, status, DEV_TIMEOUT_FULL, it)) break;
+        if (it == 0) PH(4);
         tc_fence_after();
         const uint32_t a_hi = planes_base + s * PLANE_STAGE;
         const uint32_t a_lo = a_hi + PLANE;
@@ -272,6 +332,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
         }
       }
       tc_commit(smem_u32(&acc_full));
+      PH(5);
     }
     __syncwarp();
   } else {
@@ -292,6 +353,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
         ok = false;
         break;
       }
+      if (it == 0 && threadIdx.x == 64) PH(3);
       const uint8_t* raw_stage = base_ptr + PLANE_STAGES * PLANE_STAGE + rs_i * raw_stage_bytes;
       const uint8_t* src = raw_stage + grp * RAW_TILE;
       const uint8_t* ysrc = raw_stage + 2 * RAW_TILE;
@@ -330,56 +392,53 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     if (want_rowsum && ok && m0 + (t & 127) < p.M) atomicAdd(p.rowsum + m0 + (t & 127), rs);
 
     // ===================== epilogue (all sixteen warps; 32 columns each) =====================
-    if (ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
+    const int q = warp & 3;
+    const int cgrp = (warp - 2) >> 2;  // 0..3
+    const int row = m0 + q * 32 + lane;
+    const bool row_ok = row < p.M;
+    // fetched before the wait for the accumulator, so that its latency hides behind the MMAs
+    const float bias = (p.bias != nullptr && row_ok && split == 0) ? p.bias[row] : 0.f;  // once per tile
+    const bool epi_ok = ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0);
+    if (threadIdx.x == 64) PH(6);
+    float* crow = p.C + static_cast<long long>(batch) * p.strideC + row;
+    const int c0 = cgrp * 32;
+    const bool split_k = p.split_k > 1;
+    if (epi_ok) {
       tc_fence_after();
-      const int q = warp & 3;
-      const int cgrp = (warp - 2) >> 2;  // 0..3
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const float bias = (p.bias != nullptr && row_ok && split == 0) ? p.bias[row] : 0.f;  // once per tile
-      float* crow = p.C + static_cast<long long>(batch) * p.strideC + row;
-      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
-      const int c0 = cgrp * 32;
-      const bool split_k = p.split_k > 1;
-      const bool load_c = p.accumulate && row_ok && !split_k;
-      // eight columns per pass, not unrolled (code size: see the gather kernel's epilogue)
+      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16) + c0;
+      const long long ldc = p.ldc;
+      const int mode = split_k ? 2 : (p.accumulate ? 1 : 0);
+      const int act = p.act;  // none when the contraction is split: a pass over C follows
+      const int ncols = p.N - (n0 + c0);  // columns of this warp's group that exist (may be <= 0)
+      float* dst = crow + static_cast<long long>(n0 + c0) * ldc;
+      // eight columns per pass, not unrolled (code size: a CTA runs this once, from a cold
+      // instruction cache); the per-element work is a pointer increment, an add and a store.
+      // (Issuing the next pass's tensor-memory loads ahead of this pass's stores was tried and
+      // made a pass half as long again.)
 #pragma unroll 1
-      for (int c = 0; c < 32; c += 8) {
+      for (int c = 0; c < 32 && c < ncols; c += 8, dst += 8 * ldc) {
         float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int col = n0 + c0 + c + j;
-          acc[j] = bias + ((load_c && col < p.N) ? crow[static_cast<long long>(col) * p.ldc] : 0.f);
+#ifdef GB_PHASE_TIMES
+        if (p.dbg & 2) {
+          for (int j = 0; j < 8; ++j) acc[j] = 1.f;
+        } else
+#endif
+        load_acc8(tbase + c, nkb, acc);
+#ifdef GB_PHASE_TIMES
+        if (p.dbg & 1) {
+          if (acc[0] + acc[3] + acc[7] == 12345.f) dst[0] = acc[1];
+          continue;
         }
-        uint32_t v0[8], v1[8], v2[8], v3[8];
-        if (nkb > 0) tmem_ld8(tbase + CROSS_COL + c0 + c, v0);
-        if (nkb > 0) tmem_ld8(tbase + c0 + c, v1);
-        if (nkb > 1) tmem_ld8(tbase + SBN + c0 + c, v2);
-        if (nkb > 2) tmem_ld8(tbase + 2 * SBN + c0 + c, v3);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float t = 0.f;
-          if (nkb > 0) t = __uint_as_float(v0[j]) + __uint_as_float(v1[j]);
-          if (nkb > 1) t += __uint_as_float(v2[j]);
-          if (nkb > 2) t += __uint_as_float(v3[j]);
-          acc[j] += t;
-        }
+#endif
         if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int col = n0 + c0 + c + j;
-            if (col < p.N) {
-              float* dst = crow + static_cast<long long>(col) * p.ldc;
-              if (split_k)
-                atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
-              else
-                *dst = (p.act == ACT_NONE ? acc[j] : act_forward_f32(p.act, acc[j]));
-            }
-          }
+          if (ncols - c >= 8)
+            store_acc8<true>(dst, ldc, 8, acc, bias, mode, act);
+          else
+            store_acc8<false>(dst, ldc, ncols - c, acc, bias, mode, act);
         }
       }
     }
+    if (threadIdx.x == 64) PH(7);
   }
 
   tc_fence_before();
@@ -388,6 +447,15 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+#ifdef GB_PHASE_TIMES
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const long long t9 = clock64();
+    printf("phase cycles: prologue %lld pdl_wait %lld first_raw %lld first_plane %lld mma_issued %lld "
+           "acc_ready %lld epilogue %lld exit %lld  (nkb %d)\n",
+           ph_t[1] - ph_t[0], ph_t[2] - ph_t[1], ph_t[3] - ph_t[2], ph_t[4] - ph_t[3],
+           ph_t[5] - ph_t[4], ph_t[6] - ph_t[5], ph_t[7] - ph_t[6], t9 - ph_t[7], nkb);
+  }
+#endif
 }
 
 
@@ -720,59 +788,57 @@ sgemm3x_gather_kernel(const __grid_constant__ Problem p0, const Problem* __restr
       atomicAdd(static_cast<float*>(P.rowsum) + m0 + (t & 127), rs);
 
     // ===================== epilogue (sixteen warps; 32 columns each) =====================
+    const int q = warp & 3;
+    const int c0 = ((warp - 1) >> 2) * 32;
+    const int row = m0 + q * 32 + lane;
+    const bool row_ok = row < P.M;
+    // fetched before the wait for the accumulator, so that its latency hides behind the MMAs
+    const float bias = (P.bias != nullptr && row_ok && split == 0)
+                           ? static_cast<const float*>(P.bias)[row] : 0.f;  // once per tile
     if (ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0)) {
       tc_fence_after();
-      const int q = warp & 3;
-      const int c0 = ((warp - 1) >> 2) * 32;
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < P.M;
-      const float bias = (P.bias != nullptr && row_ok && split == 0)
-                             ? static_cast<const float*>(P.bias)[row] : 0.f;  // once per tile
-      float* cbase = static_cast<float*>(P.c) + batch * P.c_batch_stride;
-      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16);
-      const bool split_k = nsplit > 1;
-      const bool load_c = P.accumulate && !split_k && row_ok;
+      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16) + c0;
+      const int mode = nsplit > 1 ? 2 : (P.accumulate ? 1 : 0);
       void* const* ccols = P.ccols;
       const long long ldc = P.ldc;
-      const int N = P.N, act = P.act;
+      const int act = P.act;
+      const int ncols = P.N - (n0 + c0);
+      float* dst = static_cast<float*>(P.c) + batch * P.c_batch_stride +
+                   static_cast<long long>(n0 + c0) * ldc + row;
       // Eight columns per pass, not unrolled: a kernel that serves 2-k-block tiles runs its code
-      // once per CTA, from a cold instruction cache, and a 32-fold unrolled epilogue was more
-      // than half of it.
+      // once per CTA, from a cold instruction cache.
 #pragma unroll 1
-      for (int c = 0; c < 32; c += 8) {
+      for (int c = 0; c < 32 && c < ncols; c += 8, dst += 8 * ldc) {
         float acc[8];
+        load_acc8(tbase + c, nkb, acc);
+        if (!row_ok) continue;
+        if (ccols == nullptr) {
+          if (ncols - c >= 8)
+            store_acc8<true>(dst, ldc, 8, acc, bias, mode, act);
+          else
+            store_acc8<false>(dst, ldc, ncols - c, acc, bias, mode, act);
+        } else {
+          // every column at its own address: the table entries first, then the same three steps
+          float* cp[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int col = n0 + c0 + c + j;
-          float v = bias;
-          if (load_c && col < N)
-            v += (ccols ? static_cast<const float*>(ccols[col]) : cbase + static_cast<long long>(col) * ldc)[row];
-          acc[j] = v;
-        }
-        uint32_t v0[8], v1[8], v2[8], v3[8];
-        if (nkb > 0) tmem_ld8(tbase + CROSS_COL + c0 + c, v0);
-        if (nkb > 0) tmem_ld8(tbase + c0 + c, v1);
-        if (nkb > 1) tmem_ld8(tbase + SBN + c0 + c, v2);
-        if (nkb > 2) tmem_ld8(tbase + 2 * SBN + c0 + c, v3);
-        tmem_ld_wait();
+          for (int j = 0; j < 8; ++j)
+            cp[j] = c + j < ncols ? static_cast<float*>(ccols[n0 + c0 + c + j]) + row : nullptr;
+          if (mode == 1) {
+            float old[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float t = 0.f;
-          if (nkb > 0) t = __uint_as_float(v0[j]) + __uint_as_float(v1[j]);
-          if (nkb > 1) t += __uint_as_float(v2[j]);
-          if (nkb > 2) t += __uint_as_float(v3[j]);
-          acc[j] += t;
-        }
-        if (row_ok) {
+            for (int j = 0; j < 8; ++j) old[j] = cp[j] ? *cp[j] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += old[j];
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const int col = n0 + c0 + c + j;
-            if (col < N) {
-              float* dst = (ccols ? static_cast<float*>(ccols[col]) : cbase + static_cast<long long>(col) * ldc) + row;
-              if (split_k)
-                atomicAdd(dst, acc[j]);  // partial sum of this CTA's k range
+            float v = acc[j] + bias;
+            if (mode != 2 && act != ACT_NONE) v = act_forward_f32(act, v);
+            if (cp[j]) {
+              if (mode == 2)
+                atomicAdd(cp[j], v);
               else
-                *dst = (act == ACT_NONE ? acc[j] : act_forward_f32(act, acc[j]));
+                *cp[j] = v;
             }
           }
         }
@@ -868,6 +934,24 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   sp.accumulate = p.accumulate;
   sp.split_k = p.split_k > 1 ? p.split_k : 1;
   sp.batches = p.batches;
+#ifdef GB_PHASE_TIMES
+  sp.dbg = getenv("GB_DBG") ? atoi(getenv("GB_DBG")) : 0;
+#endif
+  if (sp.split_k > 1) {
+    if (p.npairs != 1) return cudaErrorInvalidValue;
+    sp.act = ACT_NONE;  // applied by a pass over the summed C after the kernel
+    if (!p.accumulate) {  // partial sums are added onto zeros
+      cudaError_t ze = cudaSuccess;
+      if (p.batches == 1 || p.c_batch_stride == p.ldc * p.N)
+        ze = cudaMemset2DAsync(p.c, p.ldc * 4, 0, static_cast<size_t>(p.M) * 4,
+                               static_cast<size_t>(p.N) * p.batches, stream);
+      else
+        for (int b = 0; b < p.batches && ze == cudaSuccess; ++b)
+          ze = cudaMemset2DAsync(static_cast<float*>(p.c) + b * p.c_batch_stride, p.ldc * 4, 0,
+                                 static_cast<size_t>(p.M) * 4, p.N, stream);
+      if (ze != cudaSuccess) return ze;
+    }
+  }
   const long long total = static_cast<long long>(sp.tiles_m) * sp.tiles_n * p.batches * sp.split_k;
   if (total <= 0) return cudaSuccess;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
@@ -875,20 +959,29 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   cudaError_t e = cudaFuncSetAttribute(sgemm3x_tma_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  return launch_kernel(sgemm3x_tma_kernel, dim3(static_cast<unsigned>(total)), dim3(NTHREADS), smem,
-                       stream, pdl_enabled(), sp, status);
+  e = launch_kernel(sgemm3x_tma_kernel, dim3(static_cast<unsigned>(total)), dim3(NTHREADS), smem,
+                    stream, pdl_enabled(), sp, status);
+  if (e != cudaSuccess || sp.split_k == 1 || p.act == ACT_NONE) return e;
+  return launch_act_inplace_f32(sp.C, sp.ldc, sp.strideC, p.act, p.M, p.N, p.batches, stream);
 }
 
-// Number of K splits for a problem of `tiles` output tiles: only where partial sums can simply be
-// added to C (accumulate, no activation, one pair; a bias is added by the first CTA of a tile), when the tiles alone leave most SMs
-// idle, and never below four k-blocks per CTA.
-int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms) {
-  if (!p.accumulate || p.act != ACT_NONE || p.npairs != 1) return 1;
+// Number of K splits for a problem of `tiles` output tiles (batches included): when the tiles
+// alone leave most SMs idle, one pair, and never below two k-blocks per CTA.  Partial sums are
+// added to C atomically (a bias by the first CTA of a tile).  The gather front end only splits
+// products that add without an activation; the TMA-fed launcher (`tma_path`) splits any product:
+// it zeroes C first when the product assigns and applies an activation in a pass over the
+// summed C afterwards (measured on 512 x 128 x 784: 10 + 2.5 us against 25 us unsplit; letting
+// the last CTA of each tile apply it in the same kernel cost 8 us in fences and re-reads).
+int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms, bool tma_path) {
+  if (p.npairs != 1 || max_split() == 1) return 1;
+  const bool plain_add = p.accumulate && p.act == ACT_NONE;
+  if (!plain_add && !tma_path) return 1;
   const long long nkb = (p.k[0] + SBK - 1) / SBK;
-  if (tiles <= 0 || tiles * 2 > num_sms || nkb < 8) return 1;
+  if (tiles <= 0 || tiles * 2 > num_sms || nkb < 4) return 1;
   long long s = num_sms / tiles;
   if (s > nkb / 2) s = nkb / 2;
   if (s > 32) s = 32;
+  if (max_split() > 0 && s > max_split()) s = max_split();
   return s < 1 ? 1 : static_cast<int>(s);
 }
 

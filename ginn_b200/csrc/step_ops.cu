@@ -268,6 +268,21 @@ bias_act_half_kernel(__half* __restrict__ y, long long ldy, const __half* __rest
   }
 }
 
+// C = act(C) in place, fp32: the activation of a product whose contraction was split over
+// several CTAs (their partial sums meet in C, so the nonlinearity cannot ride on any of them).
+__global__ void __launch_bounds__(256)
+act_inplace_f32_kernel(float* __restrict__ c, long long ldc, long long stride, int act, int m, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= m) return;
+  float* p = c + blockIdx.z * stride + r;
+  for (int col = blockIdx.y; col < n; col += gridDim.y) {
+    float* q = p + col * ldc;
+    *q = act_forward<float>(act, *q);
+  }
+}
+
 // ---- LSTM cell glue of the autobatch benchmark -------------------------------------------
 // The gates of one level arrive as one 4H x n matrix (rows i | f | g | o, the order of the
 // benchmark's shared gate weight); the cell update the reference composes from CwiseProd, Tanh
@@ -489,6 +504,15 @@ cudaError_t launch_dact_half(const void* dy, long long lddy, const void* y, long
   if (vec) dact_half_kernel<true><<<grid, 256, 0, stream>>>(d, lddy, yy, ldy, act, static_cast<__half*>(da), m, n);
   else dact_half_kernel<false><<<grid, 256, 0, stream>>>(d, lddy, yy, ldy, act, static_cast<__half*>(da), m, n);
   return cudaGetLastError();
+}
+
+cudaError_t launch_act_inplace_f32(float* c, long long ldc, long long stride, int act, int m, int n,
+                                   int batches, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || batches <= 0 || act == ACT_NONE) return cudaSuccess;
+  if (batches > 65535) return cudaErrorInvalidValue;
+  dim3 grid((m + 255) / 256, n < 65535 ? n : 65535, batches);
+  return launch_kernel(act_inplace_f32_kernel, grid, dim3(256), 0, stream, pdl_enabled(), c, ldc,
+                       stride, act, m, n);
 }
 
 cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c_prev,

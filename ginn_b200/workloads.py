@@ -22,6 +22,23 @@ def _xavier(rows, cols, gen, device):
     return buf.T  # column-major rows x cols
 
 
+def graphed(step):
+    """Records one call of `step` into a CUDA graph and returns the replay function.  For steps
+    whose launches the host cannot issue as fast as the GPU runs them (a handful of small
+    kernels): the replay shows the device time.  `step` must make no allocation and pass the
+    same scalars every time."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()  # library state (function attributes, contexts) warm before the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    return g.replay
+
+
 class AffineLayer:
     """One AffineNode forward + backward with tanh through the fused entry points (config 1 at
     m, n, k = 512, 128, 784; config 5's hidden layer at 1024, 4096, 1024).  Gradients are zeroed

@@ -270,6 +270,8 @@ int ginn_b200_version(void);
  * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles; set
  * it around the one product that overlaps the collective and back to 0 afterwards.
  * "pair_group_m": m-tiles per rasterisation group of the CTA-pair kernel (0 = default).
+ * "max_split": cap on the number of CTAs an fp32 product's contraction is split over
+ * (0 = the library's choice, 1 = never split).
  * "pdl": 1 (default) launches the fp32 tensor-core kernels and the LSTM cell kernels with
  * programmatic dependent launch, so that a kernel's set-up overlaps the end of the kernel before
  * it in the stream (chains of small dependent launches, e.g. autobatch levels); 0 turns it off.

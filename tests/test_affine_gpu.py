@@ -133,6 +133,24 @@ def test_reference_elementwise_rule_on_affine(gpu, dt, act):
         check_elementwise(B.to_host(got), np.asarray(ref), dt, what)
 
 
+@pytest.mark.parametrize("act", ACTS)
+def test_forward_with_split_contraction(gpu, act):
+    """Few output tiles and a long contraction: the fp32 path splits K over several CTAs, adds
+    the partial sums (and the bias) atomically into a zeroed output and applies the activation
+    in a pass over the summed result.  Config 1's exact shape, one with ragged edge tiles, and
+    a padded output; run twice: stale contents of the output must not leak into the sums."""
+    rng = np.random.default_rng(51 + act)
+    for (m, n, k, pad) in [(512, 128, 784, 0), (130, 70, 1000, 0), (256, 96, 2048, 4)]:
+        W, X, b = randn(rng, (m, k), np.float32, 0.05), randn(rng, (k, n), np.float32), randn(rng, m, np.float32)
+        Wd, Xd, bd = map(B.from_host, (W, X, b))
+        Y = B.colmajor(m, n, torch.float32, ld=m + pad, fill=7.0)   # stale contents must not leak
+        ref = orc.affine_forward([(W, X)], b, act)
+        for _ in range(2):
+            gpu.affine_forward([gpu.Pair(Wd, Xd)], bd, act, Y)
+            torch.cuda.synchronize()
+            check(B.to_host(Y), ref, np.float32, f"{m}x{n}x{k} act {act}")
+
+
 def test_bias_gradient_alone(gpu):
     """Only the bias has a gradient (no weight gradient to ride on)."""
     rng = np.random.default_rng(31)

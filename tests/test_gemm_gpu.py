@@ -213,6 +213,26 @@ def test_fp32_accuracy_holds_at_large_k(gpu):
     run_gemm(gpu, rng, np.float32, 200, 72, 9000, False, False, False)
 
 
+def test_assigning_products_with_split_contraction(gpu):
+    """C = A*B (no accumulation) with few tiles and a long K: split over CTAs onto a zeroed C,
+    also for a small strided batch and for a padded C whose padding must stay untouched."""
+    rng = np.random.default_rng(24)
+    run_gemm(gpu, rng, np.float32, 256, 128, 4096, False, False, False)
+    run_gemm(gpu, rng, np.float32, 200, 100, 3000, True, False, False)
+    a, b = randn(rng, (128, 1024, 3), np.float32), randn(rng, (1024, 128, 3), np.float32)
+    C = B.colmajor(128, 128, torch.float32, batches=3, fill=5.0)
+    gpu.gemm_batched(B.from_host(a), B.from_host(b), C)
+    torch.cuda.synchronize()
+    check(B.to_host(C), orc.gemm_batched(a, b), np.float32, "batched assign")
+    a2, b2 = randn(rng, (128, 2048), np.float32), randn(rng, (2048, 64), np.float32)
+    buf = B.colmajor(132, 64, torch.float32, fill=3.0)
+    Cv = buf[:128]
+    gpu.gemm(B.from_host(a2), B.from_host(b2), Cv)
+    torch.cuda.synchronize()
+    check(B.to_host(Cv), orc.gemm(a2, b2), np.float32, "padded assign")
+    assert (B.to_host(buf)[128:] == 3.0).all()
+
+
 def test_empty_and_degenerate_shapes(gpu):
     rng = np.random.default_rng(19)
     c0 = randn(rng, (4, 5), np.float32)
