@@ -45,7 +45,7 @@ class _Group(C.Structure):
                 ("bias", C.c_void_p), ("ncols", C.c_int64), ("x_cols", C.POINTER(C.c_void_p)),
                 ("y_cols", C.POINTER(C.c_void_p)), ("dx_cols", C.POINTER(C.c_void_p)),
                 ("dw", C.c_void_p), ("lddw", C.c_int64), ("dbias", C.c_void_p),
-                ("accumulate", C.c_int)]
+                ("accumulate", C.c_int), ("act", C.c_int), ("out_cols", C.POINTER(C.c_void_p))]
 
 
 def lib_path() -> str:
@@ -91,6 +91,8 @@ def lib():
     L.ginn_b200_lstm_cell_backward.argtypes = [ci, vp, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp,
                                                i64, vp, i64, cf, vp, i64, vp, i64]
     L.ginn_b200_lstm_cell_forward.restype = L.ginn_b200_lstm_cell_backward.restype = ci
+    L.ginn_b200_lstm_cells.argtypes = [ci, vp, ci, i64, i64, C.POINTER(vp)]
+    L.ginn_b200_lstm_cells.restype = ci
     for name in ("ginn_b200_pick_nll_forward", "ginn_b200_pick_nll_backward",
                  "ginn_b200_adam_update", "ginn_b200_softmax_forward",
                  "ginn_b200_softmax_backward"):
@@ -243,6 +245,8 @@ class Group:
     dw: Optional[torch.Tensor] = None
     dbias: Optional[torch.Tensor] = None
     accumulate: bool = False              # forward: y += W x (+ bias)
+    act: int = ACT_NONE                   # forward: fused nonlinearity; dX / dW: its derivative
+    out_cols: Sequence[torch.Tensor] = () # dX / dW with act: the nodes' forward values (m,)
 
 
 def grouped_static(mode: int, groups: Sequence[Group]) -> None:
@@ -273,7 +277,8 @@ def _build_groups(groups: Sequence[Group]):
                         table(g.x_cols) if len(g.x_cols) else None, table(g.y_cols),
                         table(g.dx_cols) if len(g.dx_cols) else None, _ptr(g.dw),
                         _ld(g.dw) if g.dw is not None else 0, _ptr(g.dbias),
-                        int(g.accumulate))
+                        int(g.accumulate), int(g.act),
+                        table(g.out_cols) if len(g.out_cols) else None)
     return arr, keep
 
 
@@ -388,6 +393,17 @@ def lstm_cell_backward(gates, c, c_prev, dh_next, dc_next, n_next, dgates, dc_ou
         _ld(dh_next) if dh_next is not None else 0, _ptr(dc_next),
         _ld(dc_next) if dc_next is not None else 0, dh_end, dgates.data_ptr(), _ld(dgates),
         dc_out.data_ptr(), _ld(dc_out)))
+
+
+def lstm_cells(backward: bool, tables: Sequence[Sequence[Optional[torch.Tensor]]]) -> None:
+    """Cell update over per-cell tensors (ginn_b200_lstm_cells): `tables` = 4 (forward: gates,
+    c_prev, c, h) or 7 (backward: gates, c, c_prev, dh, dc, dgates, dc_prev) lists with one
+    tensor (or None where allowed) per cell.  hidden = len(c) of the first cell."""
+    n = len(tables[0])
+    flat = (C.c_void_p * (len(tables) * n))(*[_ptr(t) for tab in tables for t in tab])
+    some = tables[0][0]
+    hidden = some.numel() // 4
+    _check(lib().ginn_b200_lstm_cells(_dev(some), _stream(some), int(backward), hidden, n, flat))
 
 
 def adam_update(w: torch.Tensor, d: torch.Tensor, m: torch.Tensor, v: torch.Tensor, t: int,

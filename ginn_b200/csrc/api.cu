@@ -409,6 +409,7 @@ struct LevelPlan {
 };
 struct LevelLaunch {
   int nprobs = 0, tiles = 0;
+  bool with_y = false;  // some group forms dy (.) act'(out) on the fly
 };
 
 int plan_level(int dtype, int mode, int ngroups, const ginn_b200_group* groups, LevelPlan* plan) {
@@ -431,7 +432,13 @@ int plan_level(int dtype, int mode, int ngroups, const ginn_b200_group* groups, 
       return fail(GINN_B200_BAD_ARGUMENT, "group %d: missing column table for mode %d", g, mode);
     if (mode == GINN_B200_GROUPED_DW && (!q.dw || q.lddw < q.m))
       return fail(GINN_B200_BAD_ARGUMENT, "group %d: bad dW", g);
-    table_bytes += 2 * static_cast<size_t>(q.ncols) * sizeof(void*);
+    if (q.act < GINN_B200_ACT_NONE || q.act > GINN_B200_ACT_RELU)
+      return fail(GINN_B200_UNSUPPORTED, "group %d: activation %d cannot be fused", g, q.act);
+    const bool deriv = mode != GINN_B200_GROUPED_FORWARD && q.act != GINN_B200_ACT_NONE;
+    if (deriv && !q.out_cols)
+      return fail(GINN_B200_BAD_ARGUMENT,
+                  "group %d: the nodes' values (out_cols) are needed for the derivative", g);
+    table_bytes += (deriv ? 3 : 2) * static_cast<size_t>(q.ncols) * sizeof(void*);
     const long long N = mode == GINN_B200_GROUPED_DW ? q.k : q.ncols;
     const long long M = mode == GINN_B200_GROUPED_DX ? q.k : q.m;
     plan->max_n = N > plan->max_n ? N : plan->max_n;
@@ -463,6 +470,15 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
     const void** t1 = reinterpret_cast<const void**>(h + off);
     void* const* d_t1 = reinterpret_cast<void* const*>(d + off);
     off += tb;
+    const bool deriv = mode != GINN_B200_GROUPED_FORWARD && q.act != GINN_B200_ACT_NONE;
+    const void* const* d_t2 = nullptr;
+    if (deriv) {
+      const void** t2 = reinterpret_cast<const void**>(h + off);
+      d_t2 = reinterpret_cast<const void* const*>(d + off);
+      off += tb;
+      for (int64_t j = 0; j < q.ncols; ++j) t2[j] = q.out_cols[j];
+      ll.with_y = true;
+    }
     Problem& p = hp[ll.nprobs];
     std::memset(&p, 0, sizeof(p));
     p.npairs = 1;
@@ -482,17 +498,22 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
       p.M = (int)q.m; p.N = (int)q.ncols;
       p.ccols = d_t1;
       p.bias = q.bias;
+      p.act = q.act;
       p.accumulate = q.accumulate ? 1 : 0;
     } else if (mode == GINN_B200_GROUPED_DX) {
       for (int64_t j = 0; j < q.ncols; ++j) {
         t0[j] = q.y_cols[j];
         t1[j] = q.dx_cols[j];
-        al = al && aligned16(q.y_cols[j]);
+        al = al && aligned16(q.y_cols[j]) && (!deriv || aligned16(q.out_cols[j]));
       }
       p.a[0] = make_operand(dtype, q.w, q.ldw, 0, 1, 1);  // W^T: contraction over m
       p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 1);
       p.b[0].cols = d_t0;
       p.b[0].vec = al ? 1 : 0;
+      if (deriv) {
+        p.b[0].ycols = d_t2;
+        p.b[0].dact = q.act;
+      }
       p.k[0] = q.m;
       p.M = (int)q.k; p.N = (int)q.ncols;
       p.ccols = d_t1;
@@ -504,6 +525,10 @@ LevelLaunch fill_level_image(int dtype, int mode, int ngroups, const ginn_b200_g
       }
       p.a[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // dy columns, contraction over j
       p.a[0].cols = d_t0;
+      if (deriv) {
+        p.a[0].ycols = d_t2;
+        p.a[0].dact = q.act;
+      }
       p.b[0] = make_operand(dtype, nullptr, 0, 0, 1, 0);  // x columns
       p.b[0].cols = reinterpret_cast<const void* const*>(d_t1);
       p.k[0] = q.ncols;
@@ -567,11 +592,21 @@ bool direct_level(int dtype, int mode, int ngroups, const ginn_b200_group* group
       p.c = outc[0]; p.ldc = ldo;
       p.bias = fwd ? q.bias : nullptr;
       p.accumulate = fwd ? (q.accumulate ? 1 : 0) : 1;
+      if (fwd) {
+        p.act = q.act;
+      } else if (q.act != GINN_B200_ACT_NONE) {  // dy (.) act'(out): out must share dy's stride
+        if (!q.out_cols || table_stride(q.out_cols, q.ncols, 4, q.m) != ldi) return false;
+        p.b[0] = make_operand(dtype, in[0], ldi, 0, 1, 1, q.out_cols[0], q.act);
+      }
     } else {
       const long long ldy = table_stride(reinterpret_cast<const void* const*>(q.y_cols), q.ncols, 4, q.m);
       const long long ldx = table_stride(q.x_cols, q.ncols, 4, q.k);
       if (ldy < 0 || ldx < 0) return false;
       p.a[0] = make_operand(dtype, q.y_cols[0], ldy, 0, 1, 0);
+      if (q.act != GINN_B200_ACT_NONE) {
+        if (!q.out_cols || table_stride(q.out_cols, q.ncols, 4, q.m) != ldy) return false;
+        p.a[0] = make_operand(dtype, q.y_cols[0], ldy, 0, 1, 0, q.out_cols[0], q.act);
+      }
       p.b[0] = make_operand(dtype, q.x_cols[0], ldx, 0, 1, 0);
       p.k[0] = q.ncols;
       p.M = (int)q.m; p.N = (int)q.k;
@@ -598,7 +633,7 @@ int launch_direct_level(const std::vector<Problem>& probs, cudaStream_t stream, 
 cudaError_t launch_level(int dtype, const LevelLaunch& ll, const Problem* dprobs,
                          cudaStream_t stream, int* status) {
   if (dtype == GINN_B200_F32)
-    return gb::launch_sgemm3x_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
+    return gb::launch_sgemm3x_gather_grouped(dprobs, ll.nprobs, ll.tiles, ll.with_y, stream, status);
   return gb::launch_hgemm_gather_grouped(dprobs, ll.nprobs, ll.tiles, stream, status);
 }
 
@@ -857,7 +892,7 @@ int ginn_b200_grouped_static(int device, void* stream_, int dtype, int mode, int
   LevelLaunch ll = fill_level_image(dtype, mode, ngroups, groups, plan, num_sms, image,
                                     static_cast<unsigned char*>(scratch));
   CU_TRY(gb::launch_grouped_static(dtype, image, plan.bytes, scratch, status, ll.nprobs, ll.tiles,
-                                   static_cast<cudaStream_t>(stream_)));
+                                   ll.with_y, static_cast<cudaStream_t>(stream_)));
   g_launches.fetch_add(1);
   return GINN_B200_OK;
 }
@@ -869,6 +904,10 @@ struct ginn_b200_level {
   LevelLaunch ll;
   unsigned char* d_image;
   std::vector<Problem> direct;  // table-free form of the level (then d_image is null)
+  // cells level (ginn_b200_lstm_cells_level_create): d_image holds the pointer tables
+  int cells = 0;                // 0: grouped products, 1: cell forward, 2: cell backward
+  int hidden = 0;
+  long long ncells = 0;
 };
 
 int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
@@ -906,11 +945,82 @@ int ginn_b200_level_run(ginn_b200_level* level, void* stream) {
   if (level->d_image == nullptr && level->direct.empty()) return GINN_B200_OK;
   DevCtx* ctx;
   if (int s = get_ctx(level->device, &ctx)) return s;
+  if (level->cells) {
+    CU_TRY(gb::launch_lstm_cells(level->cells == 2,
+                                 reinterpret_cast<const void* const*>(level->d_image),
+                                 level->hidden, level->ncells, static_cast<cudaStream_t>(stream)));
+    g_launches.fetch_add(1);
+    return GINN_B200_OK;
+  }
   if (!level->direct.empty())
     return launch_direct_level(level->direct, static_cast<cudaStream_t>(stream), ctx->d_status);
   CU_TRY(launch_level(level->dtype, level->ll, reinterpret_cast<const Problem*>(level->d_image),
                       static_cast<cudaStream_t>(stream), ctx->d_status));
   g_launches.fetch_add(1);
+  return GINN_B200_OK;
+}
+
+namespace {
+int check_cells(int64_t hidden, int64_t n, const void* const* tables, int ntab) {
+  if (hidden < 0 || n < 0 || hidden > 0x7fffffffLL || n > 65535)
+    return fail(GINN_B200_BAD_ARGUMENT, "bad extents hidden=%lld n=%lld (n <= 65535)",
+                (long long)hidden, (long long)n);
+  if (hidden == 0 || n == 0) return GINN_B200_OK;
+  if (!tables) return fail(GINN_B200_BAD_ARGUMENT, "null tables");
+  for (int t = 0; t < ntab; ++t)
+    for (int64_t j = 0; j < n; ++j) {
+      const bool optional = (ntab == 4 && t == 1) || (ntab == 7 && (t == 2 || t == 6));
+      if (!optional && tables[t * n + j] == nullptr)
+        return fail(GINN_B200_BAD_ARGUMENT, "table %d, cell %lld: null pointer", t, (long long)j);
+    }
+  return GINN_B200_OK;
+}
+}  // namespace
+
+int ginn_b200_lstm_cells(int device, void* stream_, int backward, int64_t hidden, int64_t n,
+                         const void* const* tables) {
+  const int ntab = backward ? 7 : 4;
+  if (int s = check_cells(hidden, n, tables, ntab)) return s;
+  if (hidden == 0 || n == 0) return GINN_B200_OK;
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (int s = refuse_capture(stream, "ginn_b200_lstm_cells")) return s;
+  const size_t bytes = static_cast<size_t>(ntab) * n * sizeof(void*);
+  unsigned char *h, *d;
+  int half = 0;
+  if (int s = stage_alloc(ctx, bytes, stream, &h, &d, &half)) return s;
+  std::memcpy(h, tables, bytes);
+  CU_TRY(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, stream));
+  CU_TRY(gb::launch_lstm_cells(backward != 0, reinterpret_cast<const void* const*>(d), (int)hidden, n,
+                               stream));
+  g_launches.fetch_add(1);
+  return stage_mark(ctx, half, stream);
+}
+
+int ginn_b200_lstm_cells_level_create(int device, int backward, int64_t hidden, int64_t n,
+                                      const void* const* tables, ginn_b200_level** out) {
+  if (out == nullptr) return fail(GINN_B200_BAD_ARGUMENT, "null output handle");
+  *out = nullptr;
+  const int ntab = backward ? 7 : 4;
+  if (int s = check_cells(hidden, n, tables, ntab)) return s;
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  ginn_b200_level* lv = new ginn_b200_level{device, GINN_B200_F32, LevelLaunch{}, nullptr, {}};
+  lv->cells = backward ? 2 : 1;
+  lv->hidden = (int)hidden;
+  lv->ncells = n;
+  if (hidden > 0 && n > 0) {
+    const size_t bytes = static_cast<size_t>(ntab) * n * sizeof(void*);
+    cudaError_t e = cudaMalloc(&lv->d_image, bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(lv->d_image, tables, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+      cudaFree(lv->d_image);
+      delete lv;
+      return fail(GINN_B200_CUDA_ERROR, "preparing a cells level failed: %s", cudaGetErrorString(e));
+    }
+  }
+  *out = lv;
   return GINN_B200_OK;
 }
 
@@ -1103,7 +1213,7 @@ int ginn_b200_selftest(int device) {
   return GINN_B200_OK;
 }
 
-int ginn_b200_version(void) { return 100; }
+int ginn_b200_version(void) { return 200; }
 
 int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "force_path") == 0) {

@@ -57,14 +57,15 @@ cudaError_t grouped_static_scratch(int device, void** scratch, int** status) {
 // Copies the host image (descriptors followed by pointer tables, already holding device
 // addresses inside the static array) and launches the grouped kernel on it.
 cudaError_t launch_grouped_static(int dtype, const void* host_image, size_t bytes, void* scratch,
-                                  int* status, int nprobs, int total_tiles, cudaStream_t stream) {
+                                  int* status, int nprobs, int total_tiles, bool with_y,
+                                  cudaStream_t stream) {
   if (bytes > kGroupedStaticBytes) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemcpyAsync(scratch, host_image, bytes, cudaMemcpyHostToDevice, stream);
   if (e != cudaSuccess) return e;
   // Same kernels as the allocating entry point.
   if (dtype == 0)
     return launch_sgemm3x_gather_grouped(static_cast<const Problem*>(scratch), nprobs,
-                                         total_tiles, stream, status);
+                                         total_tiles, with_y, stream, status);
   return launch_hgemm_gather_grouped(static_cast<const Problem*>(scratch), nprobs, total_tiles,
                                      stream, status);
 }

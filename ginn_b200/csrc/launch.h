@@ -39,7 +39,8 @@ cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
 constexpr size_t kGroupedStaticBytes = 256 * 1024;
 cudaError_t grouped_static_scratch(int device, void** scratch, int** status);
 cudaError_t launch_grouped_static(int dtype, const void* host_image, size_t bytes, void* scratch,
-                                  int* status, int nprobs, int total_tiles, cudaStream_t stream);
+                                  int* status, int nprobs, int total_tiles, bool with_y,
+                                  cudaStream_t stream);
 
 // --- TMA-fed persistent fp16 kernel (hgemm_tma.cu) ---
 struct HgemmArgs {
@@ -87,8 +88,9 @@ int sgemm3x_pick_split(const Problem& p, long long tiles, int num_sms, bool tma_
 // Same pipeline with a cp.async gather front end: any alignment, column tables, grouped launches.
 bool sgemm3x_gather_supported(const Problem& p);
 cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status);
+// with_y: some problem of the level carries a derivative operand (dy (.) act'(y) on the fly).
 cudaError_t launch_sgemm3x_gather_grouped(const Problem* dprobs, int nprobs, int total_tiles,
-                                          cudaStream_t stream, int* status);
+                                          bool with_y, cudaStream_t stream, int* status);
 
 // One thread waits (bounded by limit_cycles) on a barrier nobody arrives on; writes 2 to *returned
 // and DEV_TIMEOUT_SELFTEST to *status when the wait ran out as it must.
@@ -138,6 +140,10 @@ cudaError_t launch_lstm_cell_backward(const float* gates, long long ldg, const f
                                       long long lddc, float dh_end, float* dgates, long long lddg,
                                       float* dc_out, long long lddo, int H, long long n,
                                       long long n_next, cudaStream_t stream);
+// Cell update over per-cell tensors: `dtab` = 4 (forward) or 7 (backward) device tables of n
+// pointers each (step_ops.cu describes them).
+cudaError_t launch_lstm_cells(bool backward, const void* const* dtab, int H, long long n,
+                              cudaStream_t stream);
 cudaError_t launch_adam(int dtype, void* w, void* d, float* m, float* v, long long n, float clip,
                         float b1, float b2, float step, float vscale, float eps, int num_sms,
                         cudaStream_t stream);

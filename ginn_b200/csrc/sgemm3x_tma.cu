@@ -1014,10 +1014,11 @@ cudaError_t launch_sgemm3x_gather(Problem& p, cudaStream_t stream, int* status) 
 
 // Descriptors in device memory, tiles_m / tiles_n / tile_start filled for 128 x 128 tiles.
 cudaError_t launch_sgemm3x_gather_grouped(const Problem* dprobs, int nprobs, int total_tiles,
-                                          cudaStream_t stream, int* status) {
+                                          bool with_y, cudaStream_t stream, int* status) {
   if (total_tiles <= 0) return cudaSuccess;
   Problem dummy{};
-  return launch_gather<true, false>(dummy, dprobs, nprobs, total_tiles, stream, status);
+  return with_y ? launch_gather<true, true>(dummy, dprobs, nprobs, total_tiles, stream, status)
+                : launch_gather<true, false>(dummy, dprobs, nprobs, total_tiles, stream, status);
 }
 
 }  // namespace gb

@@ -268,6 +268,63 @@ bias_act_half_kernel(__half* __restrict__ y, long long ldy, const __half* __rest
   }
 }
 
+__device__ __forceinline__ float sigmoid_f(float x) { return 0.5f * tanhf(0.5f * x) + 0.5f; }
+
+// The same cell update for cells that each live in tensors of their own (one column per graph
+// node, as ginn allocates them): `tab` holds tables of `n` device pointers each, one entry per
+// cell.  forward tables: gates (4H, overwritten with the activations), c_prev (H; entry may be
+// null), c (H), h (H).  backward tables: gates, c, c_prev (may be null), dh (H: gradient of h),
+// dc (H: gradient of c gathered from the next step), dgates (4H, +=), dc_prev (H, +=; null
+// where c_prev is).  Gradients accumulate, as every gradient write in ginn does.
+__global__ void __launch_bounds__(256)
+lstm_cells_forward_kernel(const void* const* __restrict__ tab, int H, long long n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long col = blockIdx.y;
+  if (r >= H || col >= n) return;
+  float* g = static_cast<float*>(const_cast<void*>(tab[col])) + r;
+  const float* cprev = static_cast<const float*>(tab[n + col]);
+  float* c = static_cast<float*>(const_cast<void*>(tab[2 * n + col]));
+  float* h = static_cast<float*>(const_cast<void*>(tab[3 * n + col]));
+  const long long Hl = H;
+  const float i = sigmoid_f(g[0]), f = sigmoid_f(g[Hl]), gg = tanhf(g[2 * Hl]), o = sigmoid_f(g[3 * Hl]);
+  g[0] = i;
+  g[Hl] = f;
+  g[2 * Hl] = gg;
+  g[3 * Hl] = o;
+  const float cv = f * (cprev ? cprev[r] : 0.f) + i * gg;
+  c[r] = cv;
+  h[r] = o * tanhf(cv);
+}
+
+__global__ void __launch_bounds__(256)
+lstm_cells_backward_kernel(const void* const* __restrict__ tab, int H, long long n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long col = blockIdx.y;
+  if (r >= H || col >= n) return;
+  const float* g = static_cast<const float*>(tab[col]) + r;
+  const float* c = static_cast<const float*>(tab[n + col]);
+  const float* cprev = static_cast<const float*>(tab[2 * n + col]);
+  const float* dhp = static_cast<const float*>(tab[3 * n + col]);
+  const float* dcp = static_cast<const float*>(tab[4 * n + col]);
+  float* dg = static_cast<float*>(const_cast<void*>(tab[5 * n + col])) + r;
+  float* dcprev = static_cast<float*>(const_cast<void*>(tab[6 * n + col]));
+  const long long Hl = H;
+  const float i = g[0], f = g[Hl], gg = g[2 * Hl], o = g[3 * Hl];
+  const float tc = tanhf(c[r]);
+  const float cp = cprev ? cprev[r] : 0.f;
+  const float dh = dhp[r];
+  const float dc = dcp[r] + dh * o * (1.f - tc * tc);
+  dg[0] += dc * gg * i * (1.f - i);
+  dg[Hl] += dc * cp * f * (1.f - f);
+  dg[2 * Hl] += dc * i * (1.f - gg * gg);
+  dg[3 * Hl] += dh * tc * o * (1.f - o);
+  if (dcprev) dcprev[r] += dc * f;
+}
+
 // C = act(C) in place, fp32: the activation of a product whose contraction was split over
 // several CTAs (their partial sums meet in C, so the nonlinearity cannot ride on any of them).
 __global__ void __launch_bounds__(256)
@@ -293,7 +350,6 @@ act_inplace_f32_kernel(float* __restrict__ c, long long ldc, long long stride, i
 //   backward: dh = upstream (next level's input gradient for columns that live on, `dh_end` for
 //             those that end here), dc = dc_next + dh o (1 - tanh(c)^2), the four gate gradients
 //             through their nonlinearities, and dc f carried to the previous level.
-__device__ __forceinline__ float sigmoid_f(float x) { return 0.5f * tanhf(0.5f * x) + 0.5f; }
 
 __global__ void __launch_bounds__(256)
 lstm_cell_forward_kernel(float* __restrict__ gates, long long ldg, const float* __restrict__ c_prev,
@@ -524,6 +580,15 @@ cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c
   dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
   return launch_kernel(lstm_cell_forward_kernel, grid, dim3(256), 0, stream, pdl_enabled(), gates,
                        ldg, c_prev, ldcp, c, ldc, h, ldh, xh_next, ldx, H, n, n_next);
+}
+
+cudaError_t launch_lstm_cells(bool backward, const void* const* dtab, int H, long long n,
+                              cudaStream_t stream) {
+  if (H <= 0 || n <= 0) return cudaSuccess;
+  if (n > 65535) return cudaErrorInvalidValue;
+  dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
+  return launch_kernel(backward ? lstm_cells_backward_kernel : lstm_cells_forward_kernel, grid,
+                       dim3(256), 0, stream, pdl_enabled(), dtab, H, n);
 }
 
 cudaError_t launch_lstm_cell_backward(const float* gates, long long ldg, const float* c,

@@ -4,6 +4,7 @@
 #include <ginn/autobatch.h>
 #include <ginn/node/affine.h>
 #include <ginn/node/data.h>
+#include <ginn/node/lstmcell.h>
 #include <ginn/node/nlnode.h>
 #include <ginn/node/pick.h>
 #include <ginn/node/prod.h>

@@ -58,6 +58,12 @@ class BaseNode {
     if (has_grad()) backward_();
   }
   virtual bool has_grad() const { return false; }
+  // What Autobatch may do with this node: 0 = run it on its own, otherwise one of the kinds
+  // BatchedGraph merges per level (it then casts statically; no RTTI on the rewrite path).
+  enum BatchKind { kPlain = 0, kProd = 1, kAffine = 2, kLstmCell = 3 };
+  virtual int batch_kind() const { return kPlain; }
+  // Scratch slot for graph passes (index of the node in the pass's own flat arrays).
+  mutable int pass_index = -1;
   virtual void init_grad() {}
   virtual void reset_grad() {}
   virtual void reset_forwarded() { forwarded = false; }

@@ -76,6 +76,9 @@ class AffineNode : public BaseDataNode<Scalar> {
 
   const std::vector<NodePtr<Scalar>>& affine_ins() const { return in_; }
   const NonlinOp<Scalar>& nonlin() const { return *nonlin_; }
+  int batch_kind() const override {
+    return std::is_same<Scalar, Real>::value ? BaseNode::kAffine : BaseNode::kPlain;
+  }
   std::string name() const override { return "Affine"; }
 };
 

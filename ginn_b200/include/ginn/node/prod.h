@@ -32,6 +32,9 @@ class ProdNode : public BaseDataNode<Scalar> {
       : BaseDataNode<Scalar>(std::vector<BaseNodePtr>{a, b}), a_(a), b_(b) {}
   const NodePtr<Scalar>& lhs() const { return a_; }
   const NodePtr<Scalar>& rhs() const { return b_; }
+  int batch_kind() const override {
+    return std::is_same<Scalar, Real>::value ? BaseNode::kProd : BaseNode::kPlain;
+  }
   std::string name() const override { return "Prod"; }
 };
 

@@ -118,6 +118,12 @@ typedef struct {
   int64_t lddw;
   void* dbias;               /* dW mode: m, accumulated (may be NULL)                       */
   int accumulate;            /* forward: y_j += W * x_j (+ bias) instead of y_j = ...       */
+  /* Affines with a fused nonlinearity (ginn/autobatch.h:30-38 leaves them unbatched):
+   * forward: y_j = act(W x_j + bias [+ y_j]) -- set it on the launch that adds a node's last
+   * product;  dX / dW mode: the upstream gradient is taken as dy_j (.) act'(out_j), where
+   * out_cols[j] is the node's forward value (m elements).  GINN_B200_ACT_NONE = identity. */
+  int act;
+  const void* const* out_cols; /* dX / dW mode with act != NONE: node values out_j (m)       */
 } ginn_b200_group;
 
 typedef enum {
@@ -232,6 +238,22 @@ int ginn_b200_lstm_cell_backward(int device, void* stream, int64_t hidden, int64
                                  int64_t lddc, float dh_end, float* dgates, int64_t lddg,
                                  float* dc_out, int64_t lddo);
 
+/* The same cell update for cells whose tensors are separate allocations -- one graph node per
+ * sequence and step, as ginn builds an LSTM -- so that all cells of one autobatch level are one
+ * launch.  `tables` is a HOST array of 4 (forward) or 7 (backward) tables of `n` DEVICE pointers
+ * each, table after table:
+ *   forward : gates (4*hidden, replaced by the activations), c_prev (hidden; an entry may be
+ *             NULL = zeros), c (hidden, written), h (hidden, written)
+ *   backward: gates, c, c_prev (entry may be NULL), dh (gradient of h), dc (gradient of c),
+ *             dgates (4*hidden, +=), dc_prev (hidden, +=; NULL where c_prev is NULL)
+ * ginn_b200_lstm_cells stages the tables and launches (not capturable, like ginn_b200_grouped);
+ * ginn_b200_lstm_cells_level_create keeps them on the device for ginn_b200_level_run /
+ * ginn_b200_level_destroy.  No reference counterpart (ginn/model/lstm.h:97-100 as node-wise ops). */
+int ginn_b200_lstm_cells(int device, void* stream, int backward, int64_t hidden, int64_t n,
+                         const void* const* tables);
+int ginn_b200_lstm_cells_level_create(int device, int backward, int64_t hidden, int64_t n,
+                                      const void* const* tables, ginn_b200_level** out);
+
 /* One Adam step on n elements: d is clipped to [-clip, clip] in place, then
  *   m = beta1 m + (1 - beta1) d,  v = beta2 v + (1 - beta2) d^2,
  *   w += -lr / (1 - beta1_t) * m / (eps + sqrt(v / (1 - beta2_t))),
@@ -259,7 +281,7 @@ int ginn_b200_device_status(int device, int reset);
 int ginn_b200_selftest(int device);
 
 /* Library version: major * 10000 + minor * 100 + patch. */
-int ginn_b200_version(void);
+int ginn_b200_version(void);   /* 200: ginn_b200_group gained `act` and `out_cols` */
 
 /* Test / benchmark knobs.  They belong to the calling host thread: a value set here affects
  * the calls this thread makes afterwards and nobody else's.

@@ -283,6 +283,56 @@ static void test_autobatch() {
   }
 }
 
+// Affines with fused nonlinearities (which the reference's Autobatch does not batch,
+// ginn/autobatch.h:30-38) and LSTM cells: a small recurrent net, node by node through Graph and
+// level by level through Autobatch.
+static void test_autobatch_nonlinear_and_cells() {
+  {  // "Recurrent" of test/autobatch.cpp with tanh inside the Affines
+    std::vector<NodePtr<Real>> x;
+    for (int i = 0; i < 12; ++i) x.push_back(Random<Real>(gpu(), {2}, 120 + i));
+    auto W = Random<Real>(gpu(), {3, 2}, 140), V = Random<Real>(gpu(), {3, 3}, 141);
+    auto b = Random<Real>(gpu(), {3}, 142);
+    std::vector<NodePtr<Real>> hs;
+    for (int i = 0; i < 3; ++i) {
+      NodePtr<Real> h = Data<Real>(gpu(), {3});
+      h->value().set_zero();
+      for (int t = 0; t < 2 + i; ++t)  // sequences of different lengths
+        h = (t % 2) ? NodePtr<Real>(Affine<TanhOp>(W, x[4 * i + t], V, h, b))
+                    : NodePtr<Real>(Affine<SigmoidOp>(W, x[4 * i + t], V, h, b));
+      hs.push_back(h);
+    }
+    auto s = identity_sum(hs, 3);
+    std::vector<NodePtr<Real>> ins = x;
+    ins.push_back(W);
+    ins.push_back(V);
+    ins.push_back(b);
+    check_autobatch(s, ins, 10);
+  }
+  {  // one Affine for the four gates + one cell node per step, three sequences of lengths 3, 2, 4
+    const Size H = 8, E = 4;
+    auto Wx = Random<Real>(gpu(), {4 * H, E}, 150), Wh = Random<Real>(gpu(), {4 * H, H}, 151);
+    auto b = Random<Real>(gpu(), {4 * H}, 152);
+    std::vector<NodePtr<Real>> ins{Wx, Wh, b}, finals;
+    const int lens[3] = {3, 2, 4};
+    size_t nodes = 0;
+    for (int q = 0; q < 3; ++q) {
+      NodePtr<Real> h = Random<Real>(gpu(), {H}, 160 + q);
+      ins.push_back(h);
+      Ptr<LstmCellNode> cell;
+      for (int t = 0; t < lens[q]; ++t) {
+        auto xt = Random<Real>(gpu(), {E}, 170 + 10 * q + t);
+        ins.push_back(xt);
+        NodePtr<Real> gates = Affine(Wx, xt, Wh, h, b);
+        cell = LstmCell(gates, cell);
+        h = cell;
+        nodes += 2;
+      }
+      finals.push_back(h);
+    }
+    check_autobatch(identity_sum(finals, H), ins, nodes);
+  }
+}
+
 static void test_prealloc_accounting() {
   auto dev = PreallocGpu(0, 1 << 20);
   auto W = Data<Real>(dev, {8, 5}), x = Data<Real>(dev, {5, 3}), b = Data<Real>(dev, {8});
@@ -424,6 +474,7 @@ int main() {
   test_affine_cpu_vs_gpu<Half, TanhOp>(GINN_B200_ACT_TANH, 1e-2f);
   test_prod_cpu_vs_gpu();
   test_autobatch();
+  test_autobatch_nonlinear_and_cells();
   test_prealloc_accounting();
   test_errors();
   test_pick_nll<Real>(1e-6f);

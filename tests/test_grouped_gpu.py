@@ -90,6 +90,51 @@ def test_reference_elementwise_rule_on_a_level(gpu, dt):
         check_elementwise(B.to_host(db), DY.astype(np.float64).sum(1).astype(dt), dt, "dbias")
 
 
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+@pytest.mark.parametrize("act", [orc.ACT_TANH, orc.ACT_SIGMOID, orc.ACT_RELU])
+@pytest.mark.parametrize("layout", ["separate", "matrix"])
+def test_level_of_affines_with_a_nonlinearity(gpu, dt, act, layout):
+    """What the reference's Autobatch leaves unbatched (ginn/autobatch.h:30-38): Affines with a
+    fused nonlinearity.  Forward applies it after the merged product; the gradient launches take
+    dy (.) act'(value) as their operand.  Against the per-node Affine of the oracle; columns as
+    separate vectors (pointer tables) and as the columns of one matrix (plain products)."""
+    rng = np.random.default_rng(61 + act)
+    tdt = torch.float32 if dt == np.float32 else torch.float16
+    specs = [(200, 96, 37), (64, 40, 130)]
+    host, devs = [], []
+    for m, k, nc in specs:
+        W, bias = randn(rng, (m, k), dt, 0.1), randn(rng, m, dt)
+        X, DY = randn(rng, (k, nc), dt), randn(rng, (m, nc), dt)
+        host.append((W, bias, X, DY))
+        if layout == "matrix":
+            Xd, DYd = B.from_host(X), B.from_host(DY)
+            Yd, dXd = B.colmajor(m, nc, tdt, fill=0.0), B.colmajor(k, nc, tdt, fill=0.0)
+            cols = lambda t: [t[:, j] for j in range(t.shape[1])]
+            devs.append((B.from_host(W), B.from_host(bias), cols(Xd), cols(DYd), cols(Yd), cols(dXd)))
+        else:
+            devs.append((B.from_host(W), B.from_host(bias),
+                         [B.from_host(np.ascontiguousarray(X[:, j])) for j in range(nc)],
+                         [B.from_host(np.ascontiguousarray(DY[:, j])) for j in range(nc)],
+                         [torch.zeros(m, device="cuda", dtype=tdt) for _ in range(nc)],
+                         [torch.zeros(k, device="cuda", dtype=tdt) for _ in range(nc)]))
+    dws = [B.colmajor(m, k, tdt, fill=0.0) for m, k, _ in specs]
+    dbs = [torch.zeros(m, device="cuda", dtype=tdt) for m, _, _ in specs]
+    gpu.grouped(GROUPED_FORWARD, [gpu.Group(w=W, x_cols=x, y_cols=y, bias=b, act=act)
+                                  for W, b, x, _, y, _ in devs])
+    gpu.grouped(GROUPED_DX, [gpu.Group(w=W, y_cols=dy, dx_cols=dx, act=act, out_cols=y)
+                             for W, _, _, dy, y, dx in devs])
+    gpu.grouped(GROUPED_DW, [gpu.Group(w=W, x_cols=x, y_cols=dy, dw=dw, dbias=db, act=act, out_cols=y)
+                             for (W, _, x, dy, y, _), dw, db in zip(devs, dws, dbs)])
+    torch.cuda.synchronize()
+    for (W, bias, X, DY), (_, _, _, _, y, dx), dw, db in zip(host, devs, dws, dbs):
+        Y = np.stack([B.to_host(t) for t in y], 1)
+        check(Y, orc.affine_forward([(W, X)], bias, act), dt, "value")
+        g = orc.affine_backward([(W, X)], DY, Y, act, dt)
+        check(np.stack([B.to_host(t) for t in dx], 1), g["db"][0], dt, "dX")
+        check(B.to_host(dw), g["da"][0], dt, "dW")
+        check(B.to_host(db), g["dbias"], dt, "dbias")
+
+
 @pytest.mark.parametrize("prepared", [False, True])
 def test_columns_of_one_matrix_need_no_tables(gpu, prepared):
     """The nodes' vectors are the columns of one padded matrix (a batched input, or tensors

@@ -170,3 +170,35 @@ def test_lstm_cell_forward_backward(gpu):
     rg0, rc0 = orc.lstm_cell_backward(act0, c0, None, None, None, 0, 0.5)
     check(B.to_host(dG), rg0, f32, "dgates, no neighbours")
     check(B.to_host(dC), rc0, f32, "dc, no neighbours")
+
+
+def test_lstm_cells_over_per_cell_tensors(gpu):
+    """The cell update with every cell in tensors of its own (one graph node per sequence and
+    step): same arithmetic as the matrix form, gradients accumulated (+=), a cell without a
+    predecessor in the same launch.  Against the fp64 restatement."""
+    rng = np.random.default_rng(92)
+    H, n = 24, 6
+    f32 = np.float32
+    G, cp = randn(rng, (4 * H, n), f32), randn(rng, (H, n), f32)
+    cp[:, 2] = 0.0                                     # cell 2 starts a sequence: no c_prev
+    dev = lambda a: [B.from_host(np.ascontiguousarray(a[:, j])) for j in range(a.shape[1])]
+    zeros = lambda r: [torch.zeros(r, device="cuda") for _ in range(n)]
+    Gs, CPs, Cs, Hs = dev(G), dev(cp), zeros(H), zeros(H)
+    CPs[2] = None
+    gpu.lstm_cells(False, [Gs, CPs, Cs, Hs])
+    torch.cuda.synchronize()
+    stack = lambda ts: np.stack([B.to_host(t) for t in ts], 1)
+    act, c, h = orc.lstm_cell_forward(G, cp)
+    check(stack(Gs), act, f32, "activations")
+    check(stack(Cs), c, f32, "c")
+    check(stack(Hs), h, f32, "h")
+    dh, dc = randn(rng, (H, n), f32), randn(rng, (H, n), f32)
+    dGs = [torch.full((4 * H,), 0.5, device="cuda") for _ in range(n)]
+    dCPs = [torch.full((H,), 0.25, device="cuda") for _ in range(n)]
+    dCPs[2] = None
+    gpu.lstm_cells(True, [Gs, Cs, CPs, dev(dh), dev(dc), dGs, dCPs])
+    torch.cuda.synchronize()
+    rg, rc = orc.lstm_cell_backward(stack(Gs), stack(Cs), cp, dh, dc, n, 0.0)
+    check(stack(dGs), 0.5 + rg, f32, "dgates +=")
+    keep = [j for j in range(n) if j != 2]
+    check(stack([dCPs[j] for j in keep]), 0.25 + rc[:, keep], f32, "dc_prev +=")
