@@ -97,6 +97,11 @@ def lib():
                  "ginn_b200_adam_update", "ginn_b200_softmax_forward",
                  "ginn_b200_softmax_backward"):
         getattr(L, name).restype = ci
+    L.ginn_b200_conv2d_workspace.argtypes = [ci] + [i64] * 9
+    L.ginn_b200_conv2d_workspace.restype = C.c_size_t
+    L.ginn_b200_conv2d_forward.argtypes = [ci, vp, ci] + [i64] * 9 + [vp, vp, vp, vp]
+    L.ginn_b200_conv2d_backward.argtypes = [ci, vp, ci] + [i64] * 9 + [vp, vp, vp, vp, vp, vp]
+    L.ginn_b200_conv2d_forward.restype = L.ginn_b200_conv2d_backward.restype = ci
     L.ginn_b200_last_error.restype = C.c_char_p
     L.ginn_b200_device_status.argtypes = [ci, ci]
     L.ginn_b200_set_option.argtypes = [C.c_char_p, ci]
@@ -404,6 +409,62 @@ def lstm_cells(backward: bool, tables: Sequence[Sequence[Optional[torch.Tensor]]
     some = tables[0][0]
     hidden = some.numel() // 4
     _check(lib().ginn_b200_lstm_cells(_dev(some), _stream(some), int(backward), hidden, n, flat))
+
+
+def _conv_dims(x: torch.Tensor, k: torch.Tensor):
+    """Extents of contiguous column-major tensors given as torch tensors whose dimensions are
+    listed in ginn's order (channels, rows, cols, batch) / (filters, channels, krows, kcols) and
+    whose strides put the first dimension fastest."""
+    for t in (x, k):
+        want, acc = [], 1
+        for d in t.shape:
+            want.append(acc)
+            acc *= d
+        assert list(t.stride()) == want, "convolution tensors must be column-major and contiguous"
+    return tuple(x.shape) + (k.shape[0], k.shape[2], k.shape[3])
+
+
+def colmajor_nd(shape, dtype, device="cuda", fill: Optional[float] = None) -> torch.Tensor:
+    """Contiguous column-major tensor of any rank (first dimension fastest)."""
+    n = 1
+    strides = []
+    for d in shape:
+        strides.append(n)
+        n *= d
+    buf = torch.empty(max(n, 1), dtype=dtype, device=device)
+    if fill is not None:
+        buf.fill_(fill)
+    return torch.as_strided(buf, tuple(shape), tuple(strides))
+
+
+def from_host_nd(a: np.ndarray, device="cuda") -> torch.Tensor:
+    tdt = {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16}[a.dtype]
+    out = colmajor_nd(a.shape, tdt, device)
+    out.copy_(torch.from_numpy(np.ascontiguousarray(a)))
+    return out
+
+
+def conv2d_workspace_bytes(x, k, row_stride=1, col_stride=1) -> int:
+    dims = _conv_dims(x, k)
+    return int(lib().ginn_b200_conv2d_workspace(_dtype_of(x), *dims, row_stride, col_stride))
+
+
+def conv2d_forward(x, k, y, row_stride=1, col_stride=1, workspace: Optional[torch.Tensor] = None):
+    """y = Conv2d(x, k) with SAME padding (ginn_b200_conv2d_forward); Conv2dNode::forward_."""
+    dims = _conv_dims(x, k)
+    _check(lib().ginn_b200_conv2d_forward(_dev(x), _stream(x), _dtype_of(x), *dims, row_stride,
+                                          col_stride, x.data_ptr(), k.data_ptr(), y.data_ptr(),
+                                          _ptr(workspace)))
+    return y
+
+
+def conv2d_backward(x, k, dy, dx=None, dk=None, row_stride=1, col_stride=1,
+                    workspace: Optional[torch.Tensor] = None) -> None:
+    """dx += ..., dk += ... (ginn_b200_conv2d_backward); Conv2dNode::backward_."""
+    dims = _conv_dims(x, k)
+    _check(lib().ginn_b200_conv2d_backward(_dev(x), _stream(x), _dtype_of(x), *dims, row_stride,
+                                           col_stride, x.data_ptr(), k.data_ptr(), dy.data_ptr(),
+                                           _ptr(dx), _ptr(dk), _ptr(workspace)))
 
 
 def adam_update(w: torch.Tensor, d: torch.Tensor, m: torch.Tensor, v: torch.Tensor, t: int,

@@ -1034,6 +1034,105 @@ int ginn_b200_level_destroy(ginn_b200_level* level) {
   return GINN_B200_OK;
 }
 
+size_t ginn_b200_conv2d_workspace(int dtype, int64_t C, int64_t R, int64_t W, int64_t B, int64_t F,
+                                  int64_t KR, int64_t KC, int64_t sr, int64_t sc) {
+  gb::ConvShape s;
+  if ((dtype != GINN_B200_F32 && dtype != GINN_B200_F16) ||
+      !gb::conv2d_geometry(C, R, W, B, F, KR, KC, sr, sc, &s))
+    return 0;
+  return (static_cast<size_t>(s.inner) * s.ncols * esize(dtype) + 255) & ~size_t(255);
+}
+
+namespace {
+// Shared set-up of the two convolution entry points: geometry, context, workspace.
+struct ConvCall {
+  gb::ConvShape shape;
+  DevCtx* ctx = nullptr;
+  void* ws = nullptr;
+  bool own_ws = false;
+};
+int conv_begin(int device, cudaStream_t stream, int dtype, int64_t C, int64_t R, int64_t W,
+               int64_t B, int64_t F, int64_t KR, int64_t KC, int64_t sr, int64_t sc,
+               void* workspace, ConvCall* call) {
+  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
+    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
+  if (!gb::conv2d_geometry(C, R, W, B, F, KR, KC, sr, sc, &call->shape))
+    return fail(GINN_B200_BAD_ARGUMENT,
+                "bad convolution extents: input %lld x %lld x %lld x %lld, filters %lld x %lld x "
+                "%lld, strides %lld, %lld", (long long)C, (long long)R, (long long)W, (long long)B,
+                (long long)F, (long long)KR, (long long)KC, (long long)sr, (long long)sc);
+  if (int s = get_ctx(device, &call->ctx)) return s;
+  call->ws = workspace;
+  if (workspace == nullptr) {
+    const size_t bytes = static_cast<size_t>(call->shape.inner) * call->shape.ncols * esize(dtype);
+    CU_TRY(cudaMallocAsync(&call->ws, bytes, stream));
+    call->own_ws = true;
+  } else if (!aligned16(workspace)) {
+    return fail(GINN_B200_BAD_ARGUMENT, "the convolution workspace must be 16-byte aligned");
+  }
+  return GINN_B200_OK;
+}
+void conv_end(ConvCall* call, cudaStream_t stream) {
+  if (call->own_ws && call->ws) cudaFreeAsync(call->ws, stream);
+}
+}  // namespace
+
+int ginn_b200_conv2d_forward(int device, void* stream_, int dtype, int64_t C, int64_t R, int64_t W,
+                             int64_t B, int64_t F, int64_t KR, int64_t KC, int64_t sr, int64_t sc,
+                             const void* x, const void* k, void* y, void* workspace) {
+  if (!x || !k || !y) return fail(GINN_B200_BAD_ARGUMENT, "null tensor pointer");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  ConvCall call;
+  if (int s = conv_begin(device, stream, dtype, C, R, W, B, F, KR, KC, sr, sc, workspace, &call))
+    return s;
+  const gb::ConvShape& g = call.shape;
+  int status = GINN_B200_OK;
+  cudaError_t e = gb::launch_im2col(dtype, x, call.ws, C, R, W, B, F, KR, KC, sr, sc, g,
+                                    call.ctx->num_sms, stream);
+  if (e != cudaSuccess) status = fail(GINN_B200_CUDA_ERROR, "patch extraction: %s", cudaGetErrorString(e));
+  g_launches.fetch_add(1);
+  if (status == GINN_B200_OK)  // y (F x N) = k (F x CKK) * patches (CKK x N)
+    status = gemm_impl(device, stream_, dtype, 0, 0, F, g.ncols, g.inner, k, F, 0, call.ws, g.inner,
+                       0, y, F, 0, 1, 0);
+  conv_end(&call, stream);
+  return status;
+}
+
+int ginn_b200_conv2d_backward(int device, void* stream_, int dtype, int64_t C, int64_t R, int64_t W,
+                              int64_t B, int64_t F, int64_t KR, int64_t KC, int64_t sr, int64_t sc,
+                              const void* x, const void* k, const void* dy, void* dx, void* dk,
+                              void* workspace) {
+  if (!dy || (dk && !x) || (dx && !k)) return fail(GINN_B200_BAD_ARGUMENT, "null tensor pointer");
+  if (!dx && !dk) return GINN_B200_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  ConvCall call;
+  if (int s = conv_begin(device, stream, dtype, C, R, W, B, F, KR, KC, sr, sc, workspace, &call))
+    return s;
+  const gb::ConvShape& g = call.shape;
+  int status = GINN_B200_OK;
+  if (dk) {  // dk (F x CKK) += dy (F x N) * patches^T (N x CKK)
+    cudaError_t e = gb::launch_im2col(dtype, x, call.ws, C, R, W, B, F, KR, KC, sr, sc, g,
+                                      call.ctx->num_sms, stream);
+    if (e != cudaSuccess) status = fail(GINN_B200_CUDA_ERROR, "patch extraction: %s", cudaGetErrorString(e));
+    g_launches.fetch_add(1);
+    if (status == GINN_B200_OK)
+      status = gemm_impl(device, stream_, dtype, 0, 1, F, g.inner, g.ncols, dy, F, 0, call.ws, g.inner,
+                         0, dk, F, 0, 1, 1);
+  }
+  if (dx && status == GINN_B200_OK) {  // dpatches (CKK x N) = k^T (CKK x F) * dy (F x N)
+    status = gemm_impl(device, stream_, dtype, 1, 0, g.inner, g.ncols, F, k, F, 0, dy, F, 0, call.ws,
+                       g.inner, 0, 1, 0);
+    if (status == GINN_B200_OK) {
+      cudaError_t e = gb::launch_col2im_add(dtype, call.ws, dx, C, R, W, B, F, KR, KC, sr, sc, g,
+                                            call.ctx->num_sms, stream);
+      if (e != cudaSuccess) status = fail(GINN_B200_CUDA_ERROR, "patch scatter: %s", cudaGetErrorString(e));
+      g_launches.fetch_add(1);
+    }
+  }
+  conv_end(&call, stream);
+  return status;
+}
+
 const char* ginn_b200_last_error(void) { return t_error.c_str(); }
 
 int ginn_b200_device_status(int device, int reset) {

@@ -109,6 +109,24 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
 cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
                           long long N, void* rowsum, cudaStream_t stream);
 
+// --- Conv2d as patch extraction + matrix products (conv.cu) ---
+struct ConvShape {
+  long long out_rows, out_cols, pad_top, pad_left;
+  long long inner;  // channels * kernel rows * kernel cols: rows of the patch matrix
+  long long ncols;  // out_rows * out_cols * batch: its columns
+};
+// Output extents and padding of a SAME convolution; false for non-positive or oversized extents.
+bool conv2d_geometry(long long C, long long R, long long W, long long B, long long F, long long KR,
+                     long long KC, long long sr, long long sc, ConvShape* out);
+cudaError_t launch_im2col(int dtype, const void* x, void* patches, long long C, long long R,
+                          long long W, long long B, long long F, long long KR, long long KC,
+                          long long sr, long long sc, const ConvShape& s, int num_sms,
+                          cudaStream_t stream);
+cudaError_t launch_col2im_add(int dtype, const void* dpatches, void* dx, long long C, long long R,
+                              long long W, long long B, long long F, long long KR, long long KC,
+                              long long sr, long long sc, const ConvShape& s, int num_sms,
+                              cudaStream_t stream);
+
 // --- elementwise neighbours of the products on a training step (step_ops.cu) ---
 cudaError_t launch_pick_nll_forward(int dtype, const void* x, long long ldx, const int* index,
                                     void* smax, long long lds, void* value, int rows,

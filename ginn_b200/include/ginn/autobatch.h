@@ -358,8 +358,23 @@ class BatchedGraph {
   BatchedGraph& reset_grad() {
     if (!zero_ready_) {
       for (auto& e : list_) e->init_grad();
-      std::vector<std::pair<char*, size_t>> r;
+      // (address, bytes, owner): ranges are merged only inside one preallocated device -- its
+      // tensors are pieces of a single allocation; two cudaMalloc'ed tensors may be neighbours
+      // in the address space and still not be one region a fill may cross.
+      struct Range {
+        char* p;
+        size_t bytes;
+        Device* owner;  // null: not mergeable
+        bool operator<(const Range& o) const { return p < o.p; }
+      };
+      std::vector<Range> r;
       bool all_gpu = true;
+      auto add = [&](Tensor<Real>& t) {
+        if (t.size() == 0) return;
+        Device* d = t.dev().get();
+        r.push_back({reinterpret_cast<char*>(t.data()), t.size() * sizeof(Real),
+                     d->precedence() > 0 ? d : nullptr});
+      };
       for (auto& e : list_) {
         if (!e->has_grad()) continue;
         auto n = dynamic_cast<Node<Real>*>(e.get());
@@ -367,13 +382,8 @@ class BatchedGraph {
           all_gpu = false;
           break;
         }
-        if (n->grad().size() > 0)
-          r.emplace_back(reinterpret_cast<char*>(n->grad().data()), n->grad().size() * sizeof(Real));
-        if (e->batch_kind() == BaseNode::kLstmCell) {
-          auto c = static_cast<LstmCellNode*>(e.get());
-          if (c->dc().size() > 0)
-            r.emplace_back(reinterpret_cast<char*>(c->dc().data()), c->dc().size() * sizeof(Real));
-        }
+        add(n->grad());
+        if (e->batch_kind() == BaseNode::kLstmCell) add(static_cast<LstmCellNode*>(e.get())->dc());
       }
       if (!all_gpu) {  // mixed graph: leave it to the nodes
         for (auto& e : list_) e->reset_grad();
@@ -381,15 +391,16 @@ class BatchedGraph {
       }
       std::sort(r.begin(), r.end());
       zero_ranges_.clear();
+      Device* last_owner = nullptr;
       for (auto& x : r) {
-        if (!zero_ranges_.empty() &&
-            zero_ranges_.back().first + zero_ranges_.back().second >= x.first) {
-          char* end = std::max(zero_ranges_.back().first + zero_ranges_.back().second,
-                               x.first + x.second);
+        if (!zero_ranges_.empty() && x.owner != nullptr && x.owner == last_owner &&
+            zero_ranges_.back().first + zero_ranges_.back().second >= x.p) {
+          char* end = std::max(zero_ranges_.back().first + zero_ranges_.back().second, x.p + x.bytes);
           zero_ranges_.back().second = static_cast<size_t>(end - zero_ranges_.back().first);
         } else {
-          zero_ranges_.push_back(x);
+          zero_ranges_.emplace_back(x.p, x.bytes);
         }
+        last_owner = x.owner;
       }
       zero_ready_ = true;
     }

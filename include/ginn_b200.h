@@ -14,6 +14,7 @@
 #ifndef GINN_B200_H
 #define GINN_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -263,6 +264,33 @@ int ginn_b200_lstm_cells_level_create(int device, int backward, int64_t hidden, 
 int ginn_b200_adam_update(int device, void* stream, int dtype, int64_t n, void* w, void* d,
                           float* m, float* v, float lr, float clip, float eps, float beta1,
                           float beta2, float beta1_t, float beta2_t);
+
+/* ---- Conv2d through the same products ------------------------------------------------------ */
+
+/* 2-d convolution with "SAME" padding, as Conv2dNode computes it (ginn/node/conv.h:28-79 over
+ * ginn/eigenop/eigen_conv.h:28-74): cross-correlation of
+ *   x (channels, rows, cols, batch)  with  k (filters, channels, krows, kcols)
+ * into y (filters, ceil(rows / row_stride), ceil(cols / col_stride), batch), all column-major and
+ * contiguous.  The reference extracts image patches and contracts them with the reshaped filters
+ * (Eigen::contract); here the patch matrix ((channels krows kcols) x (out_rows out_cols batch))
+ * is written into `workspace` by one pass over x and the contraction runs on the tensor-core
+ * kernels.  `workspace` must hold ginn_b200_conv2d_workspace(...) bytes and be 16-byte aligned;
+ * NULL makes the call take it from the stream-ordered allocator for the duration of the call. */
+size_t ginn_b200_conv2d_workspace(int dtype, int64_t channels, int64_t rows, int64_t cols,
+                                  int64_t batch, int64_t filters, int64_t krows, int64_t kcols,
+                                  int64_t row_stride, int64_t col_stride);
+int ginn_b200_conv2d_forward(int device, void* stream, int dtype, int64_t channels, int64_t rows,
+                             int64_t cols, int64_t batch, int64_t filters, int64_t krows,
+                             int64_t kcols, int64_t row_stride, int64_t col_stride, const void* x,
+                             const void* k, void* y, void* workspace);
+/* Gradients of the above (ginn/node/conv.h:52-64, eigen_conv.h:76-190), both accumulated:
+ *   dk += dy * patches(x)^T          (when dk != NULL)
+ *   dx += col2im(k^T * dy)           (when dx != NULL)
+ * `workspace` as for the forward call (the patch matrix, then the patch gradients). */
+int ginn_b200_conv2d_backward(int device, void* stream, int dtype, int64_t channels, int64_t rows,
+                              int64_t cols, int64_t batch, int64_t filters, int64_t krows,
+                              int64_t kcols, int64_t row_stride, int64_t col_stride, const void* x,
+                              const void* k, const void* dy, void* dx, void* dk, void* workspace);
 
 /* Text of the last failure on the calling thread ("" if none). */
 const char* ginn_b200_last_error(void);

@@ -18,6 +18,8 @@ Reference lines followed (paths inside the ginn source tree):
   pick_nll_backward      ginn/node/pick.h:87-131,218-224
   lstm_cell_*            ginn/model/lstm.h:97-100 (the elementwise part of the cell)
   adam_update            ginn/update/update.h:92-133
+  conv2d_*               ginn/node/conv.h:28-79 over ginn/eigenop/eigen_conv.h:28-190 (patches
+                         with Eigen's PADDING_SAME, contraction with the reshaped filters)
 
 Arithmetic: inputs exactly as handed to the GPU (fp32, or fp16-rounded), every product and sum
 in fp64, one rounding to the storage type where the reference materialises a tensor (node
@@ -194,6 +196,55 @@ def adam_update(w, d, m, v, lr, clip, eps, beta1, beta2, beta1_t, beta2_t):
     v = beta2 * v + (1.0 - beta2) * d * d
     w = w + (-lr / (1.0 - beta1_t)) * m / (eps + np.sqrt(v / (1.0 - beta2_t)))
     return w, d, m, v
+
+
+def conv2d_geometry(rows, cols, krows, kcols, row_stride, col_stride):
+    """Output extents and leading padding of Eigen's PADDING_SAME (eigen_conv.h:40-47 and the
+    patch extraction it calls): out = ceil(in / stride), total padding max(0, (out - 1) stride
+    + k - in), the smaller half in front."""
+    orows, ocols = -(-rows // row_stride), -(-cols // col_stride)
+    pr = max(0, (orows - 1) * row_stride + krows - rows)
+    pc = max(0, (ocols - 1) * col_stride + kcols - cols)
+    return orows, ocols, pr // 2, pc // 2
+
+
+def conv2d_forward(x, k, row_stride=1, col_stride=1) -> np.ndarray:
+    """x (C, R, W, B), k (F, C, KR, KC) -> y (F, OR, OC, B); cross-correlation, fp64 sums, one
+    rounding to the input type (Conv2dNode::forward_, ginn/node/conv.h:41-49)."""
+    x64, k64 = f64(x), f64(k)
+    C, R, W, B = x64.shape
+    F, _, KR, KC = k64.shape
+    OR, OC, pt, pl = conv2d_geometry(R, W, KR, KC, row_stride, col_stride)
+    xp = np.zeros((C, R + KR + row_stride, W + KC + col_stride, B))
+    xp[:, pt:pt + R, pl:pl + W] = x64
+    y = np.zeros((F, OR, OC, B))
+    for kr in range(KR):
+        for kc in range(KC):
+            patch = xp[:, kr:kr + (OR - 1) * row_stride + 1:row_stride,
+                       kc:kc + (OC - 1) * col_stride + 1:col_stride]
+            y += np.einsum("fc,crwb->frwb", k64[:, :, kr, kc], patch)
+    return y.astype(np.asarray(x).dtype)
+
+
+def conv2d_backward(x, k, dy, row_stride=1, col_stride=1):
+    """(dx, dk) of conv2d_forward for upstream gradient dy: the adjoints of the patch
+    contraction (Conv2dNode::backward_, ginn/node/conv.h:52-64)."""
+    x64, k64, dy64 = f64(x), f64(k), f64(dy)
+    C, R, W, B = x64.shape
+    F, _, KR, KC = k64.shape
+    OR, OC, pt, pl = conv2d_geometry(R, W, KR, KC, row_stride, col_stride)
+    xp = np.zeros((C, R + KR + row_stride, W + KC + col_stride, B))
+    xp[:, pt:pt + R, pl:pl + W] = x64
+    dxp = np.zeros_like(xp)
+    dk = np.zeros_like(k64)
+    for kr in range(KR):
+        for kc in range(KC):
+            rs = slice(kr, kr + (OR - 1) * row_stride + 1, row_stride)
+            cs = slice(kc, kc + (OC - 1) * col_stride + 1, col_stride)
+            dk[:, :, kr, kc] = np.einsum("frwb,crwb->fc", dy64, xp[:, rs, cs])
+            dxp[:, rs, cs] += np.einsum("fc,frwb->crwb", k64[:, :, kr, kc], dy64)
+    dt = np.asarray(x).dtype
+    return dxp[:, pt:pt + R, pl:pl + W].astype(dt), dk.astype(dt)
 
 
 def rel_frobenius(x, ref) -> float:

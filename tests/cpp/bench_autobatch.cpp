@@ -37,6 +37,11 @@ class SumOfCellsNode : public BaseDataNode<Real> {
   void forward_() override {
     value().resize({1, 1});
     value().set_zero();
+    const Size H = cells_[0]->value().rows();  // known once the cells have run
+    if (ones_.size() != H) {
+      ones_.resize({1, H});
+      ones_.set(std::vector<Real>(H, 1.f));
+    }
   }
   void backward_() override {
     const Size H = cells_[0]->value().rows();
@@ -59,11 +64,7 @@ class SumOfCellsNode : public BaseDataNode<Real> {
 
  public:
   SumOfCellsNode(DevPtr weights_dev, const std::vector<Ptr<LstmCellNode>>& cells)
-      : BaseDataNode<Real>(base(cells)), cells_(cells), ones_(std::move(weights_dev)) {
-    const Size H = cells_[0]->hidden();
-    ones_.resize({1, H});
-    ones_.set(std::vector<Real>(H, 1.f));
-  }
+      : BaseDataNode<Real>(base(cells)), cells_(cells), ones_(std::move(weights_dev)) {}
   std::string name() const override { return "SumOfCells"; }
 };
 

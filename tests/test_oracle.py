@@ -188,3 +188,31 @@ def test_bad_option_is_rejected_without_a_gpu():
     import ginn_b200
     with pytest.raises(ginn_b200.GinnB200Error):
         ginn_b200.set_option("no_such_option", 1)
+
+
+def test_conv2d_known_answers_and_gradients(kat):
+    """test/convnodes.cu.cpp:38-109: the reference's Conv2d values (SAME padding, strides), and
+    the oracle's gradients against finite differences (the reference checks them the same way)."""
+    for case in kat["conv2d"]["cases"]:
+        x = np.asarray(case["x"], np.float32)[None, :, :, None]
+        f = np.asarray(case["f"], np.float32)[None, None]
+        y = orc.conv2d_forward(x, f, *case["strides"])
+        np.testing.assert_allclose(y[0, :, :, 0], np.asarray(case["y"], np.float32), rtol=1e-6)
+    rng = np.random.default_rng(5)
+    for (C, R, W, B, F, KR, KC, sr, sc) in [(3, 5, 6, 2, 4, 3, 2, 2, 1), (2, 7, 4, 1, 3, 2, 3, 1, 3)]:
+        x, k = rng.standard_normal((C, R, W, B)), rng.standard_normal((F, C, KR, KC))
+        y = orc.conv2d_forward(x, k, sr, sc)
+        dy = rng.standard_normal(y.shape)
+        dx, dk = orc.conv2d_backward(x, k, dy, sr, sc)
+        eps = 1e-6
+        for _ in range(5):
+            i = tuple(rng.integers(0, s) for s in x.shape)
+            xp = x.copy()
+            xp[i] += eps
+            num = ((orc.conv2d_forward(xp, k, sr, sc) - y) * dy).sum() / eps
+            assert abs(num - dx[i]) <= 1e-4 * max(1.0, abs(dx[i]))
+            j = tuple(rng.integers(0, s) for s in k.shape)
+            kp = k.copy()
+            kp[j] += eps
+            num = ((orc.conv2d_forward(x, kp, sr, sc) - y) * dy).sum() / eps
+            assert abs(num - dk[j]) <= 1e-4 * max(1.0, abs(dk[j]))
