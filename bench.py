@@ -565,6 +565,27 @@ def run_mlp_dp(D: Dist, steps: int, warmup: int) -> dict:
     return out
 
 
+def run_cpp_autobatch() -> dict:
+    """Config 2 through the C++ host layer (ginn_b200/include/ginn/autobatch.h): one graph node
+    per sequence and step, tensors from a preallocated device, Autobatch(g) and the level
+    preparation inside the timed region.  Runs tests/cpp/bench_autobatch (built on demand)."""
+    cpp = os.path.join(ROOT, "tests", "cpp")
+    exe = os.path.join(cpp, "bench_autobatch")
+    try:
+        subprocess.run(["make", "-C", cpp, "bench_autobatch"], check=True, capture_output=True,
+                       timeout=300)
+        res = subprocess.run([exe, "5", "20"], capture_output=True, text=True, timeout=300)
+        line = [ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1]
+        out = json.loads(line)
+        out["what"] = ("C++ BatchedGraph on per-node tensors: rewrite_ms = Autobatch(g); "
+                       "first_pass = forward + reset_grad + backward with the one-time level "
+                       "preparation; replay = the same pass on the prepared schedule; host clock "
+                       "around device synchronisation")
+        return out
+    except Exception as e:  # the headline does not depend on it
+        return {"error": f"{type(e).__name__}: {e}"[:300]}
+
+
 def run_configs(D: Dist, args, peaks) -> dict:
     """Configs 1, 2 (recurrent and flat), 3 and 5 on one GPU: ms per step, useful TFLOP/s or
     nodes/s, fraction of the 3xTF32 ceiling, and the CPU port on the same shapes."""
@@ -618,6 +639,7 @@ def run_configs(D: Dist, args, peaks) -> dict:
            "note": "replayed from a CUDA graph; with_rewrite = one rewrite + one pass launched "
                    "level by level, as a graph built anew for every batch needs"})
     del w
+    out["C2"]["cpp_batched_graph"] = run_cpp_autobatch()
     # C2 flat
     w = wl.LstmFlat(dev)
     ms = time_steps(D, w.step, steps, warmup)
