@@ -3,6 +3,7 @@
 #define GINN_B200_HOST_GINN_H
 #include <ginn/autobatch.h>
 #include <ginn/node/affine.h>
+#include <ginn/node/conv.h>
 #include <ginn/node/data.h>
 #include <ginn/node/lstmcell.h>
 #include <ginn/node/nlnode.h>

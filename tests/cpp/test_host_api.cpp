@@ -333,6 +333,32 @@ static void test_autobatch_nonlinear_and_cells() {
   }
 }
 
+// test/convnodes.cu.cpp:38-70 ("Conv2d"): known values with and without strides, then both
+// gradients of sum(y) against the closed form (every filter tap sums the inputs it touches).
+static void test_conv2d() {
+  auto x = Data<Real>(gpu(), {1, 3, 3, 1});
+  x->value().set({1, 2, 3, 4, 5, 6, 7, 8, 9});  // column-major: element (0, r, c, 0) = 1 + r + 3c
+  auto f = Data<Real>(gpu(), {1, 1, 2, 2});
+  f->value().set({1, 2, 3, 4});                  // [[1, 3], [2, 4]]
+  auto y = Conv2d(x, f);
+  Graph g(y);
+  g.forward();
+  CHECK((y->shape() == Shape{1, 3, 3, 1}));
+  CHECK(close(y->value().vector(), {37, 47, 21, 67, 77, 33, 23, 26, 9}, 1e-6f));
+  auto y2 = Conv2d(x, f, 2, 1);
+  Graph(y2).forward();
+  CHECK((y2->shape() == Shape{1, 2, 3, 1}));
+  CHECK(close(y2->value().vector(), {37, 21, 67, 33, 23, 9}, 1e-6f));
+  auto y3 = Conv2d(x, f, 2, 3);
+  Graph(y3).forward();
+  CHECK(close(y3->value().vector(), {37, 21}, 1e-6f));
+  g.reset_grad().backward(1.);
+  // d sum(y) / d f[kr][kc] = sum of x over the window positions that tap stays inside the image
+  CHECK(close(f->grad().vector(), {45, 33, 39, 28}, 1e-5f));  // (0,0), (1,0), (0,1), (1,1)
+  // d sum(y) / d x[r][c] = sum of the taps that reach it: 1 at the top-left, 10 in the interior
+  CHECK(close(x->grad().vector(), {1, 3, 3, 4, 10, 10, 4, 10, 10}, 1e-5f));
+}
+
 static void test_prealloc_accounting() {
   auto dev = PreallocGpu(0, 1 << 20);
   auto W = Data<Real>(dev, {8, 5}), x = Data<Real>(dev, {5, 3}), b = Data<Real>(dev, {8});
@@ -475,6 +501,7 @@ int main() {
   test_prod_cpu_vs_gpu();
   test_autobatch();
   test_autobatch_nonlinear_and_cells();
+  test_conv2d();
   test_prealloc_accounting();
   test_errors();
   test_pick_nll<Real>(1e-6f);
