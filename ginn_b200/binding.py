@@ -97,6 +97,12 @@ def lib():
                  "ginn_b200_adam_update", "ginn_b200_softmax_forward",
                  "ginn_b200_softmax_backward"):
         getattr(L, name).restype = ci
+    L.ginn_b200_attention_forward.argtypes = [ci, vp, ci, i64, i64, i64, vp, i64, i64, vp, i64, i64,
+                                              vp, i64, i64, cf, ci, vp, i64, i64, vp, i64, i64]
+    L.ginn_b200_attention_backward.argtypes = [ci, vp, ci, i64, i64, i64, vp, i64, i64, vp, i64, i64,
+                                               vp, i64, i64, cf, vp, i64, i64, vp, i64, i64, vp, vp,
+                                               vp, vp]
+    L.ginn_b200_attention_forward.restype = L.ginn_b200_attention_backward.restype = ci
     L.ginn_b200_conv2d_workspace.argtypes = [ci] + [i64] * 9
     L.ginn_b200_conv2d_workspace.restype = C.c_size_t
     L.ginn_b200_conv2d_forward.argtypes = [ci, vp, ci] + [i64] * 9 + [vp, vp, vp, vp]
@@ -409,6 +415,31 @@ def lstm_cells(backward: bool, tables: Sequence[Sequence[Optional[torch.Tensor]]
     some = tables[0][0]
     hidden = some.numel() // 4
     _check(lib().ginn_b200_lstm_cells(_dev(some), _stream(some), int(backward), hidden, n, flat))
+
+
+def _bstride(t: torch.Tensor) -> int:
+    return int(t.stride(2)) if t.shape[2] > 1 else int(t.shape[1]) * _ld(t)
+
+
+def attention_forward(k, q, v, o, p=None, scale=1.0, causal=False) -> None:
+    """o = v @ softmax(scale * k @ q [masked]) per batch (ginn_b200_attention_forward).  k: (T, hs,
+    nb); q, v, o: (hs, T, nb); p: (T, T, nb) or None; column-major batched tensors."""
+    T, hs, nb = k.shape
+    _check(lib().ginn_b200_attention_forward(
+        _dev(k), _stream(k), _dtype_of(k), T, hs, nb, k.data_ptr(), _ld(k), _bstride(k), q.data_ptr(),
+        _ld(q), _bstride(q), v.data_ptr(), _ld(v), _bstride(v), scale, int(causal), o.data_ptr(),
+        _ld(o), _bstride(o), _ptr(p), _ld(p) if p is not None else 0,
+        _bstride(p) if p is not None else 0))
+
+
+def attention_backward(k, q, v, p, d_o, ds, dk=None, dq=None, dv=None, scale=1.0) -> None:
+    """dk += ..., dq += ..., dv += ... from the kept softmax output p (ginn_b200_attention_backward);
+    ds: scratch shaped like p."""
+    T, hs, nb = k.shape
+    _check(lib().ginn_b200_attention_backward(
+        _dev(k), _stream(k), _dtype_of(k), T, hs, nb, k.data_ptr(), _ld(k), _bstride(k), q.data_ptr(),
+        _ld(q), _bstride(q), v.data_ptr(), _ld(v), _bstride(v), scale, p.data_ptr(), _ld(p), _bstride(p),
+        d_o.data_ptr(), _ld(d_o), _bstride(d_o), ds.data_ptr(), _ptr(dk), _ptr(dq), _ptr(dv)))
 
 
 def _conv_dims(x: torch.Tensor, k: torch.Tensor):

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libginn_b200.so")
-SOURCES = ["api.cu", "grouped_static.cu", "hgemm_tma.cu", "hgemm_pair.cu", "hgemm_gather.cu", "sgemm3x_tma.cu", "small.cu", "step_ops.cu", "conv.cu"]
+SOURCES = ["api.cu", "grouped_static.cu", "hgemm_tma.cu", "hgemm_pair.cu", "hgemm_gather.cu", "sgemm3x_tma.cu", "small.cu", "step_ops.cu", "conv.cu", "attention.cu"]
 HEADERS = ["ptx.cuh", "math.cuh", "problem.h", "launch.h", os.path.join("..", "..", "include", "ginn_b200.h")]
 
 

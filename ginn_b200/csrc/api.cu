@@ -1034,6 +1034,99 @@ int ginn_b200_level_destroy(ginn_b200_level* level) {
   return GINN_B200_OK;
 }
 
+int ginn_b200_attention_forward(int device, void* stream_, int dtype, int64_t t, int64_t hs,
+                                int64_t batches, const void* k, int64_t ldk, int64_t stride_k,
+                                const void* q, int64_t ldq, int64_t stride_q, const void* v,
+                                int64_t ldv, int64_t stride_v, float scale, int causal, void* o,
+                                int64_t ldo, int64_t stride_o, void* p, int64_t ldp,
+                                int64_t stride_p) {
+  if (int s = check_common(dtype, t, hs, batches)) return s;
+  if (t == 0 || hs == 0 || batches == 0) return GINN_B200_OK;
+  if (!k || !q || !v || !o) return fail(GINN_B200_BAD_ARGUMENT, "null tensor pointer");
+  if (ldk < t || ldq < hs || ldv < hs || ldo < hs || (p && ldp < t))
+    return fail(GINN_B200_BAD_ARGUMENT, "leading dimension smaller than the matrix it describes");
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  gb::AttentionArgs a;
+  a.K = k; a.Q = q; a.V = v; a.O = o; a.P = p;
+  a.ldk = ldk; a.ldq = ldq; a.ldv = ldv; a.ldo = ldo; a.ldp = ldp;
+  a.strideK = stride_k; a.strideQ = stride_q; a.strideV = stride_v; a.strideO = stride_o;
+  a.strideP = stride_p;
+  a.T = (int)t; a.hs = (int)hs; a.batches = (int)batches;
+  a.scale = scale;
+  a.causal = causal ? 1 : 0;
+  if (dtype == GINN_B200_F32 && t_force_path == PATH_AUTO && gb::attention_fused_supported(a)) {
+    CU_TRY(gb::launch_attention_fwd(a, stream, ctx->d_status));
+    g_launches.fetch_add(1);
+    return GINN_B200_OK;
+  }
+  // The sequence the reference runs, with `p` as the score tensor.
+  if (!p) return fail(GINN_B200_BAD_ARGUMENT,
+                      "this shape takes the unfused path, which needs `p` as its score buffer");
+  if (int s = gemm_impl(device, stream_, dtype, 0, 0, t, t, hs, k, ldk, stride_k, q, ldq, stride_q, p,
+                        ldp, stride_p, batches, 0))
+    return s;
+  if (scale != 1.f || causal) {
+    if (dtype != GINN_B200_F32)
+      return fail(GINN_B200_UNSUPPORTED, "scale / causal mask on the unfused path are fp32 only");
+    CU_TRY(gb::launch_scale_mask_f32(static_cast<float*>(p), ldp, stride_p, (int)t, (int)batches, scale,
+                                     a.causal, stream));
+    g_launches.fetch_add(1);
+  }
+  if (stride_p != ldp * t)
+    return fail(GINN_B200_UNSUPPORTED, "the unfused path needs densely packed score matrices");
+  CU_TRY(gb::launch_pick_nll_forward(dtype, p, ldp, nullptr, p, ldp, nullptr, (int)t, t * batches,
+                                     stream));
+  g_launches.fetch_add(1);
+  return gemm_impl(device, stream_, dtype, 0, 0, hs, t, t, v, ldv, stride_v, p, ldp, stride_p, o, ldo,
+                   stride_o, batches, 0);
+}
+
+int ginn_b200_attention_backward(int device, void* stream_, int dtype, int64_t t, int64_t hs,
+                                 int64_t batches, const void* k, int64_t ldk, int64_t stride_k,
+                                 const void* q, int64_t ldq, int64_t stride_q, const void* v,
+                                 int64_t ldv, int64_t stride_v, float scale, const void* p,
+                                 int64_t ldp, int64_t stride_p, const void* d_o, int64_t ldo,
+                                 int64_t stride_o, void* ds, void* dk, void* dq, void* dv) {
+  if (int s = check_common(dtype, t, hs, batches)) return s;
+  if (t == 0 || hs == 0 || batches == 0) return GINN_B200_OK;
+  if (!k || !q || !v || !p || !d_o || !ds) return fail(GINN_B200_BAD_ARGUMENT, "null tensor pointer");
+  if (stride_p != ldp * t)
+    return fail(GINN_B200_UNSUPPORTED, "the score matrices must be densely packed (stride = ld * t)");
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // dv (hs x T) += d_o (hs x T) * P^T
+  if (dv)
+    if (int s = gemm_impl(device, stream_, dtype, 0, 1, hs, t, t, d_o, ldo, stride_o, p, ldp, stride_p,
+                          dv, ldv, stride_v, batches, 1))
+      return s;
+  if (!dk && !dq) return GINN_B200_OK;
+  // dP (T x T) = V^T * d_o, then dS = P (.) (dP - colsum(P (.) dP)) in place
+  if (int s = gemm_impl(device, stream_, dtype, 1, 0, t, t, hs, v, ldv, stride_v, d_o, ldo, stride_o, ds,
+                        ldp, stride_p, batches, 0))
+    return s;
+  CU_TRY(gb::launch_softmax_backward(dtype, p, ldp, ds, ldp, ds, ldp, (int)t, t * batches, 0, stream));
+  g_launches.fetch_add(1);
+  if (scale != 1.f) {
+    if (dtype != GINN_B200_F32) return fail(GINN_B200_UNSUPPORTED, "scale != 1 is fp32 only");
+    CU_TRY(gb::launch_scale_mask_f32(static_cast<float*>(ds), ldp, stride_p, (int)t, (int)batches,
+                                     scale, 0, stream));
+    g_launches.fetch_add(1);
+  }
+  // dk (T x hs) += dS * Q^T;  dq (hs x T) += K'^T * dS
+  if (dk)
+    if (int s = gemm_impl(device, stream_, dtype, 0, 1, t, hs, t, ds, ldp, stride_p, q, ldq, stride_q, dk,
+                          ldk, stride_k, batches, 1))
+      return s;
+  if (dq)
+    if (int s = gemm_impl(device, stream_, dtype, 1, 0, hs, t, t, k, ldk, stride_k, ds, ldp, stride_p, dq,
+                          ldq, stride_q, batches, 1))
+      return s;
+  return GINN_B200_OK;
+}
+
 size_t ginn_b200_conv2d_workspace(int dtype, int64_t C, int64_t R, int64_t W, int64_t B, int64_t F,
                                   int64_t KR, int64_t KC, int64_t sr, int64_t sc) {
   gb::ConvShape s;

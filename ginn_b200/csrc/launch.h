@@ -109,6 +109,28 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
 cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
                           long long N, void* rowsum, cudaStream_t stream);
 
+// --- fused attention forward, fp32 (attention.cu) ---
+struct AttentionArgs {
+  const void* K;  // T x hs per batch (key index contiguous)
+  const void* Q;  // hs x T
+  const void* V;  // hs x T
+  void* O;        // hs x T
+  void* P;        // T x T softmax output, or null when the caller does not need it
+  long long ldk, ldq, ldv, ldo, ldp;
+  long long strideK, strideQ, strideV, strideO, strideP;  // elements between batches
+  int T, hs, batches;
+  float scale;
+  int causal;
+};
+// True when the one-kernel path can take the problem (T <= 256, hs in {32, 64, 128}, 16-byte
+// aligned operands and strides).
+bool attention_fused_supported(const AttentionArgs& a);
+cudaError_t launch_attention_fwd(const AttentionArgs& a, cudaStream_t stream, int* status);
+// s = scale * s in place over a strided batch of T x T matrices; with `causal`, entries with
+// row > column (keys after the query) become -inf.
+cudaError_t launch_scale_mask_f32(float* s, long long ld, long long stride, int T, int batches,
+                                  float scale, int causal, cudaStream_t stream);
+
 // --- Conv2d as patch extraction + matrix products (conv.cu) ---
 struct ConvShape {
   long long out_rows, out_cols, pad_top, pad_left;

@@ -325,6 +325,19 @@ lstm_cells_backward_kernel(const void* const* __restrict__ tab, int H, long long
   if (dcprev) dcprev[r] += dc * f;
 }
 
+// S = scale * S in place over a strided batch of T x T score matrices (row = key position,
+// column = query position); with `causal`, keys after the query (row > column) become -inf, as
+// min-GPT's InPlaceMask does before the softmax (examples/min-gpt.cu.cpp:133-137).
+__global__ void __launch_bounds__(256)
+scale_mask_f32_kernel(float* __restrict__ s, long long ld, long long stride, int T, float scale,
+                      int causal) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int col = blockIdx.y;
+  if (r >= T) return;
+  float* q = s + blockIdx.z * stride + col * ld + r;
+  *q = (causal && r > col) ? -INFINITY : *q * scale;
+}
+
 // C = act(C) in place, fp32: the activation of a product whose contraction was split over
 // several CTAs (their partial sums meet in C, so the nonlinearity cannot ride on any of them).
 __global__ void __launch_bounds__(256)
@@ -580,6 +593,15 @@ cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c
   dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
   return launch_kernel(lstm_cell_forward_kernel, grid, dim3(256), 0, stream, pdl_enabled(), gates,
                        ldg, c_prev, ldcp, c, ldc, h, ldh, xh_next, ldx, H, n, n_next);
+}
+
+cudaError_t launch_scale_mask_f32(float* s, long long ld, long long stride, int T, int batches,
+                                  float scale, int causal, cudaStream_t stream) {
+  if (T <= 0 || batches <= 0) return cudaSuccess;
+  if (T > 65535 || batches > 65535) return cudaErrorInvalidValue;
+  dim3 grid((T + 255) / 256, T, batches);
+  scale_mask_f32_kernel<<<grid, 256, 0, stream>>>(s, ld, stride, T, scale, causal);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_lstm_cells(bool backward, const void* const* dtab, int H, long long n,

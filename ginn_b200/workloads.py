@@ -71,7 +71,8 @@ class Attention:
     S = K' * Q, column softmax, O = V * P, and the four backward products; 256 (batch, head)
     pairs, T = 256, head size 64, fp32."""
 
-    def __init__(self, device, T=256, hs=64, nb=256, seed=20243):
+    def __init__(self, device, T=256, hs=64, nb=256, seed=20243, fused=True):
+        self.fused = fused
         g = torch.Generator(device=device).manual_seed(seed)
         sd = math.sqrt(1 / 8)
 
@@ -90,6 +91,15 @@ class Attention:
 
     def step(self):
         gb = B
+        if self.fused:
+            # one kernel forward (scores stay on the SM; P is kept for the backward pass), then
+            # the composed backward: four batched products and one softmax-backward pass
+            for t in (self.dV, self.dQ, self.dK):
+                t.zero_()
+            gb.attention_forward(self.k, self.q, self.v, self.O, self.P)
+            gb.attention_backward(self.k, self.q, self.v, self.P, self.dO, self.dS, self.dK, self.dQ,
+                                  self.dV)
+            return
         for t in (self.dV, self.dQ, self.dK, self.dP):
             t.zero_()
         gb.gemm_batched(self.k, self.q, self.S)

@@ -265,6 +265,40 @@ int ginn_b200_adam_update(int device, void* stream, int dtype, int64_t n, void* 
                           float* m, float* v, float lr, float clip, float eps, float beta1,
                           float beta2, float beta1_t, float beta2_t);
 
+/* ---- Attention as min-GPT composes it from BatchedProd, mask and Softmax ------------------- */
+
+/* For every batch b (min-GPT folds batch and heads into it):
+ *   S = scale * K'_b * Q_b;  causal: S[i, j] = -inf for key i > query j;
+ *   P = column softmax of S;  O_b = V_b * P
+ * with ginn's layouts (examples/min-gpt.cu.cpp:108-157): K' is T x hs, Q and V are hs x T, P is
+ * T x T, O is hs x T, all column-major with the given leading dimensions and batch strides.
+ * Replaces BatchedProd -> InPlaceProdScalar -> InPlaceMask -> Softmax -> BatchedProd, which
+ * writes and re-reads two T x T tensors per batch.  fp32 with T <= 256, hs in {32, 64, 128} and
+ * 16-byte aligned operands runs as ONE kernel that keeps the scores in tensor memory; `p` is then
+ * written only because SoftmaxOp's backward needs it and may be NULL when no backward follows.
+ * Other shapes (and fp16) take the unfused sequence inside the library and need `p` as their
+ * score buffer. */
+int ginn_b200_attention_forward(int device, void* stream, int dtype, int64_t t, int64_t hs,
+                                int64_t batches, const void* k, int64_t ldk, int64_t stride_k,
+                                const void* q, int64_t ldq, int64_t stride_q, const void* v,
+                                int64_t ldv, int64_t stride_v, float scale, int causal, void* o,
+                                int64_t ldo, int64_t stride_o, void* p, int64_t ldp,
+                                int64_t stride_p);
+/* Gradients of the above from the kept softmax output `p` and the upstream gradient `d_o`, all
+ * accumulated (`+=`), NULL = input without gradient:
+ *   dv += d_o * P^T;   dP = V^T * d_o;   dS = scale * P (.) (dP - colsum(P (.) dP));
+ *   dk += dS * Q^T;    dq += K'^T * dS.
+ * `ds` is a caller-owned T x T x batches scratch with p's layout (it holds dP, then dS).
+ * Replaces the backward passes of the five nodes (ginn/node/prod.h:129-169, ginn/nonlin.h:
+ * 169-190): four batched products and one softmax-backward pass, without the mask / scale
+ * tensors. */
+int ginn_b200_attention_backward(int device, void* stream, int dtype, int64_t t, int64_t hs,
+                                 int64_t batches, const void* k, int64_t ldk, int64_t stride_k,
+                                 const void* q, int64_t ldq, int64_t stride_q, const void* v,
+                                 int64_t ldv, int64_t stride_v, float scale, const void* p,
+                                 int64_t ldp, int64_t stride_p, const void* d_o, int64_t ldo,
+                                 int64_t stride_o, void* ds, void* dk, void* dq, void* dv);
+
 /* ---- Conv2d through the same products ------------------------------------------------------ */
 
 /* 2-d convolution with "SAME" padding, as Conv2dNode computes it (ginn/node/conv.h:28-79 over

@@ -18,6 +18,9 @@ Reference lines followed (paths inside the ginn source tree):
   pick_nll_backward      ginn/node/pick.h:87-131,218-224
   lstm_cell_*            ginn/model/lstm.h:97-100 (the elementwise part of the cell)
   adam_update            ginn/update/update.h:92-133
+  attention_*            examples/min-gpt.cu.cpp:108-157 (BatchedProd, InPlaceProdScalar,
+                         InPlaceMask with an upper-triangular mask, Softmax, BatchedProd) and the
+                         backward passes of those nodes (ginn/node/prod.h:129-169, nonlin.h:169-190)
   conv2d_*               ginn/node/conv.h:28-79 over ginn/eigenop/eigen_conv.h:28-190 (patches
                          with Eigen's PADDING_SAME, contraction with the reshaped filters)
 
@@ -196,6 +199,35 @@ def adam_update(w, d, m, v, lr, clip, eps, beta1, beta2, beta1_t, beta2_t):
     v = beta2 * v + (1.0 - beta2) * d * d
     w = w + (-lr / (1.0 - beta1_t)) * m / (eps + np.sqrt(v / (1.0 - beta2_t)))
     return w, d, m, v
+
+
+def attention_forward(k, q, v, scale=1.0, causal=False):
+    """k (T, hs, nb), q and v (hs, T, nb) -> (o (hs, T, nb), p (T, T, nb)): per batch
+    S = scale * k @ q, keys after the query masked to -inf when causal, P = softmax over the
+    rows, O = v @ P.  Sums in fp64, one rounding of each returned tensor to the input type."""
+    k64, q64, v64 = f64(k), f64(q), f64(v)
+    T = k64.shape[0]
+    s = scale * np.einsum("ihb,hjb->ijb", k64, q64)
+    if causal:
+        i, j = np.arange(T)[:, None], np.arange(T)[None, :]
+        s = np.where((i > j)[:, :, None], -np.inf, s)
+    e = np.exp(s - s.max(axis=0, keepdims=True))
+    p = e / e.sum(axis=0, keepdims=True)
+    o = np.einsum("hib,ijb->hjb", v64, p)
+    dt = np.asarray(k).dtype
+    return o.astype(dt), p.astype(dt)
+
+
+def attention_backward(k, q, v, p, d_o, scale=1.0):
+    """(dk, dq, dv) for upstream gradient d_o (hs, T, nb), from the kept softmax output p."""
+    k64, q64, v64, p64, do64 = f64(k), f64(q), f64(v), f64(p), f64(d_o)
+    dv = np.einsum("hjb,ijb->hib", do64, p64)
+    dp = np.einsum("hib,hjb->ijb", v64, do64)
+    ds = scale * p64 * (dp - (p64 * dp).sum(axis=0, keepdims=True))
+    dk = np.einsum("ijb,hjb->ihb", ds, q64)
+    dq = np.einsum("ihb,ijb->hjb", k64, ds)
+    dt = np.asarray(k).dtype
+    return dk.astype(dt), dq.astype(dt), dv.astype(dt)
 
 
 def conv2d_geometry(rows, cols, krows, kcols, row_stride, col_stride):
