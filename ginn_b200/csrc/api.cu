@@ -1056,6 +1056,7 @@ int ginn_b200_attention_forward(int device, void* stream_, int dtype, int64_t t,
   a.T = (int)t; a.hs = (int)hs; a.batches = (int)batches;
   a.scale = scale;
   a.causal = causal ? 1 : 0;
+  if (!(scale > 0.f)) return fail(GINN_B200_BAD_ARGUMENT, "attention scale must be positive");
   if (dtype == GINN_B200_F32 && t_force_path == PATH_AUTO && gb::attention_fused_supported(a)) {
     CU_TRY(gb::launch_attention_fwd(a, stream, ctx->d_status));
     g_launches.fetch_add(1);

@@ -24,6 +24,7 @@
 //               (and stored to HBM if wanted), V slices split alongside; then the epilogue.
 // Limits: T <= 256, T % 4 == 0, hs in {32, 64, 128}, 16-byte aligned operands.
 #include <cuda.h>
+#include <cstdio>
 #include <cstring>
 #include "ptx.cuh"
 #include "math.cuh"
@@ -73,12 +74,13 @@ __device__ __forceinline__ void split_kc(const uint8_t* src, uint8_t* dst_hi, ui
 }
 
 // Outer-contiguous raw slice [box of 32 outer][32 k][32 outer] (unswizzled TMA boxes) ->
-// transposed, swizzled K-major planes.  `outer` rows (32, 64 or 128) are shared by 256 threads:
-// thread t owns row t % outer and 32 * outer / 256 consecutive k values.
+// transposed, swizzled K-major planes.  `outer` rows (32, 64 or 128) are shared by `nthreads`
+// threads (a power of two with 32 * outer / nthreads >= 4): thread t owns row t % outer and
+// 32 * outer / nthreads consecutive k values.
 __device__ __forceinline__ void split_oc(const uint8_t* src, uint8_t* dst_hi, uint8_t* dst_lo, int t,
-                                         int outer) {
+                                         int outer, int nthreads = 256) {
   const int o = t & (outer - 1);
-  const int kper = outer >> 3;  // 4, 8 or 16
+  const int kper = 32 * outer / nthreads;  // 4, 8 or 16
   const int kbase = (t / outer) * kper;
   const float* col = reinterpret_cast<const float*>(src + (o >> 5) * 4096) + (o & 31);
   for (int c = 0; c < kper; c += 4) {
@@ -96,6 +98,13 @@ __device__ __forceinline__ void split_oc(const uint8_t* src, uint8_t* dst_hi, ui
   }
 }
 
+// hi / lo split of a finite value of moderate size (softmax outputs): the rounding of
+// split_tf32 without its guard for infinities.
+__device__ __forceinline__ void split_finite(float x, float& hi, float& lo) {
+  hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+  lo = x - hi;
+}
+
 __global__ void __launch_bounds__(ATHREADS, 1)
 attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -106,6 +115,13 @@ attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ stat
   __shared__ __align__(8) uint64_t s_full, o_full;
   __shared__ uint32_t tmem_slot;
   __shared__ float red[4][ATM];  // per column group: row maxima, then row sums
+#ifdef GB_PHASE_TIMES  // instrumented build (-DGB_PHASE_TIMES): two CTAs print their phase durations
+  __shared__ long long ph_t[12];
+  if (threadIdx.x == 0) ph_t[0] = clock64();
+#define APH(i) do { if (threadIdx.x == 64) ph_t[i] = clock64(); } while (0)
+#else
+#define APH(i) do { } while (0)
+#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -242,6 +258,7 @@ attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ stat
       }
     };
 
+    APH(1);
     // ---- phase A: split the raw Q and K' slices ----
     for (int it = 0; it < nA && ok; ++it) {
       if (!mbar_wait(smem_u32(&raw_full[rs_i]), rph, status, DEV_TIMEOUT_FULL, 0x600 + it) ||
@@ -261,47 +278,73 @@ attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ stat
       advance();
     }
 
+    APH(2);
     // ---- phase B: softmax statistics of this thread's row over its share of the keys ----
-    // Thread (row, cg) owns keys i with (i % 32) / 8 == cg: eight consecutive keys per 32-key block.
+    // For the statistics thread (row, cg) takes a contiguous quarter of the keys (32 columns per
+    // tensor-memory load); for phase C it owns keys i with (i % 32) / 8 == cg, eight consecutive
+    // keys of every 32-key block.  Any partition serves for a maximum and a sum.
     ok = ok && mbar_wait(smem_u32(&s_full), 0, status, DEV_TIMEOUT_ACCUM, 0x700);
     tc_fence_after();
-    const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16) + cg * 8;
+    APH(3);
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t tbase = lane_base + cg * 8;
     const int last_key = p.causal ? (j < p.T - 1 ? j : p.T - 1) : p.T - 1;  // keys i <= last_key count
-    auto score = [&](uint32_t bits, int i) -> float {
-      return i <= last_key ? __uint_as_float(bits) * p.scale : -INFINITY;
-    };
-    float m = -INFINITY;
+    // exp(scale * (S - Smax)) = 2^(S * c1 - Smax * c1) with c1 = scale * log2(e): one fused
+    // multiply-add and one hardware exponential per key (scale > 0, as 1 / sqrt(hs) is).  The
+    // hardware exponential is good to about 2e-7 relative, against 1e-5 allowed; libm's expf and
+    // a per-key mask test made this phase and the next instruction-bound.
+    const float c1 = p.scale * 1.44269502f;
+    const int quarter = nC * 8;  // keys per column group (nC blocks of 32 keys in all)
+    float m = -INFINITY;         // maximum of the raw scores of this row
     if (ok) {
-      for (int kb = 0; kb < nC; ++kb) {
-        uint32_t v[8];
-        tmem_ld8(tbase + kb * 32, v);
+      for (int c = 0; c < quarter; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cg * quarter + c, v);
         tmem_ld_wait();
+        const int i0 = cg * quarter + c;
+        if (i0 + 31 <= last_key && c + 32 <= quarter) {  // the usual case: nothing masked
 #pragma unroll
-        for (int e = 0; e < 8; ++e) m = fmaxf(m, score(v[e], kb * 32 + cg * 8 + e));
+          for (int e = 0; e < 32; ++e) m = fmaxf(m, __uint_as_float(v[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c + e < quarter && i0 + e <= last_key) m = fmaxf(m, __uint_as_float(v[e]));
+        }
       }
     }
     red[cg][row] = m;
     asm volatile("bar.sync 1, %0;" ::"n"(AXFORM) : "memory");
     m = fmaxf(fmaxf(red[0][row], red[1][row]), fmaxf(red[2][row], red[3][row]));
     asm volatile("bar.sync 1, %0;" ::"n"(AXFORM) : "memory");  // everyone has read the maxima
+    const float c0 = -m * c1;
+    auto expo = [&](uint32_t bits) -> float {
+      float y;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fmaf(__uint_as_float(bits), c1, c0)));
+      return y;
+    };
     float l = 0.f;
     if (ok) {
-      for (int kb = 0; kb < nC; ++kb) {
-        uint32_t v[8];
-        tmem_ld8(tbase + kb * 32, v);
+      for (int c = 0; c < quarter; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cg * quarter + c, v);
         tmem_ld_wait();
+        const int i0 = cg * quarter + c;
+        if (i0 + 31 <= last_key && c + 32 <= quarter) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float s = score(v[e], kb * 32 + cg * 8 + e);
-          l += s == -INFINITY ? 0.f : expf(s - m);
+          for (int e = 0; e < 32; ++e) l += expo(v[e]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c + e < quarter && i0 + e <= last_key) l += expo(v[e]);
         }
       }
     }
     red[cg][row] = l;
     asm volatile("bar.sync 1, %0;" ::"n"(AXFORM) : "memory");
     l = (red[0][row] + red[1][row]) + (red[2][row] + red[3][row]);
-    const float inv = 1.f / l;  // key 0 always counts, so l >= exp(0 - ...) > 0
+    const float inv = 1.f / l;  // key 0 always counts, so l > 0
 
+    APH(4);
     // ---- phase C: P for one 32-key block at a time, V slices alongside ----
     float* prow = p.P ? p.P + static_cast<long long>(batch) * p.strideP + static_cast<long long>(j) * p.ldp
                       : nullptr;
@@ -315,26 +358,28 @@ attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ stat
       tmem_ld8(tbase + kb * 32, v);
       tmem_ld_wait();
       float pv[8];
+      const int i0 = kb * 32 + cg * 8;
+      if (i0 + 7 <= last_key) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float s = score(v[e], kb * 32 + cg * 8 + e);
-        pv[e] = s == -INFINITY ? 0.f : expf(s - m) * inv;
+        for (int e = 0; e < 8; ++e) pv[e] = expo(v[e]) * inv;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pv[e] = i0 + e <= last_key ? expo(v[e]) * inv : 0.f;
       }
       uint8_t* a_hi = base_ptr + ps_i * APLANE_STAGE;
       uint8_t* a_lo = a_hi + APLANE;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float4 h, lo4;
-        split_tf32(pv[4 * c + 0], h.x, lo4.x);
-        split_tf32(pv[4 * c + 1], h.y, lo4.y);
-        split_tf32(pv[4 * c + 2], h.z, lo4.z);
-        split_tf32(pv[4 * c + 3], h.w, lo4.w);
+        split_finite(pv[4 * c + 0], h.x, lo4.x);
+        split_finite(pv[4 * c + 1], h.y, lo4.y);
+        split_finite(pv[4 * c + 2], h.z, lo4.z);
+        split_finite(pv[4 * c + 3], h.w, lo4.w);
         const uint32_t off = sw128_offset(row, cg * 2 + c);
         *reinterpret_cast<float4*>(a_hi + off) = h;
         *reinterpret_cast<float4*>(a_lo + off) = lo4;
       }
       if (prow != nullptr && j < p.T) {
-        const int i0 = kb * 32 + cg * 8;
         if (i0 + 8 <= p.T) {
           *reinterpret_cast<float4*>(prow + i0) = make_float4(pv[0], pv[1], pv[2], pv[3]);
           *reinterpret_cast<float4*>(prow + i0 + 4) = make_float4(pv[4], pv[5], pv[6], pv[7]);
@@ -342,9 +387,10 @@ attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ stat
           for (int e = 0; e < 8 && i0 + e < p.T; ++e) prow[i0 + e] = pv[e];
         }
       }
-      if (xt < 256) {  // V slice (hs x 32 keys) -> B planes
+      {  // V slice (hs x 32 keys) -> B planes, shared by all threads (by half of them when hs = 32)
         const uint8_t* src = base_ptr + APLANE_STAGES * APLANE_STAGE + rs_i * ARAW_STAGE;
-        split_oc(src, a_hi + 2 * APLANE, a_hi + 3 * APLANE, xt, p.hs);
+        const int nthr = p.hs >= 64 ? AXFORM : 256;
+        if (xt < nthr) split_oc(src, a_hi + 2 * APLANE, a_hi + 3 * APLANE, xt, p.hs, nthr);
       }
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&plane_full[ps_i]));
@@ -352,9 +398,11 @@ attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ stat
       advance();
     }
 
+    APH(5);
     // ---- epilogue: O^T[j, h] -> O[h, j]; this thread writes hs / 4 consecutive h of column j ----
     if (ok && mbar_wait(smem_u32(&o_full), 0, status, DEV_TIMEOUT_ACCUM, 0x900)) {
       tc_fence_after();
+      APH(6);
       const int per = p.hs >> 2;  // 8, 16 or 32 values
       const uint32_t obase = tmem + (static_cast<uint32_t>(q * 32) << 16) + O_COL + cg * per;
       float* ocol = p.O + static_cast<long long>(batch) * p.strideO + static_cast<long long>(j) * p.ldo + cg * per;
@@ -372,12 +420,20 @@ attention_fwd_kernel(const __grid_constant__ AttParams p, int* __restrict__ stat
     }
   }
 
+  APH(7);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+#ifdef GB_PHASE_TIMES
+  if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == 300))
+    printf("attention phases (cycles): prologue %lld  A(split) %lld  wait S %lld  stats %lld  C %lld  "
+           "wait O %lld  epilogue %lld  total %lld\n",
+           ph_t[1] - ph_t[0], ph_t[2] - ph_t[1], ph_t[3] - ph_t[2], ph_t[4] - ph_t[3], ph_t[5] - ph_t[4],
+           ph_t[6] - ph_t[5], ph_t[7] - ph_t[6], clock64() - ph_t[0]);
+#endif
 }
 
 }  // namespace

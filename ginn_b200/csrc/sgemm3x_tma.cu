@@ -18,7 +18,6 @@
 // fourth, and the epilogue adds the four in fp32 with round-to-nearest.
 #include <cuda.h>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include "ptx.cuh"
 #include "math.cuh"
@@ -58,9 +57,6 @@ struct SParams {
   int accumulate;
   int split_k;  // CTAs per output tile along K (1 = none): partial sums are added atomically
   int batches;
-#ifdef GB_PHASE_TIMES
-  int dbg;  // instrumented build only: 1 = skip the stores, 2 = skip the tensor-memory loads
-#endif
 };
 
 // Inline: with the short tanh of math.cuh eight copies per pass are cheaper than eight calls
@@ -181,7 +177,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   __shared__ __align__(8) uint64_t plane_empty[PLANE_STAGES];
   __shared__ __align__(8) uint64_t acc_full;
   __shared__ uint32_t tmem_slot;
-#ifdef GB_PHASE_TIMES
+#ifdef GB_PHASE_TIMES  // instrumented build (-DGB_PHASE_TIMES): CTA 0 prints its phase durations
   __shared__ long long ph_t[12];
   if (threadIdx.x == 0) ph_t[0] = clock64();
 #define PH(i) do { ph_t[i] = clock64(); } while (0)
@@ -418,18 +414,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
 #pragma unroll 1
       for (int c = 0; c < 32 && c < ncols; c += 8, dst += 8 * ldc) {
         float acc[8];
-#ifdef GB_PHASE_TIMES
-        if (p.dbg & 2) {
-          for (int j = 0; j < 8; ++j) acc[j] = 1.f;
-        } else
-#endif
         load_acc8(tbase + c, nkb, acc);
-#ifdef GB_PHASE_TIMES
-        if (p.dbg & 1) {
-          if (acc[0] + acc[3] + acc[7] == 12345.f) dst[0] = acc[1];
-          continue;
-        }
-#endif
         if (row_ok) {
           if (ncols - c >= 8)
             store_acc8<true>(dst, ldc, 8, acc, bias, mode, act);
@@ -934,9 +919,6 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   sp.accumulate = p.accumulate;
   sp.split_k = p.split_k > 1 ? p.split_k : 1;
   sp.batches = p.batches;
-#ifdef GB_PHASE_TIMES
-  sp.dbg = getenv("GB_DBG") ? atoi(getenv("GB_DBG")) : 0;
-#endif
   if (sp.split_k > 1) {
     if (p.npairs != 1) return cudaErrorInvalidValue;
     sp.act = ACT_NONE;  // applied by a pass over the summed C after the kernel
