@@ -475,7 +475,9 @@ def time_steps(D: Dist, step, steps: int, warmup: int):
 def e2e_prod(D: Dist, P: ProdShard, steps: int):
     """The same pass through the C ABI with HOST buffers: every step copies this rank's operands
     in from pinned memory and its results out (C and dB shards, and this rank's slice of the
-    reduced dA), copies overlapped with the products on their own streams."""
+    reduced dA).  Three streams form a pipeline over two sets of device buffers: while step i
+    computes, step i+1's operands arrive and step i-1's results leave, so a step costs what the
+    slowest of the three takes (the host link, each way 0.4 GB per step on one GPU)."""
     import torch
     from ginn_b200.parallel import column_shard
     dev, n = D.dev, P.n
@@ -485,60 +487,57 @@ def e2e_prod(D: Dist, P: ProdShard, steps: int):
     hA, hB, hdC = pin(P.A), pin(P.B), pin(P.dC)
     hA.copy_(flat(P.A).cpu()); hB.copy_(flat(P.B).cpu()); hdC.copy_(flat(P.dC).cpu())
     s, c = column_shard(n, D.world, D.rank)
-    dA_slice = P.dA[:, s:s + c]
-    hC, hdB, hdA = pin(P.C), pin(P.dB), pin(dA_slice)
+    sets = [P, ProdShard(D, n, P.first_col, P.ncols, P.prod.panels, 0)]
+    sets[1].prod = P.prod  # same products, same reduction schedule
+    hC, hdB, hdA = pin(P.C), pin(P.dB), pin(P.dA[:, s:s + c])
     h2d, d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    computed = [None, None]   # event: the products that read / wrote buffer set b are done
+    drained = [None, None]    # event: the results of buffer set b have left the device
 
-    def step():
-        start = torch.cuda.Event()
-        start.record(main)                      # previous step's products and copies are queued
-        h2d.wait_event(start)
-        d2h_prev = torch.cuda.Event()
-        d2h_prev.record(d2h)
-        main.wait_event(d2h_prev)               # results of the previous step have left
-        ev_ab, ev_dc, ev_c = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+    def step(i):
+        b = i & 1
+        Q = sets[b]
+        if computed[b] is not None:
+            h2d.wait_event(computed[b])          # step i-2 no longer reads these operands
+        arrived = torch.cuda.Event()
         with torch.cuda.stream(h2d):
-            flat(P.A).copy_(hA, non_blocking=True)
-            flat(P.B).copy_(hB, non_blocking=True)
-            ev_ab.record(h2d)
-            flat(P.dC).copy_(hdC, non_blocking=True)
-            ev_dc.record(h2d)
-        main.wait_event(ev_ab)
-
-        def after(i):
-            if i == 0:      # dC must have arrived before the backward products; C may leave now
-                ev_c.record(main)
-                main.wait_event(ev_dc)
-                d2h.wait_event(ev_c)
-                with torch.cuda.stream(d2h):
-                    hC.copy_(flat(P.C), non_blocking=True)
-
-        P.step(between=after)
-        done = torch.cuda.Event()
-        done.record(main)
-        d2h.wait_event(done)
+            flat(Q.A).copy_(hA, non_blocking=True)
+            flat(Q.B).copy_(hB, non_blocking=True)
+            flat(Q.dC).copy_(hdC, non_blocking=True)
+            arrived.record(h2d)
+        main.wait_event(arrived)
+        if drained[b] is not None:
+            main.wait_event(drained[b])          # step i-2's results are out of these buffers
+        Q.prod.step(Q.A, Q.B, Q.dC, Q.C, Q.dA, Q.dB)
+        computed[b] = torch.cuda.Event()
+        computed[b].record(main)
+        d2h.wait_event(computed[b])
         with torch.cuda.stream(d2h):
-            hdA.copy_(flat(dA_slice), non_blocking=True)
-            hdB.copy_(flat(P.dB), non_blocking=True)
+            hC.copy_(flat(Q.C), non_blocking=True)
+            hdA.copy_(flat(Q.dA[:, s:s + c]), non_blocking=True)
+            hdB.copy_(flat(Q.dB), non_blocking=True)
+            drained[b] = torch.cuda.Event()
+            drained[b].record(d2h)
 
     def finish():
         main.wait_stream(d2h)
         main.wait_stream(h2d)
 
-    for _ in range(3):
-        step()
+    for i in range(4):
+        step(i)
     finish()
     D.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        step()
+    for i in range(steps):
+        step(i)
     finish()
     e1.record()
     D.barrier()
     ms = D.max_over_ranks(e0.elapsed_time(e1) / steps)
     h2d_b = 2 * (P.A.numel() + P.B.numel() + P.dC.numel())
-    d2h_b = 2 * (P.C.numel() + P.dB.numel() + dA_slice.numel())
+    d2h_b = 2 * (P.C.numel() + P.dB.numel() + P.dA[:, s:s + c].numel())
+    del sets
     return ms, h2d_b, d2h_b
 
 

@@ -108,6 +108,8 @@ def lib():
     L.ginn_b200_conv2d_forward.argtypes = [ci, vp, ci] + [i64] * 9 + [vp, vp, vp, vp]
     L.ginn_b200_conv2d_backward.argtypes = [ci, vp, ci] + [i64] * 9 + [vp, vp, vp, vp, vp, vp]
     L.ginn_b200_conv2d_forward.restype = L.ginn_b200_conv2d_backward.restype = ci
+    L.ginn_b200_fill.argtypes = [ci, vp, ci, i64, vp, cf]
+    L.ginn_b200_fill.restype = ci
     L.ginn_b200_last_error.restype = C.c_char_p
     L.ginn_b200_device_status.argtypes = [ci, ci]
     L.ginn_b200_set_option.argtypes = [C.c_char_p, ci]
@@ -496,6 +498,12 @@ def conv2d_backward(x, k, dy, dx=None, dk=None, row_stride=1, col_stride=1,
     _check(lib().ginn_b200_conv2d_backward(_dev(x), _stream(x), _dtype_of(x), *dims, row_stride,
                                            col_stride, x.data_ptr(), k.data_ptr(), dy.data_ptr(),
                                            _ptr(dx), _ptr(dk), _ptr(workspace)))
+
+
+def fill(x: torch.Tensor, value: float) -> None:
+    """x[...] = value for a contiguous tensor (ginn_b200_fill)."""
+    assert x.is_contiguous() or x.T.is_contiguous()
+    _check(lib().ginn_b200_fill(_dev(x), _stream(x), _dtype_of(x), x.numel(), x.data_ptr(), value))
 
 
 def adam_update(w: torch.Tensor, d: torch.Tensor, m: torch.Tensor, v: torch.Tensor, t: int,

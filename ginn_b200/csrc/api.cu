@@ -73,6 +73,16 @@ struct DevCtx {
     cudaEvent_t done;
   };
   std::vector<StageUser> stage_users[2];
+  // Prepared levels (ginn_b200_level_create) take their device images from slabs instead of one
+  // cudaMalloc each, and upload them asynchronously on a stream of the library's own: a graph
+  // with hundreds of levels is prepared in the time of a few allocations.
+  struct Slab {
+    unsigned char* base = nullptr;
+    size_t cap = 0, off = 0;
+    int refs = 0;
+  };
+  Slab* slab = nullptr;           // the slab new levels are carved from
+  cudaStream_t prep_stream = nullptr;
 };
 DevCtx g_ctx[kMaxDevices];
 
@@ -903,12 +913,85 @@ struct ginn_b200_level {
   int dtype;
   LevelLaunch ll;
   unsigned char* d_image;
+  DevCtx::Slab* slab = nullptr;     // where d_image lives
+  cudaEvent_t uploaded = nullptr;   // the image's upload on the preparation stream
+  bool upload_seen = false;
   std::vector<Problem> direct;  // table-free form of the level (then d_image is null)
   // cells level (ginn_b200_lstm_cells_level_create): d_image holds the pointer tables
   int cells = 0;                // 0: grouped products, 1: cell forward, 2: cell backward
   int hidden = 0;
   long long ncells = 0;
 };
+
+namespace {
+constexpr size_t kSlabBytes = 4u << 20;
+
+// Device memory for a level image plus its upload from `host` (pinned staging, asynchronous).
+// The level must wait for `uploaded` before its first launch.
+int level_upload(DevCtx* ctx, ginn_b200_level* lv, const void*, size_t bytes) {
+  bytes = (bytes + 255) & ~size_t(255);
+  {
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (!ctx->prep_stream) CU_TRY(cudaStreamCreateWithFlags(&ctx->prep_stream, cudaStreamNonBlocking));
+    if (!ctx->slab || ctx->slab->off + bytes > ctx->slab->cap) {
+      if (ctx->slab && ctx->slab->refs == 0) {  // nobody lives in the old slab any more
+        cudaFree(ctx->slab->base);
+        delete ctx->slab;
+      }
+      ctx->slab = new DevCtx::Slab();
+      ctx->slab->cap = bytes > kSlabBytes ? bytes : kSlabBytes;
+      cudaError_t e = cudaMalloc(&ctx->slab->base, ctx->slab->cap);
+      if (e != cudaSuccess) {
+        delete ctx->slab;
+        ctx->slab = nullptr;
+        return fail(GINN_B200_CUDA_ERROR, "preparing a level failed: %s", cudaGetErrorString(e));
+      }
+    }
+    lv->slab = ctx->slab;
+    lv->d_image = ctx->slab->base + ctx->slab->off;
+    ctx->slab->off += bytes;
+    ++ctx->slab->refs;
+  }
+  return GINN_B200_OK;
+}
+
+// Drops a level's claim on its slab; the slab goes when its last level does (unless it is the
+// one new levels are still carved from).
+void level_release(ginn_b200_level* lv) {
+  if (!lv->slab) return;
+  DevCtx& c = g_ctx[lv->device];
+  std::lock_guard<std::mutex> g(c.mu);
+  if (--lv->slab->refs == 0 && lv->slab != c.slab) {
+    cudaSetDevice(lv->device);
+    cudaFree(lv->slab->base);
+    delete lv->slab;
+  }
+  lv->slab = nullptr;
+}
+
+// Copies `bytes` of `image` (a host vector) into the level's device image: through the pinned
+// staging ring on the preparation stream, leaving an event behind.
+int level_copy(DevCtx* ctx, ginn_b200_level* lv, const unsigned char* image, size_t bytes) {
+  unsigned char *h, *d_ring;
+  int half = 0;
+  if (int s = stage_alloc(ctx, bytes, ctx->prep_stream, &h, &d_ring, &half)) return s;
+  std::memcpy(h, image, bytes);
+  CU_TRY(cudaMemcpyAsync(lv->d_image, h, bytes, cudaMemcpyHostToDevice, ctx->prep_stream));
+  CU_TRY(cudaEventCreateWithFlags(&lv->uploaded, cudaEventDisableTiming));
+  CU_TRY(cudaEventRecord(lv->uploaded, ctx->prep_stream));
+  return stage_mark(ctx, half, ctx->prep_stream);
+}
+
+// Before a level's first launch: its image must have arrived.  A host-side wait (the upload was
+// queued at preparation time and is normally long done), so it is also legal under capture.
+int level_ready(ginn_b200_level* lv) {
+  if (lv->uploaded && !lv->upload_seen) {
+    CU_TRY(cudaEventSynchronize(lv->uploaded));
+    lv->upload_seen = true;
+  }
+  return GINN_B200_OK;
+}
+}  // namespace
 
 int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
                            const ginn_b200_group* groups, ginn_b200_level** out) {
@@ -924,16 +1007,15 @@ int ginn_b200_level_create(int device, int dtype, int mode, int ngroups,
   if (!direct) lv->direct.clear();
   if (plan.live > 0 && !direct) {
     std::vector<unsigned char> h(plan.bytes);
-    cudaError_t e = cudaMalloc(&lv->d_image, plan.bytes);
-    if (e == cudaSuccess) {
+    int s = level_upload(ctx, lv, nullptr, plan.bytes);
+    if (s == GINN_B200_OK) {
       lv->ll = fill_level_image(dtype, mode, ngroups, groups, plan, ctx->num_sms, h.data(),
                                 lv->d_image);
-      e = cudaMemcpy(lv->d_image, h.data(), plan.bytes, cudaMemcpyHostToDevice);
+      s = level_copy(ctx, lv, h.data(), plan.bytes);
     }
-    if (e != cudaSuccess) {
-      cudaFree(lv->d_image);
-      delete lv;
-      return fail(GINN_B200_CUDA_ERROR, "preparing a level failed: %s", cudaGetErrorString(e));
+    if (s != GINN_B200_OK) {
+      ginn_b200_level_destroy(lv);
+      return s;
     }
   }
   *out = lv;
@@ -945,6 +1027,7 @@ int ginn_b200_level_run(ginn_b200_level* level, void* stream) {
   if (level->d_image == nullptr && level->direct.empty()) return GINN_B200_OK;
   DevCtx* ctx;
   if (int s = get_ctx(level->device, &ctx)) return s;
+  if (int s = level_ready(level)) return s;
   if (level->cells) {
     CU_TRY(gb::launch_lstm_cells(level->cells == 2,
                                  reinterpret_cast<const void* const*>(level->d_image),
@@ -1012,12 +1095,12 @@ int ginn_b200_lstm_cells_level_create(int device, int backward, int64_t hidden, 
   lv->ncells = n;
   if (hidden > 0 && n > 0) {
     const size_t bytes = static_cast<size_t>(ntab) * n * sizeof(void*);
-    cudaError_t e = cudaMalloc(&lv->d_image, bytes);
-    if (e == cudaSuccess) e = cudaMemcpy(lv->d_image, tables, bytes, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) {
-      cudaFree(lv->d_image);
-      delete lv;
-      return fail(GINN_B200_CUDA_ERROR, "preparing a cells level failed: %s", cudaGetErrorString(e));
+    int s = level_upload(ctx, lv, nullptr, bytes);
+    if (s == GINN_B200_OK)
+      s = level_copy(ctx, lv, reinterpret_cast<const unsigned char*>(tables), bytes);
+    if (s != GINN_B200_OK) {
+      ginn_b200_level_destroy(lv);
+      return s;
     }
   }
   *out = lv;
@@ -1026,10 +1109,12 @@ int ginn_b200_lstm_cells_level_create(int device, int backward, int64_t hidden, 
 
 int ginn_b200_level_destroy(ginn_b200_level* level) {
   if (level == nullptr) return GINN_B200_OK;
-  if (level->d_image) {
+  if (level->uploaded) {
     cudaSetDevice(level->device);
-    cudaFree(level->d_image);
+    cudaEventSynchronize(level->uploaded);  // the upload must not outlive the slab
+    cudaEventDestroy(level->uploaded);
   }
+  level_release(level);
   delete level;
   return GINN_B200_OK;
 }
@@ -1225,6 +1310,19 @@ int ginn_b200_conv2d_backward(int device, void* stream_, int dtype, int64_t C, i
   }
   conv_end(&call, stream);
   return status;
+}
+
+int ginn_b200_fill(int device, void* stream, int dtype, int64_t n, void* x, float value) {
+  if (dtype != GINN_B200_F32 && dtype != GINN_B200_F16)
+    return fail(GINN_B200_UNSUPPORTED, "dtype %d is not fp32 (0) or fp16 (1)", dtype);
+  if (n < 0) return fail(GINN_B200_BAD_ARGUMENT, "negative element count");
+  if (n == 0) return GINN_B200_OK;
+  if (!x) return fail(GINN_B200_BAD_ARGUMENT, "null pointer");
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  CU_TRY(gb::launch_fill(dtype, x, n, value, ctx->num_sms, static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1);
+  return GINN_B200_OK;
 }
 
 const char* ginn_b200_last_error(void) { return t_error.c_str(); }

@@ -480,8 +480,8 @@ cudaError_t launch_attention_fwd(const AttentionArgs& a, cudaStream_t stream, in
   const long long blocks = static_cast<long long>((a.T + ATM - 1) / ATM) * a.batches;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
   const int smem = APLANE_STAGES * APLANE_STAGE + ARAW_STAGES * ARAW_STAGE + 1024;
-  cudaError_t e = cudaFuncSetAttribute(attention_fwd_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static unsigned long long smem_set = 0;  // per template instantiation: per kernel
+  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(attention_fwd_kernel), smem, &smem_set);
   if (e != cudaSuccess) return e;
   return launch_kernel(attention_fwd_kernel, dim3(static_cast<unsigned>(blocks)), dim3(ATHREADS), smem,
                        stream, pdl_enabled(), p, status);

@@ -561,7 +561,8 @@ cudaError_t launch_hgather(const Problem& p, const Problem* dprobs, int nprobs, 
                            cudaStream_t stream, int* status) {
   auto kern = hgemm_gather_kernel<GROUPED, WITH_REGS>;
   const int smem = GSTAGES * GSTAGE + 1024;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static unsigned long long smem_set = 0;  // per template instantiation: per kernel
+  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(kern), smem, &smem_set);
   if (e != cudaSuccess) return e;
   kern<<<total_tiles, GTHREADS, smem, stream>>>(p, dprobs, nprobs, status);
   return cudaGetLastError();

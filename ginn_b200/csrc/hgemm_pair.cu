@@ -339,7 +339,8 @@ cudaError_t launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, co
                                 int num_sms, cudaStream_t stream, int* status) {
   auto kern = hgemm_pair_kernel<A_MN, B_MN>;
   const int smem = PSTAGES * PSTAGE_BYTES + PEPI_BYTES + 1024;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static unsigned long long smem_set = 0;  // per template instantiation: per kernel
+  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(kern), smem, &smem_set);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));

@@ -373,7 +373,8 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const H
                            cudaStream_t stream, int* status) {
   auto kern = hgemm_tma_kernel<A_MN, B_MN>;
   const int smem = TSTAGES * TSTAGE_BYTES + TEPI_BYTES + 1024;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static unsigned long long smem_set = 0;  // per template instantiation: per kernel
+  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(kern), smem, &smem_set);
   if (e != cudaSuccess) return e;
   kern<<<grid, 192, smem, stream>>>(ta, tb, p, status);
   return cudaGetLastError();

@@ -34,6 +34,11 @@ cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device instead of on every launch (the
+// attribute call costs about as much host time as the launch itself).  `done` is a bit mask per
+// call site: one bit per device ordinal below 64.
+cudaError_t set_smem_limit_once(const void* kern, int bytes, unsigned long long* done);
+
 // Allocation-free grouped launch (grouped_static.cu): descriptors live in a fixed array inside
 // the library image, and so does the status word its kernels report to.
 constexpr size_t kGroupedStaticBytes = 256 * 1024;
@@ -184,6 +189,7 @@ cudaError_t launch_lstm_cell_backward(const float* gates, long long ldg, const f
 // pointers each (step_ops.cu describes them).
 cudaError_t launch_lstm_cells(bool backward, const void* const* dtab, int H, long long n,
                               cudaStream_t stream);
+cudaError_t launch_fill(int dtype, void* x, long long n, float value, int num_sms, cudaStream_t stream);
 cudaError_t launch_adam(int dtype, void* w, void* d, float* m, float* v, long long n, float clip,
                         float b1, float b2, float step, float vscale, float eps, int num_sms,
                         cudaStream_t stream);

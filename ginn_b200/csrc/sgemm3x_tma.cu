@@ -844,7 +844,8 @@ cudaError_t launch_gather(const Problem& p, const Problem* dprobs, int nprobs, i
                           cudaStream_t stream, int* status) {
   auto kern = sgemm3x_gather_kernel<GROUPED, WITH_Y>;
   const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static unsigned long long smem_set = 0;  // per template instantiation: per kernel
+  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(kern), smem, &smem_set);
   if (e != cudaSuccess) return e;
   return launch_kernel(kern, dim3(total_tiles), dim3(GNTHREADS), smem, stream, pdl_enabled(), p,
                        dprobs, nprobs, status);
@@ -938,8 +939,8 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   if (total <= 0) return cudaSuccess;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
-  cudaError_t e = cudaFuncSetAttribute(sgemm3x_tma_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static unsigned long long smem_set = 0;  // per template instantiation: per kernel
+  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(sgemm3x_tma_kernel), smem, &smem_set);
   if (e != cudaSuccess) return e;
   e = launch_kernel(sgemm3x_tma_kernel, dim3(static_cast<unsigned>(total)), dim3(NTHREADS), smem,
                     stream, pdl_enabled(), sp, status);

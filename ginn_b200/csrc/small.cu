@@ -487,6 +487,18 @@ cudaError_t launch_wait_selftest(int* status, long long limit_cycles, int* retur
   return cudaGetLastError();
 }
 
+cudaError_t set_smem_limit_once(const void* kern, int bytes, unsigned long long* done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = dev >= 0 && dev < 64 ? 1ull << dev : 0ull;
+  // a plain read-modify-write: at worst two threads both set the attribute, which is harmless
+  if (bit != 0 && (__atomic_load_n(done, __ATOMIC_RELAXED) & bit)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && bit != 0) __atomic_fetch_or(done, bit, __ATOMIC_RELAXED);
+  return e;
+}
+
 cudaError_t launch_small(int dtype, const Problem& p, cudaStream_t stream) {
   const long long total = static_cast<long long>(p.M) * p.N * p.batches;
   if (total <= 0) return cudaSuccess;

@@ -325,6 +325,15 @@ lstm_cells_backward_kernel(const void* const* __restrict__ tab, int H, long long
   if (dcprev) dcprev[r] += dc * f;
 }
 
+// x[i] = value for n elements (what Tensor::fill / setConstant do on the device).
+template <typename T>
+__global__ void __launch_bounds__(256) fill_kernel(T* __restrict__ x, long long n, float value) {
+  const T v = from_f<T>(value);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    x[i] = v;
+}
+
 // S = scale * S in place over a strided batch of T x T score matrices (row = key position,
 // column = query position); with `causal`, keys after the query (row > column) become -inf, as
 // min-GPT's InPlaceMask does before the softmax (examples/min-gpt.cu.cpp:133-137).
@@ -593,6 +602,17 @@ cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c
   dim3 grid((H + 255) / 256, static_cast<unsigned>(n));
   return launch_kernel(lstm_cell_forward_kernel, grid, dim3(256), 0, stream, pdl_enabled(), gates,
                        ldg, c_prev, ldcp, c, ldc, h, ldh, xh_next, ldx, H, n, n_next);
+}
+
+cudaError_t launch_fill(int dtype, void* x, long long n, float value, int num_sms, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  long long blocks = (n + 255) / 256;
+  if (blocks > static_cast<long long>(num_sms) * 8) blocks = static_cast<long long>(num_sms) * 8;
+  if (dtype == 0)
+    fill_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<float*>(x), n, value);
+  else
+    fill_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<__half*>(x), n, value);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_scale_mask_f32(float* s, long long ld, long long stride, int T, int batches,

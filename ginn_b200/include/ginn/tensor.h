@@ -7,9 +7,14 @@
 #include <initializer_list>
 #include <vector>
 
+#include <ginn_b200.h>
+
 #include <ginn/dev.h>
 
 namespace ginn {
+
+inline float to_float(float x) { return x; }
+inline float to_float(Half x) { return __half2float(x); }
 
 template <typename ScalarType = Real>
 class Tensor {
@@ -131,7 +136,17 @@ class Tensor {
     cpu()->copy(*dev_, v.data(), data_, v.size() * sizeof(Scalar));
     return v;
   }
-  void fill(Scalar value) { set(std::vector<Scalar>(size(), value)); }
+  void fill(Scalar value) {
+    if (size() == 0) return;
+    if (dev_->kind() == GPU) {  // on the device's stream, no host copy and no wait
+      const int status = ginn_b200_fill(static_cast<int>(dev_->id().idx), stream_of(*dev_),
+                                        sizeof(Scalar) == 4 ? GINN_B200_F32 : GINN_B200_F16, size(),
+                                        data_, to_float(value));
+      if (status != GINN_B200_OK) GINN_CUDA_THROW(ginn_b200_last_error());
+    } else {
+      set(std::vector<Scalar>(size(), value));
+    }
+  }
   void set_zero() {
     if (size() == 0) return;
     if (dev_->kind() == GPU) {

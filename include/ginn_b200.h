@@ -326,6 +326,11 @@ int ginn_b200_conv2d_backward(int device, void* stream, int dtype, int64_t chann
                               int64_t kcols, int64_t row_stride, int64_t col_stride, const void* x,
                               const void* k, const void* dy, void* dx, void* dk, void* workspace);
 
+/* x[i] = value for n elements of type `dtype`, enqueued on `stream` (Tensor::fill on a GPU tensor,
+ * ginn/tensor.h fill / setConstant; also how Graph::backward seeds the sink's gradient without a
+ * host copy that would wait for the forward pass). */
+int ginn_b200_fill(int device, void* stream, int dtype, int64_t n, void* x, float value);
+
 /* Text of the last failure on the calling thread ("" if none). */
 const char* ginn_b200_last_error(void);
 

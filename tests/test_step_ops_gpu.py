@@ -202,3 +202,11 @@ def test_lstm_cells_over_per_cell_tensors(gpu):
     check(stack(dGs), 0.5 + rg, f32, "dgates +=")
     keep = [j for j in range(n) if j != 2]
     check(stack([dCPs[j] for j in keep]), 0.25 + rc[:, keep], f32, "dc_prev +=")
+
+
+@pytest.mark.parametrize("tdt", [torch.float32, torch.float16])
+def test_fill(gpu, tdt):
+    x = torch.zeros(100003, device="cuda", dtype=tdt)
+    gpu.fill(x, 0.375)
+    torch.cuda.synchronize()
+    assert bool((x == 0.375).all())
