@@ -717,7 +717,7 @@ def run_gpu(args):
                "bytes_are": "per rank" if world > 1 else "total"}
 
     secondary = {}
-    if world > 1:
+    if world > 1 and not args.no_secondary:
         del P
         torch.cuda.empty_cache()
         Pw = ProdShard(D, n, rank * n, n, args.panels, margin)     # weak: n columns per rank
@@ -947,10 +947,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the configs block (1 GPU)")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="N > 1: skip the weak-scaling and data-parallel MLP series")
     ap.add_argument("--no-single-thread", action="store_true",
                     help="reference arm: skip the single-thread sample")
     ap.add_argument("--config-steps", type=int, default=20, help="timed steps per configs entry")
-    ap.add_argument("--panels", type=int, default=4,
+    ap.add_argument("--panels", type=int, default=2,
                     help="column panels of dA, each all-reduced as soon as it is computed (N > 1)")
     ap.add_argument("--sm-margin", type=int, default=-1,
                     help="SMs left free for NCCL by the products that run beside a reduction "
@@ -965,12 +967,17 @@ def main():
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--force-path", type=int, default=0,
                     help="kernel choice override passed to the library (0 = automatic)")
+    ap.add_argument("--pair-group-m", type=int, default=0,
+                    help="rasterisation group of the CTA-pair kernel (0 = library default)")
     ap.add_argument("--pdl", type=int, default=1,
                     help="0: launch without programmatic dependent launch (A/B aid)")
     args = ap.parse_args()
     if args.force_path and args.impl != "reference":
         import ginn_b200
         ginn_b200.set_option("force_path", args.force_path)
+    if args.pair_group_m and args.impl != "reference":
+        import ginn_b200
+        ginn_b200.set_option("pair_group_m", args.pair_group_m)
     if not args.pdl and args.impl != "reference":
         import ginn_b200
         ginn_b200.set_option("pdl", 0)

@@ -70,6 +70,9 @@ def lib():
                                            i64]
     L.ginn_b200_affine_backward.argtypes = [ci, vp, ci, ci, C.POINTER(_PairGrad), i64, i64, vp,
                                             i64, vp, i64, ci, vp]
+    L.ginn_b200_affine_backward_scratch.argtypes = [ci, vp, ci, ci, C.POINTER(_PairGrad), i64, i64,
+                                                    vp, i64, vp, i64, ci, vp, vp]
+    L.ginn_b200_affine_backward_scratch.restype = ci
     L.ginn_b200_grouped.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
     L.ginn_b200_grouped_static.argtypes = [ci, vp, ci, ci, ci, C.POINTER(_Group)]
     L.ginn_b200_grouped_static.restype = ci
@@ -234,17 +237,19 @@ def affine_forward(pairs: Sequence[Pair], bias: Optional[torch.Tensor], act: int
 
 
 def affine_backward(pairs: Sequence[PairGrad], dout: torch.Tensor, out: Optional[torch.Tensor],
-                    act: int, dbias: Optional[torch.Tensor]) -> None:
-    """AffineNode::backward_ (ginn/node/affine.h:79-129): accumulates into da/db/dbias."""
+                    act: int, dbias: Optional[torch.Tensor],
+                    scratch: Optional[torch.Tensor] = None) -> None:
+    """AffineNode::backward_ (ginn/node/affine.h:79-129): accumulates into da/db/dbias.  `scratch`
+    (m x n, the node's d-pre-activation tensor) makes the Half path allocation-free."""
     arr = (_PairGrad * max(len(pairs), 1))()
     for i, p in enumerate(pairs):
         arr[i] = _PairGrad(p.a.data_ptr(), _ld(p.a), p.b.data_ptr(), _ld(p.b), p.a.shape[1],
                            _ptr(p.da), _ld(p.da) if p.da is not None else 0, _ptr(p.db),
                            _ld(p.db) if p.db is not None else 0)
     m, n = dout.shape
-    _check(lib().ginn_b200_affine_backward(
+    _check(lib().ginn_b200_affine_backward_scratch(
         _dev(dout), _stream(dout), _dtype_of(dout), len(pairs), arr, m, n, dout.data_ptr(),
-        _ld(dout), _ptr(out), _ld(out) if out is not None else 0, act, _ptr(dbias)))
+        _ld(dout), _ptr(out), _ld(out) if out is not None else 0, act, _ptr(dbias), _ptr(scratch)))
 
 
 @dataclass

@@ -733,6 +733,14 @@ int ginn_b200_affine_backward(int device, void* stream_, int dtype, int npairs,
                               const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,
                               const void* dout, int64_t lddout, const void* out, int64_t ldout,
                               int act, void* dbias) {
+  return ginn_b200_affine_backward_scratch(device, stream_, dtype, npairs, pairs, m, n, dout, lddout,
+                                           out, ldout, act, dbias, nullptr);
+}
+
+int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int npairs,
+                                      const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,
+                                      const void* dout, int64_t lddout, const void* out,
+                                      int64_t ldout, int act, void* dbias, void* caller_scratch) {
   if (int s = check_common(dtype, m, n, 0)) return s;
   if (npairs < 0 || (npairs > 0 && pairs == nullptr))
     return fail(GINN_B200_BAD_ARGUMENT, "bad pair list");
@@ -756,10 +764,19 @@ int ginn_b200_affine_backward(int device, void* stream_, int dtype, int npairs,
   // of the general kernel: 82 + 239 us against about 90 us for a 1024 x 1024 layer on 4096
   // columns.  The scratch is a stream-ordered allocation of the library's own.
   if (dtype == GINN_B200_F16 && t_force_path == PATH_AUTO && m * n >= 65536 && n <= 65535) {
-    void* scratch = nullptr;
+    void* scratch = nullptr;  // the library's own allocation, when the caller gave none
     const void* dA = dout;
     int64_t ldA = lddout;
-    if (act != GINN_B200_ACT_NONE) {
+    if (act != GINN_B200_ACT_NONE && caller_scratch != nullptr) {
+      if (!aligned16(caller_scratch))
+        return fail(GINN_B200_BAD_ARGUMENT, "the scratch tensor must be 16-byte aligned");
+      cudaError_t e = gb::launch_dact_half(dout, lddout, out, ldout, act, caller_scratch, (int)m, n, stream);
+      if (e != cudaSuccess)
+        return fail(GINN_B200_CUDA_ERROR, "derivative kernel: %s", cudaGetErrorString(e));
+      g_launches.fetch_add(1);
+      dA = caller_scratch;
+      ldA = m;
+    } else if (act != GINN_B200_ACT_NONE) {
       CU_TRY(cudaMallocAsync(&scratch, static_cast<size_t>(m) * n * 2, stream));
       cudaError_t e = gb::launch_dact_half(dout, lddout, out, ldout, act, scratch, (int)m, n, stream);
       if (e != cudaSuccess) {

@@ -15,6 +15,7 @@ template <typename Scalar = Real>
 class AffineNode : public BaseDataNode<Scalar> {
   std::vector<NodePtr<Scalar>> in_;
   std::unique_ptr<NonlinOp<Scalar>> nonlin_;
+  Tensor<Scalar> dpreactiv_;  // Half with a nonlinearity: dY (.) f'(Y), as in ginn/node/affine.h:82
 
   size_t npairs() const { return (in_.size() - 1) / 2; }
 
@@ -53,12 +54,19 @@ class AffineNode : public BaseDataNode<Scalar> {
               bn->has_grad() ? bn->grad().data() : nullptr, bp.rows()};
     }
     auto& bias = in_.back();
-    internal::b200_check(ginn_b200_affine_backward(
+    // Half Affines with a nonlinearity hand the library their own d-pre-activation tensor, as
+    // the reference's node owns one; fp32 forms the derivative inside the operand split.
+    void* scratch = nullptr;
+    if (std::is_same<Scalar, Half>::value && !nonlin_->is_identity()) {
+      dpreactiv_.resize(this->value().shape());
+      scratch = dpreactiv_.data();
+    }
+    internal::b200_check(ginn_b200_affine_backward_scratch(
         internal::b200_device(this->dev()), stream_of(*this->dev()),
         internal::b200_dtype<Scalar>(), static_cast<int>(npairs()), g, this->value().rows(),
         this->value().cols(), this->grad().data(), this->grad().rows(), this->value().data(),
         this->value().rows(), nonlin_->fused_act(),
-        bias->has_grad() ? bias->grad().data() : nullptr));
+        bias->has_grad() ? bias->grad().data() : nullptr, scratch));
   }
 
   static std::vector<BaseNodePtr> base(const std::vector<NodePtr<Scalar>>& v) {
@@ -67,7 +75,8 @@ class AffineNode : public BaseDataNode<Scalar> {
 
  public:
   AffineNode(std::unique_ptr<NonlinOp<Scalar>> nonlin, const std::vector<NodePtr<Scalar>>& ins)
-      : BaseDataNode<Scalar>(base(ins)), in_(ins), nonlin_(std::move(nonlin)) {
+      : BaseDataNode<Scalar>(base(ins)), in_(ins), nonlin_(std::move(nonlin)),
+        dpreactiv_(this->value().dev()) {
     GINN_ASSERT(ins.size() >= 3 && ins.size() % 2 == 1,
                 "Affine expects pairs of (A, B) inputs followed by a bias");
   }

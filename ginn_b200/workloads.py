@@ -54,6 +54,8 @@ class AffineLayer:
         self.Y = B.colmajor(m, n, tdt, device, fill=0.0)
         self.dW, self.dX = B.colmajor(m, k, tdt, device, fill=0.0), B.colmajor(k, n, tdt, device, fill=0.0)
         self.db = torch.zeros(m, device=device, dtype=tdt)
+        # the node's d-pre-activation tensor (ginn/node/affine.h:82): the Half path writes it
+        self.dpre = B.colmajor(m, n, tdt, device, fill=0.0) if half else None
         self.flops = 3 * 2 * m * n * k
         self.units = 1
 
@@ -63,7 +65,7 @@ class AffineLayer:
         self.db.zero_()
         B.affine_forward([B.Pair(self.W, self.X)], self.b, B.ACT_TANH, self.Y)
         B.affine_backward([B.PairGrad(self.W, self.X, self.dW, self.dX)], self.dY, self.Y,
-                          B.ACT_TANH, self.db)
+                          B.ACT_TANH, self.db, self.dpre)
 
 
 class Attention:

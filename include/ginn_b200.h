@@ -100,6 +100,16 @@ int ginn_b200_affine_backward(int device, void* stream, int dtype, int npairs,
                               const void* dout, int64_t lddout, const void* out, int64_t ldout,
                               int act, void* dbias);
 
+/* The same with the scratch tensor supplied by the caller: `scratch` holds m * n elements of
+ * `dtype` (16-byte aligned, leading dimension m) and is what AffineNode keeps as dpreactiv_
+ * (ginn/node/affine.h:82-88), so a node that passes its own tensor makes the call allocation-free
+ * and keeps its device's accounting (PreallocGpuDevice::used()) exactly as the reference has it.
+ * Only large Half Affines with a nonlinearity write it; NULL = as ginn_b200_affine_backward. */
+int ginn_b200_affine_backward_scratch(int device, void* stream, int dtype, int npairs,
+                                      const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,
+                                      const void* dout, int64_t lddout, const void* out,
+                                      int64_t ldout, int act, void* dbias, void* scratch);
+
 /* One group of an autobatch level: `ncols` products that share the left operand W (m x k).
  * Column j of the right-hand side lives at x_cols[j] (k contiguous elements), column j of
  * the result at y_cols[j] (m contiguous elements) -- the addresses of the individual nodes'

@@ -151,6 +151,37 @@ def test_forward_with_split_contraction(gpu, act):
             check(B.to_host(Y), ref, np.float32, f"{m}x{n}x{k} act {act}")
 
 
+def test_half_backward_with_the_nodes_own_scratch(gpu):
+    """A large Half Affine with a nonlinearity materialises dY (.) f'(Y) once.  Given the node's
+    own d-pre-activation tensor (as AffineNode owns dpreactiv_, ginn/node/affine.h:82) the call
+    allocates nothing: same gradients as with the library's stream-ordered scratch, and the
+    device's free memory does not move."""
+    rng = np.random.default_rng(55)
+    m, n, k = 512, 256, 384
+    dt = np.float16
+    W, X, b, dY = randn(rng, (m, k), dt, 0.05), randn(rng, (k, n), dt), randn(rng, m, dt), randn(rng, (m, n), dt)
+    Wd, Xd, bd, dYd = map(B.from_host, (W, X, b, dY))
+    Y = B.colmajor(m, n, torch.float16, fill=0.0)
+    gpu.affine_forward([gpu.Pair(Wd, Xd)], bd, gpu.ACT_TANH, Y)
+    scratch = B.colmajor(m, n, torch.float16, fill=0.0)
+    results = []
+    for ws in (None, scratch, scratch):
+        dW, dX = zeros_like_cm(Wd), zeros_like_cm(Xd)
+        db = torch.zeros(m, device="cuda", dtype=torch.float16)
+        torch.cuda.synchronize()
+        free0 = torch.cuda.mem_get_info()[0]
+        gpu.affine_backward([gpu.PairGrad(Wd, Xd, dW, dX)], dYd, Y, gpu.ACT_TANH, db, ws)
+        torch.cuda.synchronize()
+        if ws is not None and len(results) == 2:      # second call with the scratch: all warm
+            assert torch.cuda.mem_get_info()[0] == free0
+        results.append([B.to_host(t) for t in (dW, dX, db)])
+    g = orc.affine_backward([(W, X)], dY, B.to_host(Y), orc.ACT_TANH, dt)
+    for got in results:
+        check(got[0], g["da"][0], dt, "dW")
+        check(got[1], g["db"][0], dt, "dX")
+        check(got[2], g["dbias"], dt, "db")
+
+
 def test_bias_gradient_alone(gpu):
     """Only the bias has a gradient (no weight gradient to ride on)."""
     rng = np.random.default_rng(31)
