@@ -57,6 +57,10 @@ struct SParams {
   int accumulate;
   int split_k;  // CTAs per output tile along K (1 = none): partial sums are added atomically
   int batches;
+  int bn;       // columns of C per tile: 128, or 64 for narrow results (half the B-side work)
+  // Element (row, col) of the tile's result lives at C + row * c_rs + col * c_cs: (1, ldc) for
+  // C itself, (ldc, 1) when the launcher computes the transposed product (see launch_sgemm3x).
+  long long c_rs, c_cs;
 };
 
 // Inline: with the short tanh of math.cuh eight copies per pass are cheaper than eight calls
@@ -82,16 +86,35 @@ __device__ __forceinline__ void load_acc8(uint32_t taddr, int nkb, float (&acc)[
   }
 }
 
-// Eight results of one row into C: `dst` addresses the first, consecutive columns are `ldc`
+// Eight results of one row into C: `dst` addresses the first, consecutive columns are `cs`
 // elements apart, the first `nvalid` exist.  mode 0: store, 1: add to the previous C, 2: atomic
 // add (partial sum of a split contraction).  The bounds test is compiled out for full groups.
 template <bool FULL>
-__device__ __forceinline__ void store_acc8(float* dst, long long ldc, int nvalid, float (&acc)[8],
+__device__ __forceinline__ void store_acc8(float* dst, long long cs, int nvalid, float (&acc)[8],
                                            float bias, int mode, int act) {
+  if (FULL && cs == 1 && mode != 2 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+    // transposed result: this thread's eight columns are contiguous in memory
+    float4* d4 = reinterpret_cast<float4*>(dst);
+    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+    if (mode == 1) {
+      lo = d4[0];
+      hi = d4[1];
+    }
+    float v[8] = {acc[0] + lo.x, acc[1] + lo.y, acc[2] + lo.z, acc[3] + lo.w,
+                  acc[4] + hi.x, acc[5] + hi.y, acc[6] + hi.z, acc[7] + hi.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] += bias;
+      if (act != ACT_NONE) v[j] = act_forward_f32(act, v[j]);
+    }
+    d4[0] = make_float4(v[0], v[1], v[2], v[3]);
+    d4[1] = make_float4(v[4], v[5], v[6], v[7]);
+    return;
+  }
   if (mode == 1) {
     float old[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) old[j] = (FULL || j < nvalid) ? dst[j * ldc] : 0.f;
+    for (int j = 0; j < 8; ++j) old[j] = (FULL || j < nvalid) ? dst[j * cs] : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] += old[j];
   }
@@ -101,9 +124,9 @@ __device__ __forceinline__ void store_acc8(float* dst, long long ldc, int nvalid
     if (mode != 2 && act != ACT_NONE) v = act_forward_f32(act, v);
     if (FULL || j < nvalid) {
       if (mode == 2)
-        atomicAdd(dst + j * ldc, v);
+        atomicAdd(dst + j * cs, v);
       else
-        dst[j * ldc] = v;
+        dst[j * cs] = v;
     }
   }
 }
@@ -113,9 +136,11 @@ __device__ __forceinline__ void store_acc8(float* dst, long long ldc, int nvalid
 // 256 threads, 4 pieces of 16 bytes each.
 template <bool HAS_Y>
 __device__ __forceinline__ void transform_kc(const uint8_t* src, const uint8_t* ysrc,
-                                             uint8_t* dst_hi, uint8_t* dst_lo, int t, int dact) {
+                                             uint8_t* dst_hi, uint8_t* dst_lo, int t, int dact,
+                                             int rows = 128) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
+    if (32 * i >= rows) break;  // a 64-row slice is the first half of the tile
     const int off = (t + 256 * i) * 16;
     float4 x = *reinterpret_cast<const float4*>(src + off);
     if (HAS_Y) {
@@ -141,8 +166,10 @@ __device__ __forceinline__ void transform_kc(const uint8_t* src, const uint8_t* 
 // swizzled K-major chunks.  Returns the sum of the values it handled (bias gradient).
 template <bool HAS_Y>
 __device__ __forceinline__ float transform_oc(const uint8_t* src, const uint8_t* ysrc,
-                                              uint8_t* dst_hi, uint8_t* dst_lo, int t, int dact) {
+                                              uint8_t* dst_hi, uint8_t* dst_lo, int t, int dact,
+                                              int rows = 128) {
   const int o = t & 127;
+  if (o >= rows) return 0.f;  // a 64-row slice: the other rows of the tile do not exist
   const int kbase = (t >> 7) * 16;
   const float* col = reinterpret_cast<const float*>(src + (o >> 5) * 4096) + (o & 31);
   const float* ycol = reinterpret_cast<const float*>(ysrc + (o >> 5) * 4096) + (o & 31);
@@ -201,7 +228,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   tile /= p.tiles_n;
   const int batch = tile % p.batches;
   const int split = tile / p.batches;
-  const int m0 = m_tile * SBM, n0 = n_tile * SBN;
+  const int m0 = m_tile * SBM, n0 = n_tile * p.bn;
 
   int nkb_total = 0;
   for (int i = 0; i < p.npairs; ++i) nkb_total += (p.k[i] + SBK - 1) / SBK;
@@ -255,9 +282,12 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
         if (!mbar_wait(smem_u32(&raw_empty[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) break;
         const uint32_t bar = smem_u32(&raw_full[s]);
         const uint32_t dst = raws_base + s * raw_stage_bytes;
-        mbar_arrive_expect_tx(bar, raw_stage_bytes);
-        // k-contiguous operand: one 32(k) x 128(outer) box, 128-byte swizzle.
-        // outer-contiguous operand: four 32(outer) x 32(k) boxes, unswizzled.
+        // bytes of this stage: A (and a derivative partner of A) always 128 rows, B (and its
+        // partner) p.bn rows of 128 bytes
+        const int b_bytes = p.bn * 128;
+        mbar_arrive_expect_tx(bar, RAW_TILE + b_bytes + (p.dop == 1 ? RAW_TILE : p.dop == 2 ? b_bytes : 0));
+        // k-contiguous operand: one 32(k) x 128(outer) box, 128-byte swizzle (32 x bn for B).
+        // outer-contiguous operand: boxes of 32(outer) x 32(k), unswizzled.
         if (p.a_kc[pair]) {
           tma_load_3d(dst, &p.tmA[pair], bar, k0, m0, batch);
         } else {
@@ -270,17 +300,20 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
         } else {
 #pragma unroll
           for (int a = 0; a < 4; ++a)
-            tma_load_3d(dst + RAW_TILE + a * 4096, &p.tmB[pair], bar, n0 + 32 * a, k0, batch);
+            if (32 * a < p.bn)
+              tma_load_3d(dst + RAW_TILE + a * 4096, &p.tmB[pair], bar, n0 + 32 * a, k0, batch);
         }
         if (p.dop) {
           const int kc = p.dop == 1 ? p.a_kc[0] : p.b_kc[0];
           const int o0 = p.dop == 1 ? m0 : n0;
+          const int orows = p.dop == 1 ? SBM : p.bn;
           if (kc) {
             tma_load_3d(dst + 2 * RAW_TILE, &p.tmY, bar, k0, o0, batch);
           } else {
 #pragma unroll
             for (int a = 0; a < 4; ++a)
-              tma_load_3d(dst + 2 * RAW_TILE + a * 4096, &p.tmY, bar, o0 + 32 * a, k0, batch);
+              if (32 * a < orows)
+                tma_load_3d(dst + 2 * RAW_TILE + a * 4096, &p.tmY, bar, o0 + 32 * a, k0, batch);
           }
         }
         if (++s == raw_stages) {
@@ -298,7 +331,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (elect_one()) {
-      constexpr uint32_t IDESC = make_idesc(2, 0, 0, SBM, SBN);
+      const uint32_t IDESC = make_idesc(2, 0, 0, SBM, static_cast<uint32_t>(p.bn));
       int s = 0;
       uint32_t ph = 0;
       for (int it = 0; it < nkb; ++it) {
@@ -357,16 +390,19 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       uint8_t* dst_lo = dst_hi + PLANE;
       const int kc = grp ? p.b_kc[pair] : p.a_kc[pair];
       const bool has_y = p.dop == grp + 1;
+      const int rows = grp ? p.bn : SBM;
       if (kc) {
         if (has_y)
-          transform_kc<true>(src, ysrc, dst_hi, dst_lo, t, p.dact);
+          transform_kc<true>(src, ysrc, dst_hi, dst_lo, t, p.dact, rows);
         else
-          transform_kc<false>(src, ysrc, dst_hi, dst_lo, t, p.dact);
+          transform_kc<false>(src, ysrc, dst_hi, dst_lo, t, p.dact, rows);
       } else {
-        const float part = has_y ? transform_oc<true>(src, ysrc, dst_hi, dst_lo, t, p.dact)
-                                 : transform_oc<false>(src, ysrc, dst_hi, dst_lo, t, p.dact);
+        const float part = has_y ? transform_oc<true>(src, ysrc, dst_hi, dst_lo, t, p.dact, rows)
+                                 : transform_oc<false>(src, ysrc, dst_hi, dst_lo, t, p.dact, rows);
         if (want_rowsum && pair == 0) rs += part;
       }
+      // (One elected arrival per warp after a warp barrier was measured: 7 % slower than every
+      // thread arriving for itself.)
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&plane_full[ps_i]));
       mbar_arrive(smem_u32(&raw_empty[rs_i]));
@@ -396,16 +432,17 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     const float bias = (p.bias != nullptr && row_ok && split == 0) ? p.bias[row] : 0.f;  // once per tile
     const bool epi_ok = ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0);
     if (threadIdx.x == 64) PH(6);
-    float* crow = p.C + static_cast<long long>(batch) * p.strideC + row;
+    float* crow = p.C + static_cast<long long>(batch) * p.strideC + row * p.c_rs;
     const int c0 = cgrp * 32;
     const bool split_k = p.split_k > 1;
     if (epi_ok) {
       tc_fence_after();
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16) + c0;
-      const long long ldc = p.ldc;
+      const long long ldc = p.c_cs;  // distance between consecutive columns of the result
       const int mode = split_k ? 2 : (p.accumulate ? 1 : 0);
       const int act = p.act;  // none when the contraction is split: a pass over C follows
-      const int ncols = p.N - (n0 + c0);  // columns of this warp's group that exist (may be <= 0)
+      // columns of this warp's group that exist (may be <= 0): inside the matrix and the tile
+      const int ncols = (p.N - n0 < p.bn ? p.N - n0 : p.bn) - c0;
       float* dst = crow + static_cast<long long>(n0 + c0) * ldc;
       // eight columns per pass, not unrolled (code size: a CTA runs this once, from a cold
       // instruction cache); the per-element work is a pointer increment, an add and a store.
@@ -861,12 +898,13 @@ bool operand_tma_ok(const Operand& o, int batches) {
 }
 
 // Stored extents of operand X(outer O, inner K): k-contiguous -> K rows x O columns.
+// `tile_outer` is the tile's extent along O: 128, or 64 for the B side of a narrow tile.
 bool encode_operand(CUtensorMap* out, const void* ptr, const Operand& o, long long O, long long K,
-                    int batches) {
+                    int batches, int tile_outer = SBM) {
   const unsigned long long rows = o.k_contig ? K : O, cols = o.k_contig ? O : K;
   const unsigned long long bs = batches > 1 ? o.batch_stride : o.ld * cols;
   return encode_tmap(out, 4, ptr, rows, cols, batches, o.ld, bs ? bs : 4, 32,
-                     o.k_contig ? SBM : SBK, o.k_contig != 0);
+                     o.k_contig ? tile_outer : SBK, o.k_contig != 0);
 }
 
 }  // namespace
@@ -884,7 +922,25 @@ bool sgemm3x_supported(const Problem& p) {
   return true;
 }
 
-cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
+// Tile shape.  The tile is 128 rows of C by `bn` columns, bn = 64 when C has at most 64 columns
+// (half of a 128-column tile would be computed and thrown away).  A plain product (no bias, row
+// sums, activation or derivative operand) with at most 64 rows and more columns than that is run
+// as its transpose, C^T = B^T A^T, the operands exchanged and the tile written through strides
+// (ldc, 1): the short extent then lies along the 64-wide side.
+cudaError_t launch_sgemm3x(const Problem& p_in, cudaStream_t stream, int* status) {
+  Problem p = p_in;
+  bool transposed = false;
+  if (p.M <= 64 && p.N > 64 && p.bias == nullptr && p.rowsum == nullptr && p.act == ACT_NONE) {
+    bool plain = true;
+    for (int i = 0; i < p.npairs; ++i)
+      plain = plain && p.a[i].dact == ACT_NONE && p.b[i].dact == ACT_NONE;
+    if (plain) {
+      for (int i = 0; i < p.npairs; ++i) std::swap(p.a[i], p.b[i]);
+      std::swap(p.M, p.N);
+      transposed = true;
+    }
+  }
+  const int bn = p.N <= 64 ? 64 : SBN;
   SParams sp;
   std::memset(&sp, 0, sizeof(sp));
   sp.npairs = p.npairs;
@@ -893,7 +949,7 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
     sp.a_kc[i] = p.a[i].k_contig;
     sp.b_kc[i] = p.b[i].k_contig;
     if (!encode_operand(&sp.tmA[i], p.a[i].base, p.a[i], p.M, p.k[i], p.batches) ||
-        !encode_operand(&sp.tmB[i], p.b[i].base, p.b[i], p.N, p.k[i], p.batches))
+        !encode_operand(&sp.tmB[i], p.b[i].base, p.b[i], p.N, p.k[i], p.batches, bn))
       return cudaErrorInvalidValue;
   }
   if (p.a[0].dact != ACT_NONE) {
@@ -904,13 +960,16 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   } else if (p.b[0].dact != ACT_NONE) {
     sp.dop = 2;
     sp.dact = p.b[0].dact;
-    if (!encode_operand(&sp.tmY, p.b[0].ybase, p.b[0], p.N, p.k[0], p.batches))
+    if (!encode_operand(&sp.tmY, p.b[0].ybase, p.b[0], p.N, p.k[0], p.batches, bn))
       return cudaErrorInvalidValue;
   }
   sp.M = p.M;
   sp.N = p.N;
+  sp.bn = bn;
+  sp.c_rs = transposed ? p.ldc : 1;
+  sp.c_cs = transposed ? 1 : p.ldc;
   sp.tiles_m = (p.M + SBM - 1) / SBM;
-  sp.tiles_n = (p.N + SBN - 1) / SBN;
+  sp.tiles_n = (p.N + bn - 1) / bn;
   sp.C = static_cast<float*>(p.c);
   sp.ldc = p.ldc;
   sp.strideC = p.c_batch_stride;
@@ -925,13 +984,14 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
     sp.act = ACT_NONE;  // applied by a pass over the summed C after the kernel
     if (!p.accumulate) {  // partial sums are added onto zeros
       cudaError_t ze = cudaSuccess;
-      if (p.batches == 1 || p.c_batch_stride == p.ldc * p.N)
-        ze = cudaMemset2DAsync(p.c, p.ldc * 4, 0, static_cast<size_t>(p.M) * 4,
-                               static_cast<size_t>(p.N) * p.batches, stream);
+      // C as the caller stores it: p_in.M rows by p_in.N columns, whatever the tile orientation
+      if (p.batches == 1 || p.c_batch_stride == p.ldc * p_in.N)
+        ze = cudaMemset2DAsync(p.c, p.ldc * 4, 0, static_cast<size_t>(p_in.M) * 4,
+                               static_cast<size_t>(p_in.N) * p.batches, stream);
       else
         for (int b = 0; b < p.batches && ze == cudaSuccess; ++b)
           ze = cudaMemset2DAsync(static_cast<float*>(p.c) + b * p.c_batch_stride, p.ldc * 4, 0,
-                                 static_cast<size_t>(p.M) * 4, p.N, stream);
+                                 static_cast<size_t>(p_in.M) * 4, p_in.N, stream);
       if (ze != cudaSuccess) return ze;
     }
   }
@@ -945,6 +1005,7 @@ cudaError_t launch_sgemm3x(const Problem& p, cudaStream_t stream, int* status) {
   e = launch_kernel(sgemm3x_tma_kernel, dim3(static_cast<unsigned>(total)), dim3(NTHREADS), smem,
                     stream, pdl_enabled(), sp, status);
   if (e != cudaSuccess || sp.split_k == 1 || p.act == ACT_NONE) return e;
+  // an activated product is never run transposed, so (p.M, p.N) are the caller's here
   return launch_act_inplace_f32(sp.C, sp.ldc, sp.strideC, p.act, p.M, p.N, p.batches, stream);
 }
 

@@ -233,6 +233,35 @@ def test_assigning_products_with_split_contraction(gpu):
     assert (B.to_host(buf)[128:] == 3.0).all()
 
 
+def test_narrow_fp32_products(gpu):
+    """Products with at most 64 rows or at most 64 columns (the attention backward's dV, dQ, dK'
+    with a head of 64): the TMA kernel runs them on 128 x 64 tiles, the short-and-wide ones as the
+    transposed product written through strides.  Every layout, assigning and adding, ragged
+    extents, a padded C whose padding must survive, a long K (split) and a strided batch."""
+    rng = np.random.default_rng(31)
+    for (m, n, k) in [(64, 256, 128), (64, 128, 64), (48, 200, 96), (33, 1000, 260), (8, 136, 32),
+                      (256, 64, 128), (200, 40, 96), (1000, 24, 260), (64, 640, 4096)]:
+        for ta, tb in TRANS:
+            run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, False)
+            run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, True)
+    for (m, n, k) in [(64, 256, 128), (40, 300, 72)]:
+        a, b = randn(rng, (m, k), np.float32), randn(rng, (k, n), np.float32)
+        buf = B.colmajor(m + 4, n, torch.float32, fill=3.0)
+        Cv = buf[:m]
+        gpu.gemm(B.from_host(a), B.from_host(b), Cv)
+        torch.cuda.synchronize()
+        check(B.to_host(Cv), orc.gemm(a, b), np.float32, "padded narrow")
+        assert (B.to_host(buf)[m:] == 3.0).all()
+    for acc in (False, True):
+        a, b = randn(rng, (64, 128, 6), np.float32), randn(rng, (128, 256, 6), np.float32)
+        c0 = randn(rng, (64, 256, 6), np.float32)
+        C = B.from_host(c0)
+        gpu.gemm_batched(B.from_host(a), B.from_host(b), C, accumulate=acc)
+        torch.cuda.synchronize()
+        ref = orc.gemm_batched(a, b, c=c0, accumulate=acc)
+        check(B.to_host(C), ref, np.float32, f"batched narrow acc{acc}")
+
+
 def test_empty_and_degenerate_shapes(gpu):
     rng = np.random.default_rng(19)
     c0 = randn(rng, (4, 5), np.float32)
