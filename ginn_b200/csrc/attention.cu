@@ -58,18 +58,31 @@ struct AttParams {
 };
 
 // k-contiguous raw slice (TMA box 32 k x 128 rows, 128-byte swizzle) -> hi / lo planes.
+// One guard for the thread's sixteen values (see math.cuh).
 __device__ __forceinline__ void split_kc(const uint8_t* src, uint8_t* dst_hi, uint8_t* dst_lo, int t) {
+  float4 x[4];
+  float m = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int off = (t + 256 * i) * 16;
-    const float4 x = *reinterpret_cast<const float4*>(src + off);
-    float4 h, l;
-    split_tf32(x.x, h.x, l.x);
-    split_tf32(x.y, h.y, l.y);
-    split_tf32(x.z, h.z, l.z);
-    split_tf32(x.w, h.w, l.w);
-    *reinterpret_cast<float4*>(dst_hi + off) = h;
-    *reinterpret_cast<float4*>(dst_lo + off) = l;
+    x[i] = *reinterpret_cast<const float4*>(src + (t + 256 * i) * 16);
+    m = fmaxf(m, absmax4(x[i]));
+  }
+  if (guard_ok(m)) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 h, l;
+      split4<false>(x[i], h, l);
+      *reinterpret_cast<float4*>(dst_hi + (t + 256 * i) * 16) = h;
+      *reinterpret_cast<float4*>(dst_lo + (t + 256 * i) * 16) = l;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 h, l;
+      split4<true>(x[i], h, l);
+      *reinterpret_cast<float4*>(dst_hi + (t + 256 * i) * 16) = h;
+      *reinterpret_cast<float4*>(dst_lo + (t + 256 * i) * 16) = l;
+    }
   }
 }
 
@@ -84,14 +97,16 @@ __device__ __forceinline__ void split_oc(const uint8_t* src, uint8_t* dst_hi, ui
   const int kbase = (t / outer) * kper;
   const float* col = reinterpret_cast<const float*>(src + (o >> 5) * 4096) + (o & 31);
   for (int c = 0; c < kper; c += 4) {
-    float x[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) x[e] = col[(kbase + c + e) * 32];
+    float4 x;
+    x.x = col[(kbase + c) * 32];
+    x.y = col[(kbase + c + 1) * 32];
+    x.z = col[(kbase + c + 2) * 32];
+    x.w = col[(kbase + c + 3) * 32];
     float4 h, l;
-    split_tf32(x[0], h.x, l.x);
-    split_tf32(x[1], h.y, l.y);
-    split_tf32(x[2], h.z, l.z);
-    split_tf32(x[3], h.w, l.w);
+    if (guard_ok(absmax4(x)))
+      split4<false>(x, h, l);
+    else
+      split4<true>(x, h, l);
     const uint32_t off = sw128_offset(o, (kbase + c) >> 2);
     *reinterpret_cast<float4*>(dst_hi + off) = h;
     *reinterpret_cast<float4*>(dst_lo + off) = l;

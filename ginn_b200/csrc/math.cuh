@@ -102,4 +102,35 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   lo = ok ? x - r : 0.f;
 }
 
+// The guard hoisted out of the per-value work: `guard_ok(m)` for m = the largest magnitude of a
+// group of values (see absmax4) says whether all of them may take split_fast, which is
+// split_tf32 without its compare and selects.  The max instruction drops NaNs, so a NaN among
+// finite values takes the fast route: there it lands in the lo plane at the latest (NaN - r) and
+// still poisons every result it should; a group of NaNs only fails the test and is guarded.
+// Callers test once per thread and k-block and keep two straight-line copies of their loop, so
+// that the loads of all pieces stay ahead of the arithmetic (a test per 16-byte piece put a
+// branch between the pieces and was slower than the per-value guard).
+__device__ __forceinline__ float absmax4(const float4& x) {
+  return fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+}
+__device__ __forceinline__ bool guard_ok(float m) { return m < __uint_as_float(0x7f7ff000u); }
+template <bool GUARDED>
+__device__ __forceinline__ void split4(const float4& x, float4& hi, float4& lo) {
+  if (GUARDED) {
+    split_tf32(x.x, hi.x, lo.x);
+    split_tf32(x.y, hi.y, lo.y);
+    split_tf32(x.z, hi.z, lo.z);
+    split_tf32(x.w, hi.w, lo.w);
+  } else {
+    hi.x = __uint_as_float((__float_as_uint(x.x) + 0x1000u) & 0xffffe000u);
+    hi.y = __uint_as_float((__float_as_uint(x.y) + 0x1000u) & 0xffffe000u);
+    hi.z = __uint_as_float((__float_as_uint(x.z) + 0x1000u) & 0xffffe000u);
+    hi.w = __uint_as_float((__float_as_uint(x.w) + 0x1000u) & 0xffffe000u);
+    lo.x = x.x - hi.x;
+    lo.y = x.y - hi.y;
+    lo.z = x.z - hi.z;
+    lo.w = x.w - hi.w;
+  }
+}
+
 }  // namespace gb

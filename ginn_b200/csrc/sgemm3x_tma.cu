@@ -133,30 +133,49 @@ __device__ __forceinline__ void store_acc8(float* dst, long long cs, int nvalid,
 
 // Transform of a k-contiguous raw slice: it already is K-major and swizzled (TMA box 32 k x 128
 // outer with the 128-byte swizzle), so hi and lo go to the same offsets of their planes.
-// 256 threads, 4 pieces of 16 bytes each.
+// 256 threads, 4 pieces of 16 bytes each (2 when the slice has 64 rows: its first half).  The
+// guard of the split is tested once for the thread's sixteen values (math.cuh).
 template <bool HAS_Y>
 __device__ __forceinline__ void transform_kc(const uint8_t* src, const uint8_t* ysrc,
                                              uint8_t* dst_hi, uint8_t* dst_lo, int t, int dact,
                                              int rows = 128) {
+  const int np = rows > 64 ? 4 : 2;
+  float4 x[4];
+  float m = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    if (32 * i >= rows) break;  // a 64-row slice is the first half of the tile
+    if (i >= np) break;
     const int off = (t + 256 * i) * 16;
-    float4 x = *reinterpret_cast<const float4*>(src + off);
+    x[i] = *reinterpret_cast<const float4*>(src + off);
     if (HAS_Y) {
       const float4 y = *reinterpret_cast<const float4*>(ysrc + off);
-      x.x = act_backward<float>(dact, y.x, x.x);
-      x.y = act_backward<float>(dact, y.y, x.y);
-      x.z = act_backward<float>(dact, y.z, x.z);
-      x.w = act_backward<float>(dact, y.w, x.w);
+      x[i].x = act_backward<float>(dact, y.x, x[i].x);
+      x[i].y = act_backward<float>(dact, y.y, x[i].y);
+      x[i].z = act_backward<float>(dact, y.z, x[i].z);
+      x[i].w = act_backward<float>(dact, y.w, x[i].w);
     }
-    float4 h, l;
-    split_tf32(x.x, h.x, l.x);
-    split_tf32(x.y, h.y, l.y);
-    split_tf32(x.z, h.z, l.z);
-    split_tf32(x.w, h.w, l.w);
-    *reinterpret_cast<float4*>(dst_hi + off) = h;
-    *reinterpret_cast<float4*>(dst_lo + off) = l;
+    m = fmaxf(m, absmax4(x[i]));
+  }
+  if (guard_ok(m)) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i >= np) break;
+      const int off = (t + 256 * i) * 16;
+      float4 h, l;
+      split4<false>(x[i], h, l);
+      *reinterpret_cast<float4*>(dst_hi + off) = h;
+      *reinterpret_cast<float4*>(dst_lo + off) = l;
+    }
+  } else {
+#pragma unroll  // (a rolled loop would index x dynamically and push it to local memory)
+    for (int i = 0; i < 4; ++i) {
+      if (i >= np) break;
+      const int off = (t + 256 * i) * 16;
+      float4 h, l;
+      split4<true>(x[i], h, l);
+      *reinterpret_cast<float4*>(dst_hi + off) = h;
+      *reinterpret_cast<float4*>(dst_lo + off) = l;
+    }
   }
 }
 
@@ -173,24 +192,38 @@ __device__ __forceinline__ float transform_oc(const uint8_t* src, const uint8_t*
   const int kbase = (t >> 7) * 16;
   const float* col = reinterpret_cast<const float*>(src + (o >> 5) * 4096) + (o & 31);
   const float* ycol = reinterpret_cast<const float*>(ysrc + (o >> 5) * 4096) + (o & 31);
-  float sum = 0.f;
+  float sum = 0.f, m = 0.f;
+  float4 x[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    float x[4];
+    float v[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      x[e] = col[(kbase + 4 * c + e) * 32];
-      if (HAS_Y) x[e] = act_backward<float>(dact, ycol[(kbase + 4 * c + e) * 32], x[e]);
+      v[e] = col[(kbase + 4 * c + e) * 32];
+      if (HAS_Y) v[e] = act_backward<float>(dact, ycol[(kbase + 4 * c + e) * 32], v[e]);
     }
-    sum += (x[0] + x[1]) + (x[2] + x[3]);
-    float4 h, l;
-    split_tf32(x[0], h.x, l.x);
-    split_tf32(x[1], h.y, l.y);
-    split_tf32(x[2], h.z, l.z);
-    split_tf32(x[3], h.w, l.w);
-    const uint32_t off = sw128_offset(o, (kbase >> 2) + c);
-    *reinterpret_cast<float4*>(dst_hi + off) = h;
-    *reinterpret_cast<float4*>(dst_lo + off) = l;
+    sum += (v[0] + v[1]) + (v[2] + v[3]);
+    x[c] = make_float4(v[0], v[1], v[2], v[3]);
+    m = fmaxf(m, absmax4(x[c]));
+  }
+  if (guard_ok(m)) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float4 h, l;
+      split4<false>(x[c], h, l);
+      const uint32_t off = sw128_offset(o, (kbase >> 2) + c);
+      *reinterpret_cast<float4*>(dst_hi + off) = h;
+      *reinterpret_cast<float4*>(dst_lo + off) = l;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float4 h, l;
+      split4<true>(x[c], h, l);
+      const uint32_t off = sw128_offset(o, (kbase >> 2) + c);
+      *reinterpret_cast<float4*>(dst_hi + off) = h;
+      *reinterpret_cast<float4*>(dst_lo + off) = l;
+    }
   }
   return sum;
 }

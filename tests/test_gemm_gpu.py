@@ -262,6 +262,38 @@ def test_narrow_fp32_products(gpu):
         check(B.to_host(C), ref, np.float32, f"batched narrow acc{acc}")
 
 
+def test_non_finite_inputs_stay_where_they_belong(gpu):
+    """An infinity in A and a NaN in B (fp32): exactly the row and the column of C they feed are
+    non-finite, everything else matches the oracle (the hi/lo split must not leak inf - inf or a
+    wrapped NaN pattern into other elements)."""
+    rng = np.random.default_rng(33)
+    for (m, n, k, ta, tb) in [(192, 160, 96, False, False), (130, 140, 70, True, False),
+                              (64, 256, 128, False, True)]:
+        a = randn(rng, (k, m) if ta else (m, k), np.float32)
+        b = randn(rng, (n, k) if tb else (k, n), np.float32)
+        if ta:
+            a[5, 3] = np.inf
+        else:
+            a[3, 5] = np.inf
+        nanbits = np.array([0xffffffff], np.uint32).view(np.float32)[0]
+        if tb:
+            b[2, 7] = nanbits
+        else:
+            b[7, 2] = nanbits
+        C = B.colmajor(m, n, torch.float32, fill=0.0)
+        gpu.gemm(B.from_host(a), B.from_host(b), C, ta, tb)
+        torch.cuda.synchronize()
+        got = B.to_host(C)
+        bad = np.zeros((m, n), bool)
+        bad[3, :] = True
+        bad[:, 2] = True
+        assert not np.isfinite(got[bad]).any()
+        assert np.isnan(got[:, 2]).all()
+        a0, b0 = np.where(np.isfinite(a), a, 0), np.where(np.isfinite(b), b, 0)
+        ref = orc.gemm(a0, b0, ta, tb)
+        np.testing.assert_allclose(got[~bad], ref[~bad], rtol=1e-4, atol=1e-4)
+
+
 def test_empty_and_degenerate_shapes(gpu):
     rng = np.random.default_rng(19)
     c0 = randn(rng, (4, 5), np.float32)
