@@ -280,6 +280,43 @@ int check_common(int dtype, int64_t m, int64_t n, int64_t k) {
   return GINN_B200_OK;
 }
 
+// Half product on the TMA-fed kernels.  Returns -1 when launched, 0 when neither kernel takes
+// the problem (the caller goes on to the general path), or an error status.  `h.bias` / `h.act`
+// ask for the Affine epilogue on the result: fused by the one-CTA kernel, a pass after the pair
+// kernel.
+// Measured on B200 (Half, us): the one-CTA TMA kernel beats the cp.async kernel on every
+// aligned shape tried, down to 512 x 128 x 784 (12 against 21), and the CTA-pair kernel until
+// the pairs have about two waves of 256 x 256 tiles (1024 x 4096 x 1024: 16.5 against 19.9;
+// 2048^3: 21 against 25; 8192^3: 786 against 732).  Shapes with a tiny extent go on to the
+// CUDA-core kernels.
+static int half_tma_dispatch(DevCtx* ctx, const gb::HgemmArgs& h, cudaStream_t stream, int force) {
+  const long long m = h.M, n = h.N, k = h.K, batches = h.batches;
+  const bool big = m > 16 && n > 16 && k > 32;
+  const bool big_pair = m >= 256 && n >= 256 && k >= 128 &&
+                        ((m + 255) / 256) * ((n + 255) / 256) * batches >= ctx->num_sms;
+  if ((force == PATH_PAIR || (force == PATH_AUTO && big_pair)) && gb::hgemm_pair_supported(h)) {
+    int* counter;
+    {
+      std::lock_guard<std::mutex> g(ctx->mu);
+      counter = ctx->d_counters + 2 * (ctx->next_counter++ % kCounters);
+    }
+    CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), t_pair_group_m, counter, stream,
+                                 ctx->d_status));
+    g_launches.fetch_add(1);
+    if (h.bias != nullptr || h.act != GINN_B200_ACT_NONE) {
+      CU_TRY(gb::launch_bias_act_half(h.C, h.ldc, h.bias, h.act, h.M, h.N, stream));
+      g_launches.fetch_add(1);
+    }
+    return -1;
+  }
+  if ((big || force == PATH_TMA) && gb::hgemm_tma_supported(h)) {
+    CU_TRY(gb::launch_hgemm_tma(h, persistent_sms(ctx), stream, ctx->d_status));
+    g_launches.fetch_add(1);
+    return -1;
+  }
+  return 0;
+}
+
 int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, int64_t m, int64_t n,
               int64_t k, const void* a, int64_t lda, int64_t stride_a, const void* b, int64_t ldb,
               int64_t stride_b, void* c, int64_t ldc, int64_t stride_c, int64_t batches,
@@ -311,30 +348,8 @@ int gemm_impl(int device, void* stream_, int dtype, int trans_a, int trans_b, in
     h.transA = trans_a ? 1 : 0; h.transB = trans_b ? 1 : 0;
     h.M = (int)m; h.N = (int)n; h.K = (int)k; h.batches = (int)batches;
     h.accumulate = accumulate ? 1 : 0;
-    // Measured on B200 (Half, us): the one-CTA TMA kernel beats the cp.async kernel on every
-    // aligned shape tried, down to 512 x 128 x 784 (12 against 21), and the CTA-pair kernel until
-    // the pairs have about two waves of 256 x 256 tiles (1024 x 4096 x 1024: 16.5 against 19.9;
-    // 2048^3: 21 against 25; 8192^3: 786 against 732).  Shapes with a tiny extent go on to the
-    // CUDA-core kernels.
-    const bool big = m > 16 && n > 16 && k > 32;
-    const bool big_pair = m >= 256 && n >= 256 && k >= 128 &&
-                          ((m + 255) / 256) * ((n + 255) / 256) * batches >= ctx->num_sms;
-    if ((force == PATH_PAIR || (force == PATH_AUTO && big_pair)) && gb::hgemm_pair_supported(h)) {
-      int* counter;
-      {
-        std::lock_guard<std::mutex> g(ctx->mu);
-        counter = ctx->d_counters + 2 * (ctx->next_counter++ % kCounters);
-      }
-      CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), t_pair_group_m, counter, stream,
-                                   ctx->d_status));
-      g_launches.fetch_add(1);
-      return GINN_B200_OK;
-    }
-    if ((big || force == PATH_TMA) && gb::hgemm_tma_supported(h)) {
-      CU_TRY(gb::launch_hgemm_tma(h, persistent_sms(ctx), stream, ctx->d_status));
-      g_launches.fetch_add(1);
-      return GINN_B200_OK;
-    }
+    const int r = half_tma_dispatch(ctx, h, stream, force);
+    if (r != 0) return r < 0 ? GINN_B200_OK : r;
   }
 
   Problem p;
@@ -698,31 +713,32 @@ int ginn_b200_affine_forward(int device, void* stream_, int dtype, int npairs,
   p.bias = bias;
   p.act = act;
   p.accumulate = 0;
-  // Half with every pair on the TMA kernels: products through the plain entry (the first assigns,
-  // the others accumulate), then one elementwise pass for bias and activation -- 16 + 4 us
-  // against 29 us for the fused cp.async kernel on a 1024 x 1024 layer with 4096 columns.  The
-  // product is rounded to fp16 before the nonlinearity, as the reference's is.
+  // Half with every pair on the TMA kernels: one product per pair (the first assigns, the others
+  // accumulate) and the bias and activation in the epilogue of the last one -- fused by the
+  // one-CTA kernel, a pass after the pair kernel.
+  // 16 us for a 1024 x 1024 layer on 4096 columns against 29 us for the fused cp.async kernel.
+  // The product is rounded to fp16 before the bias and the nonlinearity, as the reference's is.
   if (dtype == GINN_B200_F16 && t_force_path == PATH_AUTO && np > 0 && m > 16 && n > 16 &&
       n <= 65535) {
+    gb::HgemmArgs h[gb::kMaxPairs];
     bool tma = true;
     for (int i = 0; i < np && tma; ++i) {
-      gb::HgemmArgs h;
-      h.A = p.a[i].base; h.B = p.b[i].base; h.C = out;
-      h.lda = p.a[i].ld; h.ldb = p.b[i].ld; h.ldc = ldo;
-      h.strideA = h.strideB = h.strideC = 0;
-      h.transA = h.transB = 0;
-      h.M = (int)m; h.N = (int)n; h.K = (int)p.k[i]; h.batches = 1;
-      h.accumulate = i > 0;
-      tma = p.k[i] > 32 && gb::hgemm_tma_supported(h);
+      h[i].A = p.a[i].base; h[i].B = p.b[i].base; h[i].C = out;
+      h[i].lda = p.a[i].ld; h[i].ldb = p.b[i].ld; h[i].ldc = ldo;
+      h[i].strideA = h[i].strideB = h[i].strideC = 0;
+      h[i].transA = h[i].transB = 0;
+      h[i].M = (int)m; h[i].N = (int)n; h[i].K = (int)p.k[i]; h[i].batches = 1;
+      h[i].accumulate = i > 0;
+      tma = p.k[i] > 32 && gb::hgemm_tma_supported(h[i]);
     }
     if (tma) {
-      for (int i = 0; i < np; ++i)
-        if (int s = gemm_impl(device, stream_, dtype, 0, 0, m, n, p.k[i], p.a[i].base, p.a[i].ld, 0,
-                              p.b[i].base, p.b[i].ld, 0, out, ldo, 0, 1, i > 0))
-          return s;
-      CU_TRY(gb::launch_bias_act_half(out, ldo, bias, act, (int)m, n,
-                                      static_cast<cudaStream_t>(stream_)));
-      if (bias != nullptr || act != GINN_B200_ACT_NONE) g_launches.fetch_add(1);
+      h[np - 1].bias = bias;
+      h[np - 1].act = act;
+      for (int i = 0; i < np; ++i) {
+        const int r = half_tma_dispatch(ctx, h[i], static_cast<cudaStream_t>(stream_), PATH_AUTO);
+        if (r > 0) return r;
+        if (r == 0) return fail(GINN_B200_CUDA_ERROR, "Half TMA dispatch declined a checked problem");
+      }
       return GINN_B200_OK;
     }
   }

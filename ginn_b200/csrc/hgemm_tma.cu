@@ -21,6 +21,7 @@
 #include <string>
 #include <cstring>
 #include "ptx.cuh"
+#include "math.cuh"
 #include "launch.h"
 
 namespace gb {
@@ -46,6 +47,10 @@ struct HParams {
   int accumulate;
   int vec_c;  // 1: C allows 16-byte accesses (base, ldc and batch stride multiples of 8 halves)
   int tiles_m, tiles_n, total_tiles;
+  // Fused Affine epilogue: out = act(fp16(acc [+ C]) + bias[row]); bias may be null, act NONE.
+  const __half* bias;
+  int act;
+  int vec_bias;  // bias allows 16-byte loads
 };
 
 __device__ __forceinline__ void decode_tile(const HParams& p, int t, int& m_idx, int& n_idx,
@@ -194,6 +199,7 @@ hgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
+    const bool fused = p.bias != nullptr || p.act != ACT_NONE;
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
       int m_idx, n_idx, batch;
       decode_tile(p, t, m_idx, n_idx, batch);
@@ -246,6 +252,52 @@ hgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const float4 x1 = *reinterpret_cast<const float4*>(stage + cl * TEPI_PITCH + rg * 8 + 4);
           float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
           __half* cp = cbase + static_cast<long long>(col) * p.ldc + row;
+          if (fused) {
+            // The reference rounds the product (and the sum with the previous pairs) to fp16,
+            // adds the bias and applies the nonlinearity to that: the same roundings here.
+            const bool vec = p.vec_c && row + 8 <= p.M;
+            if (p.accumulate) {
+              if (vec) {
+                const __half* o = reinterpret_cast<const __half*>(&cold[i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] += __half2float(o[e]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (row + e < p.M) x[e] += __half2float(cp[e]);
+              }
+            }
+            float b[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) b[e] = 0.f;
+            if (p.bias != nullptr) {
+              if (p.vec_bias && row + 8 <= p.M) {
+                const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + row);
+                const __half* bh = reinterpret_cast<const __half*>(&bv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b[e] = __half2float(bh[e]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (row + e < p.M) b[e] = __half2float(p.bias[row + e]);
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              x[e] = act_forward_half(p.act, __half2float(__float2half_rn(x[e])) + b[e]);
+            if (vec) {
+              uint4 out;
+              __half2* oh = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
+              *reinterpret_cast<uint4*>(cp) = out;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (row + e < p.M) cp[e] = __float2half_rn(x[e]);
+            }
+            continue;
+          }
           if (p.vec_c && row + 8 <= p.M) {
             if (p.accumulate) {
               const __half* o = reinterpret_cast<const __half*>(&cold[i]);
@@ -418,6 +470,10 @@ cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t strea
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batches;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   p.total_tiles = static_cast<int>(total);
+  if ((a.bias != nullptr || a.act != ACT_NONE) && a.batches != 1) return cudaErrorInvalidValue;
+  p.bias = static_cast<const __half*>(a.bias);
+  p.act = a.act;
+  p.vec_bias = (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0 ? 1 : 0;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
   if (!a.transA && !a.transB) return launch_variant<1, 0>(ta, tb, p, grid, stream, status);
   if (a.transA && !a.transB) return launch_variant<0, 0>(ta, tb, p, grid, stream, status);

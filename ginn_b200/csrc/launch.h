@@ -57,6 +57,10 @@ struct HgemmArgs {
   int transA, transB;
   int M, N, K, batches;
   int accumulate;
+  // Affine epilogue out = act(fp16(product [+ C]) + bias[row]); batches must be 1 when set.
+  // The one-CTA kernel fuses it; callers of the pair kernel run a pass after it.
+  const void* bias = nullptr;
+  int act = 0;
 };
 // Returns true when the TMA path can take the problem (alignment and size rules).
 bool hgemm_tma_supported(const HgemmArgs& a);

@@ -151,6 +151,41 @@ def test_forward_with_split_contraction(gpu, act):
             check(B.to_host(Y), ref, np.float32, f"{m}x{n}x{k} act {act}")
 
 
+@pytest.mark.parametrize("act", ACTS)
+def test_half_layers_on_the_tma_kernels(gpu, act):
+    """Half Affines large enough for the TMA-fed kernels: bias and nonlinearity run in the
+    epilogue of the last pair's product (one and two pairs, ragged edge tiles, an output whose
+    leading dimension rules out 16-byte stores); then the backward pass of a layer whose weight
+    gradient has few tiles and a long contraction, run twice onto the same gradients."""
+    rng = np.random.default_rng(61 + act)
+    dt = np.float16
+    for (m, n, k1, k2, pad) in [(256, 512, 256, 0, 0), (200, 264, 136, 72, 0), (256, 256, 128, 64, 3)]:
+        W, X, b = randn(rng, (m, k1), dt, 0.05), randn(rng, (k1, n), dt), randn(rng, m, dt)
+        pairs_h, pairs_d = [(W, X)], [gpu.Pair(B.from_host(W), B.from_host(X))]
+        if k2:
+            V, H = randn(rng, (m, k2), dt, 0.05), randn(rng, (k2, n), dt)
+            pairs_h.append((V, H))
+            pairs_d.append(gpu.Pair(B.from_host(V), B.from_host(H)))
+        Y = B.colmajor(m, n, torch.float16, ld=m + pad, fill=7.0)
+        gpu.affine_forward(pairs_d, B.from_host(b), act, Y)
+        torch.cuda.synchronize()
+        check(B.to_host(Y), orc.affine_forward(pairs_h, b, act), dt, f"value {m}x{n} pad {pad}")
+    m, n, k = 256, 4096, 256
+    W, X, b, dY = randn(rng, (m, k), dt, 0.05), randn(rng, (k, n), dt), randn(rng, m, dt), randn(rng, (m, n), dt, 0.1)
+    Wd, Xd, bd, dYd = map(B.from_host, (W, X, b, dY))
+    Y = B.colmajor(m, n, torch.float16, fill=0.0)
+    gpu.affine_forward([gpu.Pair(Wd, Xd)], bd, act, Y)
+    dW, dX = zeros_like_cm(Wd), zeros_like_cm(Xd)
+    db = torch.zeros(m, device="cuda", dtype=torch.float16)
+    for _ in range(2):
+        gpu.affine_backward([gpu.PairGrad(Wd, Xd, dW, dX)], dYd, Y, act, db)
+    torch.cuda.synchronize()
+    g = orc.affine_backward([(W, X)], dY, B.to_host(Y), act, dt)
+    check(B.to_host(dW), 2 * np.asarray(g["da"][0]), dt, "dW")
+    check(B.to_host(dX), 2 * np.asarray(g["db"][0]), dt, "dX")
+    check(B.to_host(db), 2 * np.asarray(g["dbias"]), dt, "db")
+
+
 def test_half_backward_with_the_nodes_own_scratch(gpu):
     """A large Half Affine with a nonlinearity materialises dY (.) f'(Y) once.  Given the node's
     own d-pre-activation tensor (as AffineNode owns dpreactiv_, ginn/node/affine.h:82) the call
