@@ -108,6 +108,11 @@ hgemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  // Everything above touched only shared and tensor memory and overlaps the tail of the kernel
+  // before this one in the stream when launched as its programmatic dependent; from here on the
+  // kernel reads what that kernel may have written.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ===================== TMA producer =====================
@@ -428,8 +433,7 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const H
   static unsigned long long smem_set = 0;  // per template instantiation: per kernel
   cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(kern), smem, &smem_set);
   if (e != cudaSuccess) return e;
-  kern<<<grid, 192, smem, stream>>>(ta, tb, p, status);
-  return cudaGetLastError();
+  return launch_kernel(kern, dim3(grid), dim3(192), smem, stream, pdl_enabled(), ta, tb, p, status);
 }
 
 }  // namespace

@@ -177,6 +177,9 @@ cudaError_t launch_act_inplace_f32(float* c, long long ldc, long long stride, in
 cudaError_t launch_bias_act_half(void* y, long long ldy, const void* bias, int act, int m,
                                  long long n, cudaStream_t stream);
 // da (m x n, leading dimension m) = dy (.) act'(y), fp16, n <= 65535.
+// c (m x n, ld ldc) += the sum of `parts` dense m x n fp16 matrices stored back to back at ws.
+cudaError_t launch_add_partials_half(void* c, long long ldc, const void* ws, int parts, int m,
+                                     long long n, cudaStream_t stream);
 cudaError_t launch_dact_half(const void* dy, long long lddy, const void* y, long long ldy, int act,
                              void* da, int m, long long n, cudaStream_t stream);
 cudaError_t launch_lstm_cell_forward(float* gates, long long ldg, const float* c_prev,

@@ -465,6 +465,57 @@ __global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y,
   }
 }
 
+// The same sum at memory speed for aligned matrices: a thread owns V = 16 / sizeof(T) consecutive
+// rows (one 16-byte load per column), 16 such threads cover 16 V rows of a column and 16 slices
+// share the block's range of columns; the slices meet in shared memory, the blocks in an atomic
+// add.  (The scalar kernel above reads 64 bytes per warp and load: 160 GB/s on a 1024 x 4096 Half
+// matrix, 49 us of a 110 us layer step.)  Requires ld, M multiples of V and 16-byte aligned bases.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rowsum_vec_kernel(const T* __restrict__ dy, const T* __restrict__ y, int dact, long long ld, int M,
+                  long long N, T* __restrict__ rowsum) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float part[16][16 * V + 1];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = (blockIdx.x * 16 + threadIdx.x) * V;
+  const long long per = (N + gridDim.y - 1) / gridDim.y;
+  const long long n0 = blockIdx.y * per;
+  const long long n1 = n0 + per < N ? n0 + per : N;
+  float acc[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) acc[e] = 0.f;
+  if (row < M) {
+#pragma unroll 4
+    for (long long n = n0 + threadIdx.y; n < n1; n += 16) {
+      const uint4 dv = __ldg(reinterpret_cast<const uint4*>(dy + n * ld + row));
+      const T* d = reinterpret_cast<const T*>(&dv);
+      if (dact != ACT_NONE) {
+        const uint4 yv = __ldg(reinterpret_cast<const uint4*>(y + n * ld + row));
+        const T* yy = reinterpret_cast<const T*>(&yv);
+#pragma unroll
+        for (int e = 0; e < V; ++e)
+          acc[e] += round_to<T>(act_backward<T>(dact, to_f(yy[e]), to_f(d[e])));
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] += to_f(d[e]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < V; ++e) part[threadIdx.y][threadIdx.x * V + e] = acc[e];
+  __syncthreads();
+  // 256 threads, 16 V rows: thread t sums row t (and t + 256 ... when V > 16) over the slices
+  for (int r = threadIdx.y * 16 + threadIdx.x; r < 16 * V; r += 256) {
+    const int grow = blockIdx.x * 16 * V + r;
+    if (grow >= M) continue;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sum += part[j][r];
+    atomic_add_t(rowsum + grow, sum);
+  }
+}
+
 // Self test of the bounded-wait machinery: one thread waits on an mbarrier on which nothing ever
 // arrives, with a short limit, and must come back with DEV_TIMEOUT_SELFTEST in the status word.
 // Nothing faults and nothing hangs: the wait simply runs out.
@@ -588,6 +639,26 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
 cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
                           long long N, void* rowsum, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return cudaSuccess;
+  {
+    const int esize = dtype == 0 ? 4 : 2, V = 16 / esize;
+    auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (M % V == 0 && ld % V == 0 && al(dy) && (dact == ACT_NONE || al(y)) && N >= 64) {
+      const int row_blocks = (M + 16 * V - 1) / (16 * V);
+      long long chunks = 592 / row_blocks;  // about four blocks of 256 threads per SM
+      if (chunks > (N + 63) / 64) chunks = (N + 63) / 64;
+      // every block adds its part to the fp16 sum with one more rounding: keep them few
+      if (dtype != 0 && chunks > 16) chunks = 16;
+      if (chunks < 1) chunks = 1;
+      dim3 vgrid(row_blocks, static_cast<unsigned>(chunks)), vblock(16, 16);
+      if (dtype == 0)
+        return launch_kernel(rowsum_vec_kernel<float>, vgrid, vblock, 0, stream, pdl_enabled(),
+                             static_cast<const float*>(dy), static_cast<const float*>(y), dact, ld,
+                             M, N, static_cast<float*>(rowsum));
+      return launch_kernel(rowsum_vec_kernel<__half>, vgrid, vblock, 0, stream, pdl_enabled(),
+                           static_cast<const __half*>(dy), static_cast<const __half*>(y), dact, ld, M,
+                           N, static_cast<__half*>(rowsum));
+    }
+  }
   dim3 block(32, 8);
   // enough blocks along the columns to fill the GPU when there are few rows (at least 64
   // columns per block)

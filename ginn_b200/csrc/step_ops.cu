@@ -218,6 +218,8 @@ template <bool VEC>
 __global__ void __launch_bounds__(256)
 dact_half_kernel(const __half* __restrict__ dy, long long lddy, const __half* __restrict__ y,
                  long long ldy, int act, __half* __restrict__ da, int m, long long n) {
+  pdl_wait();
+  pdl_launch_dependents();
   const long long col = blockIdx.y;
   const int per = VEC ? 8 : 1;
   const int r = (blockIdx.x * blockDim.x + threadIdx.x) * per;
@@ -239,12 +241,55 @@ dact_half_kernel(const __half* __restrict__ dy, long long lddy, const __half* __
   }
 }
 
+// C (m x n, leading dimension ldc) += sum over `parts` dense m x n fp16 matrices stored back to
+// back: the partial products of a contraction split into chunks.  Summed in fp32, rounded once.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+add_partials_half_kernel(__half* __restrict__ c, long long ldc, const __half* __restrict__ ws,
+                         int parts, int m, long long n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long col = blockIdx.y;
+  const int per = VEC ? 8 : 1;
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) * per;
+  if (r >= m || col >= n) return;
+  __half* cp = c + col * ldc + r;
+  const __half* wp = ws + col * static_cast<long long>(m) + r;
+  const long long part_stride = static_cast<long long>(m) * n;
+  if (VEC) {
+    uint4 cv = *reinterpret_cast<const uint4*>(cp);
+    __half2* c2 = reinterpret_cast<__half2*>(&cv);
+    float2 acc[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = __half22float2(c2[e]);
+    for (int q = 0; q < parts; ++q) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(wp + q * part_stride);
+      const __half2* w2 = reinterpret_cast<const __half2*>(&wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 w = __half22float2(w2[e]);
+        acc[e].x += w.x;
+        acc[e].y += w.y;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) c2[e] = __floats2half2_rn(acc[e].x, acc[e].y);
+    *reinterpret_cast<uint4*>(cp) = cv;
+  } else {
+    float acc = __half2float(*cp);
+    for (int q = 0; q < parts; ++q) acc += __half2float(wp[q * part_stride]);
+    *cp = __float2half_rn(acc);
+  }
+}
+
 // Y = act(Y + bias) in place, fp16 (bias per row, broadcast over columns): the epilogue of a large
 // Half Affine whose product ran on a TMA-fed kernel that has no fused epilogue of its own.
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 bias_act_half_kernel(__half* __restrict__ y, long long ldy, const __half* __restrict__ bias, int act,
                      int m, long long n) {
+  pdl_wait();
+  pdl_launch_dependents();
   const long long col = blockIdx.y;
   const int per = VEC ? 8 : 1;
   const int r = (blockIdx.x * blockDim.x + threadIdx.x) * per;
@@ -565,9 +610,22 @@ cudaError_t launch_bias_act_half(void* y, long long ldy, const void* bias, int a
   const bool vec = m % 8 == 0 && ldy % 8 == 0 && al(y) && (bias == nullptr || al(bias));
   const int per = vec ? 8 : 1;
   dim3 grid(((m + per - 1) / per + 255) / 256, static_cast<unsigned>(n));
-  if (vec) bias_act_half_kernel<true><<<grid, 256, 0, stream>>>(static_cast<__half*>(y), ldy, static_cast<const __half*>(bias), act, m, n);
-  else bias_act_half_kernel<false><<<grid, 256, 0, stream>>>(static_cast<__half*>(y), ldy, static_cast<const __half*>(bias), act, m, n);
-  return cudaGetLastError();
+  return launch_kernel(vec ? bias_act_half_kernel<true> : bias_act_half_kernel<false>, grid, dim3(256), 0,
+                       stream, pdl_enabled(), static_cast<__half*>(y), ldy,
+                       static_cast<const __half*>(bias), act, m, n);
+}
+
+cudaError_t launch_add_partials_half(void* c, long long ldc, const void* ws, int parts, int m,
+                                     long long n, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || parts <= 0) return cudaSuccess;
+  if (n > 65535) return cudaErrorInvalidValue;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const bool vec = m % 8 == 0 && ldc % 8 == 0 && al(c) && al(ws);
+  const int per = vec ? 8 : 1;
+  dim3 grid(((m + per - 1) / per + 255) / 256, static_cast<unsigned>(n));
+  return launch_kernel(vec ? add_partials_half_kernel<true> : add_partials_half_kernel<false>, grid,
+                       dim3(256), 0, stream, pdl_enabled(), static_cast<__half*>(c), ldc,
+                       static_cast<const __half*>(ws), parts, m, n);
 }
 
 cudaError_t launch_dact_half(const void* dy, long long lddy, const void* y, long long ldy, int act,
@@ -579,9 +637,8 @@ cudaError_t launch_dact_half(const void* dy, long long lddy, const void* y, long
   const int per = vec ? 8 : 1;
   dim3 grid(((m + per - 1) / per + 255) / 256, static_cast<unsigned>(n));
   const __half *d = static_cast<const __half*>(dy), *yy = static_cast<const __half*>(y);
-  if (vec) dact_half_kernel<true><<<grid, 256, 0, stream>>>(d, lddy, yy, ldy, act, static_cast<__half*>(da), m, n);
-  else dact_half_kernel<false><<<grid, 256, 0, stream>>>(d, lddy, yy, ldy, act, static_cast<__half*>(da), m, n);
-  return cudaGetLastError();
+  return launch_kernel(vec ? dact_half_kernel<true> : dact_half_kernel<false>, grid, dim3(256), 0, stream,
+                       pdl_enabled(), d, lddy, yy, ldy, act, static_cast<__half*>(da), m, n);
 }
 
 cudaError_t launch_act_inplace_f32(float* c, long long ldc, long long stride, int act, int m, int n,
