@@ -433,6 +433,346 @@ __global__ void __launch_bounds__(256) skinny_k_plain_kernel(const __grid_consta
   }
 }
 
+// ---- streaming variants: the same three mappings for the case that matters in practice, a
+// large fp32 operand that is read or written exactly once (the ten-class output layer of the MLP
+// configuration: logits, its weight gradient, the gradient of its input).  Measured at those
+// shapes the kernels above ran at 0.7-1.4 TB/s whether or not the large operand was in L2: a CTA
+// is a chain of dependent round trips to memory (a staging loop of scalar loads, a few loads per
+// thread and trip), so it is latency that bounds them.  These variants bring the small operand
+// in with one round of independent loads, move 16 bytes per thread and access with eight or more
+// loads in flight, keep every CTA resident at once, and send few, wide atomics. ----
+
+// Copies `count` floats of the small operand into shared memory, up to ROUNDS x 256 elements per
+// round trip: all loads of a round are issued before its first store.  Element i is described by
+// (q, r) = (i / d, i % d) for a divisor d the caller picks (the extent along which the operand is
+// contiguous); `src_of(q, r)` gives its address and `pos(q, r)` its place.  The pair is advanced
+// incrementally -- an integer division per element (a runtime divisor costs some twenty
+// instructions) had made the copy two thirds of a kernel's instructions.
+template <int ROUNDS, typename SrcFn, typename PosFn>
+__device__ __forceinline__ void stage_small(float* dst, int count, int d, SrcFn src_of, PosFn pos) {
+  int q = static_cast<int>(threadIdx.x) / d, r = static_cast<int>(threadIdx.x) % d;
+  const int dq = 256 / d, dr = 256 % d;
+  for (int base = 0; base < count; base += ROUNDS * 256) {
+    float v[ROUNDS];
+    int qq = q, rr = r;
+#pragma unroll
+    for (int t = 0; t < ROUNDS; ++t) {
+      v[t] = base + t * 256 + static_cast<int>(threadIdx.x) < count ? __ldg(src_of(qq, rr)) : 0.f;
+      qq += dq;
+      rr += dr;
+      if (rr >= d) {
+        rr -= d;
+        ++qq;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < ROUNDS; ++t) {
+      if (base + t * 256 + static_cast<int>(threadIdx.x) < count) dst[pos(q, r)] = v[t];
+      q += dq;
+      r += dr;
+      if (r >= d) {
+        r -= d;
+        ++q;
+      }
+    }
+  }
+}
+
+// The same for a source that is one contiguous, 16-byte aligned run of `count` floats (count a
+// multiple of four): 16-byte loads, up to ROUNDS x 1024 floats per round trip.
+template <int ROUNDS, typename PosFn>
+__device__ __forceinline__ void stage_run(float* dst, const float* src, int count, int d, PosFn pos) {
+  const float4* src4 = reinterpret_cast<const float4*>(src);
+  const int count4 = count >> 2;
+  int q = 4 * static_cast<int>(threadIdx.x) / d, r = 4 * static_cast<int>(threadIdx.x) % d;
+  const int dq = 1024 / d, dr = 1024 % d;
+  for (int base = 0; base < count4; base += ROUNDS * 256) {
+    float4 v[ROUNDS];
+#pragma unroll
+    for (int t = 0; t < ROUNDS; ++t) {
+      const int i = base + t * 256 + threadIdx.x;
+      v[t] = i < count4 ? __ldg(src4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int t = 0; t < ROUNDS; ++t) {
+      if (base + t * 256 + static_cast<int>(threadIdx.x) < count4) {
+        const float e[4] = {v[t].x, v[t].y, v[t].z, v[t].w};
+        int qq = q, rr = r;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dst[pos(qq, rr)] = e[j];
+          if (++rr == d) {
+            rr = 0;
+            ++qq;
+          }
+        }
+      }
+      q += dq;
+      r += dr;
+      if (r >= d) {
+        r -= d;
+        ++q;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool run_ok(const float* p, long long count) {
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && count % 4 == 0;
+}
+
+// m <= 16, fp32, B contraction-contiguous with 16-byte aligned columns, the whole of A (m x K)
+// resident in shared memory as [m][kpad]; a CTA owns sixteen columns of C (two per warp), every
+// CTA of the grid is resident at once.
+__global__ void __launch_bounds__(256) skinny_m_stream_kernel(const __grid_constant__ Problem P,
+                                                              int kpad) {
+  extern __shared__ __align__(16) float As_dyn[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long batch = blockIdx.y;
+  const Plain<float> A(P.a[0], batch), Bm(P.b[0], batch);
+  const int M = P.M;
+  const int K = static_cast<int>(P.k[0]);
+  // A in the order it is stored: element i = (q, r) with r the fast index -- m when m is
+  // contiguous (q = k), else k (q = m)
+  const bool m_fast = A.so == 1;
+  const int d = m_fast ? M : K;
+  auto a_pos = [&](int q, int r) { return m_fast ? r * kpad + q : q * kpad + r; };
+  if ((m_fast ? A.sk == M : A.so == K) && run_ok(A.p, static_cast<long long>(M) * K))
+    stage_run<10>(As_dyn, A.p, M * K, d, a_pos);  // A is one run: 10 K floats per round trip
+  else
+    stage_small<16>(
+        As_dyn, M * K, d,
+        [&](int q, int r) { return A.p + (m_fast ? static_cast<long long>(q) * A.sk + r
+                                                 : static_cast<long long>(q) * A.so + r); },
+        a_pos);
+  if (kpad > K && threadIdx.x < M)  // the padding is read by the last 16-byte load of each row
+    for (int k = K; k < kpad; ++k) As_dyn[threadIdx.x * kpad + k] = 0.f;
+  __syncthreads();
+  const long long col0 = static_cast<long long>(blockIdx.x) * 16 + warp * 2;
+  const bool live0 = col0 < P.N, live1 = col0 + 1 < P.N;
+  const float* b0 = Bm.p + (live0 ? col0 : 0) * Bm.so;
+  const float* b1 = Bm.p + (live1 ? col0 + 1 : 0) * Bm.so;
+  float acc0[kSkinny], acc1[kSkinny];
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m) acc0[m] = acc1[m] = 0.f;
+#pragma unroll 4
+  for (int kk = 4 * lane; kk < K; kk += 128) {
+    float x0[4], x1[4];
+    if (kk + 3 < K) {
+      ld4(b0 + kk, x0);
+      ld4(b1 + kk, x1);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x0[e] = kk + e < K ? __ldg(b0 + kk + e) : 0.f;
+        x1[e] = kk + e < K ? __ldg(b1 + kk + e) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < kSkinny; ++m)
+      if (m < M) {
+        const float4 a = *reinterpret_cast<const float4*>(&As_dyn[m * kpad + kk]);
+        // one fused multiply-add per product (the kernel is bound by instruction issue)
+        acc0[m] = fmaf(a.w, x0[3], fmaf(a.z, x0[2], fmaf(a.y, x0[1], fmaf(a.x, x0[0], acc0[m]))));
+        acc1[m] = fmaf(a.w, x1[3], fmaf(a.z, x1[2], fmaf(a.y, x1[1], fmaf(a.x, x1[0], acc1[m]))));
+      }
+  }
+  float mine0 = 0.f, mine1 = 0.f;
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m)
+    if (m < M) {
+      float v0 = acc0[m], v1 = acc1[m];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        v0 += __shfl_xor_sync(0xffffffffu, v0, off);
+        v1 += __shfl_xor_sync(0xffffffffu, v1, off);
+      }
+      if (lane == m) {
+        mine0 = v0;
+        mine1 = v1;
+      }
+    }
+  if (live0 && lane < M) finish<float>(P, batch, lane, col0, mine0);
+  if (live1 && lane < M) finish<float>(P, batch, lane, col0 + 1, mine1);
+}
+
+// m <= 16, fp32, accumulating, B outer-contiguous with 16-byte aligned rows (a weight gradient).
+// A CTA owns 128 columns of C and 128 contraction indices: a lane reads four neighbouring columns
+// of B in one load, the eight warps interleave along the contraction (sixteen loads per lane,
+// eight in flight), A's slice sits in shared memory as [k][16] (read as broadcasts), the warps
+// meet in shared memory through conflict-free shared atomics and the CTA sends its 128 x m sums
+// to C -- as 16-byte vector atomics when C is one contiguous, aligned run (ldc = m).
+// blockIdx.x = 0 also sums A along k (bias gradient).
+__global__ void __launch_bounds__(256, 2) skinny_mt_stream_kernel(const __grid_constant__ Problem P) {
+  __shared__ __align__(16) float As[128 * kSkinny];
+  __shared__ __align__(16) float red[kSkinny * 128];  // [m][j][lane]: column 4 * lane + j
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long batch = blockIdx.z;
+  const Plain<float> A(P.a[0], batch), Bm(P.b[0], batch);
+  const int M = P.M;
+  const long long K = P.k[0];
+  const long long kb = static_cast<long long>(blockIdx.y) * 128;
+  const int kn = K - kb < 128 ? static_cast<int>(K - kb) : 128;
+  const long long col = static_cast<long long>(blockIdx.x) * 128 + 4 * lane;
+  const bool live = col < P.N;  // N is a multiple of four: a lane's columns live or die together
+  // A's slice in the order it is stored: (q, r) = (k, m) when m is contiguous, else (m, k)
+  const bool m_fast = A.so == 1;
+  stage_small<8>(
+      As, kn * M, m_fast ? M : kn,
+      [&](int q, int r) { return A.p + (m_fast ? (kb + q) * A.sk + r
+                                               : (kb + r) * A.sk + static_cast<long long>(q) * A.so); },
+      [&](int q, int r) { return m_fast ? q * kSkinny + r : r * kSkinny + q; });
+  for (int idx = threadIdx.x; idx < kSkinny * 128; idx += 256) red[idx] = 0.f;
+  __syncthreads();
+  float acc[4][kSkinny];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int m = 0; m < kSkinny; ++m) acc[j][m] = 0.f;
+  const float* bp = Bm.p + (live ? col : 0);  // outer-contiguous: so = 1
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float4 b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int kl = warp + 8 * (half * 8 + i);
+      b[i] = (live && kl < kn) ? __ldg(reinterpret_cast<const float4*>(bp + (kb + kl) * Bm.sk))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int kl = warp + 8 * (half * 8 + i);
+      if (kl >= kn) continue;
+#pragma unroll
+      for (int m = 0; m < kSkinny; ++m)
+        if (m < M) {
+          const float a = As[kl * kSkinny + m];  // the same word in every lane
+          acc[0][m] += a * b[i].x;
+          acc[1][m] += a * b[i].y;
+          acc[2][m] += a * b[i].z;
+          acc[3][m] += a * b[i].w;
+        }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < kSkinny; ++m)
+    if (m < M) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) atomicAdd(&red[(m * 4 + j) * 32 + lane], acc[j][m]);
+    }
+  __syncthreads();
+  float* cbase = static_cast<float*>(P.c) + batch * P.c_batch_stride;
+  const long long cfirst = static_cast<long long>(blockIdx.x) * 128;
+  const int ncols = P.N - cfirst < 128 ? static_cast<int>(P.N - cfirst) : 128;
+  const bool flat = P.ldc == M && (reinterpret_cast<uintptr_t>(cbase + cfirst * P.ldc) & 15u) == 0 &&
+                    (ncols * M) % 4 == 0;
+  if (flat) {
+    // the CTA's part of C is the run [cfirst * m, (cfirst + ncols) * m): element e is row e % m of
+    // column e / m
+    float* run = cbase + cfirst * P.ldc;
+    for (int e4 = threadIdx.x * 4; e4 < ncols * M; e4 += 1024) {
+      float v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = e4 + i, c = e / M, m = e - c * M;
+        v[i] = red[(m * 4 + (c & 3)) * 32 + (c >> 2)];
+      }
+      atomicAdd(reinterpret_cast<float4*>(run + e4), make_float4(v[0], v[1], v[2], v[3]));
+    }
+  } else {
+    for (int e = threadIdx.x; e < ncols * M; e += 256) {
+      const int c = e / M, m = e - c * M;
+      atomicAdd(cbase + (cfirst + c) * P.ldc + m, red[(m * 4 + (c & 3)) * 32 + (c >> 2)]);
+    }
+  }
+  if (P.rowsum != nullptr && blockIdx.x == 0 && threadIdx.x < M) {
+    float r = 0.f;
+    for (int kl = 0; kl < kn; ++kl) r += As[kl * kSkinny + threadIdx.x];
+    atomicAdd(static_cast<float*>(P.rowsum) + threadIdx.x, r);
+  }
+}
+
+// k <= 16, fp32, M a multiple of four, C 16-byte aligned: a thread owns four consecutive rows
+// (their rows of A in registers), a CTA 1024 rows and sixteen columns; C is read (for +=) and
+// written with 16-byte accesses, eight columns of loads in flight per thread, two CTAs per SM.
+constexpr int kSkinnyKS = 16;  // largest contraction of the streaming variant
+__global__ void __launch_bounds__(256, 2) skinny_k_stream_kernel(const __grid_constant__ Problem P) {
+  __shared__ __align__(16) float Bs[kSkinnyKCols * kSkinnyKS];
+  extern __shared__ __align__(16) float Ak_dyn[];  // [1024][K + 1]
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long batch = blockIdx.z;
+  const Plain<float> A(P.a[0], batch), Bm(P.b[0], batch);
+  const int K = static_cast<int>(P.k[0]);
+  const long long row0 = static_cast<long long>(blockIdx.x) * 1024;
+  const long long col0 = static_cast<long long>(blockIdx.y) * kSkinnyKCols;
+  const int rows = P.M - row0 < 1024 ? static_cast<int>(P.M - row0) : 1024;
+  const int cols = P.N - col0 < kSkinnyKCols ? static_cast<int>(P.N - col0) : kSkinnyKCols;
+  for (int idx = threadIdx.x; idx < kSkinnyKCols * kSkinnyKS; idx += 256) {
+    const int c = idx / kSkinnyKS, kk = idx % kSkinnyKS;
+    Bs[idx] = (c < cols && kk < K) ? __ldg(Bm.p + (col0 + c) * Bm.so + kk * Bm.sk) : 0.f;
+  }
+  // A tile in the order it is stored: (q, r) = (row, k) when the contraction is contiguous, else
+  // (k, row)
+  const bool k_fast = A.sk == 1;
+  auto a_pos = [&](int q, int r) { return k_fast ? q * (K + 1) + r : r * (K + 1) + q; };
+  if (k_fast && A.so == K && run_ok(A.p + row0 * K, static_cast<long long>(rows) * K))
+    stage_run<10>(Ak_dyn, A.p + row0 * K, rows * K, K, a_pos);  // the rows are one run
+  else
+    stage_small<16>(
+        Ak_dyn, rows * K, k_fast ? K : rows,
+        [&](int q, int r) { return A.p + (k_fast ? (row0 + q) * A.so + r
+                                                 : (row0 + r) * A.so + static_cast<long long>(q) * A.sk); },
+        a_pos);
+  __syncthreads();
+  const int r4 = threadIdx.x * 4;
+  if (r4 >= rows) return;  // M is a multiple of four: the thread's rows exist together
+  float a[4][kSkinnyKS];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int kk = 0; kk < kSkinnyKS; ++kk) a[i][kk] = kk < K ? Ak_dyn[(r4 + i) * (K + 1) + kk] : 0.f;
+  const long long row = row0 + r4;
+  float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (P.bias) {
+    const float* bp = static_cast<const float*>(P.bias) + row;
+    bias = make_float4(__ldg(bp), __ldg(bp + 1), __ldg(bp + 2), __ldg(bp + 3));
+  }
+  float* crow = static_cast<float*>(P.c) + batch * P.c_batch_stride + row;
+  for (int c0 = 0; c0 < cols; c0 += 8) {
+    float4 x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      x[j] = (P.accumulate && c0 + j < cols)
+                 ? *reinterpret_cast<const float4*>(crow + (col0 + c0 + j) * P.ldc)
+                 : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j < cols ? c0 + j : 0;
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < kSkinnyKS; kk += 4) {
+        // the same words in every lane (zero beyond K)
+        const float4 b = *reinterpret_cast<const float4*>(&Bs[c * kSkinnyKS + kk]);
+        s0 = fmaf(a[0][kk + 3], b.w, fmaf(a[0][kk + 2], b.z, fmaf(a[0][kk + 1], b.y, fmaf(a[0][kk], b.x, s0))));
+        s1 = fmaf(a[1][kk + 3], b.w, fmaf(a[1][kk + 2], b.z, fmaf(a[1][kk + 1], b.y, fmaf(a[1][kk], b.x, s1))));
+        s2 = fmaf(a[2][kk + 3], b.w, fmaf(a[2][kk + 2], b.z, fmaf(a[2][kk + 1], b.y, fmaf(a[2][kk], b.x, s2))));
+        s3 = fmaf(a[3][kk + 3], b.w, fmaf(a[3][kk + 2], b.z, fmaf(a[3][kk + 1], b.y, fmaf(a[3][kk], b.x, s3))));
+      }
+      x[j].x = act_forward<float>(P.act, x[j].x + s0 + bias.x);
+      x[j].y = act_forward<float>(P.act, x[j].y + s1 + bias.y);
+      x[j].z = act_forward<float>(P.act, x[j].z + s2 + bias.z);
+      x[j].w = act_forward<float>(P.act, x[j].w + s3 + bias.w);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j < cols) *reinterpret_cast<float4*>(crow + (col0 + c0 + j) * P.ldc) = x[j];
+  }
+}
+
 __device__ __forceinline__ void atomic_add_t(float* p, float v) { atomicAdd(p, v); }
 __device__ __forceinline__ void atomic_add_t(__half* p, float v) { atomicAdd(p, __float2half_rn(v)); }
 
@@ -591,6 +931,19 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
     const long long blocks = (warps + 7) / 8;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
     const unsigned g = static_cast<unsigned>(blocks);
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    const long long kpad = (p.k[0] + 3) / 4 * 4;
+    const long long a_bytes = static_cast<long long>(p.M) * kpad * 4;
+    if (plain && dtype == 0 && p.batches <= 65535 && a_bytes <= 64 * 1024 && p.N >= 256 &&
+        al16(p.b[0].base) && p.b[0].ld % 4 == 0 && p.b[0].batch_stride % 4 == 0) {
+      dim3 grid(static_cast<unsigned>((p.N + 15) / 16), static_cast<unsigned>(p.batches));
+      static unsigned long long set_f = 0;
+      cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(skinny_m_stream_kernel),
+                                          64 * 1024, &set_f);
+      if (e != cudaSuccess) return e;
+      return launch_kernel(skinny_m_stream_kernel, grid, dim3(256), static_cast<size_t>(a_bytes),
+                           stream, pdl_enabled(), p, static_cast<int>(kpad));
+    }
     if (plain && p.batches <= 65535) {
       dim3 grid(static_cast<unsigned>((p.N + 15) / 16), static_cast<unsigned>(p.batches));
       if (dtype == 0) skinny_m_plain_kernel<float><<<grid, 256, 0, stream>>>(p);
@@ -605,6 +958,13 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
     long long chunks = 0;
     for (int i = 0; i < p.npairs; ++i) chunks += (p.k[i] + chunk - 1) / chunk;
     if (chunks > 65535) return cudaErrorInvalidValue;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (plain && !p.b[0].k_contig && p.N % 4 == 0 && p.N >= 128 && al16(p.b[0].base) &&
+        p.b[0].ld % 4 == 0 && p.b[0].batch_stride % 4 == 0 && (p.k[0] + 127) / 128 <= 65535) {
+      dim3 grid(static_cast<unsigned>((p.N + 127) / 128), static_cast<unsigned>((p.k[0] + 127) / 128),
+                static_cast<unsigned>(p.batches));
+      return launch_kernel(skinny_mt_stream_kernel, grid, dim3(256), 0, stream, pdl_enabled(), p);
+    }
     if (plain) {
       dim3 grid(static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>(chunks),
                 static_cast<unsigned>(p.batches));
@@ -614,6 +974,21 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
                 static_cast<unsigned>(p.batches));
       skinny_mt_kernel<<<grid, 128, 0, stream>>>(p);
     }
+  } else if (plain && dtype == 0 && p.batches <= 65535 && p.M % 4 == 0 && p.M >= 1024 &&
+             p.k[0] <= kSkinnyKS &&
+             p.ldc % 4 == 0 && p.c_batch_stride % 4 == 0 &&
+             (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0 &&
+             (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 3u) == 0) &&
+             (p.N + kSkinnyKCols - 1) / kSkinnyKCols <= 65535) {
+    dim3 grid(static_cast<unsigned>((p.M + 1023) / 1024),
+              static_cast<unsigned>((p.N + kSkinnyKCols - 1) / kSkinnyKCols),
+              static_cast<unsigned>(p.batches));
+    const size_t smem = 1024 * (static_cast<size_t>(p.k[0]) + 1) * 4;  // at most 68 KiB
+    static unsigned long long set16 = 0;
+    cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(skinny_k_stream_kernel),
+                                        1024 * 17 * 4, &set16);
+    if (e != cudaSuccess) return e;
+    return launch_kernel(skinny_k_stream_kernel, grid, dim3(256), smem, stream, pdl_enabled(), p);
   } else if (plain && p.batches <= 65535 && (p.N + kSkinnyKCols - 1) / kSkinnyKCols <= 65535) {
     dim3 grid(static_cast<unsigned>((p.M + 255) / 256),
               static_cast<unsigned>((p.N + kSkinnyKCols - 1) / kSkinnyKCols),

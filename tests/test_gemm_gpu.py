@@ -336,12 +336,17 @@ def test_skinny_products_on_cuda_cores(gpu, dt):
     and the same shapes on the tensor-core path as a cross-check of the dispatch."""
     rng = np.random.default_rng(21)
     shapes = [(10, 4096, 1024), (1024, 512, 10), (10, 1024, 4096), (16, 300, 77), (3, 5, 2000),
-              (200, 300, 7), (1, 513, 640), (7, 129, 33)]
+              (200, 300, 7), (1, 513, 640), (7, 129, 33),
+              # the streaming variants' edges: ragged column groups, K not a multiple of the
+              # vector, row blocks beyond 1024, a contraction between 17 and 32
+              (12, 600, 516), (10, 1000, 4096), (16, 132, 640), (2048, 300, 12), (1028, 70, 25)]
     for (m, n, k) in shapes:
         for ta, tb in TRANS:
             for acc in (False, True):
                 run_gemm(gpu, rng, dt, m, n, k, ta, tb, acc)
     run_gemm(gpu, rng, dt, 10, 333, 129, False, True, True, 3, 1)  # padded, unaligned, NT +=
+    run_gemm(gpu, rng, dt, 10, 1024, 2048, False, True, True, 2, 0)  # padded C: scalar atomics
+    run_gemm(gpu, rng, dt, 1024, 256, 10, True, False, True, 4, 0)   # padded C, aligned
     a, b = randn(rng, (10, 96, 6), dt), randn(rng, (96, 200, 6), dt)
     c0 = randn(rng, (10, 200, 6), dt)
     for acc in (False, True):
