@@ -30,6 +30,7 @@ thread_local int t_pdl = 1;           // programmatic dependent launch for the k
 }  // namespace
 bool gb::pdl_enabled() { return t_pdl != 0; }
 int gb::max_split() { return t_max_split; }
+int gb::sm_margin() { return t_sm_margin; }
 namespace {
 
 int fail(int status, const char* fmt, ...) {

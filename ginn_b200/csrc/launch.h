@@ -14,6 +14,8 @@ namespace gb {
 bool pdl_enabled();
 // Cap on the K split of fp32 products (option "max_split" of the calling thread; 0 = no cap).
 int max_split();
+// SMs the persistent kernels leave free (option "sm_margin" of the calling thread).
+int sm_margin();
 
 // Launch with the programmatic-stream-serialization attribute when `pdl` is set: the kernel may
 // begin while its predecessor in the stream drains; it must call pdl_wait() before it touches

@@ -57,6 +57,7 @@ struct SParams {
   int accumulate;
   int split_k;  // CTAs per output tile along K (1 = none): partial sums are added atomically
   int batches;
+  int total_tiles;  // tiles_m * tiles_n * batches * split_k: a CTA takes tiles blockIdx.x, + gridDim.x, ...
   int bn;       // columns of C per tile: 128, or 64 for narrow results (half the B-side work)
   // Element (row, col) of the tile's result lives at C + row * c_rs + col * c_cs: (1, ldc) for
   // C itself, (ldc, 1) when the launcher computes the transposed product (see launch_sgemm3x).
@@ -228,6 +229,10 @@ __device__ __forceinline__ float transform_oc(const uint8_t* src, const uint8_t*
   return sum;
 }
 
+// PERSISTENT: the CTA walks tiles blockIdx.x, + gridDim.x, ...; otherwise it serves exactly one
+// (the loops below then run once and compile to straight-line code, which the long-tile launches
+// need: the walking form cost them 3-5 %).
+template <bool PERSISTENT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -236,6 +241,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   __shared__ __align__(8) uint64_t plane_full[PLANE_STAGES];
   __shared__ __align__(8) uint64_t plane_empty[PLANE_STAGES];
   __shared__ __align__(8) uint64_t acc_full;
+  __shared__ __align__(8) uint64_t acc_empty;
   __shared__ uint32_t tmem_slot;
 #ifdef GB_PHASE_TIMES  // instrumented build (-DGB_PHASE_TIMES): CTA 0 prints its phase durations
   __shared__ long long ph_t[12];
@@ -254,21 +260,31 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   const int raw_stages = p.dop ? 2 : 3;
   const int raw_stage_bytes = p.dop ? 3 * RAW_TILE : 2 * RAW_TILE;
 
-  int tile = blockIdx.x;
-  const int m_tile = tile % p.tiles_m;
-  tile /= p.tiles_m;
-  const int n_tile = tile % p.tiles_n;
-  tile /= p.tiles_n;
-  const int batch = tile % p.batches;
-  const int split = tile / p.batches;
-  const int m0 = m_tile * SBM, n0 = n_tile * p.bn;
-
+  // A CTA works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...: the barriers, the raw and
+  // plane rings and the tensor-memory allocation are set up once, the producer runs ahead into
+  // the next tile's slices while this tile's accumulator is written out (one prologue and one
+  // first round trip to memory per CTA instead of per tile: 6-7 of the ~17 thousand cycles a
+  // two-k-block tile costs).
   int nkb_total = 0;
   for (int i = 0; i < p.npairs; ++i) nkb_total += (p.k[i] + SBK - 1) / SBK;
-  // k-blocks [kb_begin, kb_begin + nkb) belong to this CTA (single pair when split)
-  const int kb_begin = static_cast<int>(static_cast<long long>(nkb_total) * split / p.split_k);
-  const int nkb =
-      static_cast<int>(static_cast<long long>(nkb_total) * (split + 1) / p.split_k) - kb_begin;
+  struct Tile {
+    int m0, n0, n_tile, batch, split, kb_begin, nkb;
+  };
+  auto decode = [&](int tile) {
+    Tile t;
+    const int m_tile = tile % p.tiles_m;
+    tile /= p.tiles_m;
+    t.n_tile = tile % p.tiles_n;
+    tile /= p.tiles_n;
+    t.batch = tile % p.batches;
+    t.split = tile / p.batches;
+    t.m0 = m_tile * SBM;
+    t.n0 = t.n_tile * p.bn;
+    // k-blocks [kb_begin, kb_begin + nkb) belong to this tile (single pair when split)
+    t.kb_begin = static_cast<int>(static_cast<long long>(nkb_total) * t.split / p.split_k);
+    t.nkb = static_cast<int>(static_cast<long long>(nkb_total) * (t.split + 1) / p.split_k) - t.kb_begin;
+    return t;
+  };
 
   if (warp == 0 && lane == 0) {
     for (int i = 0; i < p.npairs; ++i) {
@@ -288,6 +304,7 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
         mbar_init(smem_u32(&plane_empty[s]), 1);
       }
       mbar_init(smem_u32(&acc_full), 1);
+      mbar_init(smem_u32(&acc_empty), XFORM_THREADS);
       fence_mbar_init();
     }
     __syncwarp();
@@ -310,9 +327,16 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     if (elect_one()) {
       int s = 0;
       uint32_t ph = 0;
-      int pair = 0, k0 = kb_begin * SBK;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      const Tile tl = decode(tile);
+      const int m0 = tl.m0, n0 = tl.n0, batch = tl.batch, nkb = tl.nkb;
+      int pair = 0, k0 = tl.kb_begin * SBK;
       for (int it = 0; it < nkb; ++it) {
-        if (!mbar_wait(smem_u32(&raw_empty[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) break;
+        if (!mbar_wait(smem_u32(&raw_empty[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) {
+          ok = false;
+          break;
+        }
         const uint32_t bar = smem_u32(&raw_full[s]);
         const uint32_t dst = raws_base + s * raw_stage_bytes;
         // bytes of this stage: A (and a derivative partner of A) always 128 rows, B (and its
@@ -359,6 +383,8 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
           k0 = 0;
         }
       }
+      if (!PERSISTENT) break;
+      }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -367,8 +393,22 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       const uint32_t IDESC = make_idesc(2, 0, 0, SBM, static_cast<uint32_t>(p.bn));
       int s = 0;
       uint32_t ph = 0;
+      bool ok = true;
+      int local = 0;  // tiles this CTA has started
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++local) {
+      const int nkb = decode(tile).nkb;
+      // the epilogue of the previous tile has read the accumulators
+      if (PERSISTENT && local > 0 &&
+          !mbar_wait(smem_u32(&acc_empty), (local - 1) & 1u, status, DEV_TIMEOUT_TMEM_FREE, local)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
       for (int it = 0; it < nkb; ++it) {
-        if (!mbar_wait(smem_u32(&plane_full[s]), ph, status, DEV_TIMEOUT_FULL, it)) break;
+        if (!mbar_wait(smem_u32(&plane_full[s]), ph, status, DEV_TIMEOUT_FULL, it)) {
+          ok = false;
+          break;
+        }
         if (it == 0) PH(4);
         tc_fence_after();
         const uint32_t a_hi = planes_base + s * PLANE_STAGE;
@@ -393,8 +433,10 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
           ph ^= 1u;
         }
       }
-      tc_commit(smem_u32(&acc_full));
+      if (ok) tc_commit(smem_u32(&acc_full));
       PH(5);
+      if (!PERSISTENT) break;
+      }
     }
     __syncwarp();
   } else {
@@ -402,12 +444,16 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     const int xt = threadIdx.x - 64;
     const int grp = xt >> 8;  // 0 = A operand, 1 = B operand
     const int t = xt & 255;
-    const bool want_rowsum = grp == 0 && p.rowsum != nullptr && n_tile == 0;
-    float rs = 0.f;
     bool ok = true;
     int rs_i = 0, ps_i = 0;
     uint32_t rph = 0, pph = 0;
-    int pair = 0, k0 = kb_begin * SBK;
+    int local = 0;  // tiles this CTA has started
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++local) {
+    const Tile tl = decode(tile);
+    const int m0 = tl.m0, n0 = tl.n0, batch = tl.batch, split = tl.split, nkb = tl.nkb;
+    const bool want_rowsum = grp == 0 && p.rowsum != nullptr && tl.n_tile == 0;
+    float rs = 0.f;
+    int pair = 0, k0 = tl.kb_begin * SBK;
     for (int it = 0; it < nkb; ++it) {
       if (!mbar_wait(smem_u32(&raw_full[rs_i]), rph, status, DEV_TIMEOUT_FULL, 0x100 + it) ||
           !mbar_wait(smem_u32(&plane_empty[ps_i]), pph ^ 1u, status, DEV_TIMEOUT_EMPTY,
@@ -463,7 +509,8 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     const bool row_ok = row < p.M;
     // fetched before the wait for the accumulator, so that its latency hides behind the MMAs
     const float bias = (p.bias != nullptr && row_ok && split == 0) ? p.bias[row] : 0.f;  // once per tile
-    const bool epi_ok = ok && mbar_wait(smem_u32(&acc_full), 0, status, DEV_TIMEOUT_ACCUM, 0);
+    const bool epi_ok =
+        ok && mbar_wait(smem_u32(&acc_full), local & 1u, status, DEV_TIMEOUT_ACCUM, local);
     if (threadIdx.x == 64) PH(6);
     float* crow = p.C + static_cast<long long>(batch) * p.strideC + row * p.c_rs;
     const int c0 = cgrp * 32;
@@ -494,6 +541,11 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
       }
     }
     if (threadIdx.x == 64) PH(7);
+    if (!PERSISTENT || !epi_ok) break;
+    // this thread has read its part of the accumulators: the next tile's MMAs may overwrite them
+    tc_fence_before();
+    mbar_arrive(smem_u32(&acc_empty));
+    }
   }
 
   tc_fence_before();
@@ -942,6 +994,19 @@ bool encode_operand(CUtensorMap* out, const void* ptr, const Operand& o, long lo
 
 }  // namespace
 
+// SM count of the current device (queried once per device).
+static int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  int n = __atomic_load_n(&cached[dev], __ATOMIC_RELAXED);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    __atomic_store_n(&cached[dev], n, __ATOMIC_RELAXED);
+  }
+  return n;
+}
+
 bool sgemm3x_supported(const Problem& p) {
   if (p.npairs < 1 || p.ccols != nullptr || !tmap_encoder_available()) return false;
   int nderiv = 0;
@@ -1031,11 +1096,23 @@ cudaError_t launch_sgemm3x(const Problem& p_in, cudaStream_t stream, int* status
   const long long total = static_cast<long long>(sp.tiles_m) * sp.tiles_n * p.batches * sp.split_k;
   if (total <= 0) return cudaSuccess;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
+  sp.total_tiles = static_cast<int>(total);
   const int smem = PLANE_STAGES * PLANE_STAGE + RAW_BYTES_TOTAL + 1024;
-  static unsigned long long smem_set = 0;  // per template instantiation: per kernel
-  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(sgemm3x_tma_kernel), smem, &smem_set);
+  // Tiles with few k-blocks (the batched products of attention: two to eight) are walked by one
+  // CTA per SM, which saves the per-CTA prologue and first round trip to memory (256 x
+  // (256 x 64 x 256): 57 -> 46 us).  Long tiles gain nothing from that and lose the hardware's
+  // dynamic placement of CTAs (4096^3: 3-5 % slower), so they keep one CTA per tile.
+  long long nkb_tile = 0;
+  for (int i = 0; i < p.npairs; ++i) nkb_tile += (p.k[i] + SBK - 1) / SBK;
+  nkb_tile = (nkb_tile + sp.split_k - 1) / sp.split_k;
+  int sms = device_sm_count() - sm_margin();
+  if (sms < 1) sms = 1;
+  const bool walk = nkb_tile <= 16 && total > sms;
+  static unsigned long long smem_set[2] = {0, 0};  // per kernel
+  auto kern = walk ? sgemm3x_tma_kernel<true> : sgemm3x_tma_kernel<false>;
+  cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(kern), smem, &smem_set[walk ? 1 : 0]);
   if (e != cudaSuccess) return e;
-  e = launch_kernel(sgemm3x_tma_kernel, dim3(static_cast<unsigned>(total)), dim3(NTHREADS), smem,
+  e = launch_kernel(kern, dim3(static_cast<unsigned>(walk ? sms : total)), dim3(NTHREADS), smem,
                     stream, pdl_enabled(), sp, status);
   if (e != cudaSuccess || sp.split_k == 1 || p.act == ACT_NONE) return e;
   // an activated product is never run transposed, so (p.M, p.N) are the caller's here
