@@ -806,7 +806,21 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
     }
     int status = GINN_B200_OK;
     if (dbias != nullptr) {
-      cudaError_t e = gb::launch_rowsum(dtype, dA, nullptr, gb::ACT_NONE, ldA, (int)m, n, dbias, stream);
+      // large aligned matrices: fp32 partial sums in a stream-ordered allocation, then one pass
+      // (atomics from many blocks onto the few lines of the bias gradient serialise)
+      const int parts = gb::rowsum_ws_parts((int)m, n);
+      cudaError_t e = cudaErrorInvalidValue;
+      if (parts > 0 && ldA % 8 == 0 && aligned16(dA)) {
+        void* rws = nullptr;
+        e = cudaMallocAsync(&rws, static_cast<size_t>(parts) * m * 4, stream);
+        if (e == cudaSuccess) {
+          e = gb::launch_rowsum_half_ws(dA, ldA, (int)m, n, dbias, static_cast<float*>(rws), stream);
+          cudaFreeAsync(rws, stream);
+          g_launches.fetch_add(1);
+        }
+      } else {
+        e = gb::launch_rowsum(dtype, dA, nullptr, gb::ACT_NONE, ldA, (int)m, n, dbias, stream);
+      }
       if (e != cudaSuccess) status = fail(GINN_B200_CUDA_ERROR, "bias gradient: %s", cudaGetErrorString(e));
       g_launches.fetch_add(1);
     }

@@ -179,6 +179,11 @@ cudaError_t launch_act_inplace_f32(float* c, long long ldc, long long stride, in
 cudaError_t launch_bias_act_half(void* y, long long ldy, const void* bias, int act, int m,
                                  long long n, cudaStream_t stream);
 // da (m x n, leading dimension m) = dy (.) act'(y), fp16, n <= 65535.
+// fp16 bias gradient without atomics (small.cu): `ws` holds rowsum_ws_parts(M, N) vectors of M
+// floats; 0 parts = the shape does not qualify.
+int rowsum_ws_parts(int M, long long N);
+cudaError_t launch_rowsum_half_ws(const void* dy, long long ld, int M, long long N, void* rowsum,
+                                  float* ws, cudaStream_t stream);
 // c (m x n, ld ldc) += the sum of `parts` dense m x n fp16 matrices stored back to back at ws.
 cudaError_t launch_add_partials_half(void* c, long long ldc, const void* ws, int parts, int m,
                                      long long n, cudaStream_t stream);

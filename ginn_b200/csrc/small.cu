@@ -810,10 +810,14 @@ __global__ void rowsum_kernel(const T* __restrict__ dy, const T* __restrict__ y,
 // share the block's range of columns; the slices meet in shared memory, the blocks in an atomic
 // add.  (The scalar kernel above reads 64 bytes per warp and load: 160 GB/s on a 1024 x 4096 Half
 // matrix, 49 us of a 110 us layer step.)  Requires ld, M multiples of V and 16-byte aligned bases.
+// With `partials` set the block writes its fp32 sums to partials[blockIdx.y][row] instead of
+// adding them to `rowsum`: atomics from many blocks onto the few cache lines of a short vector
+// serialise (16 k fp16 atomics onto the 16 lines of a 1024-row bias gradient took 20 us; the sums
+// themselves take 3), so large fp16 bias gradients are finished by rowsum_finish_kernel.
 template <typename T>
 __global__ void __launch_bounds__(256)
 rowsum_vec_kernel(const T* __restrict__ dy, const T* __restrict__ y, int dact, long long ld, int M,
-                  long long N, T* __restrict__ rowsum) {
+                  long long N, T* __restrict__ rowsum, float* __restrict__ partials) {
   constexpr int V = 16 / sizeof(T);
   __shared__ float part[16][16 * V + 1];
   pdl_wait();
@@ -852,8 +856,24 @@ rowsum_vec_kernel(const T* __restrict__ dy, const T* __restrict__ y, int dact, l
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < 16; ++j) sum += part[j][r];
-    atomic_add_t(rowsum + grow, sum);
+    if (partials != nullptr)
+      partials[static_cast<long long>(blockIdx.y) * M + grow] = sum;
+    else
+      atomic_add_t(rowsum + grow, sum);
   }
+}
+
+// rowsum[row] += sum over `parts` fp32 partial vectors of length M stored back to back.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rowsum_finish_kernel(const float* __restrict__ partials, int parts, int M, T* __restrict__ rowsum) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float sum = 0.f;
+  for (int q = 0; q < parts; ++q) sum += partials[static_cast<long long>(q) * M + row];
+  rowsum[row] = from_f<T>(to_f(rowsum[row]) + sum);
 }
 
 // Self test of the bounded-wait machinery: one thread waits on an mbarrier on which nothing ever
@@ -1011,6 +1031,30 @@ cudaError_t launch_skinny(int dtype, int kind, const Problem& p, cudaStream_t st
   return cudaGetLastError();
 }
 
+// fp16 bias gradient of an aligned matrix in two launches and no atomics: fp32 partial sums of
+// `rowsum_ws_parts(M, N)` column chunks into `ws` (that many vectors of M floats), then one pass
+// that adds their sum to rowsum.  Returns cudaErrorInvalidValue when the shape does not qualify
+// (the caller then uses launch_rowsum).
+int rowsum_ws_parts(int M, long long N) {
+  if (M % 8 != 0 || N < 1024) return 0;
+  long long chunks = N / 64;
+  return static_cast<int>(chunks > 64 ? 64 : chunks);
+}
+cudaError_t launch_rowsum_half_ws(const void* dy, long long ld, int M, long long N, void* rowsum,
+                                  float* ws, cudaStream_t stream) {
+  const int parts = rowsum_ws_parts(M, N);
+  auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  if (parts == 0 || ld % 8 != 0 || !al(dy)) return cudaErrorInvalidValue;
+  dim3 grid((M + 127) / 128, static_cast<unsigned>(parts)), block(16, 16);
+  cudaError_t e = launch_kernel(rowsum_vec_kernel<__half>, grid, block, 0, stream, pdl_enabled(),
+                                static_cast<const __half*>(dy), static_cast<const __half*>(nullptr),
+                                static_cast<int>(ACT_NONE), ld, M, N, static_cast<__half*>(rowsum), ws);
+  if (e != cudaSuccess) return e;
+  return launch_kernel(rowsum_finish_kernel<__half>, dim3((M + 255) / 256), dim3(256), 0, stream,
+                       pdl_enabled(), static_cast<const float*>(ws), parts, M,
+                       static_cast<__half*>(rowsum));
+}
+
 cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, long long ld, int M,
                           long long N, void* rowsum, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return cudaSuccess;
@@ -1028,10 +1072,10 @@ cudaError_t launch_rowsum(int dtype, const void* dy, const void* y, int dact, lo
       if (dtype == 0)
         return launch_kernel(rowsum_vec_kernel<float>, vgrid, vblock, 0, stream, pdl_enabled(),
                              static_cast<const float*>(dy), static_cast<const float*>(y), dact, ld,
-                             M, N, static_cast<float*>(rowsum));
+                             M, N, static_cast<float*>(rowsum), static_cast<float*>(nullptr));
       return launch_kernel(rowsum_vec_kernel<__half>, vgrid, vblock, 0, stream, pdl_enabled(),
                            static_cast<const __half*>(dy), static_cast<const __half*>(y), dact, ld, M,
-                           N, static_cast<__half*>(rowsum));
+                           N, static_cast<__half*>(rowsum), static_cast<float*>(nullptr));
     }
   }
   dim3 block(32, 8);
