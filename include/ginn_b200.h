@@ -91,7 +91,10 @@ typedef struct {
  * fp32: dA is formed on the fly inside the operand loaders (no dpreactiv_ tensor is written).
  * fp16 with m * n >= 65536: dA is materialised once in a stream-ordered scratch allocation of the
  * library's own (cudaMallocAsync / cudaFreeAsync on `stream`), as the reference materialises
- * dpreactiv_, so that both products run on the TMA-fed kernels.
+ * dpreactiv_, so that both products run on the TMA-fed kernels.  Large layers also take two small
+ * stream-ordered buffers from the same pool: fp32 partial sums of the bias gradient (at most
+ * 64 * m floats) and, when a weight gradient has few output tiles and n >= 1024, fp16 partial
+ * products of its column chunks (at most 8 * m * k elements), which one pass adds to da.
  * Replaces the GPU branch of AffineNode::backward_ (ginn/node/affine.h:79-87,103-125).
  * `out` is the node's value (needed for tanh/sigmoid/relu derivatives; may be NULL for
  * ACT_NONE); dbias may be NULL. */
@@ -102,8 +105,10 @@ int ginn_b200_affine_backward(int device, void* stream, int dtype, int npairs,
 
 /* The same with the scratch tensor supplied by the caller: `scratch` holds m * n elements of
  * `dtype` (16-byte aligned, leading dimension m) and is what AffineNode keeps as dpreactiv_
- * (ginn/node/affine.h:82-88), so a node that passes its own tensor makes the call allocation-free
- * and keeps its device's accounting (PreallocGpuDevice::used()) exactly as the reference has it.
+ * (ginn/node/affine.h:82-88), so a node that passes its own tensor keeps dA out of the library's
+ * pool and its device's accounting (PreallocGpuDevice::used()) exactly as the reference has it;
+ * the two small partial-sum buffers described above still come from the stream-ordered pool
+ * (which hands the same blocks back call after call: the device's free memory does not move).
  * Only large Half Affines with a nonlinearity write it; NULL = as ginn_b200_affine_backward. */
 int ginn_b200_affine_backward_scratch(int device, void* stream, int dtype, int npairs,
                                       const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,

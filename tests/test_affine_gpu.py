@@ -188,9 +188,9 @@ def test_half_layers_on_the_tma_kernels(gpu, act):
 
 def test_half_backward_with_the_nodes_own_scratch(gpu):
     """A large Half Affine with a nonlinearity materialises dY (.) f'(Y) once.  Given the node's
-    own d-pre-activation tensor (as AffineNode owns dpreactiv_, ginn/node/affine.h:82) the call
-    allocates nothing: same gradients as with the library's stream-ordered scratch, and the
-    device's free memory does not move."""
+    own d-pre-activation tensor (as AffineNode owns dpreactiv_, ginn/node/affine.h:82) dA stays
+    out of the library's pool: same gradients as with the library's stream-ordered scratch, and
+    the device's free memory does not move once the pool holds the small partial-sum buffers."""
     rng = np.random.default_rng(55)
     m, n, k = 512, 256, 384
     dt = np.float16
