@@ -578,8 +578,9 @@ def run_cpp_autobatch() -> dict:
         out = json.loads(line)
         out["what"] = ("C++ BatchedGraph on per-node tensors: rewrite_ms = Autobatch(g); "
                        "first_pass = forward + reset_grad + backward with the one-time level "
-                       "preparation; replay = the same pass on the prepared schedule; host clock "
-                       "around device synchronisation")
+                       "preparation; replay = the same pass on the prepared schedule, launch by "
+                       "launch; graph = the pass replayed from a CUDA graph "
+                       "(BatchedGraph::capture_pass); host clock around device synchronisation")
         return out
     except Exception as e:  # the headline does not depend on it
         return {"error": f"{type(e).__name__}: {e}"[:300]}
