@@ -90,8 +90,11 @@ class BatchedGraph {
     ginn_b200_level* cells_bwd = nullptr;
     bool fwd_ready = false, bwd_ready = false, sized = false;
     cudaEvent_t ready = nullptr;  // the level's output gradients are final (run_backward)
-    // Storage the level's batched nodes are moved into (see rehome()).
+    // Storage the level's batched nodes are moved into (see place()), and the tensors that alias
+    // it: they are detached again (left empty) when the BatchedGraph goes, since the storage goes
+    // with it -- copy out what should outlive the BatchedGraph.
     std::vector<std::unique_ptr<Tensor<Real>>> slabs;
+    std::vector<Tensor<Real>*> placed;
   };
 
   std::vector<BaseNodePtr> list_;
@@ -215,6 +218,7 @@ class BatchedGraph {
     Size off = static_cast<Size>(((16 - (reinterpret_cast<uintptr_t>(slab.data()) & 15u)) & 15u) / sizeof(Real));
     for (auto* t : ts) {
       t->map(slab, shapes[0], off);
+      lv.placed.push_back(t);
       off += n;
     }
   }
@@ -552,6 +556,10 @@ class BatchedGraph {
       cudaEventDestroy(join_);
       side_ = nullptr;
       join_ = nullptr;
+    }
+    for (auto& lv : levels_) {  // the nodes outlive this object: end their aliases of its storage
+      for (auto* t : lv.placed) t->unmap();
+      lv.placed.clear();
     }
     if (hoisted_.ready) cudaEventDestroy(hoisted_.ready);
     hoisted_.ready = nullptr;

@@ -106,6 +106,14 @@ class Tensor {
     return *this;
   }
   Tensor& map(Tensor& other) { return map(other, other.shape_); }
+  // Ends an alias: the tensor becomes an empty one that owns (nothing) again and can be resized.
+  // No effect on a tensor that owns its memory.
+  void unmap() {
+    if (owns_) return;
+    data_ = nullptr;
+    shape_ = {0};
+    owns_ = true;
+  }
   Tensor reshaped(const Shape& s) {
     GINN_ASSERT(size(s) == size());
     Tensor t(dev_);

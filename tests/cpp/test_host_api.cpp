@@ -331,6 +331,53 @@ static void test_autobatch_nonlinear_and_cells() {
     }
     check_autobatch(identity_sum(finals, H), ins, nodes);
   }
+  {  // the same net on inputs without gradients: their products W_x x_t are hoisted out of the
+     // levels (one launch ahead of them, one weight-gradient launch after), the levels' tensors
+     // lie back to back, and the whole pass is replayed from a CUDA graph with new input data
+    const Size H = 8, E = 4;
+    auto Wx = Random<Real>(gpu(), {4 * H, E}, 250), Wh = Random<Real>(gpu(), {4 * H, H}, 251);
+    auto b = Random<Real>(gpu(), {4 * H}, 252);
+    std::vector<NodePtr<Real>> ins{Wx, Wh, b}, finals, xs;
+    const int lens[4] = {2, 5, 3, 5};
+    size_t nodes = 0;
+    for (int q = 0; q < 4; ++q) {
+      NodePtr<Real> h = Random<Real>(gpu(), {H}, 260 + q);
+      ins.push_back(h);
+      Ptr<LstmCellNode> cell;
+      for (int t = 0; t < lens[q]; ++t) {
+        auto xt = Random<Real>(gpu(), {E}, 270 + 10 * q + t);
+        xt->set_has_grad(false);
+        xs.push_back(xt);
+        NodePtr<Real> gates = Affine(Wx, xt, Wh, h, b);
+        cell = LstmCell(gates, cell);
+        h = cell;
+        nodes += 2;
+      }
+      finals.push_back(h);
+    }
+    auto sink = identity_sum(finals, H);
+    check_autobatch(sink, ins, nodes);
+    // replayed pass: new inputs, Graph as the reference
+    for (size_t i = 0; i < xs.size(); ++i) {
+      auto v = xs[i]->value().vector();
+      for (auto& e : v) e = 0.5f * e - 0.1f;
+      xs[i]->value().set(v);
+    }
+    Graph g(sink);
+    auto bg = Autobatch(g);
+    bg.capture_pass(1.);
+    bg.replay_pass();
+    GINN_CUDA_CALL(cudaDeviceSynchronize());
+    auto value = sink->value().vector();
+    std::vector<std::vector<Real>> grads;
+    for (auto& in : ins) grads.push_back(in->grad().vector());
+    CHECK(bg.launches() < 5 * 5 + 4 * 5 + 6);  // one forward launch per level, not two
+    Graph g2(sink);  // the nodes' tensors stay where Autobatch put them; Graph runs node by node
+    g2.reset_forwarded().forward();
+    CHECK(close(sink->value().vector(), value, 1e-4f, 1e-5f));
+    g2.reset_grad().backward(1.);
+    for (size_t i = 0; i < ins.size(); ++i) CHECK(close(ins[i]->grad().vector(), grads[i], 1e-4f, 1e-5f));
+  }
 }
 
 // test/convnodes.cu.cpp:38-70 ("Conv2d"): known values with and without strides, then both
