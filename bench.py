@@ -553,8 +553,11 @@ def run_mlp_dp(D: Dist, steps: int, warmup: int) -> dict:
     from ginn_b200 import workloads as wl
     w = wl.MlpDataParallel(D.dev, D.rank, D.world,
                            allreduce=D.allreduce_async if D.world > 1 else None)
-    ms = time_steps(D, w.step, steps, max(warmup, 3))
-    out = {"ms_per_step": ms, "tflops": D.world * w.flops / (ms * 1e-3) / 1e12,
+    # the first all-reduces of a new size still set NCCL channels up: at least ten untimed steps
+    # when ranks communicate (0.55 ms measured after three, 0.46-0.50 after ten, at N = 2)
+    warm = max(warmup, 10 if D.world > 1 else 3)
+    ms = time_steps(D, w.step, max(steps, 30) if D.world > 1 else steps, warm)
+    out = {"ms_per_step": ms, "warmup": warm, "tflops": D.world * w.flops / (ms * 1e-3) / 1e12,
            "flops_per_step_per_gpu": w.flops, "loss": float(w.loss)}
     if D.world > 1:
         import torch.distributed as dist
