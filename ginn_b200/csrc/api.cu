@@ -31,6 +31,8 @@ thread_local int t_pdl = 1;           // programmatic dependent launch for the k
 bool gb::pdl_enabled() { return t_pdl != 0; }
 int gb::max_split() { return t_max_split; }
 int gb::sm_margin() { return t_sm_margin; }
+thread_local int t_walk_kblocks = 16;  // fp32: CTAs walk the tiles of products with at most this many k-blocks per tile
+int gb::walk_kblocks() { return t_walk_kblocks; }
 namespace {
 
 int fail(int status, const char* fmt, ...) {
@@ -1603,6 +1605,11 @@ int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "max_split") == 0) {
     if (value < 0 || value > 32) return fail(GINN_B200_BAD_ARGUMENT, "max_split must be 0..32");
     t_max_split = value;
+    return GINN_B200_OK;
+  }
+  if (name && std::strcmp(name, "walk_kblocks") == 0) {
+    if (value < 0 || value > 4096) return fail(GINN_B200_BAD_ARGUMENT, "walk_kblocks must be 0..4096");
+    t_walk_kblocks = value;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "pdl") == 0) {

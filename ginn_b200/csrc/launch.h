@@ -16,6 +16,9 @@ bool pdl_enabled();
 int max_split();
 // SMs the persistent kernels leave free (option "sm_margin" of the calling thread).
 int sm_margin();
+// fp32 TMA kernel: products whose tiles have at most this many k-blocks (and outnumber the SMs)
+// run with one CTA per SM walking the tiles (option "walk_kblocks"; 0 = never).
+int walk_kblocks();
 
 // Launch with the programmatic-stream-serialization attribute when `pdl` is set: the kernel may
 // begin while its predecessor in the stream drains; it must call pdl_wait() before it touches

@@ -1107,7 +1107,7 @@ cudaError_t launch_sgemm3x(const Problem& p_in, cudaStream_t stream, int* status
   nkb_tile = (nkb_tile + sp.split_k - 1) / sp.split_k;
   int sms = device_sm_count() - sm_margin();
   if (sms < 1) sms = 1;
-  const bool walk = nkb_tile <= 16 && total > sms;
+  const bool walk = nkb_tile <= walk_kblocks() && total > sms;
   static unsigned long long smem_set[2] = {0, 0};  // per kernel
   auto kern = walk ? sgemm3x_tma_kernel<true> : sgemm3x_tma_kernel<false>;
   cudaError_t e = set_smem_limit_once(reinterpret_cast<const void*>(kern), smem, &smem_set[walk ? 1 : 0]);

@@ -370,14 +370,17 @@ int ginn_b200_version(void);   /* 200: ginn_b200_group gained `act` and `out_col
  * "force_path": 0 = automatic, 2 = one-CTA TMA fp16 kernel, 4 = CTA-pair fp16 kernel (both fall
  * back to automatic when not applicable), 3 = CUDA-core kernel, 5 = cp.async gather kernels
  * (the fallbacks for operands a tensor map cannot describe).
- * "sm_margin": number of SMs the persistent fp16 kernels leave unoccupied (default 0), so that a
+ * "sm_margin": number of SMs the persistent kernels (fp16, and fp32 products whose CTAs walk
+ * their tiles) leave unoccupied (default 0), so that a
  * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles; set
  * it around the one product that overlaps the collective and back to 0 afterwards.
  * "pair_group_m": m-tiles per rasterisation group of the CTA-pair kernel (0 = default).
- * "max_split": cap on the number of CTAs an fp32 product's contraction is split over
- * (0 = the library's choice, 1 = never split).
- * "pdl": 1 (default) launches the fp32 tensor-core kernels and the LSTM cell kernels with
- * programmatic dependent launch, so that a kernel's set-up overlaps the end of the kernel before
+ * "max_split": cap on the number of CTAs an fp32 product's contraction is split over, and on the
+ * column chunks of a large fp16 weight gradient (0 = the library's choice, 1 = never split).
+ * "walk_kblocks": fp32 products whose tiles have at most this many 32-deep k-blocks (and
+ * outnumber the SMs) run with one CTA per SM walking the tiles (default 16; 0 = one CTA per tile).
+ * "pdl": 1 (default) launches the tensor-core kernels (fp32, one-CTA fp16) and the small
+ * elementwise kernels around them with programmatic dependent launch, so that a kernel's set-up overlaps the end of the kernel before
  * it in the stream (chains of small dependent launches, e.g. autobatch levels); 0 turns it off.
  * Returns GINN_B200_UNSUPPORTED for unknown names. */
 int ginn_b200_set_option(const char* name, int value);
