@@ -262,6 +262,30 @@ def test_narrow_fp32_products(gpu):
         check(B.to_host(C), ref, np.float32, f"batched narrow acc{acc}")
 
 
+def test_short_contractions_with_more_tiles_than_sms(gpu):
+    """fp32 products whose tiles have few k-blocks and outnumber the SMs: one CTA per SM walks the
+    tiles (barriers and tensor memory set up once, accumulators handed back through a barrier).
+    Ragged edges, every layout, assigning and adding, a strided batch, and the same product with
+    the walk switched off."""
+    rng = np.random.default_rng(35)
+    for (m, n, k) in [(2000, 1500, 96), (1300, 2100, 40), (3000, 70, 200)]:
+        for ta, tb in TRANS:
+            run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, False)
+        run_gemm(gpu, rng, np.float32, m, n, k, False, False, True)
+    a, b = randn(rng, (200, 100, 40), np.float32), randn(rng, (100, 150, 40), np.float32)
+    c0 = randn(rng, (200, 150, 40), np.float32)
+    for acc in (False, True):
+        C = B.from_host(c0)
+        gpu.gemm_batched(B.from_host(a), B.from_host(b), C, accumulate=acc)
+        torch.cuda.synchronize()
+        check(B.to_host(C), orc.gemm_batched(a, b, c=c0, accumulate=acc), np.float32, f"batched walk acc{acc}")
+    gpu.set_option("walk_kblocks", 0)
+    try:
+        run_gemm(gpu, rng, np.float32, 2000, 1500, 96, False, False, True)
+    finally:
+        gpu.set_option("walk_kblocks", 16)
+
+
 def test_non_finite_inputs_stay_where_they_belong(gpu):
     """An infinity in A and a NaN in B (fp32): exactly the row and the column of C they feed are
     non-finite, everything else matches the oracle (the hi/lo split must not leak inf - inf or a
