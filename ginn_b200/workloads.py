@@ -87,7 +87,13 @@ class Attention:
         self.dO = cm(hs, T)
         z = lambda r, c: B.colmajor(r, c, torch.float32, device, batches=nb, fill=0.0)
         self.S, self.P, self.dP, self.dS = z(T, T), z(T, T), z(T, T), z(T, T)
-        self.O, self.dV, self.dQ, self.dK = z(hs, T), z(hs, T), z(hs, T), z(T, hs)
+        self.O = z(hs, T)
+        # the three gradients in one allocation (a PreallocGpu slab hands them out back to back):
+        # reset_grad is one fill
+        n = hs * T * nb
+        self.grads = torch.zeros(3 * n, device=device)
+        as3 = lambda off, r, c: torch.as_strided(self.grads, (r, c, nb), (1, r, r * c), off)
+        self.dV, self.dQ, self.dK = as3(0, hs, T), as3(n, hs, T), as3(2 * n, T, hs)
         self.flops = 6 * nb * 2 * T * hs * T
         self.units = nb
 
@@ -96,14 +102,13 @@ class Attention:
         if self.fused:
             # one kernel forward (scores stay on the SM; P is kept for the backward pass), then
             # the composed backward: four batched products and one softmax-backward pass
-            for t in (self.dV, self.dQ, self.dK):
-                t.zero_()
+            self.grads.zero_()
             gb.attention_forward(self.k, self.q, self.v, self.O, self.P)
             gb.attention_backward(self.k, self.q, self.v, self.P, self.dO, self.dS, self.dK, self.dQ,
                                   self.dV)
             return
-        for t in (self.dV, self.dQ, self.dK, self.dP):
-            t.zero_()
+        self.grads.zero_()
+        self.dP.zero_()
         gb.gemm_batched(self.k, self.q, self.S)
         gb.softmax_forward(self.S, self.P)  # SoftmaxOp::forward, ginn/nonlin.h:162-168
         gb.gemm_batched(self.v, self.P, self.O)
