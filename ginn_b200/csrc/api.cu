@@ -285,8 +285,7 @@ int check_common(int dtype, int64_t m, int64_t n, int64_t k) {
 
 // Half product on the TMA-fed kernels.  Returns -1 when launched, 0 when neither kernel takes
 // the problem (the caller goes on to the general path), or an error status.  `h.bias` / `h.act`
-// ask for the Affine epilogue on the result: fused by the one-CTA kernel, a pass after the pair
-// kernel.
+// ask for the Affine epilogue on the result; both kernels fuse it.
 // Measured on B200 (Half, us): the one-CTA TMA kernel beats the cp.async kernel on every
 // aligned shape tried, down to 512 x 128 x 784 (12 against 21), and the CTA-pair kernel until
 // the pairs have about two waves of 256 x 256 tiles (1024 x 4096 x 1024: 16.5 against 19.9;
@@ -306,10 +305,6 @@ static int half_tma_dispatch(DevCtx* ctx, const gb::HgemmArgs& h, cudaStream_t s
     CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), t_pair_group_m, counter, stream,
                                  ctx->d_status));
     g_launches.fetch_add(1);
-    if (h.bias != nullptr || h.act != GINN_B200_ACT_NONE) {
-      CU_TRY(gb::launch_bias_act_half(h.C, h.ldc, h.bias, h.act, h.M, h.N, stream));
-      g_launches.fetch_add(1);
-    }
     return -1;
   }
   if ((big || force == PATH_TMA) && gb::hgemm_tma_supported(h)) {
@@ -717,8 +712,7 @@ int ginn_b200_affine_forward(int device, void* stream_, int dtype, int npairs,
   p.act = act;
   p.accumulate = 0;
   // Half with every pair on the TMA kernels: one product per pair (the first assigns, the others
-  // accumulate) and the bias and activation in the epilogue of the last one -- fused by the
-  // one-CTA kernel, a pass after the pair kernel.
+  // accumulate) and the bias and activation in the epilogue of the last one.
   // 16 us for a 1024 x 1024 layer on 4096 columns against 29 us for the fused cp.async kernel.
   // The product is rounded to fp16 before the bias and the nonlinearity, as the reference's is.
   if (dtype == GINN_B200_F16 && t_force_path == PATH_AUTO && np > 0 && m > 16 && n > 16 &&

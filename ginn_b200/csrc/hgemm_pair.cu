@@ -17,6 +17,7 @@
 #include <cuda.h>
 #include <cstring>
 #include "ptx.cuh"
+#include "math.cuh"
 #include "launch.h"
 
 namespace gb {
@@ -47,6 +48,10 @@ struct PParams {
   int vec_c;
   int tiles_m, tiles_n, total_tiles;
   int group_m;  // m-tiles per rasterisation group (L2 reuse of the A rows across waves)
+  // Fused Affine epilogue: out = act(fp16(acc [+ C]) + bias[row]); bias may be null, act NONE.
+  const __half* bias;
+  int act;
+  int vec_bias;  // bias allows 16-byte loads
   // Work queue: tiles [0, #pairs) are taken statically, every further tile is claimed with an
   // atomic add on counter[0].  A pair that starts late -- because another kernel, e.g. an NCCL
   // collective, holds its SMs for a while -- then simply finds fewer tiles left instead of
@@ -236,6 +241,7 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
+    const bool fused = p.bias != nullptr || p.act != ACT_NONE;
     for (; ok; ++it) {
       const int t = announced_tile(it);
       if (t < 0) break;
@@ -290,6 +296,52 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const float4 x1 = *reinterpret_cast<const float4*>(stage + cl * PEPI_PITCH + rg * 8 + 4);
           float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
           __half* cp = cbase + static_cast<long long>(col) * p.ldc + row;
+          if (fused) {
+            // The reference rounds the product (and the sum with the previous pairs) to fp16,
+            // adds the bias and applies the nonlinearity to that: the same roundings here.
+            const bool vec = p.vec_c && row + 8 <= p.M;
+            if (p.accumulate) {
+              if (vec) {
+                const __half* o = reinterpret_cast<const __half*>(&cold[i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] += __half2float(o[e]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (row + e < p.M) x[e] += __half2float(cp[e]);
+              }
+            }
+            float b[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) b[e] = 0.f;
+            if (p.bias != nullptr) {
+              if (p.vec_bias && row + 8 <= p.M) {
+                const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + row);
+                const __half* bh = reinterpret_cast<const __half*>(&bv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b[e] = __half2float(bh[e]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (row + e < p.M) b[e] = __half2float(p.bias[row + e]);
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              x[e] = act_forward_half(p.act, __half2float(__float2half_rn(x[e])) + b[e]);
+            if (vec) {
+              uint4 out;
+              __half2* oh = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
+              *reinterpret_cast<uint4*>(cp) = out;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (row + e < p.M) cp[e] = __float2half_rn(x[e]);
+            }
+            continue;
+          }
           if (p.vec_c && row + 8 <= p.M) {
             if (p.accumulate) {
               const __half* o = reinterpret_cast<const __half*>(&cold[i]);
@@ -402,6 +454,10 @@ cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int*
   p.total_tiles = static_cast<int>(total);
   p.group_m = group_m > 0 ? group_m : 8;
   p.counter = counter;
+  if ((a.bias != nullptr || a.act != ACT_NONE) && a.batches != 1) return cudaErrorInvalidValue;
+  p.bias = static_cast<const __half*>(a.bias);
+  p.act = a.act;
+  p.vec_bias = (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0 ? 1 : 0;
   if (!a.transA && !a.transB) return launch_pair_variant<1, 0>(ta, tb, p, num_sms, stream, status);
   if (a.transA && !a.transB) return launch_pair_variant<0, 0>(ta, tb, p, num_sms, stream, status);
   return launch_pair_variant<1, 1>(ta, tb, p, num_sms, stream, status);

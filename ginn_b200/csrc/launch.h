@@ -63,7 +63,6 @@ struct HgemmArgs {
   int M, N, K, batches;
   int accumulate;
   // Affine epilogue out = act(fp16(product [+ C]) + bias[row]); batches must be 1 when set.
-  // The one-CTA kernel fuses it; callers of the pair kernel run a pass after it.
   const void* bias = nullptr;
   int act = 0;
 };

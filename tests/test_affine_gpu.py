@@ -186,6 +186,22 @@ def test_half_layers_on_the_tma_kernels(gpu, act):
     check(B.to_host(db), 2 * np.asarray(g["dbias"]), dt, "db")
 
 
+def test_half_layer_on_the_cta_pair_kernel(gpu):
+    """A Half Affine with at least a wave of 256 x 256 tiles runs on the CTA-pair kernel, which
+    applies bias and nonlinearity in its epilogue too (second pair accumulating onto the first)."""
+    rng = np.random.default_rng(67)
+    dt = np.float16
+    m, n, k1, k2 = 2048, 4864, 256, 128
+    W, X, b = randn(rng, (m, k1), dt, 0.05), randn(rng, (k1, n), dt), randn(rng, m, dt)
+    V, H = randn(rng, (m, k2), dt, 0.05), randn(rng, (k2, n), dt)
+    for act in (orc.ACT_TANH, orc.ACT_NONE):
+        Y = B.colmajor(m, n, torch.float16, fill=7.0)
+        gpu.affine_forward([gpu.Pair(B.from_host(W), B.from_host(X)), gpu.Pair(B.from_host(V), B.from_host(H))],
+                           B.from_host(b), act, Y)
+        torch.cuda.synchronize()
+        check(B.to_host(Y), orc.affine_forward([(W, X), (V, H)], b, act), dt, f"pair kernel act {act}")
+
+
 def test_half_backward_with_the_nodes_own_scratch(gpu):
     """A large Half Affine with a nonlinearity materialises dY (.) f'(Y) once.  Given the node's
     own d-pre-activation tensor (as AffineNode owns dpreactiv_, ginn/node/affine.h:82) dA stays
