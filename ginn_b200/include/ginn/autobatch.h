@@ -162,9 +162,11 @@ class BatchedGraph {
     // order, both the outputs and the recurrent inputs of every level are equally spaced
     // columns and the library runs the level as plain TMA-fed products instead of following
     // pointer tables.
+    std::vector<int> kind(N);
+    for (size_t i = 0; i < N; ++i) kind[i] = kind_of(list_[i].get());
     std::vector<int> reach(height);
     for (size_t i = N; i-- > 0;) {
-      if (kind_of(list_[i].get()) == BaseNode::kPlain) continue;
+      if (kind[i] == BaseNode::kPlain) continue;
       for (auto& in : list_[i]->ins())
         reach[in->pass_index] = std::max(reach[in->pass_index], reach[i]);
     }
@@ -174,7 +176,7 @@ class BatchedGraph {
     // keep their order in the graph
     std::vector<int> rank(N);
     for (size_t i = 0; i < N; ++i)
-      rank[i] = kind_of(list_[i].get()) == BaseNode::kPlain ? -1 : static_cast<int>(N) - reach[i];
+      rank[i] = kind[i] == BaseNode::kPlain ? -1 : static_cast<int>(N) - reach[i];
     std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
       if (height[a] != height[b]) return height[a] < height[b];
       return rank[a] < rank[b];
@@ -184,11 +186,11 @@ class BatchedGraph {
     for (size_t i : order) {
       BaseNode* n = list_[i].get();
       Level& lv = levels_[height[i]];
-      const int kind = kind_of(n);
-      if (n->dev()->kind() == GPU && !dev_) dev_ = n->dev();
-      if (kind == BaseNode::kProd || kind == BaseNode::kAffine) {
+      const int k = kind[i];
+      if (!dev_ && n->dev()->kind() == GPU) dev_ = n->dev();
+      if (k == BaseNode::kProd || k == BaseNode::kAffine) {
         add_items(n, lv);
-      } else if (kind == BaseNode::kLstmCell) {
+      } else if (k == BaseNode::kLstmCell) {
         lv.cells.push_back(static_cast<LstmCellNode*>(n));
       } else {
         lv.plain.push_back(n);
@@ -671,7 +673,9 @@ class BatchedGraph {
       GINN_AB_TIME(4);
       // gradients of a level's batched nodes: one allocation per kind, laid out like the values
       // (init_grad then finds them in place and allocates nothing for them)
+      std::vector<std::pair<char*, size_t>> slab_ranges;  // the gradient storage placed below
       for (auto& lv : levels_) {
+        const size_t first_slab = lv.slabs.size();
         std::vector<Tensor<Real>*> g, gh, gc;
         std::vector<Shape> gs, hs;
         for (auto* o : lv.outs)
@@ -688,6 +692,9 @@ class BatchedGraph {
         place(lv, g, gs);
         place(lv, gh, hs);
         place(lv, gc, hs);
+        for (size_t i = first_slab; i < lv.slabs.size(); ++i)
+          slab_ranges.emplace_back(reinterpret_cast<char*>(lv.slabs[i]->data()),
+                                   static_cast<size_t>(lv.slabs[i]->size()) * sizeof(Real));
       }
       for (auto& e : list_) e->init_grad();
       // (address, bytes, owner): ranges are merged only inside one preallocated device -- its
@@ -702,15 +709,17 @@ class BatchedGraph {
       std::vector<Range> r;
       bool all_gpu = true;
       auto add = [&](Tensor<Real>& t) {
-        if (t.size() == 0) return;
+        if (t.size() == 0 || t.is_mapped()) return;  // aliases: covered by what they alias
         Device* d = t.dev().get();
         r.push_back({reinterpret_cast<char*>(t.data()), t.size() * sizeof(Real),
                      d->precedence() > 0 ? d : nullptr});
       };
       for (auto& e : list_) {
         if (!e->has_grad()) continue;
-        auto n = dynamic_cast<Node<Real>*>(e.get());
-        if (!n || n->dev()->kind() != GPU) {
+        // the batched kinds are Node<Real>s by construction: no run-time cast needed for them
+        auto n = e->batch_kind() != BaseNode::kPlain ? static_cast<Node<Real>*>(e.get())
+                                                     : dynamic_cast<Node<Real>*>(e.get());
+        if (!n || n->value().dev()->kind() != GPU) {
           all_gpu = false;
           break;
         }
@@ -721,6 +730,7 @@ class BatchedGraph {
         for (auto& e : list_) e->reset_grad();
         return *this;
       }
+      for (auto& sr : slab_ranges) r.push_back({sr.first, sr.second, nullptr});
       std::sort(r.begin(), r.end());
       zero_ranges_.clear();
       Device* last_owner = nullptr;

@@ -56,8 +56,8 @@ class Tensor {
     return *this;
   }
 
-  DevPtr dev() const { return dev_; }
-  Shape shape() const { return shape_; }
+  const DevPtr& dev() const { return dev_; }  // (by reference: a copy is two atomic operations)
+  const Shape& shape() const { return shape_; }
   Scalar* data() { return data_; }
   const Scalar* data() const { return data_; }
 
@@ -76,8 +76,14 @@ class Tensor {
     return out;
   }
   Shape shape2() const { return reduce(shape_, 2); }
-  Size rows() const { return shape2()[0]; }
-  Size cols() const { return shape2()[1]; }
+  // (computed in place: the host side of an autobatched graph asks these tens of thousands of
+  // times per pass, and shape2() builds a vector)
+  Size rows() const { return shape_.empty() ? 1 : shape_[0]; }
+  Size cols() const {
+    Size n = 1;
+    for (size_t i = 1; i < shape_.size(); ++i) n *= shape_[i];
+    return n;
+  }
 
   // Reallocates only when the element count changes; GPU contents are then lost.
   void resize(const Shape& s) {
@@ -106,6 +112,7 @@ class Tensor {
     return *this;
   }
   Tensor& map(Tensor& other) { return map(other, other.shape_); }
+  bool is_mapped() const { return !owns_; }
   // Ends an alias: the tensor becomes an empty one that owns (nothing) again and can be resized.
   // No effect on a tensor that owns its memory.
   void unmap() {
