@@ -3,6 +3,8 @@ BatchedProd -> scale -> mask -> Softmax -> BatchedProd, examples/min-gpt.cu.cpp:
 one-kernel forward at several shapes with and without scale / causal mask / kept softmax output,
 the unfused sequence the library takes for other shapes, the composed backward, and the full
 config-3 size against the separate BatchedProd + Softmax calls."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -23,6 +25,8 @@ def make(rng, T, hs, nb, dt=np.float32):
                                       (192, 64, 2), (64, 32, 5), (36, 32, 2)])
 @pytest.mark.parametrize("scale,causal", [(1.0, False), (0.125, True)])
 def test_fused_forward(gpu, T, hs, nb, scale, causal):
+    if os.environ.get("GINN_B200_TEST_PATH", "0") != "0":
+        pytest.skip("the fused kernel serves the automatic path only; a forced path composes the pass")
     rng = np.random.default_rng(71)
     k, q, v = make(rng, T, hs, nb)
     kd, qd, vd = map(B.from_host, (k, q, v))
