@@ -27,6 +27,10 @@
 #define GINN_B200_HOST_AUTOBATCH_H
 
 #include <memory>
+#ifdef GINN_AUTOBATCH_TIMES
+#include <chrono>
+#include <cstdio>
+#endif
 #include <algorithm>
 #include <tuple>
 
@@ -37,7 +41,6 @@
 namespace ginn {
 
 #ifdef GINN_AUTOBATCH_TIMES  // host-time breakdown of the preparation (bench builds only)
-#include <chrono>
 struct AbTimes {
   double t[8] = {0};
   ~AbTimes() {
