@@ -973,6 +973,8 @@ def main():
                     help="kernel choice override passed to the library (0 = automatic)")
     ap.add_argument("--pair-group-m", type=int, default=0,
                     help="rasterisation group of the CTA-pair kernel (0 = library default)")
+    ap.add_argument("--pair-l2-hint", type=int, default=-1,
+                    help="L2 eviction hints of the CTA-pair kernel, 0..3 (-1 = library default)")
     ap.add_argument("--pdl", type=int, default=1,
                     help="0: launch without programmatic dependent launch (A/B aid)")
     args = ap.parse_args()
@@ -982,6 +984,9 @@ def main():
     if args.pair_group_m and args.impl != "reference":
         import ginn_b200
         ginn_b200.set_option("pair_group_m", args.pair_group_m)
+    if args.pair_l2_hint >= 0 and args.impl != "reference":
+        import ginn_b200
+        ginn_b200.set_option("pair_l2_hint", args.pair_l2_hint)
     if not args.pdl and args.impl != "reference":
         import ginn_b200
         ginn_b200.set_option("pdl", 0)

@@ -24,6 +24,7 @@ std::atomic<long long> g_launches{0};
 thread_local int t_force_path = 0;
 thread_local int t_sm_margin = 0;     // SMs the persistent kernels leave free (e.g. for NCCL)
 thread_local int t_pair_group_m = 0;  // rasterisation group of the CTA-pair kernel (0 = default)
+thread_local int t_pair_l2_hint = 3;  // L2 eviction hints of the CTA-pair kernel (bits, see PParams)
 thread_local int t_max_split = 0;     // cap on the K split of fp32 products (0 = none, 1 = no split)
 thread_local int t_pdl = 1;           // programmatic dependent launch for the kernels that support it
 
@@ -302,8 +303,8 @@ static int half_tma_dispatch(DevCtx* ctx, const gb::HgemmArgs& h, cudaStream_t s
       std::lock_guard<std::mutex> g(ctx->mu);
       counter = ctx->d_counters + 2 * (ctx->next_counter++ % kCounters);
     }
-    CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), t_pair_group_m, counter, stream,
-                                 ctx->d_status));
+    CU_TRY(gb::launch_hgemm_pair(h, persistent_sms(ctx), t_pair_group_m, t_pair_l2_hint, counter,
+                                 stream, ctx->d_status));
     g_launches.fetch_add(1);
     return -1;
   }
@@ -1594,6 +1595,11 @@ int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "pair_group_m") == 0) {
     if (value < 0 || value > 1024) return fail(GINN_B200_BAD_ARGUMENT, "pair_group_m must be 0..1024");
     t_pair_group_m = value;
+    return GINN_B200_OK;
+  }
+  if (name && std::strcmp(name, "pair_l2_hint") == 0) {
+    if (value < 0 || value > 3) return fail(GINN_B200_BAD_ARGUMENT, "pair_l2_hint must be 0..3");
+    t_pair_l2_hint = value;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "max_split") == 0) {

@@ -48,6 +48,10 @@ struct PParams {
   int vec_c;
   int tiles_m, tiles_n, total_tiles;
   int group_m;  // m-tiles per rasterisation group (L2 reuse of the A rows across waves)
+  // L2 eviction hints.  Bit 0: the A slices (re-read by every column of a rasterisation group)
+  // are loaded evict-last, the B slices (used by one wave) evict-first; bit 1: C is read and
+  // written with streaming accesses.
+  int l2_hint;
   // Fused Affine epilogue: out = act(fp16(acc [+ C]) + bias[row]); bias may be null, act NONE.
   const __half* bias;
   int act;
@@ -151,6 +155,7 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const uint64_t pol_a = make_l2_policy(true), pol_b = make_l2_policy(false);
       for (int i = 0; ok; ++i) {
         const int t = rank == 0 ? claim_tile(i) : announced_tile(i);
         if (t < 0) break;
@@ -169,17 +174,32 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int k0 = kb * PBK;
           // The even CTA announces the bytes of both CTAs for this stage.
           if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[s]), 2 * PSTAGE_BYTES);
-          if (A_MN) {
-            tma_load_3d_pair(a_s, &tmA, bar, m0, k0, batch);
-            tma_load_3d_pair(a_s + PATOM_BYTES, &tmA, bar, m0 + 64, k0, batch);
+          if (p.l2_hint & 1) {
+            if (A_MN) {
+              tma_load_3d_pair_hint(a_s, &tmA, bar, m0, k0, batch, pol_a);
+              tma_load_3d_pair_hint(a_s + PATOM_BYTES, &tmA, bar, m0 + 64, k0, batch, pol_a);
+            } else {
+              tma_load_3d_pair_hint(a_s, &tmA, bar, k0, m0, batch, pol_a);
+            }
+            if (B_MN) {
+              tma_load_3d_pair_hint(b_s, &tmB, bar, n0, k0, batch, pol_b);
+              tma_load_3d_pair_hint(b_s + PATOM_BYTES, &tmB, bar, n0 + 64, k0, batch, pol_b);
+            } else {
+              tma_load_3d_pair_hint(b_s, &tmB, bar, k0, n0, batch, pol_b);
+            }
           } else {
-            tma_load_3d_pair(a_s, &tmA, bar, k0, m0, batch);
-          }
-          if (B_MN) {
-            tma_load_3d_pair(b_s, &tmB, bar, n0, k0, batch);
-            tma_load_3d_pair(b_s + PATOM_BYTES, &tmB, bar, n0 + 64, k0, batch);
-          } else {
-            tma_load_3d_pair(b_s, &tmB, bar, k0, n0, batch);
+            if (A_MN) {
+              tma_load_3d_pair(a_s, &tmA, bar, m0, k0, batch);
+              tma_load_3d_pair(a_s + PATOM_BYTES, &tmA, bar, m0 + 64, k0, batch);
+            } else {
+              tma_load_3d_pair(a_s, &tmA, bar, k0, m0, batch);
+            }
+            if (B_MN) {
+              tma_load_3d_pair(b_s, &tmB, bar, n0, k0, batch);
+              tma_load_3d_pair(b_s + PATOM_BYTES, &tmB, bar, n0 + 64, k0, batch);
+            } else {
+              tma_load_3d_pair(b_s, &tmB, bar, k0, n0, batch);
+            }
           }
           if (++s == PSTAGES) {
             s = 0;
@@ -271,7 +291,10 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int col = n0 + c0 + (piece >> 2), row = row0 + (piece & 3) * 8;
             cold[i] = make_uint4(0, 0, 0, 0);
             if (col < p.N && row + 8 <= p.M)
-              cold[i] = *reinterpret_cast<const uint4*>(cbase + static_cast<long long>(col) * p.ldc + row);
+              {
+                const uint4* src = reinterpret_cast<const uint4*>(cbase + static_cast<long long>(col) * p.ldc + row);
+                cold[i] = (p.l2_hint & 2) ? __ldcs(src) : *src;
+              }
           }
         }
         uint32_t v[32];
@@ -334,7 +357,8 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               __half2* oh = reinterpret_cast<__half2*>(&out);
 #pragma unroll
               for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
-              *reinterpret_cast<uint4*>(cp) = out;
+              if (p.l2_hint & 2) __stcs(reinterpret_cast<uint4*>(cp), out);
+              else *reinterpret_cast<uint4*>(cp) = out;
             } else {
 #pragma unroll
               for (int e = 0; e < 8; ++e)
@@ -352,7 +376,8 @@ hgemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __half2* oh = reinterpret_cast<__half2*>(&out);
 #pragma unroll
             for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
-            *reinterpret_cast<uint4*>(cp) = out;
+            if (p.l2_hint & 2) __stcs(reinterpret_cast<uint4*>(cp), out);
+              else *reinterpret_cast<uint4*>(cp) = out;
           } else {
             for (int e = 0; e < 8 && row + e < p.M; ++e) {
               float y = x[e];
@@ -428,8 +453,8 @@ bool hgemm_pair_supported(const HgemmArgs& a) {
          (a.batches == 1 || a.strideC % 8 == 0);
 }
 
-cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int* counter,
-                              cudaStream_t stream, int* status) {
+cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int l2_hint,
+                              int* counter, cudaStream_t stream, int* status) {
   const unsigned long long a_rows = a.transA ? a.K : a.M, a_cols = a.transA ? a.M : a.K;
   const unsigned long long b_rows = a.transB ? a.N : a.K, b_cols = a.transB ? a.K : a.N;
   const unsigned long long sa = a.batches > 1 ? a.strideA : a.lda * a_cols;
@@ -452,6 +477,7 @@ cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int*
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batches;
   if (total > 0x7fffffffLL) return cudaErrorInvalidValue;
   p.total_tiles = static_cast<int>(total);
+  p.l2_hint = l2_hint & 3;
   p.group_m = group_m > 0 ? group_m : 8;
   p.counter = counter;
   if ((a.bias != nullptr || a.act != ACT_NONE) && a.batches != 1) return cudaErrorInvalidValue;

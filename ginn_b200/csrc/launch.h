@@ -74,9 +74,10 @@ cudaError_t launch_hgemm_tma(const HgemmArgs& a, int num_sms, cudaStream_t strea
 bool hgemm_pair_supported(const HgemmArgs& a);
 // `counter`: two ints of device memory for the launch's tile queue, zero when the kernel starts;
 // the kernel leaves them zero again.  Launches that may run at the same time need different
-// counters.  group_m: m-tiles per rasterisation group (0 = default).
-cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int* counter,
-                              cudaStream_t stream, int* status);
+// counters.  group_m: m-tiles per rasterisation group (0 = default).  l2_hint: bit 0 = eviction
+// policies on the operand loads, bit 1 = streaming accesses to C.
+cudaError_t launch_hgemm_pair(const HgemmArgs& a, int num_sms, int group_m, int l2_hint,
+                              int* counter, cudaStream_t stream, int* status);
 
 // --- general fp16 kernel with a cp.async front end (hgemm_gather.cu) ---
 bool hgemm_gather_supported(const Problem& p);

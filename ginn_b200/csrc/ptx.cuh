@@ -269,6 +269,26 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap,
       "r"(z)
       : "memory");
 }
+// The same load with an L2 eviction policy (from make_l2_policy).
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst, const void* tmap,
+                                                      uint32_t bar_cluster_addr, int x, int y,
+                                                      int z, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y),
+      "r"(z), "l"(policy)
+      : "memory");
+}
+// L2 eviction policies for whole operands: keep (evict last) or stream (evict first).
+__device__ __forceinline__ uint64_t make_l2_policy(bool keep) {
+  uint64_t pol;
+  if (keep)
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  else
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
                "r"(ncols)
