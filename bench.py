@@ -556,9 +556,20 @@ def run_mlp_dp(D: Dist, steps: int, warmup: int) -> dict:
     # the first all-reduces of a new size still set NCCL channels up: at least ten untimed steps
     # when ranks communicate (0.55 ms measured after three, 0.46-0.50 after ten, at N = 2)
     warm = max(warmup, 10 if D.world > 1 else 3)
+    for _ in range(3):
+        w.step()
+    torch.cuda.synchronize(D.dev)
+    # the kernel launches of a step replayed from two CUDA graphs (collectives and Adam stay
+    # ordinary calls), the same at every N: with eight processes on one host the launches
+    # otherwise take the host as long as the GPU
+    try:
+        w.capture()
+        launched = "two CUDA graphs per step (before / after the first all-reduce); NCCL and Adam called directly"
+    except Exception as e:
+        launched = f"call by call (graph capture failed: {type(e).__name__})"
     ms = time_steps(D, w.step, max(steps, 30) if D.world > 1 else steps, warm)
     out = {"ms_per_step": ms, "warmup": warm, "tflops": D.world * w.flops / (ms * 1e-3) / 1e12,
-           "flops_per_step_per_gpu": w.flops, "loss": float(w.loss)}
+           "flops_per_step_per_gpu": w.flops, "loss": float(w.loss), "launched": launched}
     if D.world > 1:
         import torch.distributed as dist
         ref = w.params.clone()

@@ -52,17 +52,20 @@ class AffineLayer:
         self.b = _xavier(m, 1, g, device).reshape(-1).contiguous().to(tdt)
         self.dY = torch.randn(n, m, device=device, generator=g).to(tdt).T
         self.Y = B.colmajor(m, n, tdt, device, fill=0.0)
-        self.dW, self.dX = B.colmajor(m, k, tdt, device, fill=0.0), B.colmajor(k, n, tdt, device, fill=0.0)
-        self.db = torch.zeros(m, device=device, dtype=tdt)
+        # dW | dX | db in one buffer (16-byte aligned pieces), so that reset_grad is one fill
+        pad = lambda c: (c + 7) // 8 * 8
+        o_x, o_b = pad(m * k), pad(m * k) + pad(k * n)
+        self.grads = torch.zeros(o_b + m, device=device, dtype=tdt)
+        self.dW = torch.as_strided(self.grads, (m, k), (1, m))
+        self.dX = torch.as_strided(self.grads, (k, n), (1, k), o_x)
+        self.db = self.grads[o_b:o_b + m]
         # the node's d-pre-activation tensor (ginn/node/affine.h:82): the Half path writes it
         self.dpre = B.colmajor(m, n, tdt, device, fill=0.0) if half else None
         self.flops = 3 * 2 * m * n * k
         self.units = 1
 
     def step(self):
-        self.dW.zero_()
-        self.dX.zero_()
-        self.db.zero_()
+        self.grads.zero_()
         B.affine_forward([B.Pair(self.W, self.X)], self.b, B.ACT_TANH, self.Y)
         B.affine_backward([B.PairGrad(self.W, self.X, self.dW, self.dX)], self.dY, self.Y,
                           B.ACT_TANH, self.db, self.dpre)
@@ -320,14 +323,17 @@ class LstmFlat:
         self.nodes = n = int(lens.sum())
         self.W = _xavier(4 * H, E + H, g, device)
         self.b = _xavier(4 * H, 1, g, device).reshape(-1).contiguous()
-        self.dW = B.colmajor(4 * H, E + H, torch.float32, device, fill=0.0)
-        self.db = torch.zeros(4 * H, device=device)
+        # all gradients in one buffer (dW | db | dXH), so that reset_grad is one fill
+        n_w, n_b = 4 * H * (E + H), 4 * H
+        self.grads = torch.zeros(n_w + n_b + (E + H) * n, device=device)
+        self.dW = torch.as_strided(self.grads[:n_w], (4 * H, E + H), (1, 4 * H))
+        self.db = self.grads[n_w:n_w + n_b]
         self.XH = B.colmajor(E + H, n, torch.float32, device)
         self.XH.copy_(torch.randn(E + H, n, device=device, generator=g))
         self.dG = B.colmajor(4 * H, n, torch.float32, device)
         self.dG.copy_(torch.randn(4 * H, n, device=device, generator=g))
         self.G = B.colmajor(4 * H, n, torch.float32, device, fill=0.0)
-        self.dXH = B.colmajor(E + H, n, torch.float32, device, fill=0.0)
+        self.dXH = torch.as_strided(self.grads[n_w + n_b:], (E + H, n), (1, E + H))
         cols = lambda m: [m[:, j] for j in range(m.shape[1])]
         x, y, dy, dx = cols(self.XH), cols(self.G), cols(self.dG), cols(self.dXH)
         self.fwd = B.GroupedCall(GROUPED_FORWARD, [B.Group(w=self.W, x_cols=x, y_cols=y, bias=self.b)])
@@ -338,9 +344,7 @@ class LstmFlat:
         self.units = n
 
     def step(self):
-        self.dW.zero_()
-        self.db.zero_()
-        self.dXH.zero_()
+        self.grads.zero_()
         self.fwd()
         self.dx()
         self.dw()
@@ -389,7 +393,11 @@ class MlpDataParallel:
         self.nll = torch.zeros(batch, device=device)
         self.ones = torch.ones(batch, device=device)  # d(sum of the losses) / d(each loss)
         self.h = [self.x] + [B.colmajor(d[i + 1], batch, torch.float32, device, fill=0.0) for i in range(3)]
-        self.dh = [None] + [B.colmajor(d[i + 1], batch, torch.float32, device, fill=0.0) for i in range(3)]
+        # the three activation gradients in one buffer: one fill per step
+        self.dh_flat = torch.zeros(sum(d[1:]) * batch, device=device)
+        offs = [0, d[1] * batch, (d[1] + d[2]) * batch]
+        self.dh = [None] + [torch.as_strided(self.dh_flat, (d[i + 1], batch), (1, d[i + 1]), offs[i])
+                            for i in range(3)]
         self.acts = (B.ACT_RELU, B.ACT_RELU, B.ACT_NONE)
         self.allreduce, self.world, self.batch, self.t = allreduce, world, batch, 0
         self.loss = torch.zeros((), device=device)
@@ -397,26 +405,46 @@ class MlpDataParallel:
         self.flops = 2 * fwd + sum(2 * d[i + 1] * d[i] * batch for i in (1, 2))  # fwd + dW + dX(2,3)
         self.units = batch
 
-    def step(self):
+    def _front(self):
+        """reset_grad, forward, loss, backward of layers 3 and 2 (everything before the first
+        all-reduce can start)."""
         gb = B
         self.grads.zero_()
-        for i in (1, 2, 3):
-            self.dh[i].zero_()
+        self.dh_flat.zero_()
         for i in range(3):
             gb.affine_forward([gb.Pair(self.W[i], self.h[i])], self.b[i], self.acts[i], self.h[i + 1])
         # loss = Sum(PickNegLogSoftmax(logits, labels)) (examples/mnist-dp.cu:141) and its gradient
         gb.pick_nll_forward(self.h[3], self.labels32, self.smax, self.nll)
         self.loss = self.nll.sum()
         gb.pick_nll_backward(self.smax, self.labels32, self.ones, self.dh[3])
+        for i in (2, 1):
+            self._backward_layer(i)
+
+    def _backward_layer(self, i):
+        B.affine_backward([B.PairGrad(self.W[i], self.h[i], self.dW[i],
+                                      self.dh[i] if i > 0 else None)],
+                          self.dh[i + 1], self.h[i + 1], self.acts[i], self.db[i])
+
+    def _back(self):
+        self._backward_layer(0)
+
+    def capture(self):
+        """Records the two launch sequences of a step (before the first all-reduce; layer 1's
+        backward) into CUDA graphs; the collectives and Adam (whose step count is a host scalar)
+        stay ordinary calls.  With eight processes on one host the ~25 launches of a step
+        otherwise take the host about as long as they take the GPU."""
+        self._graphs = (graphed(self._front), graphed(self._back))
+
+    def step(self):
+        gb = B
+        front, back = getattr(self, "_graphs", None) or (self._front, self._back)
+        front()
         wait = []
-        for i in (2, 1, 0):
-            gb.affine_backward([gb.PairGrad(self.W[i], self.h[i], self.dW[i],
-                                            self.dh[i] if i > 0 else None)],
-                               self.dh[i + 1], self.h[i + 1], self.acts[i], self.db[i])
-            # data parallel: the all-reduce of layers 2 and 3 runs beside layer 1's backward
-            # product; `allreduce` returns a function that makes this stream wait for the result
-            if self.allreduce is not None and self.world > 1 and i == 1:
-                wait.append(self.allreduce(self.bucket_early))
+        # data parallel: the all-reduce of layers 2 and 3 runs beside layer 1's backward
+        # product; `allreduce` returns a function that makes this stream wait for the result
+        if self.allreduce is not None and self.world > 1:
+            wait.append(self.allreduce(self.bucket_early))
+        back()
         if self.allreduce is not None and self.world > 1:
             wait.append(self.allreduce(self.bucket_late))
             for w in wait:

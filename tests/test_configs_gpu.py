@@ -212,3 +212,24 @@ def test_mlp_harness_matches_autograd_and_adam(gpu):
                 want = p + (-1e-3 / (1 - 0.9 ** t)) * m[i] / (1e-8 + (v[i] / (1 - 0.999 ** t)).sqrt())
                 now = views[i].double()
                 assert float((now - want).norm() / want.norm()) <= 1e-6, f"parameter {i} step {t}"
+
+
+def test_mlp_step_replayed_from_graphs_matches_the_launched_step(gpu):
+    """The two CUDA graphs that replay a step's kernel launches must leave the loss, the gradients
+    and the parameters where the call-by-call step leaves them (not bit for bit: products whose
+    contraction is split over CTAs add their parts in the order the CTAs finish)."""
+    from ginn_b200.workloads import MlpDataParallel
+    dev = torch.device("cuda", 0)
+    a, b = MlpDataParallel(dev, batch=512), MlpDataParallel(dev, batch=512)
+    assert torch.equal(a.params, b.params)
+    a.step()
+    b.step()
+    b.capture()
+    for _ in range(3):
+        a.step()
+        b.step()
+    torch.cuda.synchronize()
+    rel = lambda x, y: float((x.double() - y.double()).norm() / y.double().norm())
+    assert abs(float(a.loss) - float(b.loss)) <= 1e-6 * abs(float(a.loss))
+    assert rel(b.grads, a.grads) <= 1e-5
+    assert rel(b.params, a.params) <= 1e-5

@@ -152,6 +152,29 @@ def test_tma_path_half(gpu, trans, path):
     check(B.to_host(C), orc.gemm_batched(a, b), np.float16)
 
 
+def test_pair_kernel_l2_hints_do_not_change_results(gpu):
+    """The CTA-pair kernel's L2 eviction hints only steer caching: the same product with and
+    without them must agree bit for bit, with and without accumulation."""
+    gpu.set_option("force_path", 4)
+    rng = np.random.default_rng(23)
+    a, b = randn(rng, (512, 320), np.float16), randn(rng, (768, 320), np.float16)
+    c0 = randn(rng, (512, 768), np.float16)
+    outs = []
+    try:
+        for hint in (0, 1, 2, 3):
+            gpu.set_option("pair_l2_hint", hint)
+            C = B.from_host(c0)
+            gpu.gemm(B.from_host(a), B.from_host(b), C, trans_b=True, accumulate=True)
+            torch.cuda.synchronize()
+            outs.append(B.to_host(C))
+    finally:
+        gpu.set_option("pair_l2_hint", 3)
+        gpu.set_option("force_path", 0)
+    check(outs[0], orc.gemm(a, b, trans_b=True, c=c0, accumulate=True), np.float16)
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+
+
 def test_large_half_product_by_linearity(gpu):
     """C4 size (8192^3): (A*B)*v must equal A*(B*v).  Both sides are formed from fp16-rounded
     data with fp32 matrix-vector products, so the check is independent of any other GEMM."""
