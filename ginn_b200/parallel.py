@@ -34,9 +34,12 @@ class ShardedProd:
 
     def __init__(self, gemm: Callable, zero: Callable, allreduce_async: Callable, panels: int = 1,
                  col_block: Callable = None, row_block: Callable = None,
-                 overlapped: Callable = None):
+                 overlapped: Callable = None, zero_beside: Callable = None):
         self.gemm = gemm
         self.zero = zero
+        # optional: zero_beside([tensors]) clears the gradients off the main stream (they are
+        # first touched by the second product) and returns the function that waits for it
+        self.zero_beside = zero_beside
         self.allreduce_async = allreduce_async
         self.panels = max(1, panels)
         self.col_block = col_block or (lambda x, s, c: x[:, s:s + c])
@@ -48,9 +51,15 @@ class ShardedProd:
     def step(self, A, B_shard, dC_shard, C_shard, dA, dB_shard, between: Callable = None):
         """C = A*B; dA += dC*B^T (all-reduced); dB += A^T*dC.  Gradients are zeroed first, as
         Graph::reset_grad does.  `between(i)` is called after product i (timing hooks)."""
-        self.zero(dA)
-        self.zero(dB_shard)
+        zeroed = None
+        if self.zero_beside is not None:
+            zeroed = self.zero_beside([dA, dB_shard])   # runs beside the forward product
+        else:
+            self.zero(dA)
+            self.zero(dB_shard)
         self.gemm(A, B_shard, C_shard, False, False, False)
+        if zeroed is not None:
+            zeroed()
         if between:
             between(0)
         waits = []
