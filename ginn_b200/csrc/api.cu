@@ -24,7 +24,7 @@ std::atomic<long long> g_launches{0};
 thread_local int t_force_path = 0;
 thread_local int t_sm_margin = 0;     // SMs the persistent kernels leave free (e.g. for NCCL)
 thread_local int t_pair_group_m = 0;  // rasterisation group of the CTA-pair kernel (0 = default)
-thread_local int t_attention_streams = 1;  // attention backward: independent products side by side
+thread_local int t_fork_streams = 1;  // backward entries: independent products side by side
 thread_local int t_pair_l2_hint = 3;  // L2 eviction hints of the CTA-pair kernel (bits, see PParams)
 thread_local int t_max_split = 0;     // cap on the K split of fp32 products (0 = none, 1 = no split)
 thread_local int t_pdl = 1;           // programmatic dependent launch for the kernels that support it
@@ -143,6 +143,52 @@ Operand make_operand(int dtype, const void* base, long long ld, long long batch_
   o.vec = v ? 1 : 0;
   return o;
 }
+
+// Fork of the caller's stream onto the library's second stream for one entry point: products
+// that do not depend on each other run side by side, so that the CTAs of one take the SMs the
+// other leaves idle in its last wave.  begin() makes the second stream wait for everything
+// queued on the caller's stream so far; join() (also run by the destructor, on every path out)
+// makes the caller's stream wait for the second one.  Both are legal inside a stream capture.
+struct Fork {
+  DevCtx* ctx = nullptr;
+  cudaStream_t main = nullptr, side = nullptr;
+  std::unique_lock<std::mutex> lock;
+  bool active = false;
+  cudaError_t begin(DevCtx* c, cudaStream_t caller) {
+    ctx = c;
+    main = caller;
+    lock = std::unique_lock<std::mutex>(c->fork_mu);  // keeps this call's record/wait pairs together
+    cudaError_t e = cudaSuccess;
+    if (c->side_stream == nullptr) {
+      e = cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_mid, cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming);
+      if (e != cudaSuccess) return e;
+    }
+    e = cudaEventRecord(c->ev_fork, main);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0);
+    if (e != cudaSuccess) return e;
+    side = c->side_stream;
+    active = true;
+    return cudaSuccess;
+  }
+  // The second stream also waits for what the caller's stream has queued since begin().
+  cudaError_t sync_side() {
+    cudaError_t e = cudaEventRecord(ctx->ev_mid, main);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(side, ctx->ev_mid, 0);
+    return e;
+  }
+  cudaError_t join() {
+    if (!active) return cudaSuccess;
+    active = false;
+    cudaError_t e = cudaEventRecord(ctx->ev_join, side);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(main, ctx->ev_join, 0);
+    lock.unlock();
+    return e;
+  }
+  ~Fork() { join(); }
+};
 
 // SMs a persistent kernel may occupy: all of them minus the margin the host asked to keep free.
 int persistent_sms(const DevCtx* ctx) {
@@ -758,6 +804,17 @@ int ginn_b200_affine_backward(int device, void* stream_, int dtype, int npairs,
                                            out, ldout, act, dbias, nullptr);
 }
 
+// True when a backward call has both an input gradient and a weight gradient to form.
+static bool wants_both(int npairs, const ginn_b200_pair_grad* pairs) {
+  int n_dx = 0, n_dw = 0;
+  for (int i = 0; i < npairs; ++i) {
+    if (pairs[i].k <= 0) continue;
+    n_dx += pairs[i].db != nullptr;
+    n_dw += pairs[i].da != nullptr;
+  }
+  return n_dx > 0 && n_dw > 0;
+}
+
 int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int npairs,
                                       const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,
                                       const void* dout, int64_t lddout, const void* out,
@@ -809,6 +866,18 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
       ldA = m;
     }
     int status = GINN_B200_OK;
+    // The input gradients go to the second stream (after the derivative pass above), the weight
+    // and bias gradients stay on the caller's: they only share read-only operands.
+    Fork fk;
+    cudaStream_t dx_stream = stream;
+    if (t_fork_streams && wants_both(npairs, pairs)) {
+      cudaError_t e = fk.begin(ctx, stream);
+      if (e != cudaSuccess) {
+        if (scratch) cudaFreeAsync(scratch, stream);
+        return fail(GINN_B200_CUDA_ERROR, "second stream: %s", cudaGetErrorString(e));
+      }
+      dx_stream = fk.side;
+    }
     if (dbias != nullptr) {
       // large aligned matrices: fp32 partial sums in a stream-ordered allocation, then one pass
       // (atomics from many blocks onto the few lines of the bias gradient serialise)
@@ -836,7 +905,7 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
         if (!q.a || q.lda < m || q.lddb < q.k)
           status = fail(GINN_B200_BAD_ARGUMENT, "pair %d: bad A / db", i);
         else
-          status = gemm_impl(device, stream_, dtype, 1, 0, q.k, n, m, q.a, q.lda, 0, dA, ldA, 0, q.db,
+          status = gemm_impl(device, dx_stream, dtype, 1, 0, q.k, n, m, q.a, q.lda, 0, dA, ldA, 0, q.db,
                              q.lddb, 0, 1, 1);
       }
       if (status == GINN_B200_OK && q.da) {  // da (m x k) += dA (m x n) * B^T (n x k)
@@ -881,10 +950,21 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
         }
       }
     }
+    const cudaError_t je = fk.join();
+    if (je != cudaSuccess && status == GINN_B200_OK)
+      status = fail(GINN_B200_CUDA_ERROR, "joining the second stream failed: %s", cudaGetErrorString(je));
     if (scratch) cudaFreeAsync(scratch, stream);
     return status;
   }
 
+  // Input gradients on the second stream, weight and bias gradients on the caller's: they only
+  // share read-only operands, and the CTAs of one fill the SMs the other leaves idle.
+  Fork fk;
+  cudaStream_t dx_stream = stream;
+  if (t_fork_streams && wants_both(npairs, pairs)) {
+    CU_TRY(fk.begin(ctx, stream));
+    dx_stream = fk.side;
+  }
   for (int i = 0; i < npairs; ++i) {
     const ginn_b200_pair_grad& q = pairs[i];
     if (q.k < 0 || q.k > 0x7fffffffLL) return fail(GINN_B200_BAD_ARGUMENT, "pair %d: bad k", i);
@@ -901,7 +981,7 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
       p.M = (int)q.k; p.N = (int)n; p.batches = 1;
       p.c = q.db; p.ldc = q.lddb;
       p.accumulate = 1;
-      if (int s = run_problem(ctx, dtype, p, stream)) return s;
+      if (int s = run_problem(ctx, dtype, p, dx_stream)) return s;
     }
     if (q.da) {  // da (m x k) += dA (m x n) * B^T (n x k)
       if (!q.b || q.ldb < q.k || q.ldda < m)
@@ -927,6 +1007,7 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
                              (int)m, n, dbias, stream));
     g_launches.fetch_add(1);
   }
+  CU_TRY(fk.join());
   return GINN_B200_OK;
 }
 
@@ -1272,26 +1353,15 @@ int ginn_b200_attention_backward(int device, void* stream_, int dtype, int64_t t
   // dV and dQ do not depend on the chain dP -> dS -> dK': they run on a second stream, where
   // their CTAs take the SMs the other products leave idle at the end of their last wave and
   // during the softmax pass (256 x (256, 64): 0.33 -> 0.31 ms per forward + backward step).
-  const bool fork = t_attention_streams && (dv != nullptr) + (dq != nullptr) + (dk != nullptr) >= 2;
-  std::unique_lock<std::mutex> fork_lock(ctx->fork_mu, std::defer_lock);
+  Fork fk;
+  const bool fork = t_fork_streams && (dv != nullptr) + (dq != nullptr) + (dk != nullptr) >= 2;
   cudaStream_t side = stream;
   if (fork) {
-    fork_lock.lock();
-    if (ctx->side_stream == nullptr) {
-      CU_TRY(cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
-      CU_TRY(cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming));
-      CU_TRY(cudaEventCreateWithFlags(&ctx->ev_mid, cudaEventDisableTiming));
-      CU_TRY(cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming));
-    }
-    side = ctx->side_stream;
-    CU_TRY(cudaEventRecord(ctx->ev_fork, stream));
-    CU_TRY(cudaStreamWaitEvent(side, ctx->ev_fork, 0));
+    CU_TRY(fk.begin(ctx, stream));
+    side = fk.side;
   }
-  // Joins the second stream back; on every path out once it has been forked.
   auto join = [&](int status) {
-    if (!fork) return status;
-    cudaError_t e = cudaEventRecord(ctx->ev_join, side);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, ctx->ev_join, 0);
+    cudaError_t e = fk.join();
     if (e != cudaSuccess && status == GINN_B200_OK)
       return fail(GINN_B200_CUDA_ERROR, "joining the second stream failed: %s", cudaGetErrorString(e));
     return status;
@@ -1320,8 +1390,7 @@ int ginn_b200_attention_backward(int device, void* stream_, int dtype, int64_t t
   }
   // dk (T x hs) += dS * Q^T;  dq (hs x T) += K'^T * dS (on the second stream once dS is there)
   if (fork && dq && dk) {
-    e = cudaEventRecord(ctx->ev_mid, stream);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(side, ctx->ev_mid, 0);
+    e = fk.sync_side();
     if (e != cudaSuccess)
       return join(fail(GINN_B200_CUDA_ERROR, "forking the second stream failed: %s", cudaGetErrorString(e)));
   }
@@ -1642,9 +1711,9 @@ int ginn_b200_set_option(const char* name, int value) {
     t_pair_group_m = value;
     return GINN_B200_OK;
   }
-  if (name && std::strcmp(name, "attention_streams") == 0) {
-    if (value < 0 || value > 1) return fail(GINN_B200_BAD_ARGUMENT, "attention_streams must be 0 or 1");
-    t_attention_streams = value;
+  if (name && std::strcmp(name, "fork_streams") == 0) {
+    if (value < 0 || value > 1) return fail(GINN_B200_BAD_ARGUMENT, "fork_streams must be 0 or 1");
+    t_fork_streams = value;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "pair_l2_hint") == 0) {

@@ -375,9 +375,11 @@ int ginn_b200_version(void);   /* 200: ginn_b200_group gained `act` and `out_col
  * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles; set
  * it around the one product that overlaps the collective and back to 0 afterwards.
  * "pair_group_m": m-tiles per rasterisation group of the CTA-pair kernel (0 = default).
- * "attention_streams": 1 (default) lets ginn_b200_attention_backward run the products that do
- * not depend on each other (dV, dQ) on a second stream of the library's own, forked from and
- * joined back into the caller's stream inside the call; 0 keeps every launch on the caller's stream.
+ * "fork_streams": 1 (default) lets ginn_b200_affine_backward and ginn_b200_attention_backward
+ * run the products of a call that do not depend on each other (input gradient beside weight
+ * gradient; dV and dQ beside dP -> dS -> dK') on a second stream of the library's own, forked
+ * from and joined back into the caller's stream inside the call (also under stream capture);
+ * 0 keeps every launch on the caller's stream.
  * "pair_l2_hint": L2 eviction hints of the CTA-pair kernel: bit 0 = A slices loaded evict-last
  * and B slices evict-first, bit 1 = streaming reads and writes of C (default 3; 0 = none).
  * "max_split": cap on the number of CTAs an fp32 product's contraction is split over, and on the

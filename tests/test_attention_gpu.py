@@ -141,10 +141,10 @@ def test_backward_on_one_stream_in_a_graph_and_with_missing_gradients(gpu):
     close = lambda x, y: float((x.double() - y.double()).norm() / y.double().norm()) <= 2e-6
     same = lambda a, b: all(x is None or close(x, y) for x, y in zip(a, b))
     try:
-        gpu.set_option("attention_streams", 0)
+        gpu.set_option("fork_streams", 0)
         assert same(run(), ref)
     finally:
-        gpu.set_option("attention_streams", 1)
+        gpu.set_option("fork_streams", 1)
     assert same(run(dk=False), ref)
     assert same(run(dq=False), ref)
     assert same(run(dk=False, dq=False), ref)
