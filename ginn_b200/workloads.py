@@ -342,12 +342,20 @@ class LstmFlat:
                                                      dbias=self.db)])
         self.flops = 3 * 2 * 4 * H * (E + H) * n
         self.units = n
+        self.side, self.zeroed = torch.cuda.Stream(), torch.cuda.Event()
 
     def step(self):
+        # The weight gradient runs on a second stream beside the forward and input-gradient
+        # launches (as the C++ BatchedGraph schedules it): its CTAs fill the SMs those leave idle
+        # in their last wave.
+        main = torch.cuda.current_stream()
         self.grads.zero_()
+        self.zeroed.record(main)
+        self.side.wait_event(self.zeroed)
         self.fwd()
+        self.dw.run(self.side.cuda_stream)
         self.dx()
-        self.dw()
+        main.wait_stream(self.side)
 
 
 class MlpDataParallel:
