@@ -88,8 +88,9 @@ struct DevCtx {
   };
   Slab* slab = nullptr;           // the slab new levels are carved from
   cudaStream_t prep_stream = nullptr;
-  // Second stream for entry points that run independent products side by side (the attention
-  // backward pass): forked from and joined back into the caller's stream with these events.
+  // Second stream for entry points that run independent products side by side (the Affine and
+  // attention backward passes): forked from and joined back into the caller's stream with these
+  // events.
   // `fork_mu` keeps one call's record/wait pairs together.
   std::mutex fork_mu;
   cudaStream_t side_stream = nullptr;
@@ -115,6 +116,10 @@ int get_ctx(int device, DevCtx** out) {
     CU_TRY(cudaMemset(c.d_status, 0, sizeof(int)));
     CU_TRY(cudaMalloc(&c.d_counters, 2 * kCounters * sizeof(int)));
     CU_TRY(cudaMemset(c.d_counters, 0, 2 * kCounters * sizeof(int)));
+    CU_TRY(cudaStreamCreateWithFlags(&c.side_stream, cudaStreamNonBlocking));
+    CU_TRY(cudaEventCreateWithFlags(&c.ev_fork, cudaEventDisableTiming));
+    CU_TRY(cudaEventCreateWithFlags(&c.ev_mid, cudaEventDisableTiming));
+    CU_TRY(cudaEventCreateWithFlags(&c.ev_join, cudaEventDisableTiming));
     c.ready = true;
   }
   *out = &c;
@@ -158,15 +163,8 @@ struct Fork {
     ctx = c;
     main = caller;
     lock = std::unique_lock<std::mutex>(c->fork_mu);  // keeps this call's record/wait pairs together
-    cudaError_t e = cudaSuccess;
-    if (c->side_stream == nullptr) {
-      e = cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking);
-      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
-      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_mid, cudaEventDisableTiming);
-      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming);
-      if (e != cudaSuccess) return e;
-    }
-    e = cudaEventRecord(c->ev_fork, main);
+    // the stream and the events exist since the device's first call (never created in a capture)
+    cudaError_t e = cudaEventRecord(c->ev_fork, main);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0);
     if (e != cudaSuccess) return e;
     side = c->side_stream;
