@@ -66,6 +66,9 @@ def lib():
     L.ginn_b200_gemm.argtypes = [ci, vp, ci, ci, ci, i64, i64, i64, vp, i64, vp, i64, vp, i64, ci]
     L.ginn_b200_gemm_batched.argtypes = [ci, vp, ci, ci, ci, i64, i64, i64, vp, i64, i64, vp, i64,
                                          i64, vp, i64, i64, i64, ci]
+    L.ginn_b200_prod_backward.argtypes = [ci, vp, ci, i64, i64, i64, i64, vp, i64, i64, vp, i64, i64,
+                                          vp, i64, i64, vp, i64, i64, vp, i64, i64]
+    L.ginn_b200_prod_backward.restype = ci
     L.ginn_b200_affine_forward.argtypes = [ci, vp, ci, ci, C.POINTER(_Pair), i64, i64, vp, ci, vp,
                                            i64]
     L.ginn_b200_affine_backward.argtypes = [ci, vp, ci, ci, C.POINTER(_PairGrad), i64, i64, vp,
@@ -204,6 +207,22 @@ def gemm_batched(a, b, c, trans_a=False, trans_b=False, accumulate=False):
         _dev(c), _stream(c), _dtype_of(c), int(trans_a), int(trans_b), m, n, k, a.data_ptr(),
         _ld(a), sa, b.data_ptr(), _ld(b), sb, c.data_ptr(), _ld(c), sc, batches, int(accumulate)))
     return c
+
+
+def prod_backward(a, b, dc, da=None, db=None) -> None:
+    """Both gradient products of c = a @ b (per batch for rank-3 tensors): da += dc @ b^T,
+    db += a^T @ dc; ProdNode::backward_ / BatchedProdNode::backward_ (ginn/node/prod.h:51-66,
+    118-130)."""
+    batched = a.dim() == 3
+    m, k = a.shape[0], a.shape[1]
+    n = b.shape[1]
+    batches = a.shape[2] if batched else 1
+    st = lambda t: 0 if t is None else (t.stride(2) if batched and batches > 1 else t.shape[0] * t.shape[1])
+    ld = lambda t: 0 if t is None else _ld(t)
+    _check(lib().ginn_b200_prod_backward(
+        _dev(dc), _stream(dc), _dtype_of(dc), m, n, k, batches, a.data_ptr(), _ld(a), st(a),
+        b.data_ptr(), _ld(b), st(b), dc.data_ptr(), _ld(dc), st(dc), _ptr(da), ld(da), st(da),
+        _ptr(db), ld(db), st(db)))
 
 
 @dataclass

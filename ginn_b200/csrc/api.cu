@@ -802,15 +802,42 @@ int ginn_b200_affine_backward(int device, void* stream_, int dtype, int npairs,
                                            out, ldout, act, dbias, nullptr);
 }
 
-// True when a backward call has both an input gradient and a weight gradient to form.
-static bool wants_both(int npairs, const ginn_b200_pair_grad* pairs) {
+// Byte range of a column-major matrix.
+struct ByteRange {
+  const char* lo;
+  const char* hi;
+};
+static ByteRange range_of(const void* p, int64_t rows, int64_t cols, int64_t ld, int es) {
+  const char* lo = static_cast<const char*>(p);
+  if (p == nullptr || rows <= 0 || cols <= 0) return ByteRange{lo, lo};
+  return ByteRange{lo, lo + ((cols - 1) * ld + rows) * es};
+}
+static bool overlap(const ByteRange& a, const ByteRange& b) { return a.lo < b.hi && b.lo < a.hi; }
+
+// True when a backward call has both an input gradient and a weight gradient to form and no
+// input gradient shares memory with a weight or bias gradient (the two kinds then run on
+// different streams).
+static bool wants_both(int dtype, int npairs, const ginn_b200_pair_grad* pairs, int64_t m, int64_t n,
+                       const void* dbias) {
+  const int es = dtype == GINN_B200_F32 ? 4 : 2;
   int n_dx = 0, n_dw = 0;
   for (int i = 0; i < npairs; ++i) {
     if (pairs[i].k <= 0) continue;
     n_dx += pairs[i].db != nullptr;
     n_dw += pairs[i].da != nullptr;
   }
-  return n_dx > 0 && n_dw > 0;
+  if (n_dx == 0 || n_dw == 0) return false;
+  const ByteRange bias = range_of(dbias, m, 1, m, es);
+  for (int i = 0; i < npairs; ++i) {
+    if (pairs[i].k <= 0 || pairs[i].db == nullptr) continue;
+    const ByteRange dx = range_of(pairs[i].db, pairs[i].k, n, pairs[i].lddb, es);
+    if (overlap(dx, bias)) return false;
+    for (int j = 0; j < npairs; ++j) {
+      if (pairs[j].k <= 0 || pairs[j].da == nullptr) continue;
+      if (overlap(dx, range_of(pairs[j].da, m, pairs[j].k, pairs[j].ldda, es))) return false;
+    }
+  }
+  return true;
 }
 
 int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int npairs,
@@ -868,7 +895,7 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
     // and bias gradients stay on the caller's: they only share read-only operands.
     Fork fk;
     cudaStream_t dx_stream = stream;
-    if (t_fork_streams && wants_both(npairs, pairs)) {
+    if (t_fork_streams && wants_both(dtype, npairs, pairs, m, n, dbias)) {
       cudaError_t e = fk.begin(ctx, stream);
       if (e != cudaSuccess) {
         if (scratch) cudaFreeAsync(scratch, stream);
@@ -959,7 +986,7 @@ int ginn_b200_affine_backward_scratch(int device, void* stream_, int dtype, int 
   // share read-only operands, and the CTAs of one fill the SMs the other leaves idle.
   Fork fk;
   cudaStream_t dx_stream = stream;
-  if (t_fork_streams && wants_both(npairs, pairs)) {
+  if (t_fork_streams && wants_both(dtype, npairs, pairs, m, n, dbias)) {
     CU_TRY(fk.begin(ctx, stream));
     dx_stream = fk.side;
   }
@@ -1352,7 +1379,18 @@ int ginn_b200_attention_backward(int device, void* stream_, int dtype, int64_t t
   // their CTAs take the SMs the other products leave idle at the end of their last wave and
   // during the softmax pass (256 x (256, 64): 0.33 -> 0.31 ms per forward + backward step).
   Fork fk;
-  const bool fork = t_fork_streams && (dv != nullptr) + (dq != nullptr) + (dk != nullptr) >= 2;
+  bool fork = t_fork_streams && (dv != nullptr) + (dq != nullptr) + (dk != nullptr) >= 2;
+  if (fork && dk) {  // gradients that share memory (tied inputs) stay on one stream
+    const int es = dtype == GINN_B200_F32 ? 4 : 2;
+    auto span = [&](const void* p0, int64_t rows, int64_t cols, int64_t ld, int64_t stride) {
+      ByteRange r = range_of(p0, rows, cols, ld, es);
+      if (p0) r.hi += (batches - 1) * stride * es;
+      return r;
+    };
+    const ByteRange rk = span(dk, t, hs, ldk, stride_k);
+    if (overlap(rk, span(dv, hs, t, ldv, stride_v)) || overlap(rk, span(dq, hs, t, ldq, stride_q)))
+      fork = false;
+  }
   cudaStream_t side = stream;
   if (fork) {
     CU_TRY(fk.begin(ctx, stream));
@@ -1402,6 +1440,44 @@ int ginn_b200_attention_backward(int device, void* stream_, int dtype, int64_t t
                           ldq, stride_q, batches, 1))
       return join(s);
   return join(GINN_B200_OK);
+}
+
+int ginn_b200_prod_backward(int device, void* stream_, int dtype, int64_t m, int64_t n, int64_t k,
+                            int64_t batches, const void* a, int64_t lda, int64_t stride_a,
+                            const void* b, int64_t ldb, int64_t stride_b, const void* dc,
+                            int64_t lddc, int64_t stride_dc, void* da, int64_t ldda,
+                            int64_t stride_da, void* db, int64_t lddb, int64_t stride_db) {
+  if (int s = check_common(dtype, m, n, k)) return s;
+  if (batches < 0) return fail(GINN_B200_BAD_ARGUMENT, "negative batch count");
+  if (!da && !db) return GINN_B200_OK;
+  if (m == 0 || n == 0 || k == 0 || batches == 0) return GINN_B200_OK;  // nothing to add
+  if (!dc || (da && !b) || (db && !a)) return fail(GINN_B200_BAD_ARGUMENT, "null tensor pointer");
+  DevCtx* ctx;
+  if (int s = get_ctx(device, &ctx)) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  Fork fk;
+  cudaStream_t db_stream = stream;
+  if (t_fork_streams && da && db) {
+    const int es = dtype == GINN_B200_F32 ? 4 : 2;
+    ByteRange ra = range_of(da, m, k, ldda, es), rb = range_of(db, k, n, lddb, es);
+    ra.hi += (batches - 1) * stride_da * es;
+    rb.hi += (batches - 1) * stride_db * es;
+    if (!overlap(ra, rb)) {  // Prod(x, x) adds both gradients into one tensor: one stream then
+      CU_TRY(fk.begin(ctx, stream));
+      db_stream = fk.side;
+    }
+  }
+  int status = GINN_B200_OK;
+  if (da)  // da (m x k) += dc (m x n) * b^T (n x k)
+    status = gemm_impl(device, stream_, dtype, 0, 1, m, k, n, dc, lddc, stride_dc, b, ldb, stride_b, da,
+                       ldda, stride_da, batches, 1);
+  if (db && status == GINN_B200_OK)  // db (k x n) += a^T (k x m) * dc (m x n)
+    status = gemm_impl(device, db_stream, dtype, 1, 0, k, n, m, a, lda, stride_a, dc, lddc, stride_dc,
+                       db, lddb, stride_db, batches, 1);
+  const cudaError_t je = fk.join();
+  if (je != cudaSuccess && status == GINN_B200_OK)
+    status = fail(GINN_B200_CUDA_ERROR, "joining the second stream failed: %s", cudaGetErrorString(je));
+  return status;
 }
 
 size_t ginn_b200_conv2d_workspace(int dtype, int64_t C, int64_t R, int64_t W, int64_t B, int64_t F,

@@ -20,11 +20,11 @@ class ProdNode : public BaseDataNode<Scalar> {
     internal::gpu_prod(this->value(), a_->value(), b_->value());
   }
   void backward_() override {
-    using namespace internal;
-    if (b_->has_grad())
-      gpu_prod(b_->grad(), a_->value(), this->grad(), ProdResult::Add, ProdTranspose::First);
-    if (a_->has_grad())
-      gpu_prod(a_->grad(), this->grad(), b_->value(), ProdResult::Add, ProdTranspose::Second);
+    // db += a^T * d and da += d * b^T in one call: the library runs them side by side
+    if (a_->has_grad() || b_->has_grad())
+      internal::gpu_prod_backward(a_->has_grad() ? &a_->grad() : nullptr,
+                                  b_->has_grad() ? &b_->grad() : nullptr, this->grad(),
+                                  a_->value(), b_->value());
   }
 
  public:
@@ -56,13 +56,10 @@ class BatchedProdNode : public BaseDataNode<Scalar> {
     internal::gpu_batched_prod(this->value(), a_->value(), b_->value());
   }
   void backward_() override {
-    using namespace internal;
-    if (a_->has_grad())
-      gpu_batched_prod(a_->grad(), this->grad(), b_->value(), ProdResult::Add,
-                       ProdTranspose::Second);
-    if (b_->has_grad())
-      gpu_batched_prod(b_->grad(), a_->value(), this->grad(), ProdResult::Add,
-                       ProdTranspose::First);
+    if (a_->has_grad() || b_->has_grad())
+      internal::gpu_batched_prod_backward(a_->has_grad() ? &a_->grad() : nullptr,
+                                          b_->has_grad() ? &b_->grad() : nullptr, this->grad(),
+                                          a_->value(), b_->value());
   }
 
  public:

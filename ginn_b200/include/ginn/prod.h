@@ -71,6 +71,46 @@ inline void gpu_batched_prod(Tensor<Scalar>& c, Tensor<Scalar>& a, Tensor<Scalar
                                     a_outer * b_outer, as[2], res == ProdResult::Add));
 }
 
+// Both gradient products of C = A * B in one call (ProdNode::backward_, ginn/node/prod.h:51-66):
+// da += dc * B^T and db += A^T * dc; a null `da` / `db` skips that product.  The library runs the
+// two side by side when their outputs do not overlap.
+template <typename Scalar>
+inline void gpu_prod_backward(Tensor<Scalar>* da, Tensor<Scalar>* db, Tensor<Scalar>& dc,
+                              Tensor<Scalar>& a, Tensor<Scalar>& b) {
+  GINN_ASSERT(a.cols() == b.rows());
+  GINN_ASSERT(a.rows() == dc.rows());
+  GINN_ASSERT(b.cols() == dc.cols());
+  if (da) GINN_ASSERT(da->rows() == a.rows() && da->cols() == a.cols());
+  if (db) GINN_ASSERT(db->rows() == b.rows() && db->cols() == b.cols());
+  const int dev = b200_device(dc.dev());
+  b200_check(ginn_b200_prod_backward(dev, stream_of(*dc.dev()), b200_dtype<Scalar>(), a.rows(),
+                                     b.cols(), a.cols(), 1, a.data(), a.rows(), 0, b.data(),
+                                     b.rows(), 0, dc.data(), dc.rows(), 0,
+                                     da ? da->data() : nullptr, a.rows(), 0,
+                                     db ? db->data() : nullptr, b.rows(), 0));
+}
+
+// The batched form (BatchedProdNode::backward_, ginn/node/prod.h:118-130); ranks above 3 fold
+// into the batch index.
+template <typename Scalar>
+inline void gpu_batched_prod_backward(Tensor<Scalar>* da, Tensor<Scalar>* db, Tensor<Scalar>& dc,
+                                      Tensor<Scalar>& a, Tensor<Scalar>& b) {
+  const Shape as = Tensor<Scalar>::reduce(a.shape(), 3), bs = Tensor<Scalar>::reduce(b.shape(), 3),
+              cs = Tensor<Scalar>::reduce(dc.shape(), 3);
+  GINN_ASSERT(as[1] == bs[0]);
+  GINN_ASSERT(as[0] == cs[0]);
+  GINN_ASSERT(bs[1] == cs[1]);
+  GINN_ASSERT(as[2] == bs[2] && as[2] == cs[2]);
+  if (da) GINN_ASSERT(da->size() == a.size());
+  if (db) GINN_ASSERT(db->size() == b.size());
+  const int dev = b200_device(dc.dev());
+  b200_check(ginn_b200_prod_backward(dev, stream_of(*dc.dev()), b200_dtype<Scalar>(), as[0], bs[1],
+                                     as[1], as[2], a.data(), as[0], as[0] * as[1], b.data(), bs[0],
+                                     bs[0] * bs[1], dc.data(), cs[0], cs[0] * cs[1],
+                                     da ? da->data() : nullptr, as[0], as[0] * as[1],
+                                     db ? db->data() : nullptr, bs[0], bs[0] * bs[1]));
+}
+
 }  // namespace internal
 }  // namespace ginn
 #endif

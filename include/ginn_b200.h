@@ -56,6 +56,21 @@ int ginn_b200_gemm_batched(int device, void* stream, int dtype, int trans_a, int
                            int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, void* c,
                            int64_t ldc, int64_t stride_c, int64_t batches, int accumulate);
 
+/* Both gradient products of a ProdNode / BatchedProdNode whose forward pass was
+ * C (m x n) = A (m x k) * B (k x n), per batch:
+ *     da (m x k) += dc (m x n) * B^T      (skipped when da is NULL)
+ *     db (k x n) += A^T * dc (m x n)      (skipped when db is NULL)
+ * Replaces the two gpu_prod / gpu_batched_prod calls of ProdNode::backward_ and
+ * BatchedProdNode::backward_ (ginn/node/prod.h:51-66, 118-130).  The two products share only
+ * read-only operands; when their outputs do not overlap they run side by side (the second on
+ * a stream of the library's own, forked from and joined back into `stream` inside the call;
+ * option "fork_streams").  batches = 1 with strides 0 is the plain product. */
+int ginn_b200_prod_backward(int device, void* stream, int dtype, int64_t m, int64_t n, int64_t k,
+                            int64_t batches, const void* a, int64_t lda, int64_t stride_a,
+                            const void* b, int64_t ldb, int64_t stride_b, const void* dc,
+                            int64_t lddc, int64_t stride_dc, void* da, int64_t ldda,
+                            int64_t stride_da, void* db, int64_t lddb, int64_t stride_db);
+
 /* One (A_i, B_i) term of an Affine node: A_i is m x k (leading dimension lda), B_i is k x n. */
 typedef struct {
   const void* a;
@@ -375,9 +390,9 @@ int ginn_b200_version(void);   /* 200: ginn_b200_group gained `act` and `out_col
  * collective running beside them (NCCL) finds free SMs instead of delaying the last tiles; set
  * it around the one product that overlaps the collective and back to 0 afterwards.
  * "pair_group_m": m-tiles per rasterisation group of the CTA-pair kernel (0 = default).
- * "fork_streams": 1 (default) lets ginn_b200_affine_backward and ginn_b200_attention_backward
- * run the products of a call that do not depend on each other (input gradient beside weight
- * gradient; dV and dQ beside dP -> dS -> dK') on a second stream of the library's own, forked
+ * "fork_streams": 1 (default) lets ginn_b200_affine_backward, ginn_b200_prod_backward and
+ * ginn_b200_attention_backward run the products of a call that do not depend on each other
+ * (input gradient beside weight gradient; dA beside dB; dV and dQ beside dP -> dS -> dK') on a second stream of the library's own, forked
  * from and joined back into the caller's stream inside the call (also under stream capture);
  * 0 keeps every launch on the caller's stream.
  * "pair_l2_hint": L2 eviction hints of the CTA-pair kernel: bit 0 = A slices loaded evict-last

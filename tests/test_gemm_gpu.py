@@ -404,3 +404,51 @@ def test_skinny_products_on_cuda_cores(gpu, dt):
     launches = gpu.launch_count()
     run_gemm(gpu, rng, dt, 10, 4096, 1024, False, False, False)
     assert gpu.launch_count() == launches + 1
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_prod_backward_in_one_call(gpu, dt):
+    """ProdNode::backward_ and BatchedProdNode::backward_ (ginn/node/prod.h:51-66, 118-130) as
+    one entry: da += dc b^T and db += a^T dc, run side by side by the library; either gradient
+    alone; the option that keeps them on one stream; and Prod(x, x), whose two gradients are one
+    tensor and therefore must not run side by side."""
+    rng = np.random.default_rng(29)
+    for (m, n, k) in [(3, 2, 5), (200, 96, 130), (512, 768, 256), (1024, 1024, 1024)]:
+        a, b, dc = randn(rng, (m, k), dt), randn(rng, (k, n), dt), randn(rng, (m, n), dt)
+        da0, db0 = randn(rng, (m, k), dt), randn(rng, (k, n), dt)
+        rda = orc.gemm(dc, b, trans_b=True, c=da0, accumulate=True)
+        rdb = orc.gemm(a, dc, trans_a=True, c=db0, accumulate=True)
+        for fork in (1, 0):
+            gpu.set_option("fork_streams", fork)
+            try:
+                A, Bm, dC, dA, dB = map(B.from_host, (a, b, dc, da0, db0))
+                gpu.prod_backward(A, Bm, dC, dA, dB)
+                torch.cuda.synchronize()
+            finally:
+                gpu.set_option("fork_streams", 1)
+            check(B.to_host(dA), rda, dt, f"da {m} {n} {k} fork{fork}")
+            check(B.to_host(dB), rdb, dt, f"db {m} {n} {k} fork{fork}")
+        dA, dB = B.from_host(da0), B.from_host(db0)
+        gpu.prod_backward(B.from_host(a), B.from_host(b), B.from_host(dc), dA, None)
+        gpu.prod_backward(B.from_host(a), B.from_host(b), B.from_host(dc), None, dB)
+        torch.cuda.synchronize()
+        check(B.to_host(dA), rda, dt, "da alone")
+        check(B.to_host(dB), rdb, dt, "db alone")
+    # c = x x with x square: both gradients accumulate into x's one gradient tensor
+    x, dc, g0 = randn(rng, (256, 256), dt), randn(rng, (256, 256), dt), randn(rng, (256, 256), dt)
+    X, G = B.from_host(x), B.from_host(g0)
+    gpu.prod_backward(X, X, B.from_host(dc), G, G)
+    torch.cuda.synchronize()
+    ref = orc.gemm(dc, x, trans_b=True, c=g0, accumulate=True)
+    if dt == np.float16:  # the library rounds to fp16 between the two additions
+        ref = ref.astype(np.float16)
+    ref = orc.gemm(x, dc, trans_a=True, c=ref, accumulate=True)
+    check(B.to_host(G), ref, dt, "Prod(x, x)")
+    # batched, rank 3
+    a, b, dc = randn(rng, (64, 48, 7), dt), randn(rng, (48, 80, 7), dt), randn(rng, (64, 80, 7), dt)
+    dA = B.colmajor(64, 48, torch.from_numpy(a[:1, :1, 0]).dtype, batches=7, fill=0.0)
+    dB = B.colmajor(48, 80, torch.from_numpy(a[:1, :1, 0]).dtype, batches=7, fill=0.0)
+    gpu.prod_backward(B.from_host(a), B.from_host(b), B.from_host(dc), dA, dB)
+    torch.cuda.synchronize()
+    check(B.to_host(dA), orc.gemm_batched(dc, b, trans_b=True), dt, "batched da")
+    check(B.to_host(dB), orc.gemm_batched(a, dc, trans_a=True), dt, "batched db")
