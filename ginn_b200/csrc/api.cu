@@ -25,12 +25,14 @@ thread_local int t_force_path = 0;
 thread_local int t_sm_margin = 0;     // SMs the persistent kernels leave free (e.g. for NCCL)
 thread_local int t_pair_group_m = 0;  // rasterisation group of the CTA-pair kernel (0 = default)
 thread_local int t_fork_streams = 1;  // backward entries: independent products side by side
+thread_local int t_presplit = 1;  // large fp32 products: operands split once in a scratch allocation
 thread_local int t_pair_l2_hint = 3;  // L2 eviction hints of the CTA-pair kernel (bits, see PParams)
 thread_local int t_max_split = 0;     // cap on the K split of fp32 products (0 = none, 1 = no split)
 thread_local int t_pdl = 1;           // programmatic dependent launch for the kernels that support it
 
 }  // namespace
 bool gb::pdl_enabled() { return t_pdl != 0; }
+bool gb::presplit_enabled() { return t_presplit != 0; }
 int gb::max_split() { return t_max_split; }
 int gb::sm_margin() { return t_sm_margin; }
 thread_local int t_walk_kblocks = 16;  // fp32: CTAs walk the tiles of products with at most this many k-blocks per tile
@@ -116,6 +118,16 @@ int get_ctx(int device, DevCtx** out) {
     CU_TRY(cudaMemset(c.d_status, 0, sizeof(int)));
     CU_TRY(cudaMalloc(&c.d_counters, 2 * kCounters * sizeof(int)));
     CU_TRY(cudaMemset(c.d_counters, 0, 2 * kCounters * sizeof(int)));
+    {
+      // Scratch of the entry points that need one comes from the device's stream-ordered pool;
+      // without a release threshold the pool hands its memory back to the driver at every
+      // synchronisation and the next call pays for a fresh allocation (tens of microseconds).
+      cudaMemPool_t pool = nullptr;
+      if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess && pool != nullptr) {
+        unsigned long long keep = 1ull << 32;  // keep up to 4 GiB cached
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+      }
+    }
     CU_TRY(cudaStreamCreateWithFlags(&c.side_stream, cudaStreamNonBlocking));
     CU_TRY(cudaEventCreateWithFlags(&c.ev_fork, cudaEventDisableTiming));
     CU_TRY(cudaEventCreateWithFlags(&c.ev_mid, cudaEventDisableTiming));
@@ -1788,6 +1800,11 @@ int ginn_b200_set_option(const char* name, int value) {
   if (name && std::strcmp(name, "fork_streams") == 0) {
     if (value < 0 || value > 1) return fail(GINN_B200_BAD_ARGUMENT, "fork_streams must be 0 or 1");
     t_fork_streams = value;
+    return GINN_B200_OK;
+  }
+  if (name && std::strcmp(name, "presplit") == 0) {
+    if (value < 0 || value > 1) return fail(GINN_B200_BAD_ARGUMENT, "presplit must be 0 or 1");
+    t_presplit = value;
     return GINN_B200_OK;
   }
   if (name && std::strcmp(name, "pair_l2_hint") == 0) {

@@ -12,6 +12,9 @@ namespace gb {
 // Whether kernels that support it are launched with programmatic dependent launch (option
 // "pdl" of the calling thread, default on).
 bool pdl_enabled();
+// Large fp32 products split their operands into hi / lo planes once, in a scratch allocation,
+// instead of in every tile that reads them (option "presplit"; 0 = never).
+bool presplit_enabled();
 // Cap on the K split of fp32 products (option "max_split" of the calling thread; 0 = no cap).
 int max_split();
 // SMs the persistent kernels leave free (option "sm_margin" of the calling thread).

@@ -567,6 +567,256 @@ sgemm3x_tma_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
 
 
 // ===========================================================================================
+// Operands split once in HBM.  A large product re-reads every operand slice from many tiles (a
+// row panel of A from every column tile, a column panel of B from every row tile) and the kernel
+// above splits it into hi and lo planes again each time: that transform, not the tensor pipe,
+// bounds it.  For products with at least four tiles along both extents the launcher therefore
+// splits both operands ONCE, into K-major hi / lo planes in a stream-ordered scratch allocation
+// (rows padded with zeros to a multiple of 32 along the contraction), and runs the kernel below,
+// whose producer lets TMA drop the four planes of a k-block straight into the layout the MMA
+// descriptors read: no transform warps, three 64 KiB stages.  The derivative of a fused
+// nonlinearity is applied by the split pass.
+// ===========================================================================================
+constexpr int PRE_STAGES = 3;
+
+// Both operands X(o, kk) (see Operand) -> hi[o * kp + kk], lo[o * kp + kk] in one launch:
+// blockIdx.z = operand, blockIdx.x = 32-wide tile along o, blockIdx.y = along kk; 256 threads,
+// 16 bytes each way per thread.  Bases are 16-byte aligned and leading dimensions multiples of
+// four elements (what the tensor maps of the unsplit path need as well).
+struct SplitJob {
+  const float* base;
+  const float* ybase;
+  long long ld;
+  int k_contig, dact, O;
+  float* hi;
+  float* lo;
+};
+struct SplitJobs {
+  SplitJob op[2];
+  int K, kp;
+};
+
+__device__ __forceinline__ float4 load4_guarded(const float* p0, int valid) {
+  if (valid >= 4) return *reinterpret_cast<const float4*>(p0);
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (valid > 0) v.x = p0[0];
+  if (valid > 1) v.y = p0[1];
+  if (valid > 2) v.z = p0[2];
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+presplit_kernel(const SplitJobs jobs) {
+  __shared__ float th[32][33], tl[32][33];
+  // field by field: indexing the parameter with blockIdx.z would copy it to local memory
+  const bool second = blockIdx.z != 0;
+  SplitJob jb;
+  jb.base = second ? jobs.op[1].base : jobs.op[0].base;
+  jb.ybase = second ? jobs.op[1].ybase : jobs.op[0].ybase;
+  jb.ld = second ? jobs.op[1].ld : jobs.op[0].ld;
+  jb.k_contig = second ? jobs.op[1].k_contig : jobs.op[0].k_contig;
+  jb.dact = second ? jobs.op[1].dact : jobs.op[0].dact;
+  jb.O = second ? jobs.op[1].O : jobs.op[0].O;
+  jb.hi = second ? jobs.op[1].hi : jobs.op[0].hi;
+  jb.lo = second ? jobs.op[1].lo : jobs.op[0].lo;
+  const int o0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  if (o0 >= jb.O) return;
+  const int q = threadIdx.x & 7, r = threadIdx.x >> 3;  // 8 quads x 32 rows
+  const int K = jobs.K, kp = jobs.kp;
+  pdl_wait();
+  if (jb.k_contig) {
+    const int o = o0 + r, kk = k0 + 4 * q;
+    if (o >= jb.O) return;
+    const long long off = static_cast<long long>(o) * jb.ld + kk;
+    float4 v = load4_guarded(jb.base + off, K - kk);
+    if (jb.ybase) {
+      const float4 y = load4_guarded(jb.ybase + off, K - kk);
+      v.x = act_backward<float>(jb.dact, y.x, v.x);
+      v.y = act_backward<float>(jb.dact, y.y, v.y);
+      v.z = act_backward<float>(jb.dact, y.z, v.z);
+      v.w = act_backward<float>(jb.dact, y.w, v.w);
+      // beyond K the planes must hold zeros whatever act'(0) is
+      if (K - kk < 4) {
+        if (K - kk < 1) v.x = 0.f;
+        if (K - kk < 2) v.y = 0.f;
+        if (K - kk < 3) v.z = 0.f;
+        v.w = 0.f;
+      }
+    }
+    float4 h, l;
+    split4<true>(v, h, l);
+    *reinterpret_cast<float4*>(jb.hi + static_cast<long long>(o) * kp + kk) = h;
+    *reinterpret_cast<float4*>(jb.lo + static_cast<long long>(o) * kp + kk) = l;
+  } else {
+    {
+      const int kk = k0 + r, o = o0 + 4 * q;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kk < K) {
+        const long long off = static_cast<long long>(kk) * jb.ld + o;
+        v = load4_guarded(jb.base + off, jb.O - o);
+        if (jb.ybase) {
+          const float4 y = load4_guarded(jb.ybase + off, jb.O - o);
+          v.x = act_backward<float>(jb.dact, y.x, v.x);
+          v.y = act_backward<float>(jb.dact, y.y, v.y);
+          v.z = act_backward<float>(jb.dact, y.z, v.z);
+          v.w = act_backward<float>(jb.dact, y.w, v.w);
+        }
+      }
+      float4 h, l;
+      split4<true>(v, h, l);
+      th[r][4 * q] = h.x; th[r][4 * q + 1] = h.y; th[r][4 * q + 2] = h.z; th[r][4 * q + 3] = h.w;
+      tl[r][4 * q] = l.x; tl[r][4 * q + 1] = l.y; tl[r][4 * q + 2] = l.z; tl[r][4 * q + 3] = l.w;
+    }
+    __syncthreads();
+    const int o = o0 + r, kk = k0 + 4 * q;
+    if (o >= jb.O) return;
+    // rows of the tile beyond K were filled with zeros above
+    const float4 h = make_float4(th[4 * q][r], th[4 * q + 1][r], th[4 * q + 2][r], th[4 * q + 3][r]);
+    const float4 l = make_float4(tl[4 * q][r], tl[4 * q + 1][r], tl[4 * q + 2][r], tl[4 * q + 3][r]);
+    *reinterpret_cast<float4*>(jb.hi + static_cast<long long>(o) * kp + kk) = h;
+    *reinterpret_cast<float4*>(jb.lo + static_cast<long long>(o) * kp + kk) = l;
+  }
+}
+
+// C tile = A_hi B_hi + (A_hi B_lo + A_lo B_hi) from planes TMA loads directly; p.tmA[0] / [1]
+// describe A's hi / lo planes, p.tmB[0] / [1] B's; one CTA per tile, one pair, no split.
+// Warp 0: producer, warp 1: MMA issuer, warps 2-17: epilogue (as in sgemm3x_tma_kernel).
+__global__ void __launch_bounds__(NTHREADS, 1)
+sgemm3x_pre_kernel(const __grid_constant__ SParams p, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full[PRE_STAGES];
+  __shared__ __align__(8) uint64_t empty[PRE_STAGES];
+  __shared__ __align__(8) uint64_t acc_full;
+  __shared__ uint32_t tmem_slot;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int m0 = static_cast<int>(blockIdx.x % p.tiles_m) * SBM;
+  const int n0 = static_cast<int>(blockIdx.x / p.tiles_m) * p.bn;
+  const int nkb = (p.k[0] + SBK - 1) / SBK;
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&p.tmA[0]);
+    prefetch_tmap(&p.tmA[1]);
+    prefetch_tmap(&p.tmB[0]);
+    prefetch_tmap(&p.tmB[1]);
+  }
+  if (warp == 1) {
+    if (lane == 0) {
+      for (int s = 0; s < PRE_STAGES; ++s) {
+        mbar_init(smem_u32(&full[s]), 1);
+        mbar_init(smem_u32(&empty[s]), 1);
+      }
+      mbar_init(smem_u32(&acc_full), 1);
+      fence_mbar_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  pdl_wait();  // the planes are written by the launches before this one
+  pdl_launch_dependents();
+
+  bool ok = true;
+  if (warp == 0) {
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      const int b_bytes = p.bn * 128;
+      for (int it = 0; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, status, DEV_TIMEOUT_EMPTY, it)) break;
+        const uint32_t bar = smem_u32(&full[s]);
+        const uint32_t dst = base + s * PLANE_STAGE;
+        mbar_arrive_expect_tx(bar, 2 * RAW_TILE + 2 * b_bytes);
+        const int k0 = it * SBK;
+        tma_load_3d(dst, &p.tmA[0], bar, k0, m0, 0);
+        tma_load_3d(dst + PLANE, &p.tmA[1], bar, k0, m0, 0);
+        tma_load_3d(dst + 2 * PLANE, &p.tmB[0], bar, k0, n0, 0);
+        tma_load_3d(dst + 3 * PLANE, &p.tmB[1], bar, k0, n0, 0);
+        if (++s == PRE_STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t IDESC = make_idesc(2, 0, 0, SBM, static_cast<uint32_t>(p.bn));
+      int s = 0;
+      uint32_t ph = 0;
+      bool mok = true;
+      for (int it = 0; it < nkb; ++it) {
+        if (!mbar_wait(smem_u32(&full[s]), ph, status, DEV_TIMEOUT_FULL, it)) {
+          mok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_hi = base + s * PLANE_STAGE;
+        const uint32_t a_lo = a_hi + PLANE;
+        const uint32_t b_hi = a_hi + 2 * PLANE;
+        const uint32_t b_lo = a_hi + 3 * PLANE;
+        const uint32_t d_main = tmem + (it % 3) * SBN;
+        const uint32_t d_cross = tmem + CROSS_COL;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t dah = make_smem_desc(a_hi + ks * 32, 16, 1024);
+          const uint64_t dal = make_smem_desc(a_lo + ks * 32, 16, 1024);
+          const uint64_t dbh = make_smem_desc(b_hi + ks * 32, 16, 1024);
+          const uint64_t dbl = make_smem_desc(b_lo + ks * 32, 16, 1024);
+          mma_tf32(d_cross, dal, dbh, IDESC, (it > 0 || ks > 0) ? 1u : 0u);
+          mma_tf32(d_cross, dah, dbl, IDESC, 1u);
+          mma_tf32(d_main, dah, dbh, IDESC, (it >= 3 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&empty[s]));
+        if (++s == PRE_STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+      if (mok) tc_commit(smem_u32(&acc_full));
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    const int cgrp = (warp - 2) >> 2;  // 0..3
+    const int row = m0 + q * 32 + lane;
+    const bool row_ok = row < p.M;
+    const float bias = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
+    ok = mbar_wait(smem_u32(&acc_full), 0u, status, DEV_TIMEOUT_ACCUM, 0);
+    if (ok) {
+      tc_fence_after();
+      const int c0 = cgrp * 32;
+      const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16) + c0;
+      const int mode = p.accumulate ? 1 : 0;
+      const int ncols = (p.N - n0 < p.bn ? p.N - n0 : p.bn) - c0;
+      float* dst = p.C + row + static_cast<long long>(n0 + c0) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < 32 && c < ncols; c += 8, dst += 8 * p.ldc) {
+        float acc[8];
+        load_acc8(tbase + c, nkb, acc);
+        if (row_ok) {
+          if (ncols - c >= 8)
+            store_acc8<true>(dst, p.ldc, 8, acc, bias, mode, p.act);
+          else
+            store_acc8<false>(dst, p.ldc, ncols - c, acc, bias, mode, p.act);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ===========================================================================================
 // Gather front end: the same transform / MMA / epilogue pipeline, but the raw slices are
 // brought in by the transform threads themselves with cp.async (4- or 16-byte pieces, zero
 // filled outside the matrix) instead of TMA.  It takes what a tensor map cannot describe:
@@ -1025,7 +1275,83 @@ bool sgemm3x_supported(const Problem& p) {
 // sums, activation or derivative operand) with at most 64 rows and more columns than that is run
 // as its transpose, C^T = B^T A^T, the operands exchanged and the tile written through strides
 // (ldc, 1): the short extent then lies along the 64-wide side.
+// Operands split once (see sgemm3x_pre_kernel): a single unsplit product without a batch, a bias
+// gradient or column tables, at least four tiles along both extents and a full wave of tiles, so
+// that every plane is read several times and no SM idles for lack of a split contraction.
+static bool presplit_wanted(const Problem& p) {
+  if (!presplit_enabled() || p.npairs != 1 || p.batches != 1 || p.split_k > 1) return false;
+  if (p.rowsum != nullptr || p.ccols != nullptr) return false;
+  if (p.M < 4 * SBM || p.N < 4 * SBN || p.k[0] < 256 || p.k[0] > (1LL << 20)) return false;
+  const long long tiles = static_cast<long long>((p.M + SBM - 1) / SBM) * ((p.N + SBN - 1) / SBN);
+  if (tiles < device_sm_count()) return false;
+  const long long kp = (p.k[0] + SBK - 1) / SBK * SBK;
+  return 2 * (static_cast<long long>(p.M) + p.N) * kp * 4 <= (2LL << 30);  // scratch of at most 2 GiB
+}
+
+static cudaError_t launch_sgemm3x_pre(const Problem& p, cudaStream_t stream, int* status) {
+  const long long K = p.k[0], kp = (K + SBK - 1) / SBK * SBK;
+  const size_t a_plane = static_cast<size_t>(p.M) * kp * 4, b_plane = static_cast<size_t>(p.N) * kp * 4;
+  void* ws = nullptr;
+  cudaError_t e = cudaMallocAsync(&ws, 2 * (a_plane + b_plane), stream);
+  if (e != cudaSuccess) return e;
+  float* a_hi = static_cast<float*>(ws);
+  float* a_lo = a_hi + a_plane / 4;
+  float* b_hi = a_lo + a_plane / 4;
+  float* b_lo = b_hi + b_plane / 4;
+  {
+    SplitJobs jobs;
+    jobs.op[0] = SplitJob{static_cast<const float*>(p.a[0].base), static_cast<const float*>(p.a[0].ybase),
+                          p.a[0].ld, p.a[0].k_contig, p.a[0].dact, p.M, a_hi, a_lo};
+    jobs.op[1] = SplitJob{static_cast<const float*>(p.b[0].base), static_cast<const float*>(p.b[0].ybase),
+                          p.b[0].ld, p.b[0].k_contig, p.b[0].dact, p.N, b_hi, b_lo};
+    jobs.K = static_cast<int>(K);
+    jobs.kp = static_cast<int>(kp);
+    const int omax = p.M > p.N ? p.M : p.N;
+    const dim3 grid(static_cast<unsigned>((omax + 31) / 32), static_cast<unsigned>(kp / 32), 2);
+    e = launch_kernel(presplit_kernel, grid, dim3(256), 0, stream, pdl_enabled(), jobs);
+  }
+  SParams sp;
+  std::memset(&sp, 0, sizeof(sp));
+  if (e == cudaSuccess) {
+    const unsigned long long ukp = static_cast<unsigned long long>(kp);
+    const bool enc =
+        encode_tmap(&sp.tmA[0], 4, a_hi, ukp, p.M, 1, ukp, ukp * p.M, 32, SBM, true) &&
+        encode_tmap(&sp.tmA[1], 4, a_lo, ukp, p.M, 1, ukp, ukp * p.M, 32, SBM, true) &&
+        encode_tmap(&sp.tmB[0], 4, b_hi, ukp, p.N, 1, ukp, ukp * p.N, 32, SBN, true) &&
+        encode_tmap(&sp.tmB[1], 4, b_lo, ukp, p.N, 1, ukp, ukp * p.N, 32, SBN, true);
+    if (!enc) e = cudaErrorInvalidValue;
+  }
+  if (e == cudaSuccess) {
+    sp.npairs = 1;
+    sp.k[0] = static_cast<int>(kp);
+    sp.M = p.M;
+    sp.N = p.N;
+    sp.bn = SBN;
+    sp.tiles_m = (p.M + SBM - 1) / SBM;
+    sp.tiles_n = (p.N + SBN - 1) / SBN;
+    sp.C = static_cast<float*>(p.c);
+    sp.ldc = p.ldc;
+    sp.c_rs = 1;
+    sp.c_cs = p.ldc;
+    sp.bias = static_cast<const float*>(p.bias);
+    sp.act = p.act;
+    sp.accumulate = p.accumulate;
+    sp.split_k = 1;
+    sp.batches = 1;
+    sp.total_tiles = sp.tiles_m * sp.tiles_n;
+    const int smem = PRE_STAGES * PLANE_STAGE + 1024;
+    static unsigned long long smem_set = 0;
+    e = set_smem_limit_once(reinterpret_cast<const void*>(sgemm3x_pre_kernel), smem, &smem_set);
+    if (e == cudaSuccess)
+      e = launch_kernel(sgemm3x_pre_kernel, dim3(static_cast<unsigned>(sp.total_tiles)),
+                        dim3(NTHREADS), smem, stream, pdl_enabled(), sp, status);
+  }
+  const cudaError_t fe = cudaFreeAsync(ws, stream);
+  return e != cudaSuccess ? e : fe;
+}
+
 cudaError_t launch_sgemm3x(const Problem& p_in, cudaStream_t stream, int* status) {
+  if (presplit_wanted(p_in)) return launch_sgemm3x_pre(p_in, stream, status);
   Problem p = p_in;
   bool transposed = false;
   if (p.M <= 64 && p.N > 64 && p.bias == nullptr && p.rowsum == nullptr && p.act == ACT_NONE) {

@@ -395,6 +395,10 @@ int ginn_b200_version(void);   /* 200: ginn_b200_group gained `act` and `out_col
  * (input gradient beside weight gradient; dA beside dB; dV and dQ beside dP -> dS -> dK') on a second stream of the library's own, forked
  * from and joined back into the caller's stream inside the call (also under stream capture);
  * 0 keeps every launch on the caller's stream.
+ * "presplit": 1 (default) lets large fp32 products (at least four 128-wide tiles along both
+ * extents, a full wave of tiles, contraction of 256 or more, no batch) split both operands into
+ * hi / lo planes once, in a stream-ordered scratch allocation of 8 * (m + n) * k bytes taken from
+ * the device's default memory pool, instead of in every tile that reads them; 0 turns it off.
  * "pair_l2_hint": L2 eviction hints of the CTA-pair kernel: bit 0 = A slices loaded evict-last
  * and B slices evict-first, bit 1 = streaming reads and writes of C (default 3; 0 = none).
  * "max_split": cap on the number of CTAs an fp32 product's contraction is split over, and on the

@@ -452,3 +452,31 @@ def test_prod_backward_in_one_call(gpu, dt):
     torch.cuda.synchronize()
     check(B.to_host(dA), orc.gemm_batched(dc, b, trans_b=True), dt, "batched da")
     check(B.to_host(dB), orc.gemm_batched(a, dc, trans_a=True), dt, "batched db")
+
+
+def test_large_fp32_products_with_operands_split_once(gpu):
+    """Products with at least four tiles along both extents and a full wave of tiles split their
+    operands into hi / lo planes once, in a scratch allocation, and run on a kernel that TMA feeds
+    directly.  Every transpose form, accumulation, ragged extents with a contraction that is not
+    a multiple of 32, padded leading dimensions, and the same products with the option off."""
+    rng = np.random.default_rng(31)
+    for (m, n, k) in [(1024, 4096, 1024), (1500, 2100, 300), (2048, 1300, 2050)]:
+        for ta, tb in TRANS:
+            for acc in (False, True):
+                got, ref = run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, acc)
+    run_gemm(gpu, rng, np.float32, 1100, 2200, 516, False, True, True, ld_pad=4, offset=8)
+    # same answers (to rounding) without the split-once path
+    a, b = randn(rng, (1536, 640), np.float32), randn(rng, (640, 2048), np.float32)
+    outs = []
+    try:
+        for on in (1, 0):
+            gpu.set_option("presplit", on)
+            C = B.colmajor(1536, 2048, torch.float32, fill=0.0)
+            gpu.gemm(B.from_host(a), B.from_host(b), C)
+            torch.cuda.synchronize()
+            outs.append(B.to_host(C))
+    finally:
+        gpu.set_option("presplit", 1)
+    check(outs[0], orc.gemm(a, b), np.float32)
+    check_elementwise(outs[0], orc.gemm(a, b), np.float32)
+    assert np.abs(outs[0] - outs[1]).max() <= 1e-5 * np.abs(outs[1]).max()
