@@ -594,6 +594,7 @@ struct SplitJob {
 struct SplitJobs {
   SplitJob op[2];
   int K, kp;
+  float* rowsum;  // when set: rowsum[o] += sum over kk of operand 0 (outer-contiguous only)
 };
 
 __device__ __forceinline__ float4 load4_guarded(const float* p0, int valid) {
@@ -669,17 +670,26 @@ presplit_kernel(const SplitJobs jobs) {
     }
     __syncthreads();
     const int o = o0 + r, kk = k0 + 4 * q;
-    if (o >= jb.O) return;
     // rows of the tile beyond K were filled with zeros above
     const float4 h = make_float4(th[4 * q][r], th[4 * q + 1][r], th[4 * q + 2][r], th[4 * q + 3][r]);
     const float4 l = make_float4(tl[4 * q][r], tl[4 * q + 1][r], tl[4 * q + 2][r], tl[4 * q + 3][r]);
+    if (!second && jobs.rowsum != nullptr) {
+      // hi + lo is the value itself; the eight threads of a row add up their quads
+      float part = (h.x + l.x) + (h.y + l.y) + (h.z + l.z) + (h.w + l.w);
+      part += __shfl_xor_sync(0xffffffffu, part, 1);
+      part += __shfl_xor_sync(0xffffffffu, part, 2);
+      part += __shfl_xor_sync(0xffffffffu, part, 4);
+      if (q == 0 && o < jb.O) atomicAdd(jobs.rowsum + o, part);
+    }
+    if (o >= jb.O) return;
     *reinterpret_cast<float4*>(jb.hi + static_cast<long long>(o) * kp + kk) = h;
     *reinterpret_cast<float4*>(jb.lo + static_cast<long long>(o) * kp + kk) = l;
   }
 }
 
 // C tile = A_hi B_hi + (A_hi B_lo + A_lo B_hi) from planes TMA loads directly; p.tmA[0] / [1]
-// describe A's hi / lo planes, p.tmB[0] / [1] B's; one CTA per tile, one pair, no split.
+// describe A's hi / lo planes, p.tmB[0] / [1] B's; one CTA per tile and part of the contraction
+// (p.split_k parts: partial sums are added atomically, as in the kernel above), one pair.
 // Warp 0: producer, warp 1: MMA issuer, warps 2-17: epilogue (as in sgemm3x_tma_kernel).
 __global__ void __launch_bounds__(NTHREADS, 1)
 sgemm3x_pre_kernel(const __grid_constant__ SParams p, int* __restrict__ status) {
@@ -691,9 +701,15 @@ sgemm3x_pre_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int m0 = static_cast<int>(blockIdx.x % p.tiles_m) * SBM;
-  const int n0 = static_cast<int>(blockIdx.x / p.tiles_m) * p.bn;
-  const int nkb = (p.k[0] + SBK - 1) / SBK;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int tile = static_cast<int>(blockIdx.x) % tiles;
+  const int split = static_cast<int>(blockIdx.x) / tiles;  // part of the contraction (p.split_k parts)
+  const int m0 = (tile % p.tiles_m) * SBM;
+  const int n0 = (tile / p.tiles_m) * p.bn;
+  const int nkb_total = (p.k[0] + SBK - 1) / SBK;
+  const int kb_begin = static_cast<int>(static_cast<long long>(nkb_total) * split / p.split_k);
+  const int nkb =
+      static_cast<int>(static_cast<long long>(nkb_total) * (split + 1) / p.split_k) - kb_begin;
 
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&p.tmA[0]);
@@ -732,7 +748,7 @@ sgemm3x_pre_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
         const uint32_t bar = smem_u32(&full[s]);
         const uint32_t dst = base + s * PLANE_STAGE;
         mbar_arrive_expect_tx(bar, 2 * RAW_TILE + 2 * b_bytes);
-        const int k0 = it * SBK;
+        const int k0 = (kb_begin + it) * SBK;
         tma_load_3d(dst, &p.tmA[0], bar, k0, m0, 0);
         tma_load_3d(dst + PLANE, &p.tmA[1], bar, k0, m0, 0);
         tma_load_3d(dst + 2 * PLANE, &p.tmB[0], bar, k0, n0, 0);
@@ -786,13 +802,13 @@ sgemm3x_pre_kernel(const __grid_constant__ SParams p, int* __restrict__ status) 
     const int cgrp = (warp - 2) >> 2;  // 0..3
     const int row = m0 + q * 32 + lane;
     const bool row_ok = row < p.M;
-    const float bias = (p.bias != nullptr && row_ok) ? p.bias[row] : 0.f;
+    const float bias = (p.bias != nullptr && row_ok && split == 0) ? p.bias[row] : 0.f;
     ok = mbar_wait(smem_u32(&acc_full), 0u, status, DEV_TIMEOUT_ACCUM, 0);
     if (ok) {
       tc_fence_after();
       const int c0 = cgrp * 32;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(q * 32) << 16) + c0;
-      const int mode = p.accumulate ? 1 : 0;
+      const int mode = p.split_k > 1 ? 2 : (p.accumulate ? 1 : 0);  // 2: atomic partial sums
       const int ncols = (p.N - n0 < p.bn ? p.N - n0 : p.bn) - c0;
       float* dst = p.C + row + static_cast<long long>(n0 + c0) * p.ldc;
 #pragma unroll 1
@@ -1279,11 +1295,14 @@ bool sgemm3x_supported(const Problem& p) {
 // gradient or column tables, at least four tiles along both extents and a full wave of tiles, so
 // that every plane is read several times and no SM idles for lack of a split contraction.
 static bool presplit_wanted(const Problem& p) {
-  if (!presplit_enabled() || p.npairs != 1 || p.batches != 1 || p.split_k > 1) return false;
-  if (p.rowsum != nullptr || p.ccols != nullptr) return false;
+  if (!presplit_enabled() || p.npairs != 1 || p.batches != 1 || p.ccols != nullptr) return false;
+  if (p.rowsum != nullptr && p.a[0].k_contig) return false;
   if (p.M < 4 * SBM || p.N < 4 * SBN || p.k[0] < 256 || p.k[0] > (1LL << 20)) return false;
   const long long tiles = static_cast<long long>((p.M + SBM - 1) / SBM) * ((p.N + SBN - 1) / SBN);
-  if (tiles < device_sm_count()) return false;
+  const int split = p.split_k > 1 ? p.split_k : 1;
+  // a full wave of tiles, or a split contraction long enough to pay for the split pass
+  if (split == 1 ? tiles < device_sm_count() : (tiles * split * 2 < device_sm_count() || p.k[0] < 2048))
+    return false;
   const long long kp = (p.k[0] + SBK - 1) / SBK * SBK;
   return 2 * (static_cast<long long>(p.M) + p.N) * kp * 4 <= (2LL << 30);  // scratch of at most 2 GiB
 }
@@ -1306,6 +1325,7 @@ static cudaError_t launch_sgemm3x_pre(const Problem& p, cudaStream_t stream, int
                           p.b[0].ld, p.b[0].k_contig, p.b[0].dact, p.N, b_hi, b_lo};
     jobs.K = static_cast<int>(K);
     jobs.kp = static_cast<int>(kp);
+    jobs.rowsum = static_cast<float*>(p.rowsum);
     const int omax = p.M > p.N ? p.M : p.N;
     const dim3 grid(static_cast<unsigned>((omax + 31) / 32), static_cast<unsigned>(kp / 32), 2);
     e = launch_kernel(presplit_kernel, grid, dim3(256), 0, stream, pdl_enabled(), jobs);
@@ -1336,15 +1356,23 @@ static cudaError_t launch_sgemm3x_pre(const Problem& p, cudaStream_t stream, int
     sp.bias = static_cast<const float*>(p.bias);
     sp.act = p.act;
     sp.accumulate = p.accumulate;
-    sp.split_k = 1;
+    sp.split_k = p.split_k > 1 ? p.split_k : 1;
     sp.batches = 1;
-    sp.total_tiles = sp.tiles_m * sp.tiles_n;
+    sp.total_tiles = sp.tiles_m * sp.tiles_n * sp.split_k;
+    if (sp.split_k > 1) {
+      sp.act = ACT_NONE;  // applied by a pass over the summed C after the kernel
+      if (!p.accumulate)  // partial sums are added onto zeros
+        e = cudaMemset2DAsync(p.c, p.ldc * 4, 0, static_cast<size_t>(p.M) * 4, p.N, stream);
+    }
     const int smem = PRE_STAGES * PLANE_STAGE + 1024;
     static unsigned long long smem_set = 0;
-    e = set_smem_limit_once(reinterpret_cast<const void*>(sgemm3x_pre_kernel), smem, &smem_set);
+    if (e == cudaSuccess)
+      e = set_smem_limit_once(reinterpret_cast<const void*>(sgemm3x_pre_kernel), smem, &smem_set);
     if (e == cudaSuccess)
       e = launch_kernel(sgemm3x_pre_kernel, dim3(static_cast<unsigned>(sp.total_tiles)),
                         dim3(NTHREADS), smem, stream, pdl_enabled(), sp, status);
+    if (e == cudaSuccess && sp.split_k > 1 && p.act != ACT_NONE)
+      e = launch_act_inplace_f32(sp.C, sp.ldc, 0, p.act, p.M, p.N, 1, stream);
   }
   const cudaError_t fe = cudaFreeAsync(ws, stream);
   return e != cudaSuccess ? e : fe;

@@ -396,7 +396,8 @@ int ginn_b200_version(void);   /* 200: ginn_b200_group gained `act` and `out_col
  * from and joined back into the caller's stream inside the call (also under stream capture);
  * 0 keeps every launch on the caller's stream.
  * "presplit": 1 (default) lets large fp32 products (at least four 128-wide tiles along both
- * extents, a full wave of tiles, contraction of 256 or more, no batch) split both operands into
+ * extents, no batch; a full wave of tiles and a contraction of 256 or more, or fewer tiles with
+ * a split contraction of 2048 or more) split both operands into
  * hi / lo planes once, in a stream-ordered scratch allocation of 8 * (m + n) * k bytes taken from
  * the device's default memory pool, instead of in every tile that reads them; 0 turns it off.
  * "pair_l2_hint": L2 eviction hints of the CTA-pair kernel: bit 0 = A slices loaded evict-last

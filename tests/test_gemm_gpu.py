@@ -465,6 +465,10 @@ def test_large_fp32_products_with_operands_split_once(gpu):
             for acc in (False, True):
                 got, ref = run_gemm(gpu, rng, np.float32, m, n, k, ta, tb, acc)
     run_gemm(gpu, rng, np.float32, 1100, 2200, 516, False, True, True, ld_pad=4, offset=8)
+    # few tiles and a long contraction: the split-once kernel with the contraction split over CTAs
+    for ta, tb in TRANS:
+        for acc in (False, True):
+            run_gemm(gpu, rng, np.float32, 1024, 784, 4100, ta, tb, acc)
     # same answers (to rounding) without the split-once path
     a, b = randn(rng, (1536, 640), np.float32), randn(rng, (640, 2048), np.float32)
     outs = []
