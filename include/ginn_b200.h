@@ -8,6 +8,19 @@
  * earlier launches that read that half.  Every function returns a ginn_b200_status; on a
  * non-zero status ginn_b200_last_error() describes the failure for the calling thread.
  *
+ * Scratch memory: a few entry points take scratch for the duration of a call from the device's
+ * default stream-ordered memory pool (cudaMallocAsync / cudaFreeAsync on the caller's stream):
+ * large fp16 Affine backward passes (documented at ginn_b200_affine_backward), convolutions
+ * without a caller workspace, and large fp32 products (option "presplit": 8 * (m + n) * k bytes).
+ * On the first call for a device the library gives that pool a release threshold of 4 GiB, so
+ * that freed scratch stays cached instead of going back to the driver at every synchronisation.
+ * ginn_b200_grouped_static is the entry point that allocates nothing.
+ *
+ * Streams: every call orders its work on `stream`.  ginn_b200_affine_backward,
+ * ginn_b200_prod_backward and ginn_b200_attention_backward run part of their launches on one
+ * extra stream per device that the library owns, forked from and joined back into `stream`
+ * inside the call (option "fork_streams").
+ *
  * dtype: GINN_B200_F32 computes with three TF32 tensor-core products per term (fp32-level
  * accuracy, fp32 accumulation); GINN_B200_F16 uses fp16 inputs/outputs with fp32 accumulation.
  */
