@@ -1379,7 +1379,11 @@ static cudaError_t launch_sgemm3x_pre(const Problem& p, cudaStream_t stream, int
 }
 
 cudaError_t launch_sgemm3x(const Problem& p_in, cudaStream_t stream, int* status) {
-  if (presplit_wanted(p_in)) return launch_sgemm3x_pre(p_in, stream, status);
+  if (presplit_wanted(p_in)) {
+    const cudaError_t e = launch_sgemm3x_pre(p_in, stream, status);
+    if (e != cudaErrorMemoryAllocation) return e;
+    cudaGetLastError();  // no scratch to be had: nothing was queued, take the path below
+  }
   Problem p = p_in;
   bool transposed = false;
   if (p.M <= 64 && p.N > 64 && p.bias == nullptr && p.rowsum == nullptr && p.act == ACT_NONE) {

@@ -412,7 +412,8 @@ int ginn_b200_version(void);   /* 200: ginn_b200_group gained `act` and `out_col
  * extents, no batch; a full wave of tiles and a contraction of 256 or more, or fewer tiles with
  * a split contraction of 2048 or more) split both operands into
  * hi / lo planes once, in a stream-ordered scratch allocation of 8 * (m + n) * k bytes taken from
- * the device's default memory pool, instead of in every tile that reads them; 0 turns it off.
+ * the device's default memory pool, instead of in every tile that reads them (a product whose
+ * scratch cannot be allocated runs on the ordinary path); 0 turns it off.
  * "pair_l2_hint": L2 eviction hints of the CTA-pair kernel: bit 0 = A slices loaded evict-last
  * and B slices evict-first, bit 1 = streaming reads and writes of C (default 3; 0 = none).
  * "max_split": cap on the number of CTAs an fp32 product's contraction is split over, and on the
