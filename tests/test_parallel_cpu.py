@@ -70,3 +70,41 @@ def test_sharded_prod_matches_unsharded_on_two_ranks(panels):
     for p in procs:
         p.join(timeout=60)
     assert sorted(results) == [(0, True), (1, True)]
+
+
+def test_gradients_cleared_beside_the_forward_product():
+    """`zero_beside` replaces the two `zero` calls: it is handed both gradients before the
+    forward product, and its waiter runs before the first product that adds to them."""
+    rng = np.random.default_rng(5)
+    m, k, n = 12, 9, 14
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    Bm = rng.standard_normal((k, n)).astype(np.float32)
+    dC = rng.standard_normal((m, n)).astype(np.float32)
+    events, pending = [], []
+
+    def gemm(a, b, out, ta, tb, acc):
+        events.append("add" if acc else "assign")
+        out[...] = orc.gemm(a, b, ta, tb, out, acc).astype(np.float32)
+
+    def zero(x):
+        raise AssertionError("zero() must not be called when zero_beside is given")
+
+    def zero_beside(ts):
+        events.append("fork")
+        pending.extend(ts)                 # cleared only when the waiter runs, as on a second stream
+
+        def wait():
+            events.append("join")
+            for t in pending:
+                t[...] = 0
+        return wait
+
+    C = np.empty((m, n), np.float32)
+    dA = np.full((m, k), 3.0, np.float32)
+    dB = np.full((k, n), 3.0, np.float32)
+    ShardedProd(gemm, zero, lambda x: (lambda: None), panels=2, zero_beside=zero_beside).step(
+        A, Bm, dC, C, dA, dB)
+    assert events[:3] == ["fork", "assign", "join"] and events[3:] == ["add", "add", "add"]
+    assert np.allclose(C, A @ Bm, rtol=1e-5, atol=1e-5)
+    assert np.allclose(dA, dC @ Bm.T, rtol=1e-4, atol=1e-4)
+    assert np.allclose(dB, A.T @ dC, rtol=1e-5, atol=1e-5)
